@@ -1,0 +1,135 @@
+/*
+ * kda_b200.h — C ABI of the B200 (sm_100a) Kimi Delta Attention kernels.
+ *
+ * The reference has no C/FFI interface for this path: its fast path is one Python call,
+ * fla.ops.kda.chunk_kda(...) at k3mini/model.py:197-216, selected by
+ * k3mini/backends.py:155-243.  The entry points below are what a binding for that call
+ * needs: plain pointers and sizes in, an int status out.  They never allocate device
+ * memory, never synchronise the device and never abort; every buffer (inputs, outputs and
+ * the workspace) is owned by the caller and must live on the current CUDA device.
+ *
+ * Tensor layouts (row-major, innermost last):
+ *   q, k, g : [B, T, H, dk]      v, o, do : [B, T, H, dv]      beta : [B, T, H]
+ *   A_log   : [H] float          dt_bias  : [H * dk] float (may be NULL)
+ *   h0/ht/dh0/dht : [N, H, dk, dv] float, or [N, H, dv, dk] with KDA_FLAG_STATE_V_FIRST
+ *   cu_seqlens : [N + 1] int64 on the device (requires B == 1), or NULL for N == B
+ * q, k, v, g, beta, o, do and the gradients of the first five share one element type
+ * (KDA_DTYPE_F32 or KDA_DTYPE_BF16); parameters, states and their gradients are float.
+ */
+#ifndef KDA_B200_H
+#define KDA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KDA_CHUNK 64
+
+enum { KDA_DTYPE_F32 = 0, KDA_DTYPE_BF16 = 1 };
+
+enum {
+    KDA_FLAG_QK_L2NORM = 1,     /* use_qk_l2norm_in_kernel   (k3mini/model.py:209) */
+    KDA_FLAG_GATE = 2,          /* use_gate_in_kernel        (k3mini/model.py:210) */
+    KDA_FLAG_BETA_SIGMOID = 4,  /* use_beta_sigmoid_in_kernel(k3mini/model.py:211) */
+    KDA_FLAG_STATE_V_FIRST = 8, /* state_v_first             (k3mini/model.py:214) */
+    KDA_FLAG_FORCE_SIMT = 16    /* FP32 CUDA-core arithmetic in every stage (validation mode) */
+};
+
+enum {
+    KDA_OK = 0,
+    KDA_ERR_NULL = 1,        /* a required pointer is NULL */
+    KDA_ERR_SHAPE = 2,       /* unsupported or inconsistent sizes */
+    KDA_ERR_DTYPE = 3,
+    KDA_ERR_WORKSPACE = 4,   /* workspace too small or misaligned */
+    KDA_ERR_ALIGN = 5,       /* a tensor pointer is not 16-byte aligned */
+    KDA_ERR_LAUNCH = 6,      /* the CUDA runtime refused a launch (see kda_last_cuda_error) */
+    KDA_ERR_DEVICE_WAIT = 7, /* a bounded device-side wait gave up (read from the status word) */
+    KDA_ERR_GUARD = 8        /* guard span is not a finite value <= 232 (or negative = exact) */
+};
+
+/* One call's description.  Replaces the keyword arguments of chunk_kda
+ * (k3mini/model.py:200-216) plus the tensors autograd hands to its backward. */
+typedef struct KdaParams {
+    int32_t B, T, H, dk, dv;
+    int32_t N;             /* number of sequences: B, or len(cu_seqlens) - 1 */
+    int32_t NT;            /* total number of 64-token chunks over all sequences */
+    int32_t dtype;         /* KDA_DTYPE_* */
+    int32_t flags;         /* KDA_FLAG_* */
+    float scale;           /* k3mini/model.py:208 */
+    float guard_span;      /* log2 span limit of the guarded diagonal (k3mini/backends.py:18);
+                              negative forces the exact pairwise path everywhere */
+    /* forward inputs */
+    const void *q, *k, *v, *g, *beta;
+    const float *A_log, *dt_bias;
+    const float *h0;            /* may be NULL (zero state) */
+    const int64_t *cu_seqlens;  /* device, may be NULL */
+    const int32_t *chunk_seq;   /* device [NT]: sequence of each chunk (needed with cu_seqlens) */
+    const int32_t *seq_chunk_off; /* device [N+1]: first chunk of each sequence (with cu_seqlens) */
+    /* forward outputs */
+    void *o;
+    float *ht;                  /* may be NULL */
+    /* workspace: kda_workspace_bytes(); written by kda_fwd, read by kda_bwd */
+    void *workspace;
+    size_t workspace_bytes;
+    /* backward inputs / outputs (ignored by kda_fwd) */
+    const void *grad_o;
+    const float *grad_ht;       /* may be NULL */
+    void *grad_q, *grad_k, *grad_v, *grad_g, *grad_beta;
+    float *grad_A_log, *grad_dt_bias; /* may be NULL unless KDA_FLAG_GATE */
+    float *grad_h0;             /* may be NULL */
+    void *bwd_scratch;          /* kda_workspace_bytes() second result */
+    size_t bwd_scratch_bytes;
+    int32_t *status;            /* device word, zero-initialised by the caller; a kernel whose
+                                   bounded wait gives up ORs a non-zero code into it */
+} KdaParams;
+
+/* Bytes of forward workspace (saved for the backward) and of backward scratch for these
+ * sizes.  Replaces the torch.empty calls inside the reference's third-party op. */
+int kda_workspace_bytes(const KdaParams *p, size_t *fwd_bytes, size_t *bwd_bytes);
+
+/* Forward of chunk_kda (k3mini/model.py:200-216): o, optional final state, and the
+ * per-chunk intermediates in the workspace. */
+int kda_fwd(const KdaParams *p, void *cuda_stream);
+
+/* Backward of chunk_kda (what autograd runs for k3mini/model.py:200-216):
+ * dq, dk, dv, dg, dbeta, dA_log, ddt_bias, dh0 from do, dht and the forward workspace. */
+int kda_bwd(const KdaParams *p, void *cuda_stream);
+
+/* Causal depthwise short convolution + SiLU over [B, T, C] (k3mini/model.py:76-88; the
+ * fast path's fla.modules.ShortConvolution at k3mini/model.py:147-155).  weight is
+ * [C, 1, ksize] float, ksize <= 4; cu_seqlens as above (no tap crosses a document). */
+int kda_short_conv_fwd(const void *x, const float *weight, void *y, int32_t B, int32_t T, int32_t C,
+                       int32_t ksize, int32_t dtype, const int64_t *cu_seqlens, int32_t N,
+                       void *cuda_stream);
+/* dweight [C, ksize] is reduced in a fixed order from partial [n_partial, C, ksize]
+ * (caller scratch; n_partial token-tile groups run in parallel, 64..512 is a good range). */
+int kda_short_conv_bwd(const void *x, const float *weight, const void *dy, void *dx, float *dweight,
+                       float *partial, int32_t n_partial, int32_t B, int32_t T, int32_t C, int32_t ksize,
+                       int32_t dtype, const int64_t *cu_seqlens, int32_t N, void *cuda_stream);
+
+/* Headwise RMSNorm(x) * sigmoid(gate) over [rows, dim] (k3mini/model.py:91-98; the fast
+ * path's fla.modules.FusedRMSNormGated at k3mini/model.py:171-175). */
+int kda_norm_gate_fwd(const void *x, const void *gate, const float *weight, void *y, float *rstd,
+                      int64_t rows, int32_t dim, float eps, int32_t dtype, void *cuda_stream);
+/* dweight [dim] is reduced in a fixed order from partial [n_partial, dim] (caller scratch). */
+int kda_norm_gate_bwd(const void *x, const void *gate, const float *weight, const void *dy, void *dx,
+                      void *dgate, float *dweight, float *partial, int32_t n_partial, int64_t rows,
+                      int32_t dim, float eps, int32_t dtype, void *cuda_stream);
+
+/* Guarded-diagonal contract of the reference's backend check (k3mini/backends.py:17-19,
+ * 68-109): version 1, "tf32x3"-class precision, span <= 232. */
+int kda_guard_version(void);
+float kda_guard_max_span(void);
+const char *kda_guard_dot_precision(void);
+
+const char *kda_status_string(int status);
+const char *kda_last_cuda_error(void);
+int kda_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KDA_B200_H */

@@ -1,0 +1,11 @@
+"""B200-native Kimi Delta Attention: ``chunk_kda`` and its sublayer companions, as a drop-in
+for the fast path the reference selects in k3mini/backends.py and calls at
+k3mini/model.py:197-216."""
+
+from . import chunk_intra
+from .backend import KdaBackendStatus, resolve_kda_backend, validated_kda_backend_name
+from .modules import FusedRMSNormGated, KimiDeltaAttention, ShortConvolution
+from .ops import chunk_kda
+
+__all__ = ["chunk_kda", "chunk_intra", "ShortConvolution", "FusedRMSNormGated", "KimiDeltaAttention",
+           "resolve_kda_backend", "validated_kda_backend_name", "KdaBackendStatus"]

@@ -1,0 +1,110 @@
+// C ABI of the KDA library: argument validation and stage dispatch.  No allocation, no
+// device synchronisation; every error is a return code.
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "kda_common.cuh"
+
+namespace kda {
+cudaError_t simt_fwd(const KdaParams& p, cudaStream_t s);
+cudaError_t simt_bwd(const KdaParams& p, cudaStream_t s);
+cudaError_t tc_fwd(const KdaParams& p, cudaStream_t s);
+cudaError_t tc_bwd(const KdaParams& p, cudaStream_t s);
+bool tc_supported(const KdaParams& p);
+
+static thread_local char g_last_error[256] = "";
+
+static int fail_cuda(cudaError_t e) {
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+    return KDA_ERR_LAUNCH;
+}
+
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+static int validate(const KdaParams* p, bool bwd) {
+    if (!p) return KDA_ERR_NULL;
+    if (p->dtype != KDA_DTYPE_F32 && p->dtype != KDA_DTYPE_BF16) return KDA_ERR_DTYPE;
+    if (p->B <= 0 || p->T <= 0 || p->H <= 0 || p->N <= 0 || p->NT <= 0) return KDA_ERR_SHAPE;
+    if (p->dk != p->dv || (p->dk != 64 && p->dk != 128)) return KDA_ERR_SHAPE;
+    if (p->cu_seqlens) {
+        if (p->B != 1 || !p->chunk_seq || !p->seq_chunk_off) return KDA_ERR_SHAPE;
+    } else {
+        if (p->N != p->B || p->NT != p->B * ((p->T + C - 1) / C)) return KDA_ERR_SHAPE;
+    }
+    if (!p->q || !p->k || !p->v || !p->g || !p->beta || !p->o || !p->workspace) return KDA_ERR_NULL;
+    if ((p->flags & KDA_FLAG_GATE) && !p->A_log) return KDA_ERR_NULL;
+    if (!(p->guard_span < 0.f) && !(isfinite(p->guard_span) && p->guard_span <= kda_guard_max_span()))
+        return KDA_ERR_GUARD;
+    const void* ptrs[] = {p->q, p->k, p->v, p->g, p->o, p->workspace, p->h0, p->ht};
+    for (const void* x : ptrs)
+        if (!aligned16(x)) return KDA_ERR_ALIGN;
+    WsLayout L = ws_layout(p->NT, p->H, p->dk, p->dv, p->dtype);
+    if (p->workspace_bytes < L.total || ((uintptr_t)p->workspace & 255)) return KDA_ERR_WORKSPACE;
+    if (bwd) {
+        if (!p->grad_o || !p->grad_q || !p->grad_k || !p->grad_v || !p->grad_g || !p->grad_beta || !p->bwd_scratch) return KDA_ERR_NULL;
+        if ((p->flags & KDA_FLAG_GATE) && !p->grad_A_log) return KDA_ERR_NULL;
+        if (p->bwd_scratch_bytes < L.bwd_total || ((uintptr_t)p->bwd_scratch & 255)) return KDA_ERR_WORKSPACE;
+        const void* bp[] = {p->grad_o, p->grad_q, p->grad_k, p->grad_v, p->grad_g, p->grad_ht, p->grad_h0};
+        for (const void* x : bp)
+            if (!aligned16(x)) return KDA_ERR_ALIGN;
+    }
+    return KDA_OK;
+}
+}  // namespace kda
+
+using namespace kda;
+
+extern "C" {
+
+int kda_abi_version(void) { return 1; }
+
+int kda_guard_version(void) { return 1; }
+float kda_guard_max_span(void) { return 232.0f; }
+const char* kda_guard_dot_precision(void) { return "tf32x3"; }
+
+const char* kda_last_cuda_error(void) { return g_last_error; }
+
+const char* kda_status_string(int s) {
+    switch (s) {
+        case KDA_OK: return "ok";
+        case KDA_ERR_NULL: return "a required pointer is NULL";
+        case KDA_ERR_SHAPE: return "unsupported or inconsistent sizes (need dk == dv in {64,128}, chunk 64)";
+        case KDA_ERR_DTYPE: return "unsupported element type";
+        case KDA_ERR_WORKSPACE: return "workspace too small or not 256-byte aligned";
+        case KDA_ERR_ALIGN: return "tensor pointer not 16-byte aligned";
+        case KDA_ERR_LAUNCH: return "CUDA launch failed";
+        case KDA_ERR_DEVICE_WAIT: return "a bounded device-side wait gave up";
+        case KDA_ERR_GUARD: return "guard span must be negative (exact) or a finite value <= 232";
+        default: return "unknown status";
+    }
+}
+
+int kda_workspace_bytes(const KdaParams* p, size_t* fwd_bytes, size_t* bwd_bytes) {
+    if (!p) return KDA_ERR_NULL;
+    if (p->NT <= 0 || p->H <= 0 || p->dk <= 0 || p->dv <= 0) return KDA_ERR_SHAPE;
+    WsLayout L = ws_layout(p->NT, p->H, p->dk, p->dv, p->dtype);
+    if (fwd_bytes) *fwd_bytes = L.total;
+    if (bwd_bytes) *bwd_bytes = L.bwd_total;
+    return KDA_OK;
+}
+
+int kda_fwd(const KdaParams* p, void* stream) {
+    int v = validate(p, false);
+    if (v != KDA_OK) return v;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool tc = !(p->flags & KDA_FLAG_FORCE_SIMT) && tc_supported(*p);
+    cudaError_t e = tc ? tc_fwd(*p, s) : simt_fwd(*p, s);
+    return e == cudaSuccess ? KDA_OK : fail_cuda(e);
+}
+
+int kda_bwd(const KdaParams* p, void* stream) {
+    int v = validate(p, true);
+    if (v != KDA_OK) return v;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool tc = !(p->flags & KDA_FLAG_FORCE_SIMT) && tc_supported(*p);
+    cudaError_t e = tc ? tc_bwd(*p, s) : simt_bwd(*p, s);
+    return e == cudaSuccess ? KDA_OK : fail_cuda(e);
+}
+
+}  // extern "C"

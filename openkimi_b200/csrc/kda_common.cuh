@@ -1,0 +1,115 @@
+// Shared definitions of the KDA kernels: parameter block, chunk indexing, workspace layout,
+// element load/store helpers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/kda_b200.h"
+
+namespace kda {
+
+constexpr int C = KDA_CHUNK;       // tokens per chunk
+constexpr float LOG2E = 1.4426950408889634f;
+
+// ---------------------------------------------------------------------------------------
+// element access
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// ---------------------------------------------------------------------------------------
+// chunk indexing.  Chunks never straddle a sequence boundary: with cu_seqlens every
+// document restarts its own chunk grid (the last chunk of a document may be partial).
+// ---------------------------------------------------------------------------------------
+struct ChunkInfo {
+    int seq;        // sequence (document) index
+    int lc;         // chunk index inside the sequence
+    long long tok0; // flattened token index (b * T + t) of the chunk's first row
+    int len;        // valid rows, 1..64
+};
+
+__device__ __forceinline__ ChunkInfo chunk_info(const KdaParams& p, int c) {
+    ChunkInfo ci;
+    if (p.cu_seqlens != nullptr) {
+        ci.seq = p.chunk_seq[c];
+        ci.lc = c - p.seq_chunk_off[ci.seq];
+        long long s = p.cu_seqlens[ci.seq], e = p.cu_seqlens[ci.seq + 1];
+        ci.tok0 = s + (long long)ci.lc * C;
+        long long rem = e - ci.tok0;
+        ci.len = rem < C ? (int)rem : C;
+    } else {
+        int nts = (p.T + C - 1) / C;
+        ci.seq = c / nts;
+        ci.lc = c - ci.seq * nts;
+        ci.tok0 = (long long)ci.seq * p.T + (long long)ci.lc * C;
+        int rem = p.T - ci.lc * C;
+        ci.len = rem < C ? rem : C;
+    }
+    return ci;
+}
+
+// first chunk and number of chunks of sequence n
+__device__ __forceinline__ void seq_chunks(const KdaParams& p, int n, int& c0, int& nc) {
+    if (p.cu_seqlens != nullptr) {
+        c0 = p.seq_chunk_off[n];
+        nc = p.seq_chunk_off[n + 1] - c0;
+    } else {
+        nc = (p.T + C - 1) / C;
+        c0 = n * nc;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// workspace layout (byte offsets).  All per-(chunk, head) records are stored
+// [NT][H][...] so that consecutive heads of one chunk are adjacent.
+// ---------------------------------------------------------------------------------------
+struct WsLayout {
+    size_t W, U, Aqk, Qt, Kh, Tm, S0, gamC, total;      // forward workspace
+    size_t dS, dVn, dA_part, dbias_part, bwd_total;     // backward scratch
+};
+
+__host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+__host__ __device__ inline WsLayout ws_layout(int NT, int H, int dk, int dv, int dtype) {
+    size_t es = dtype == KDA_DTYPE_BF16 ? 2 : 4;
+    size_t n = (size_t)NT * H;
+    WsLayout w;
+    size_t off = 0;
+    w.W = off;    off = align256(off + n * C * dk * es);
+    w.U = off;    off = align256(off + n * C * dv * es);
+    w.Aqk = off;  off = align256(off + n * C * C * es);
+    w.Qt = off;   off = align256(off + n * C * dk * es);
+    w.Kh = off;   off = align256(off + n * C * dk * es);
+    w.Tm = off;   off = align256(off + n * C * C * es);
+    w.S0 = off;   off = align256(off + n * dk * dv * es);
+    w.gamC = off; off = align256(off + n * dk * 4);
+    w.total = off;
+    off = 0;
+    w.dS = off;         off = align256(off + n * dk * dv * es);
+    w.dVn = off;        off = align256(off + n * C * dv * es);
+    w.dA_part = off;    off = align256(off + n * 4);
+    w.dbias_part = off; off = align256(off + n * dk * 4);
+    w.bwd_total = off;
+    return w;
+}
+
+// state element index for logical (d, e) of a [dk, dv] state, honouring the v-first layout
+__device__ __forceinline__ size_t state_idx(const KdaParams& p, int d, int e) {
+    return (p.flags & KDA_FLAG_STATE_V_FIRST) ? (size_t)e * p.dk + d : (size_t)d * p.dv + e;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// softplus with torch's threshold of 20 (F.softplus, k3mini/model.py:220)
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+}  // namespace kda

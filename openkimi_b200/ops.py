@@ -1,0 +1,246 @@
+"""``chunk_kda``: the KDA chunkwise gated delta rule, forward and backward, on B200.
+
+Drop-in for the call the reference makes at k3mini/model.py:197-216
+(``fla.ops.kda.chunk_kda``): same arguments, same gate / beta / initial-state /
+final-state / ``cu_seqlens`` meaning, same return value ``(o, final_state_or_None)``.
+The arithmetic runs in ``libkda_b200.so`` (hand-written CUDA for sm_100a) through the C ABI
+of include/kda_b200.h; PyTorch only owns the memory and the stream.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from functools import lru_cache
+
+import torch
+
+from . import _lib, chunk_intra
+
+_DTYPES = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16}
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+@lru_cache(maxsize=64)
+def _chunk_tables_cached(cu: tuple, device_index: int):
+    lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)]
+    if any(l < 0 for l in lens):
+        raise ValueError("cu_seqlens must be non-decreasing")
+    counts = [(l + _lib.CHUNK - 1) // _lib.CHUNK for l in lens]
+    off = [0]
+    for c in counts:
+        off.append(off[-1] + c)
+    seq = [n for n, c in enumerate(counts) for _ in range(c)]
+    dev = torch.device("cuda", device_index)
+    return (torch.tensor(seq if seq else [0], dtype=torch.int32, device=dev),
+            torch.tensor(off, dtype=torch.int32, device=dev), off[-1])
+
+
+def _chunk_tables(cu_seqlens, cu_seqlens_cpu, device):
+    """Per-chunk sequence index and per-sequence first chunk.  Chunks never straddle a
+    document boundary, so the table depends on the lengths; it is built on the host
+    (``cu_seqlens_cpu`` avoids the device-to-host copy) and cached per length tuple."""
+    host = cu_seqlens_cpu if cu_seqlens_cpu is not None else cu_seqlens.cpu()
+    return _chunk_tables_cached(tuple(int(x) for x in host.tolist()), device.index or 0)
+
+
+class _Call:
+    """Builds the KdaParams block for one forward (+ backward) call."""
+
+    def __init__(self, q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags):
+        B, T, H, dk = q.shape
+        self.shape = (B, T, H, dk, v.shape[-1])
+        self.dev = q.device
+        self.cu = None
+        if cu_seqlens is not None:
+            self.cu = cu_seqlens.to(device=q.device, dtype=torch.int64).contiguous()
+            self.chunk_seq, self.seq_off, self.NT = _chunk_tables(cu_seqlens, cu_seqlens_cpu, q.device)
+            self.N = self.cu.numel() - 1
+        else:
+            self.chunk_seq = self.seq_off = None
+            self.N = B
+            self.NT = B * ((T + _lib.CHUNK - 1) // _lib.CHUNK)
+        p = _lib.KdaParams()
+        p.B, p.T, p.H, p.dk, p.dv = self.shape
+        p.N, p.NT = self.N, max(self.NT, 1)
+        p.dtype = _DTYPES[q.dtype]
+        p.flags = flags
+        p.scale = float(scale)
+        p.guard_span = chunk_intra.current_guard_span()
+        p.q, p.k, p.v, p.g, p.beta = (t.data_ptr() for t in (q, k, v, g, beta))
+        p.A_log = A_log.data_ptr() if A_log is not None else None
+        p.dt_bias = dt_bias.data_ptr() if dt_bias is not None else None
+        p.h0 = h0.data_ptr() if h0 is not None else None
+        if self.cu is not None:
+            p.cu_seqlens = self.cu.data_ptr()
+            p.chunk_seq = self.chunk_seq.data_ptr()
+            p.seq_chunk_off = self.seq_off.data_ptr()
+        self.p = p
+        fb, bb = C.c_size_t(0), C.c_size_t(0)
+        _lib.check(_lib.load().kda_workspace_bytes(C.byref(p), C.byref(fb), C.byref(bb)), "kda_workspace_bytes")
+        self.fwd_bytes, self.bwd_bytes = fb.value, bb.value
+
+    def stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+
+
+def _require_cuda(t):
+    if not t.is_cuda:
+        raise RuntimeError("chunk_kda runs only on a CUDA device (sm_100a); there is no CPU fallback")
+
+
+class ChunkKDAFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, A_log, dt_bias, h0, scale, flags, output_final_state, cu_seqlens,
+                cu_seqlens_cpu, disable_recompute):
+        lib = _lib.load()
+        in_dtypes = (g.dtype, beta.dtype)
+        dt = q.dtype
+        q, k, v, g, beta = (t.to(dt).contiguous() for t in (q, k, v, g, beta))
+        A_log = A_log.float().contiguous() if A_log is not None else None
+        dt_bias = dt_bias.float().contiguous() if dt_bias is not None else None
+        h0 = h0.contiguous() if h0 is not None else None
+        with torch.cuda.device(q.device):
+            call = _Call(q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags)
+            B, T, H, dk, dv = call.shape
+            o = torch.empty(B, T, H, dv, dtype=dt, device=q.device)
+            state_shape = (call.N, H, dv, dk) if flags & _lib.FLAG_STATE_V_FIRST else (call.N, H, dk, dv)
+            ht = torch.empty(state_shape, dtype=torch.float32, device=q.device) if output_final_state else None
+            ws = torch.empty(call.fwd_bytes, dtype=torch.uint8, device=q.device)
+            p = call.p
+            p.o, p.ht = o.data_ptr(), (ht.data_ptr() if ht is not None else None)
+            p.workspace, p.workspace_bytes = ws.data_ptr(), call.fwd_bytes
+            if call.NT > 0:
+                _lib.check(lib.kda_fwd(C.byref(p), call.stream()), "kda_fwd")
+            elif ht is not None:
+                ht.copy_(h0 if h0 is not None else torch.zeros_like(ht))
+        ctx.save_for_backward(q, k, v, g, beta, A_log, dt_bias, h0, cu_seqlens, cu_seqlens_cpu,
+                              ws if disable_recompute else None)
+        ctx.meta = (scale, flags, in_dtypes, state_shape)
+        return o, ht
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        lib = _lib.load()
+        q, k, v, g, beta, A_log, dt_bias, h0, cu_seqlens, cu_seqlens_cpu, ws = ctx.saved_tensors
+        scale, flags, in_dtypes, state_shape = ctx.meta
+        dt = q.dtype
+        with torch.cuda.device(q.device):
+            call = _Call(q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags)
+            p = call.p
+            B, T, H, dk, dv = call.shape
+            if ws is None:  # recompute policy: rebuild the per-chunk records instead of keeping them
+                ws = torch.empty(call.fwd_bytes, dtype=torch.uint8, device=q.device)
+                o_tmp = torch.empty(B, T, H, dv, dtype=dt, device=q.device)
+                p.o, p.ht = o_tmp.data_ptr(), None
+                p.workspace, p.workspace_bytes = ws.data_ptr(), call.fwd_bytes
+                if call.NT > 0:
+                    _lib.check(lib.kda_fwd(C.byref(p), call.stream()), "kda_fwd (recompute)")
+            do = (do if do is not None else torch.zeros(B, T, H, dv, dtype=dt, device=q.device)).to(dt).contiguous()
+            dht = dht.float().contiguous() if dht is not None else None
+            dq, dk_, dg = torch.empty_like(q), torch.empty_like(k), torch.empty_like(g)
+            dv_, dbeta = torch.empty_like(v), torch.empty_like(beta)
+            gate = bool(flags & _lib.FLAG_GATE)
+            dA = torch.zeros(H, dtype=torch.float32, device=q.device) if gate else None
+            dbias = torch.zeros(H * dk, dtype=torch.float32, device=q.device) if gate and dt_bias is not None else None
+            dh0 = torch.empty(state_shape, dtype=torch.float32, device=q.device) if h0 is not None else None
+            scratch = torch.empty(call.bwd_bytes, dtype=torch.uint8, device=q.device)
+            p.o = dq.data_ptr()  # unused by the backward; must be non-NULL
+            p.workspace, p.workspace_bytes = ws.data_ptr(), call.fwd_bytes
+            p.grad_o = do.data_ptr()
+            p.grad_ht = dht.data_ptr() if dht is not None else None
+            p.grad_q, p.grad_k, p.grad_v = dq.data_ptr(), dk_.data_ptr(), dv_.data_ptr()
+            p.grad_g, p.grad_beta = dg.data_ptr(), dbeta.data_ptr()
+            p.grad_A_log = dA.data_ptr() if dA is not None else None
+            p.grad_dt_bias = dbias.data_ptr() if dbias is not None else None
+            p.grad_h0 = dh0.data_ptr() if dh0 is not None else None
+            p.bwd_scratch, p.bwd_scratch_bytes = scratch.data_ptr(), call.bwd_bytes
+            if call.NT > 0:
+                _lib.check(lib.kda_bwd(C.byref(p), call.stream()), "kda_bwd")
+            else:
+                for t in (dq, dk_, dv_, dg, dbeta):
+                    t.zero_()
+                if dh0 is not None:
+                    dh0.copy_(dht if dht is not None else torch.zeros_like(dh0))
+        return (dq, dk_, dv_, dg.to(in_dtypes[0]), dbeta.to(in_dtypes[1]), dA, dbias, dh0,
+                None, None, None, None, None, None)
+
+
+@torch.compiler.disable
+def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
+              use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
+              cu_seqlens=None, cu_seqlens_cpu=None, safe_gate=False, lower_bound=None, disable_recompute=False,
+              state_v_first=False, A_log=None, dt_bias=None, chunk_size=64, fp32_math=False, **kwargs):
+    """Kimi Delta Attention, chunkwise (k3mini/model.py:200-216).
+
+    q, k, g: [B, T, H, K]; v: [B, T, H, V]; beta: [B, T, H].  With
+    ``use_gate_in_kernel`` g is the raw gate input and the op applies
+    ``-exp(A_log) * softplus(g + dt_bias)`` (k3mini/model.py:220-222), otherwise g is the
+    natural-log decay per token.  ``use_qk_l2norm_in_kernel`` normalises q and k as
+    k3mini/model.py:218-219 does; ``use_beta_sigmoid_in_kernel`` treats beta as logits.
+    ``initial_state`` / the returned final state are FP32 ``[N, H, K, V]`` (``[N, H, V, K]``
+    with ``state_v_first``).  ``cu_seqlens`` ([N+1], batch 1) packs N documents; chunks and
+    the state restart at every document.  ``disable_recompute=True`` keeps the per-chunk
+    records between forward and backward, ``False`` rebuilds them in the backward.
+    ``fp32_math=True`` forces FP32 CUDA-core arithmetic in every stage (validation mode;
+    FP32 inputs always run that way).  Returns ``(o, final_state or None)``.
+    """
+    state_v_first = bool(kwargs.pop("transpose_state_layout", state_v_first))
+    for name in ("return_intermediate_states", "cp_context"):
+        if kwargs.pop(name, None):
+            raise NotImplementedError(f"chunk_kda: {name} is not supported by the B200 kernels")
+    if kwargs:
+        raise TypeError(f"chunk_kda: unexpected arguments {sorted(kwargs)}")
+    for t in (q, k, v, g, beta):
+        _require_cuda(t)
+    if safe_gate or lower_bound is not None:
+        raise NotImplementedError("chunk_kda: safe_gate/lower_bound are not part of the reference path "
+                                  "(k3mini/model.py:212 always passes safe_gate=False)")
+    if chunk_size != 64:
+        raise ValueError(f"`chunk_size` must be 64 for the B200 KDA kernels, got {chunk_size}.")
+    if q.dim() != 4 or q.shape != k.shape:
+        raise ValueError(f"q and k must have the same shape [B,T,H,K], got q={tuple(q.shape)} vs k={tuple(k.shape)}")
+    B, T, H, K = q.shape
+    if v.shape[:3] != q.shape[:3]:
+        raise ValueError("grouped value heads (HV != H) are not supported: v must be [B,T,H,V]")
+    if g.shape != (B, T, H, K):
+        raise ValueError(f"g must have shape {[B, T, H, K]}, got {list(g.shape)}")
+    if beta.shape != (B, T, H):
+        raise ValueError(f"beta must have shape {[B, T, H]}, got {list(beta.shape)}")
+    if K != v.shape[-1] or K not in (64, 128):
+        raise ValueError(f"the B200 KDA kernels need K == V in (64, 128), got K={K}, V={v.shape[-1]}")
+    if q.dtype not in _DTYPES:
+        raise TypeError(f"q/k/v must be float32 or bfloat16, got {q.dtype}")
+    if cu_seqlens is not None:
+        if B != 1:
+            raise ValueError(f"The batch size is expected to be 1 rather than {B} when using `cu_seqlens`."
+                             "Please flatten variable-length inputs before processing.")
+        if initial_state is not None and initial_state.shape[0] != len(cu_seqlens) - 1:
+            raise ValueError("The number of initial states is expected to be equal to the number of input "
+                             f"sequences, i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}.")
+    n_seq = B if cu_seqlens is None else len(cu_seqlens) - 1
+    if initial_state is not None:
+        if initial_state.dtype != torch.float32:
+            raise TypeError("initial_state must be in float32.")
+        want = (n_seq, H, v.shape[-1], K) if state_v_first else (n_seq, H, K, v.shape[-1])
+        if tuple(initial_state.shape) != want:
+            raise ValueError(f"initial_state must have shape {want}, got {tuple(initial_state.shape)}")
+    if use_gate_in_kernel:
+        if A_log is None:
+            raise ValueError("A_log must be provided when use_gate_in_kernel=True.")
+        if A_log.numel() != H or (dt_bias is not None and dt_bias.numel() != H * K):
+            raise ValueError("A_log must have H entries and dt_bias H*K entries")
+    else:
+        A_log = dt_bias = None
+    if scale is None:
+        scale = K ** -0.5
+    flags = ((_lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0) | (_lib.FLAG_GATE if use_gate_in_kernel else 0)
+             | (_lib.FLAG_BETA_SIGMOID if use_beta_sigmoid_in_kernel else 0)
+             | (_lib.FLAG_STATE_V_FIRST if state_v_first else 0))
+    if fp32_math or os.environ.get("OPENKIMI_B200_FP32_MATH") == "1":
+        flags |= _lib.FLAG_FORCE_SIMT
+    return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, initial_state, float(scale), flags,
+                                  bool(output_final_state), cu_seqlens, cu_seqlens_cpu, bool(disable_recompute))

@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""KDA forward+backward throughput on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1|c2|c3]
+
+One "step" = one forward + backward of ``chunk_kda`` over one batch of seeded synthetic
+input (default: B=16, T=2048, H=6, d=128, BF16 operands, FP32 state, final state returned,
+upstream gradient do ~ N(0,1)).  With N > 1 (torchrun, one rank per GPU) every rank runs the
+same per-GPU batch on its own data -- sequences are independent, so there is no collective
+on the kernel path -- and the reported value is all ranks' tokens / the slowest rank's time.
+
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, T, H, d, x_mean, a_lo, a_hi, beta_mean, n_docs)
+    "c1": dict(B=16, T=2048, H=6, d=128, x_mean=0.0, a_lo=1.0, a_hi=16.0, beta_mean=0.0, docs=0,
+               label="kda_fwd_bwd B=16 T=2048 H=6 d=128 bf16 chunk=64 (primary profile)"),
+    "c2": dict(B=4, T=4096, H=6, d=128, x_mean=3.0, a_lo=8.0, a_hi=64.0, beta_mean=2.0, docs=0,
+               label="kda_fwd_bwd B=4 T=4096 H=6 d=128 bf16 adversarial gate span"),
+    "c3": dict(B=1, T=65536, H=6, d=128, x_mean=0.0, a_lo=1.0, a_hi=16.0, beta_mean=0.0, docs=16,
+               label="kda_fwd_bwd packed T=65536 16 docs H=6 d=128 bf16 cu_seqlens"),
+}
+METRIC = "kda_fwd_bwd_throughput"
+UNIT = "Mtok/s"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm_gbs=d["hbm_gbs"], tflops=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+
+
+def stage_model(name, d, C=64, es=2):
+    """Algorithmic FLOPs and HBM bytes of one (chunk, head) unit of each kernel (dense tiles,
+    every tensor touched once; es = bytes per element of the BF16 records)."""
+    t = C * d * es          # one [64, d] tile
+    a = C * C * es          # one [64, 64] tile
+    s = d * d * es          # one state
+    m = {
+        "fwd_intra": (8 * C * C * d + 2 * C ** 3 // 3, 4 * t + C * es + (4 * t + 2 * a + 4 * d)),
+        "fwd_state": (6 * C * d * d + 2 * C * C * d, (4 * t + a + 4 * d) + (2 * t + s)),
+        "bwd_state": (6 * C * d * d + 2 * C * C * d, (4 * t + a + 4 * d) + (t + s)),
+        "bwd_chunk": (6 * C * d * d + 16 * C * C * d + 4 * C ** 3, (5 * t + C * es) + 2 * t + 2 * s + a + (4 * t + C * es)),
+        "param_reduce": (0, 4 * d + 4),
+    }
+    return m[name]
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "20", "-i", str(self.gpu)], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.count(",") >= 8]
+        os.unlink(self.path)
+        if not rows:
+            return out
+        clk = [float(r[1]) for r in rows]
+        out["sm_mhz"] = statistics.median(clk)
+        out["sm_max_mhz"] = float(rows[0][2])
+        out["power_w_max"] = max(float(r[3]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        out["reasons"] = [n for i, n in enumerate(names) if any(r[5 + i].strip() == "Active" for r in rows)]
+        out["samples"] = len(rows)
+        return out
+
+
+def make_workload(w, seed, device=None, pin=False):
+    from openkimi_b200.synthetic import make_inputs, random_cu_seqlens
+    inp = make_inputs(w["B"], w["T"], w["H"], w["d"], seed=seed, dtype=torch.bfloat16, x_mean=w["x_mean"],
+                      a_lo=w["a_lo"], a_hi=w["a_hi"], beta_mean=w["beta_mean"])
+    cu = h0 = None
+    if w["docs"]:
+        cu = random_cu_seqlens(w["T"], w["docs"], seed=seed)
+        h0 = torch.randn(w["docs"], w["H"], w["d"], w["d"], generator=torch.Generator().manual_seed(seed + 1)) * 0.02
+    host = dict(inp, cu=cu, h0=h0)
+    if pin:
+        host = {k: (v.pin_memory() if isinstance(v, torch.Tensor) else v) for k, v in host.items()}
+    return host
+
+
+def step_device(dev_in, w):
+    """One forward + backward through the public op with inputs already on the device."""
+    from openkimi_b200 import chunk_kda
+    leaves = [dev_in[n].requires_grad_(True) for n in ("q", "k", "v", "g", "beta", "a_log", "dt_bias")]
+    for t in leaves:
+        t.grad = None
+    h0 = dev_in.get("h0")
+    if h0 is not None:
+        h0.requires_grad_(True)
+        h0.grad = None
+    o, ht = chunk_kda(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], A_log=leaves[5], dt_bias=leaves[6],
+                      scale=w["d"] ** -0.5, initial_state=h0, output_final_state=True, use_qk_l2norm_in_kernel=True,
+                      use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True, cu_seqlens=dev_in.get("cu"),
+                      cu_seqlens_cpu=dev_in.get("cu_cpu"), state_v_first=True, disable_recompute=True)
+    o.backward(dev_in["do"])
+    return o, ht, leaves, h0
+
+
+def to_device(host, device):
+    dev = {k: v.to(device, non_blocking=True) for k, v in host.items() if isinstance(v, torch.Tensor)}
+    if host.get("cu") is not None:
+        dev["cu_cpu"] = host["cu"]
+    return dev
+
+
+def cpu_oracle_rate(w, sample_T, threads=None):
+    """tokens/s of the CPU oracle (PyTorch port of k3mini/model.py:101-129 + prologue :217-223)
+    forward + autograd backward on one [1, sample_T, H, d] slice of the workload."""
+    from oracle.kda_oracle import kda_oracle_fwd_bwd, make_inputs
+    if threads:
+        torch.set_num_threads(threads)
+    inp = make_inputs(1, sample_T, w["H"], w["d"], seed=0, dtype=torch.bfloat16, x_mean=w["x_mean"], a_lo=w["a_lo"],
+                      a_hi=w["a_hi"], beta_mean=w["beta_mean"])
+    t0 = time.perf_counter()
+    kda_oracle_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["do"], a_log=inp["a_log"],
+                       dt_bias=inp["dt_bias"], scale=w["d"] ** -0.5)
+    dt = time.perf_counter() - t0
+    return sample_T / dt, dt
+
+
+def run_reference(args, w, rank, world):
+    """The reference's CPU implementation of the path (the oracle port; the reference is Python
+    and cannot travel to the GPU box) on the host cores."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    sample_T = 256
+    for _ in range(args.warmup):
+        cpu_oracle_rate(w, sample_T)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_rate(w, sample_T)
+    dt = time.perf_counter() - t0
+    val = args.steps * sample_T / dt / 1e6
+    sample = f"each step = oracle fwd+bwd of one [1,{sample_T},{w['H']},{w['d']}] slice of the workload"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["label"], "sample": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=1024)
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size (profiling cases)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="profiling case: device-resident steps only (no end-to-end leg, no CPU baseline)")
+    args = ap.parse_args()
+    if args.impl == "ours" and not args.kernel_only:
+        args.warmup = max(args.warmup, 3)
+    w = dict(WORKLOADS[args.workload])
+    if args.batch:
+        w["B"] = args.batch
+        w["label"] += f" [batch overridden to {args.batch}]"
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+        return
+
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    from openkimi_b200 import _lib
+    lib = _lib.load()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    host = make_workload(w, seed=rank, pin=True)
+    dev_in = to_device(host, device)
+    tokens = w["B"] * w["T"]
+    units = None
+
+    # ---- device-resident timing -------------------------------------------------------
+    for _ in range(args.warmup):
+        step_device(dev_in, w)
+    barrier()
+    n_calls = 2 * args.steps
+    lib.kda_profile_begin(n_calls)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_device(dev_in, w)
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = e0.elapsed_time(e1)
+    # per-kernel durations from the events recorded inside the timed region
+    names = {0: ["fwd_intra", "fwd_state"], 1: ["bwd_state", "bwd_chunk", "param_reduce"]}
+    stage_ms, launches = {}, 0
+    buf, kind = (C.c_float * 8)(), C.c_int()
+    for call in range(n_calls):
+        n = lib.kda_profile_read(call, C.byref(kind), buf, 8)
+        for i in range(max(n, 0)):
+            nm = names[kind.value][i] if i < len(names[kind.value]) else f"stage{i}"
+            stage_ms.setdefault(nm, []).append(buf[i])
+            launches += 1
+    lib.kda_profile_begin(0)
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+
+    if args.kernel_only:
+        if rank == 0:
+            avg = {k: sum(v) / len(v) for k, v in stage_ms.items()}
+            print(json.dumps({"metric": METRIC, "value": world * tokens * args.steps / (ms / 1e3) / 1e6, "unit": UNIT,
+                              "kernel_only": True, "ms_per_step": ms / args.steps, "kernels_ms": avg,
+                              "config": {"workload": w["label"]}}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- end to end: pinned host inputs -> device -> op -> host results ----------------
+    pinned_out = []
+
+    def e2e_step():
+        d = to_device(host, device)
+        o, ht, leaves, h0 = step_device(d, w)
+        outs = [o, ht] + [x.grad for x in leaves] + ([h0.grad] if h0 is not None else [])
+        if not pinned_out:
+            pinned_out.extend(torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs)
+        for dst, src in zip(pinned_out, outs):
+            dst.copy_(src, non_blocking=True)
+        return d, pinned_out
+
+    h2d = sum(v.numel() * v.element_size() for v in host.values() if isinstance(v, torch.Tensor))
+    for _ in range(2):
+        _, res = e2e_step()
+    d2h = sum(x.numel() * x.element_size() for x in res)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(args.steps, 10))
+    f0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    t2 = torch.tensor([f0.elapsed_time(f1)], device=device)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t2.item()) / e2e_steps
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = _peaks()
+    value = world * tokens * args.steps / (ms / 1e3) / 1e6
+    nt_h = (w["B"] * math.ceil(w["T"] / 64) if not w["docs"] else None)
+    if nt_h is None:
+        cu = host["cu"].tolist()
+        nt_h = sum(math.ceil((cu[i + 1] - cu[i]) / 64) for i in range(len(cu) - 1))
+    units = nt_h * w["H"]
+    avg = {k: sum(v) / len(v) for k, v in stage_ms.items()}
+    dom = max(avg, key=avg.get)
+    flops, byts = stage_model(dom, w["d"])
+    intensity = flops / byts
+    ridge = peaks["tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+    if intensity < ridge:
+        ach = byts * units / (avg[dom] / 1e3) / 1e9
+        roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"]}
+    else:
+        ach = flops * units / (avg[dom] / 1e3) / 1e12
+        roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"]}
+    roof.update({"kernel": dom, "kernel_ms": avg[dom], "peak_source": peaks["source"], "traffic": None,
+                 "units_per_launch": units, "algorithmic_bytes_per_unit": byts, "algorithmic_flops_per_unit": flops})
+    # whole-op fractions: dense-tile FLOPs 3*(10*C*d + 6*d^2) per (token, head); minimal HBM bytes
+    d = w["d"]
+    op_flops = 3 * (10 * 64 * d + 6 * d * d) * w["H"] * tokens
+    op_bytes = (4 * 2 * d + 2 + 2 * d + 4 * 2 * d + 2 + 2 * d + 4 * 2 * d + 2) * w["H"] * tokens
+    step_s = ms / 1e3 / args.steps
+    whole = {"dense_mma_frac": op_flops / step_s / (peaks["tflops"] * 1e12),
+             "min_hbm_frac": op_bytes / step_s / (peaks["hbm_gbs"] * 1e9),
+             "tflops": op_flops / step_s / 1e12, "flops_per_token": op_flops / tokens}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["label"], "per_gpu_tokens": tokens, "state": "fp32", "chunk": 64,
+                   "l2": "inputs + per-chunk records of one step ~1 GB > 126 MB L2, no explicit flush",
+                   "partition": f"{world} x independent batches (sequence-parallel, no collective)"},
+        "clocks": clocks,
+        "e2e": {"value": world * tokens / (e2e_ms / 1e3) / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "gpu_launches": launches,
+        "kernels_ms": avg,
+        "roofline": roof,
+        "whole_op": whole,
+    }
+    if not args.no_cpu_baseline:
+        rate, secs = cpu_oracle_rate(w, args.cpu_sample_tokens, threads=os.cpu_count())
+        line["cpu_baseline"] = {"value": rate / 1e6, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"oracle fwd+bwd of one [1,{args.cpu_sample_tokens},{w['H']},{w['d']}] slice, "
+                                          f"{secs:.1f} s"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

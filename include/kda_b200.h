@@ -125,6 +125,15 @@ int kda_guard_version(void);
 float kda_guard_max_span(void);
 const char *kda_guard_dot_precision(void);
 
+/* Benchmark instrumentation (no reference counterpart; the reference times its op from
+ * Python with CUDA events, scripts/benchmark_kda_backends.py:119-165).  After
+ * kda_profile_begin(n) the next n kda_fwd / kda_bwd calls bracket each of their kernels with
+ * CUDA events on the caller's stream.  After the stream is synchronised,
+ * kda_profile_read(call, &kind, ms, max) returns the number of stages of that call
+ * (kind 0 = forward, 1 = backward) and their durations in milliseconds, or -1. */
+int kda_profile_begin(int max_calls);
+int kda_profile_read(int call, int *kind, float *stage_ms, int max_stages);
+
 const char *kda_status_string(int status);
 const char *kda_last_cuda_error(void);
 int kda_abi_version(void);

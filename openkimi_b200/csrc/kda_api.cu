@@ -20,6 +20,29 @@ static int fail_cuda(cudaError_t e) {
     return KDA_ERR_LAUNCH;
 }
 
+// ---- optional per-stage timing (benchmark instrumentation) ---------------------------------
+// Each kda_fwd / kda_bwd call made while profiling is on takes the next slot and brackets
+// its stages with CUDA events on the caller's stream; nothing is synchronised here.
+constexpr int PROF_STAGES = 8;
+struct ProfSlot { cudaEvent_t ev[PROF_STAGES + 1]; int n; int kind; };
+static ProfSlot* g_prof = nullptr;
+static int g_prof_cap = 0, g_prof_used = 0;
+static bool g_prof_on = false;
+static ProfSlot* g_cur = nullptr;
+
+void prof_mark(cudaStream_t s) {
+    if (g_cur && g_cur->n <= PROF_STAGES) cudaEventRecord(g_cur->ev[g_cur->n++], s);
+}
+static void prof_open(int kind, cudaStream_t s) {
+    g_cur = nullptr;
+    if (g_prof_on && g_prof_used < g_prof_cap) {
+        g_cur = &g_prof[g_prof_used++];
+        g_cur->n = 0;
+        g_cur->kind = kind;
+        prof_mark(s);
+    }
+}
+
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 static int validate(const KdaParams* p, bool bwd) {
@@ -94,7 +117,9 @@ int kda_fwd(const KdaParams* p, void* stream) {
     if (v != KDA_OK) return v;
     cudaStream_t s = (cudaStream_t)stream;
     const bool tc = !(p->flags & KDA_FLAG_FORCE_SIMT) && tc_supported(*p);
+    prof_open(0, s);
     cudaError_t e = tc ? tc_fwd(*p, s) : simt_fwd(*p, s);
+    g_cur = nullptr;
     return e == cudaSuccess ? KDA_OK : fail_cuda(e);
 }
 
@@ -103,8 +128,38 @@ int kda_bwd(const KdaParams* p, void* stream) {
     if (v != KDA_OK) return v;
     cudaStream_t s = (cudaStream_t)stream;
     const bool tc = !(p->flags & KDA_FLAG_FORCE_SIMT) && tc_supported(*p);
+    prof_open(1, s);
     cudaError_t e = tc ? tc_bwd(*p, s) : simt_bwd(*p, s);
+    g_cur = nullptr;
     return e == cudaSuccess ? KDA_OK : fail_cuda(e);
+}
+
+int kda_profile_begin(int max_calls) {
+    if (max_calls < 0) return KDA_ERR_SHAPE;
+    if (max_calls > g_prof_cap) {
+        ProfSlot* n = new ProfSlot[max_calls];
+        for (int i = 0; i < max_calls; ++i)
+            for (int j = 0; j <= PROF_STAGES; ++j)
+                if (i < g_prof_cap) n[i].ev[j] = g_prof[i].ev[j];
+                else if (cudaEventCreate(&n[i].ev[j]) != cudaSuccess) return KDA_ERR_LAUNCH;
+        delete[] g_prof;
+        g_prof = n;
+        g_prof_cap = max_calls;
+    }
+    g_prof_used = 0;
+    g_prof_on = max_calls > 0;
+    return KDA_OK;
+}
+
+int kda_profile_read(int call, int* kind, float* stage_ms, int max_stages) {
+    g_prof_on = false;
+    if (call < 0 || call >= g_prof_used || !stage_ms) return -1;
+    ProfSlot& sl = g_prof[call];
+    if (kind) *kind = sl.kind;
+    int n = sl.n - 1 < max_stages ? sl.n - 1 : max_stages;
+    for (int i = 0; i < n; ++i)
+        if (cudaEventElapsedTime(&stage_ms[i], sl.ev[i], sl.ev[i + 1]) != cudaSuccess) return -1;
+    return n;
 }
 
 }  // extern "C"

@@ -15,6 +15,8 @@
 
 namespace kda {
 
+void prof_mark(cudaStream_t s);
+
 constexpr int NTHREADS = 256;
 constexpr int KS = 16;  // k-slice of the tile product
 
@@ -661,22 +663,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
         for (int cc = 0; cc < D / 16; ++cc) {
             const int d = tx + 16 * cc;
             const float gi = sG[i * D + d], qi = sq[i * D + d], ki = sk[i * D + d];
+            // strictly-lower / strictly-upper parts; the diagonal pair (j == i) has decay 1 and
+            // contributes equal and opposite amounts to dG, so it is kept out of dG exactly
             float a1 = 0.f, a2 = 0.f;
-            for (int j = 0; j <= i; ++j) {
+            for (int j = 0; j < i; ++j) {
                 float kd = sk[j * D + d] * exp2f(gi - sG[j * D + d]);
                 a1 = fmaf(sdA[i * 65 + j], kd, a1);
-                a2 = fmaf(sdM[i * 65 + j], kd, a2);  // sdM is zero on and above the diagonal
+                a2 = fmaf(sdM[i * 65 + j], kd, a2);
             }
             float c1 = 0.f;
-            for (int ii = i; ii < C; ++ii) {
+            for (int ii = i + 1; ii < C; ++ii) {
                 float e = exp2f(sG[ii * D + d] - gi);
                 float t = scale * sdA[ii * 65 + i] * sq[ii * D + d] + sbeta[ii] * sdM[ii * 65 + i] * sk[ii * D + d];
                 c1 = fmaf(t, e, c1);
             }
+            const float diag = scale * sdA[i * 65 + i];
             float dq_in = scale * a1, dk_row = sbeta[i] * a2;
             db_r[r] += ki * a2;
-            dq_a[r][cc] += dq_in;
-            dk_a[r][cc] += dk_row + c1;
+            dq_a[r][cc] += dq_in + diag * ki;
+            dk_a[r][cc] += dk_row + c1 + diag * qi;
             dG_a[r][cc] += qi * dq_in + ki * dk_row - ki * c1;
         }
     }
@@ -814,7 +819,9 @@ static cudaError_t launch_fwd(const KdaParams& p, cudaStream_t s) {
     if ((e = set_smem(kda_fwd_intra_simt<T, D>, smem_intra<D>())) != cudaSuccess) return e;
     if ((e = set_smem(kda_fwd_state_simt<T, D, BV>, smem_state<D, BV>())) != cudaSuccess) return e;
     kda_fwd_intra_simt<T, D><<<p.NT * p.H, NTHREADS, smem_intra<D>(), s>>>(p);
+    prof_mark(s);
     kda_fwd_state_simt<T, D, BV><<<dim3(D / BV, p.H, p.N), NTHREADS, smem_state<D, BV>(), s>>>(p);
+    prof_mark(s);
     return cudaGetLastError();
 }
 
@@ -825,8 +832,11 @@ static cudaError_t launch_bwd(const KdaParams& p, cudaStream_t s) {
     if ((e = set_smem(kda_bwd_state_simt<T, D, BV>, smem_state<D, BV>())) != cudaSuccess) return e;
     if ((e = set_smem(kda_bwd_chunk_simt<T, D>, smem_bwd_chunk<D>())) != cudaSuccess) return e;
     kda_bwd_state_simt<T, D, BV><<<dim3(D / BV, p.H, p.N), NTHREADS, smem_state<D, BV>(), s>>>(p);
+    prof_mark(s);
     kda_bwd_chunk_simt<T, D><<<p.NT * p.H, NTHREADS, smem_bwd_chunk<D>(), s>>>(p);
+    prof_mark(s);
     if (p.flags & KDA_FLAG_GATE) kda_param_reduce<<<p.H, 128, 0, s>>>(p);
+    prof_mark(s);
     return cudaGetLastError();
 }
 

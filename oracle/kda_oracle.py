@@ -27,34 +27,36 @@ import torch.nn.functional as F
 LOG2E = 1.0 / math.log(2.0)
 
 
-def l2_normalize(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+def l2_normalize(x: torch.Tensor, eps: float = 1e-6, dtype=torch.float32) -> torch.Tensor:
     """x / max(||x||_2, eps) over the last axis in FP32 (k3mini/model.py:218-219)."""
-    xf = x.float()
+    xf = x.to(dtype)
     return xf / xf.norm(dim=-1, keepdim=True).clamp_min(eps)
 
 
-def kda_gate(raw: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor | None) -> torch.Tensor:
+def kda_gate(raw: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor | None, dtype=torch.float32) -> torch.Tensor:
     """log-decay  -exp(A_log)[h] * softplus(raw + dt_bias[h, :])  (k3mini/model.py:220-222)."""
     heads, dim = raw.shape[-2], raw.shape[-1]
-    x = raw.float()
+    x = raw.to(dtype)
     if dt_bias is not None:
-        x = x + dt_bias.float().view(heads, dim)
-    return -a_log.float().exp().view(heads, 1) * F.softplus(x)
+        x = x + dt_bias.to(dtype).view(heads, dim)
+    return -a_log.to(dtype).exp().view(heads, 1) * F.softplus(x)
 
 
 def kda_prologue(q, k, g, beta, *, a_log=None, dt_bias=None, use_qk_l2norm=True,
-                 use_gate=True, use_beta_sigmoid=True, round_to=None):
+                 use_gate=True, use_beta_sigmoid=True, round_to=None, dtype=torch.float32):
     """Reference-branch prologue of KimiDeltaAttention.forward (k3mini/model.py:217-223).
 
     ``round_to`` reproduces the ``.to(x.dtype)`` round trip the reference applies to the
-    normalised q and k (model.py:218-219) when the activations are BF16.
+    normalised q and k (model.py:218-219) when the activations are BF16.  ``dtype`` is the
+    arithmetic type: float32 as in the reference, float64 for a check free of the oracle's
+    own rounding.
     """
     if use_qk_l2norm:
-        q, k = l2_normalize(q), l2_normalize(k)
+        q, k = l2_normalize(q, dtype=dtype), l2_normalize(k, dtype=dtype)
         if round_to is not None:
             q, k = q.to(round_to), k.to(round_to)
-    log_alpha = kda_gate(g, a_log, dt_bias) if use_gate else g.float()
-    beta = beta.float().sigmoid() if use_beta_sigmoid else beta.float()
+    log_alpha = kda_gate(g, a_log, dt_bias, dtype) if use_gate else g.to(dtype)
+    beta = beta.to(dtype).sigmoid() if use_beta_sigmoid else beta.to(dtype)
     return q, k, log_alpha, beta
 
 
@@ -124,7 +126,7 @@ def kda_oracle(q, k, v, g, beta, *, a_log=None, dt_bias=None, scale=None, initia
     (k3mini/model.py:217-223) with the state extensions described above."""
     qn, kn, log_alpha, b = kda_prologue(q, k, g, beta, a_log=a_log, dt_bias=dt_bias,
                                         use_qk_l2norm=use_qk_l2norm, use_gate=use_gate,
-                                        use_beta_sigmoid=use_beta_sigmoid, round_to=round_qk_to)
+                                        use_beta_sigmoid=use_beta_sigmoid, round_to=round_qk_to, dtype=dtype)
     return kda_recurrent_oracle(qn, kn, v, log_alpha, b, scale=scale, initial_state=initial_state,
                                 output_final_state=output_final_state, cu_seqlens=cu_seqlens,
                                 dtype=dtype)

@@ -59,8 +59,15 @@ def run_oracle(inp, *, fused=True, h0=None, dht=None, cu=None, dtype=torch.float
                                 use_gate=fused, use_beta_sigmoid=fused, dtype=dtype)
 
 
-def compare(dev, ref, tol_max, tol_l2, names=None):
-    """Returns a list of (name, max_rel, rel_l2, ok)."""
+def max_abs(a, r):
+    return float((a.double().cpu() - r.double().cpu()).abs().max())
+
+
+def compare(dev, ref, tol_max, tol_l2, names=None, abs_escape=0.0):
+    """Returns a list of (name, max_rel, rel_l2, ok).  ``abs_escape`` is the reference's own
+    rule for references that are numerically zero
+    (experiments/kda_sm90/validate_fla_guarded_integration.py:24-25,40-48): a tensor whose
+    largest absolute error is below it passes whatever the relative error."""
     rows = []
     for name in names or (("o", "ht") + GRADS):
         if name not in ref or name not in dev or dev[name] is None:
@@ -68,7 +75,8 @@ def compare(dev, ref, tol_max, tol_l2, names=None):
         r = ref[name].reshape(dev[name].shape)
         m, l = max_rel(dev[name], r), rel_l2(dev[name], r)
         finite = bool(torch.isfinite(dev[name].float()).all())
-        rows.append((name, m, l, finite and m <= tol_max and l <= tol_l2))
+        ok = finite and ((m <= tol_max and l <= tol_l2) or max_abs(dev[name], r) <= abs_escape)
+        rows.append((name, m, l, ok))
     return rows
 
 

@@ -27,11 +27,11 @@ def test_short_conv(dtype, tol, B, T, Cc, cu):
     mod = ShortConvolution(Cc, 4).cuda()
     w = mod.weight.detach().cpu().clone()
     cu_t = None if cu is None else torch.tensor(cu)
-    xr = x.float().requires_grad_(True)
+    xr = x.float().clone().requires_grad_(True)
     wr = w.clone().requires_grad_(True)
     yr = O.short_conv_oracle(xr, wr, cu_t)
     yr.backward(dy.float())
-    xd = x.cuda().requires_grad_(True)
+    xd = x.detach().cuda().requires_grad_(True)
     yd, _ = mod(xd, cu_seqlens=None if cu is None else cu_t.cuda())
     yd.backward(dy.cuda())
     _check(yd, yr.detach(), tol)
@@ -61,10 +61,10 @@ def test_norm_gate(dtype, tol):
     with torch.no_grad():
         mod.weight.uniform_(0.5, 1.5)
     w = mod.weight.detach().cpu().clone().requires_grad_(True)
-    xr, gr = x.float().requires_grad_(True), g.float().requires_grad_(True)
+    xr, gr = x.float().clone().requires_grad_(True), g.float().clone().requires_grad_(True)
     yr = O.rms_norm_gate_oracle(xr, gr, w)
     yr.backward(dy.float())
-    xd, gd = x.cuda().requires_grad_(True), g.cuda().requires_grad_(True)
+    xd, gd = x.detach().cuda().requires_grad_(True), g.detach().cuda().requires_grad_(True)
     yd = mod(xd, gd)
     yd.backward(dy.cuda())
     _check(yd, yr.detach(), tol)

@@ -35,7 +35,10 @@ enum {
     KDA_FLAG_GATE = 2,          /* use_gate_in_kernel        (k3mini/model.py:210) */
     KDA_FLAG_BETA_SIGMOID = 4,  /* use_beta_sigmoid_in_kernel(k3mini/model.py:211) */
     KDA_FLAG_STATE_V_FIRST = 8, /* state_v_first             (k3mini/model.py:214) */
-    KDA_FLAG_FORCE_SIMT = 16    /* FP32 CUDA-core arithmetic in every stage (validation mode) */
+    KDA_FLAG_FORCE_SIMT = 16,   /* FP32 CUDA-core arithmetic in every stage (validation mode) */
+    /* per-stage variants of the same switch (debugging / A-B measurements) */
+    KDA_FLAG_SIMT_FWD_INTRA = 32, KDA_FLAG_SIMT_FWD_STATE = 64,
+    KDA_FLAG_SIMT_BWD_STATE = 128, KDA_FLAG_SIMT_BWD_CHUNK = 256
 };
 
 enum {
@@ -133,6 +136,14 @@ const char *kda_guard_dot_precision(void);
  * (kind 0 = forward, 1 = backward) and their durations in milliseconds, or -1. */
 int kda_profile_begin(int max_calls);
 int kda_profile_read(int call, int *kind, float *stage_ms, int max_stages);
+
+/* Device self-test of the tcgen05 building block (no reference counterpart): one CTA
+ * computes D[128,N] = A[128,K] * B[K,N] (FP32 in, BF16 operands, FP32 accumulate) with the
+ * operand view (shared K-major / MN-major, or A in tensor memory) and the descriptor strides
+ * given by the caller.  Used by the tests to pin the operand layouts the kernels rely on. */
+int kda_selftest_mma(const float *A, const float *B, float *D, int N, int K, int a_mode, int b_mode,
+                     int lbo_a, int sbo_a, int step_a, int lbo_b, int sbo_b, int step_b, int neg_a,
+                     int m_rows, int *status, void *cuda_stream);
 
 const char *kda_status_string(int status);
 const char *kda_last_cuda_error(void);

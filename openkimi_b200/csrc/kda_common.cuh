@@ -65,7 +65,13 @@ __device__ __forceinline__ void seq_chunks(const KdaParams& p, int n, int& c0, i
 
 // ---------------------------------------------------------------------------------------
 // workspace layout (byte offsets).  All per-(chunk, head) records are stored
-// [NT][H][...] so that consecutive heads of one chunk are adjacent.
+// [NT][H][...] so that consecutive heads of one chunk are adjacent.  Inside a record the
+// elements are in the core-matrix order of kda_tc.cuh (cm_idx), so that a record is a
+// ready-made tcgen05 operand after one linear bulk copy into shared memory:
+//   W    as W^T   cm(d, i; 64)      U / V'  as V'^T  cm(e, i; 64)     (i = token in chunk)
+//   Aqk, Tm       cm(i, j; 64)      Qt, Kh           cm(i, d; dk)
+//   S0, dS as S^T cm(e, d; dk)      dVn     as dV'^T cm(e, i; 64)
+// gamC is a plain float[dk].
 // ---------------------------------------------------------------------------------------
 struct WsLayout {
     size_t W, U, Aqk, Qt, Kh, Tm, S0, gamC, total;      // forward workspace

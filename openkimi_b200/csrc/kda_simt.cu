@@ -12,6 +12,7 @@
 //
 // The math follows the recurrence of k3mini/model.py:115-129 rewritten per 64-token chunk.
 #include "kda_common.cuh"
+#include "kda_tc.cuh"
 
 namespace kda {
 
@@ -235,15 +236,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_fwd_intra_simt(const KdaParam
     // records that depend only on the prologue
     for (int idx = tid; idx < C * C; idx += NTHREADS) {
         int i = idx / C, j = idx % C;
-        stf(gA + idx, sA[i * 65 + j]);
-        stf(gT + idx, sT[i * 65 + j]);
+        stf(gA + tc::cm_idx(i, j, C), sA[i * 65 + j]);
+        stf(gT + tc::cm_idx(i, j, C), sT[i * 65 + j]);
     }
     for (int idx = tid; idx < C * D; idx += NTHREADS) {
         int i = idx / D, d = idx % D;
         float G = sG[idx], gl = sG[(C - 1) * D + d];
         float gam = exp2f(G);
-        stf(gQt + idx, p.scale * sq[idx] * gam);
-        stf(gKh + idx, sk[idx] * exp2f(gl - G));
+        stf(gQt + tc::cm_idx(i, d, D), p.scale * sq[idx] * gam);
+        stf(gKh + tc::cm_idx(i, d, D), sk[idx] * exp2f(gl - G));
         if (i == C - 1) gGam[d] = gam;
     }
     __syncthreads();
@@ -262,14 +263,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_fwd_intra_simt(const KdaParam
 #pragma unroll
         for (int r = 0; r < 4; ++r)
 #pragma unroll
-            for (int cc = 0; cc < D / 16; ++cc) stf(gW + (ty + 16 * r) * D + tx + 16 * cc, acc[r][cc]);
+            for (int cc = 0; cc < D / 16; ++cc) stf(gW + tc::cm_idx(tx + 16 * cc, ty + 16 * r, C), acc[r][cc]);
         zero_acc(acc);
         mm_tile<C, D>(acc, C, [&](int m, int k) { return sT[m * 65 + k]; }, [&](int k, int n) { return sv[k * D + n]; },
                       st, true, false);
 #pragma unroll
         for (int r = 0; r < 4; ++r)
 #pragma unroll
-            for (int cc = 0; cc < D / 16; ++cc) stf(gU + (ty + 16 * r) * D + tx + 16 * cc, acc[r][cc]);
+            for (int cc = 0; cc < D / 16; ++cc) stf(gU + tc::cm_idx(tx + 16 * cc, ty + 16 * r, C), acc[r][cc]);
     }
 }
 
@@ -312,31 +313,31 @@ __global__ void __launch_bounds__(NTHREADS) kda_fwd_state_simt(const KdaParams p
 
         for (int idx = tid; idx < D * BV; idx += NTHREADS) {
             int d = idx / BV, e = idx % BV;
-            stf(gS0 + d * D + e0 + e, sS[d * (BV + 1) + e]);
+            stf(gS0 + tc::cm_idx(e0 + e, d, D), sS[d * (BV + 1) + e]);
         }
         // V' = U - W S
         {
             float acc[4][BV / 16];
             zero_acc(acc);
-            mm_tile<C, BV>(acc, D, [&](int m, int k) { return ldf(gW + m * D + k); },
+            mm_tile<C, BV>(acc, D, [&](int m, int k) { return ldf(gW + tc::cm_idx(k, m, C)); },
                            [&](int k, int nn) { return sS[k * (BV + 1) + nn]; }, st, true, false);
 #pragma unroll
             for (int r = 0; r < 4; ++r)
 #pragma unroll
                 for (int cc = 0; cc < BV / 16; ++cc) {
                     int i = ty + 16 * r, e = tx + 16 * cc;
-                    float vn = ldf(gU + i * D + e0 + e) - acc[r][cc];
+                    float vn = ldf(gU + tc::cm_idx(e0 + e, i, C)) - acc[r][cc];
                     sVn[i * (BV + 1) + e] = vn;
-                    stf(gU + i * D + e0 + e, vn);
+                    stf(gU + tc::cm_idx(e0 + e, i, C), vn);
                 }
         }
         // O = Qt S + Aqk V'
         {
             float acc[4][BV / 16];
             zero_acc(acc);
-            mm_tile<C, BV>(acc, D, [&](int m, int k) { return ldf(gQt + m * D + k); },
+            mm_tile<C, BV>(acc, D, [&](int m, int k) { return ldf(gQt + tc::cm_idx(m, k, D)); },
                            [&](int k, int nn) { return sS[k * (BV + 1) + nn]; }, st, true, false);
-            mm_tile<C, BV>(acc, C, [&](int m, int k) { return ldf(gA + m * C + k); },
+            mm_tile<C, BV>(acc, C, [&](int m, int k) { return ldf(gA + tc::cm_idx(m, k, C)); },
                            [&](int k, int nn) { return sVn[k * (BV + 1) + nn]; }, st, true, false);
 #pragma unroll
             for (int r = 0; r < 4; ++r)
@@ -350,7 +351,7 @@ __global__ void __launch_bounds__(NTHREADS) kda_fwd_state_simt(const KdaParams p
         {
             float acc[D / 16][BV / 16];
             zero_acc(acc);
-            mm_tile<D, BV>(acc, C, [&](int m, int k) { return ldf(gKh + k * D + m); },
+            mm_tile<D, BV>(acc, C, [&](int m, int k) { return ldf(gKh + tc::cm_idx(k, m, D)); },
                            [&](int k, int nn) { return sVn[k * (BV + 1) + nn]; }, st, false, false);
 #pragma unroll
             for (int r = 0; r < D / 16; ++r)
@@ -412,14 +413,14 @@ __global__ void __launch_bounds__(NTHREADS) kda_bwd_state_simt(const KdaParams p
         };
         for (int idx = tid; idx < D * BV; idx += NTHREADS) {
             int d = idx / BV, e = idx % BV;
-            stf(gdS + d * D + e0 + e, sS[d * (BV + 1) + e]);
+            stf(gdS + tc::cm_idx(e0 + e, d, D), sS[d * (BV + 1) + e]);
         }
         {
             float acc[4][BV / 16];
             zero_acc(acc);
-            mm_tile<C, BV>(acc, C, [&](int m, int k) { return ldf(gA + k * C + m); },
+            mm_tile<C, BV>(acc, C, [&](int m, int k) { return ldf(gA + tc::cm_idx(k, m, C)); },
                            [&](int k, int nn) { return ldo(k, nn); }, st, false, false);
-            mm_tile<C, BV>(acc, D, [&](int m, int k) { return ldf(gKh + m * D + k); },
+            mm_tile<C, BV>(acc, D, [&](int m, int k) { return ldf(gKh + tc::cm_idx(m, k, D)); },
                            [&](int k, int nn) { return sS[k * (BV + 1) + nn]; }, st, true, false);
 #pragma unroll
             for (int r = 0; r < 4; ++r)
@@ -427,15 +428,15 @@ __global__ void __launch_bounds__(NTHREADS) kda_bwd_state_simt(const KdaParams p
                 for (int cc = 0; cc < BV / 16; ++cc) {
                     int i = ty + 16 * r, e = tx + 16 * cc;
                     sVn[i * (BV + 1) + e] = acc[r][cc];
-                    stf(gdV + i * D + e0 + e, acc[r][cc]);
+                    stf(gdV + tc::cm_idx(e0 + e, i, C), acc[r][cc]);
                 }
         }
         {
             float acc[D / 16][BV / 16];
             zero_acc(acc);
-            mm_tile<D, BV>(acc, C, [&](int m, int k) { return ldf(gQt + k * D + m); },
+            mm_tile<D, BV>(acc, C, [&](int m, int k) { return ldf(gQt + tc::cm_idx(k, m, D)); },
                            [&](int k, int nn) { return ldo(k, nn); }, st, false, false);
-            mm_tile<D, BV>(acc, C, [&](int m, int k) { return -ldf(gW + k * D + m); },
+            mm_tile<D, BV>(acc, C, [&](int m, int k) { return -ldf(gW + tc::cm_idx(m, k, C)); },
                            [&](int k, int nn) { return sVn[k * (BV + 1) + nn]; }, st, false, false);
 #pragma unroll
             for (int r = 0; r < D / 16; ++r)
@@ -496,7 +497,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
     const float scale = p.scale;
 
     load_prologue<T, D>(p, ci, h, sq, sk, sG, nullptr, sbeta, srq, srk);
-    for (int idx = tid; idx < C * C; idx += NTHREADS) sT[(idx / C) * 65 + idx % C] = ldf(gT + idx);
+    for (int idx = tid; idx < C * C; idx += NTHREADS) sT[(idx / C) * 65 + idx % C] = ldf(gT + tc::cm_idx(idx / C, idx % C, C));
     if (tid < C) sdb[tid] = 0.f;
 
     auto ldo = [&](int i, int e) { return i < ci.len ? ldf(dO + ((size_t)(ci.tok0 + i) * p.H + h) * D + e) : 0.f; };
@@ -512,7 +513,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
     {
         float acc[4][4];
         zero_acc(acc);
-        mm_tile<C, C>(acc, D, [&](int m, int k) { return ldo(m, k); }, [&](int k, int n) { return ldf(gVn + n * D + k); }, st,
+        mm_tile<C, C>(acc, D, [&](int m, int k) { return ldo(m, k); }, [&](int k, int n) { return ldf(gVn + tc::cm_idx(k, n, C)); }, st,
                       true, true);
 #pragma unroll
         for (int r = 0; r < 4; ++r)
@@ -526,8 +527,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
     {
         float acc[4][D / 16];
         zero_acc(acc);
-        mm_tile<C, D>(acc, D, [&](int m, int k) { return ldf(gdV + m * D + k); },
-                      [&](int k, int n) { return ldf(gS0 + n * D + k); }, st, true, true);
+        mm_tile<C, D>(acc, D, [&](int m, int k) { return ldf(gdV + tc::cm_idx(k, m, C)); },
+                      [&](int k, int n) { return ldf(gS0 + tc::cm_idx(k, n, D)); }, st, true, true);
 #pragma unroll
         for (int r = 0; r < 4; ++r)
 #pragma unroll
@@ -539,7 +540,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
         zero_acc(acc);
         mm_tile<C, C>(acc, D, [&](int m, int k) { return sW[m * D + k]; },
                       [&](int k, int n) { return sbeta[n] * sk[n * D + k] * exp2f(sG[n * D + k]); }, st, true, true);
-        mm_tile<C, C>(acc, D, [&](int m, int k) { return ldf(gdV + m * D + k); },
+        mm_tile<C, C>(acc, D, [&](int m, int k) { return ldf(gdV + tc::cm_idx(k, m, C)); },
                       [&](int k, int n) { return sbeta[n] * ldv(n, k); }, st, true, true);
 #pragma unroll
         for (int r = 0; r < 4; ++r)
@@ -593,7 +594,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
     {
         float acc[4][D / 16];
         zero_acc(acc);
-        mm_tile<C, D>(acc, C, [&](int m, int k) { return sT[k * 65 + m]; }, [&](int k, int n) { return ldf(gdV + k * D + n); },
+        mm_tile<C, D>(acc, C, [&](int m, int k) { return sT[k * 65 + m]; }, [&](int k, int n) { return ldf(gdV + tc::cm_idx(n, k, C)); },
                       st, false, false);
         T* dv = (T*)p.grad_v;
 #pragma unroll
@@ -611,7 +612,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
     {
         float acc[4][D / 16];
         zero_acc(acc);
-        mm_tile<C, D>(acc, D, [&](int m, int k) { return ldo(m, k); }, [&](int k, int n) { return ldf(gS0 + n * D + k); }, st,
+        mm_tile<C, D>(acc, D, [&](int m, int k) { return ldo(m, k); }, [&](int k, int n) { return ldf(gS0 + tc::cm_idx(k, n, D)); }, st,
                       true, true);
 #pragma unroll
         for (int r = 0; r < 4; ++r)
@@ -627,8 +628,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
     {
         float acc[4][D / 16];
         zero_acc(acc);
-        mm_tile<C, D>(acc, D, [&](int m, int k) { return ldf(gVn + m * D + k); },
-                      [&](int k, int n) { return ldf(gdS + n * D + k); }, st, true, true);
+        mm_tile<C, D>(acc, D, [&](int m, int k) { return ldf(gVn + tc::cm_idx(k, m, C)); },
+                      [&](int k, int n) { return ldf(gdS + tc::cm_idx(k, n, D)); }, st, true, true);
 #pragma unroll
         for (int r = 0; r < 4; ++r)
 #pragma unroll
@@ -651,7 +652,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
     // 9. d(gamC)[d] = sum_e dS[d][e] S0[d][e]
     for (int d = warp; d < D; d += NTHREADS / 32) {
         float s = 0.f;
-        for (int e = lane; e < D; e += 32) s = fmaf(ldf(gdS + d * D + e), ldf(gS0 + d * D + e), s);
+        for (int e = lane; e < D; e += 32) s = fmaf(ldf(gdS + tc::cm_idx(e, d, D)), ldf(gS0 + tc::cm_idx(e, d, D)), s);
         s = warp_sum(s);
         if (lane == 0) scol[d] += s * gGam[d];
     }
@@ -813,41 +814,56 @@ static cudaError_t set_smem(K kernel, size_t bytes) {
 }
 
 template <typename T, int D>
-static cudaError_t launch_fwd(const KdaParams& p, cudaStream_t s) {
+static cudaError_t launch_stage(const KdaParams& p, int stage, cudaStream_t s) {
     constexpr int BV = 32;
-    cudaError_t e;
-    if ((e = set_smem(kda_fwd_intra_simt<T, D>, smem_intra<D>())) != cudaSuccess) return e;
-    if ((e = set_smem(kda_fwd_state_simt<T, D, BV>, smem_state<D, BV>())) != cudaSuccess) return e;
-    kda_fwd_intra_simt<T, D><<<p.NT * p.H, NTHREADS, smem_intra<D>(), s>>>(p);
-    prof_mark(s);
-    kda_fwd_state_simt<T, D, BV><<<dim3(D / BV, p.H, p.N), NTHREADS, smem_state<D, BV>(), s>>>(p);
-    prof_mark(s);
+    cudaError_t e = cudaSuccess;
+    switch (stage) {
+        case 0:
+            if ((e = set_smem(kda_fwd_intra_simt<T, D>, smem_intra<D>())) != cudaSuccess) return e;
+            kda_fwd_intra_simt<T, D><<<p.NT * p.H, NTHREADS, smem_intra<D>(), s>>>(p);
+            break;
+        case 1:
+            if ((e = set_smem(kda_fwd_state_simt<T, D, BV>, smem_state<D, BV>())) != cudaSuccess) return e;
+            kda_fwd_state_simt<T, D, BV><<<dim3(D / BV, p.H, p.N), NTHREADS, smem_state<D, BV>(), s>>>(p);
+            break;
+        case 2:
+            if ((e = set_smem(kda_bwd_state_simt<T, D, BV>, smem_state<D, BV>())) != cudaSuccess) return e;
+            kda_bwd_state_simt<T, D, BV><<<dim3(D / BV, p.H, p.N), NTHREADS, smem_state<D, BV>(), s>>>(p);
+            break;
+        case 3:
+            if ((e = set_smem(kda_bwd_chunk_simt<T, D>, smem_bwd_chunk<D>())) != cudaSuccess) return e;
+            kda_bwd_chunk_simt<T, D><<<p.NT * p.H, NTHREADS, smem_bwd_chunk<D>(), s>>>(p);
+            break;
+        default:
+            kda_param_reduce<<<p.H, 128, 0, s>>>(p);
+    }
     return cudaGetLastError();
 }
 
-template <typename T, int D>
-static cudaError_t launch_bwd(const KdaParams& p, cudaStream_t s) {
-    constexpr int BV = 32;
-    cudaError_t e;
-    if ((e = set_smem(kda_bwd_state_simt<T, D, BV>, smem_state<D, BV>())) != cudaSuccess) return e;
-    if ((e = set_smem(kda_bwd_chunk_simt<T, D>, smem_bwd_chunk<D>())) != cudaSuccess) return e;
-    kda_bwd_state_simt<T, D, BV><<<dim3(D / BV, p.H, p.N), NTHREADS, smem_state<D, BV>(), s>>>(p);
-    prof_mark(s);
-    kda_bwd_chunk_simt<T, D><<<p.NT * p.H, NTHREADS, smem_bwd_chunk<D>(), s>>>(p);
-    prof_mark(s);
-    if (p.flags & KDA_FLAG_GATE) kda_param_reduce<<<p.H, 128, 0, s>>>(p);
-    prof_mark(s);
-    return cudaGetLastError();
+// stage: 0 fwd_intra, 1 fwd_state, 2 bwd_state, 3 bwd_chunk, 4 param_reduce
+cudaError_t simt_stage(const KdaParams& p, int stage, cudaStream_t s) {
+    if (p.dtype == KDA_DTYPE_F32)
+        return p.dk == 64 ? launch_stage<float, 64>(p, stage, s) : launch_stage<float, 128>(p, stage, s);
+    return p.dk == 64 ? launch_stage<__nv_bfloat16, 64>(p, stage, s) : launch_stage<__nv_bfloat16, 128>(p, stage, s);
 }
 
 cudaError_t simt_fwd(const KdaParams& p, cudaStream_t s) {
-    if (p.dtype == KDA_DTYPE_F32) return p.dk == 64 ? launch_fwd<float, 64>(p, s) : launch_fwd<float, 128>(p, s);
-    return p.dk == 64 ? launch_fwd<__nv_bfloat16, 64>(p, s) : launch_fwd<__nv_bfloat16, 128>(p, s);
+    cudaError_t e;
+    for (int st = 0; st < 2; ++st) {
+        if ((e = simt_stage(p, st, s)) != cudaSuccess) return e;
+        prof_mark(s);
+    }
+    return cudaSuccess;
 }
 
 cudaError_t simt_bwd(const KdaParams& p, cudaStream_t s) {
-    if (p.dtype == KDA_DTYPE_F32) return p.dk == 64 ? launch_bwd<float, 64>(p, s) : launch_bwd<float, 128>(p, s);
-    return p.dk == 64 ? launch_bwd<__nv_bfloat16, 64>(p, s) : launch_bwd<__nv_bfloat16, 128>(p, s);
+    cudaError_t e;
+    for (int st = 2; st < 5; ++st) {
+        if (st == 4 && !(p.flags & KDA_FLAG_GATE)) break;
+        if ((e = simt_stage(p, st, s)) != cudaSuccess) return e;
+        prof_mark(s);
+    }
+    return cudaSuccess;
 }
 
 }  // namespace kda

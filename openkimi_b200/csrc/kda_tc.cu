@@ -488,6 +488,7 @@ __global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
 }
 
 cudaError_t simt_stage(const KdaParams& p, int stage, cudaStream_t s);
+cudaError_t launch_fwd_intra_tc(const KdaParams& p, cudaStream_t s);
 void prof_mark(cudaStream_t s);
 
 enum { ST_FWD_INTRA = 0, ST_FWD_STATE = 1, ST_BWD_STATE = 2, ST_BWD_CHUNK = 3, ST_PARAM_REDUCE = 4 };
@@ -498,7 +499,7 @@ static bool stage_simt(const KdaParams& p, int stage) { return (p.flags >> (5 + 
 
 cudaError_t tc_fwd(const KdaParams& p, cudaStream_t s) {
     cudaError_t e;
-    if ((e = simt_stage(p, ST_FWD_INTRA, s)) != cudaSuccess) return e;
+    if ((e = stage_simt(p, ST_FWD_INTRA) ? simt_stage(p, ST_FWD_INTRA, s) : launch_fwd_intra_tc(p, s)) != cudaSuccess) return e;
     prof_mark(s);
     if (stage_simt(p, ST_FWD_STATE)) {
         if ((e = simt_stage(p, ST_FWD_STATE, s)) != cudaSuccess) return e;

@@ -1,0 +1,401 @@
+// fwd_intra on tensor cores (BF16 operands, d = 128): one CTA per (chunk, head).
+//
+//   0  load q, k, v, beta row-wise with 16-byte accesses: L2 norm, sigmoid, beta*v operand;
+//      load the gate channel-wise: activation and the within-chunk cumulative sum G (log2)
+//   1  decay-scaled operands: Qt, Kh records; beta*k*2^G; and for every 16-row block I >= 1
+//      the factorised operands  k_j 2^(r_I - G_j) (j < 16 I)  and  x_i 2^(G_i - r_I) (i in I),
+//      r_I = G at the first row of block I, so that every exponent is <= 0
+//   2  off-diagonal blocks of Aqk and L as tcgen05 MMAs (M = 64 keys, N = 32 = q and k rows of
+//      block I, K = 128), while the CUDA cores evaluate the four diagonal 16x16 blocks with
+//      exact pairwise decays
+//   3  T = (I + diag(beta) L)^-1: forward substitution inside the diagonal blocks, block
+//      forward substitution for the rest (FP32)
+//   4  Aqk and T records; 5  W^T = (beta k 2^G)^T T^T and U^T = (beta v)^T T^T as tcgen05 MMAs
+//      (M = 128 channels); 6  W, U, gamC records.
+#include "kda_common.cuh"
+#include "kda_tc.cuh"
+
+namespace kda {
+
+using namespace tc;
+
+namespace fi {
+constexpr int D = 128, NTHR = 256;
+constexpr uint32_t SQ = 0;                   // q^  bf16 [64][128] row-major
+constexpr uint32_t SK = SQ + 16384;          // k^  bf16 [64][128]
+constexpr uint32_t SG = SK + 16384;          // G   f32  [64][128]
+constexpr uint32_t KSC = SG + 32768;         // 3 x cm(j, d; 128) bf16; block 0 later holds T (bf16)
+constexpr uint32_t XSC = KSC + 3 * 16384;    // 3 x cm(n, d; 128) bf16, 32 rows each
+constexpr uint32_t KB = XSC + 3 * 8192;      // beta k 2^G  cm(j, d; 128)
+constexpr uint32_t BV = KB + 16384;          // beta v      cm(j, e; 128)
+constexpr uint32_t SA = BV + 16384;          // f32 [64][65]
+constexpr uint32_t SL = SA + 16640;
+constexpr uint32_t ST = SL + 16640;
+constexpr uint32_t SP = ST + 16640;          // f32 [3][16][17]
+constexpr uint32_t SBETA = SP + 3328;        // f32 [64]
+constexpr uint32_t STOT = SBETA + 256;       // f32 [128]
+constexpr uint32_t TOTAL = STOT + 512;
+constexpr uint32_t T_D = 0, T_W = 96, T_U = 160, TMEM_COLS = 256;
+}  // namespace fi
+
+__global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams p) {
+    using namespace fi;
+    extern __shared__ __align__(128) unsigned char dyn[];
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_s;
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dyn + SQ);
+    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(dyn + SK);
+    float* sG = reinterpret_cast<float*>(dyn + SG);
+    __nv_bfloat16* sKB = reinterpret_cast<__nv_bfloat16*>(dyn + KB);
+    __nv_bfloat16* sBV = reinterpret_cast<__nv_bfloat16*>(dyn + BV);
+    float* sA = reinterpret_cast<float*>(dyn + SA);
+    float* sL = reinterpret_cast<float*>(dyn + SL);
+    float* sT = reinterpret_cast<float*>(dyn + ST);
+    float* sP = reinterpret_cast<float*>(dyn + SP);
+    float* sbeta = reinterpret_cast<float*>(dyn + SBETA);
+    float* stot = reinterpret_cast<float*>(dyn + STOT);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int c = blockIdx.x / p.H, h = blockIdx.x % p.H;
+    const ChunkInfo ci = chunk_info(p, c);
+    const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
+    char* ws = (char*)p.workspace;
+    const size_t rec = (size_t)c * p.H + h;
+    __nv_bfloat16* gW = (__nv_bfloat16*)(ws + L.W) + rec * C * D;
+    __nv_bfloat16* gU = (__nv_bfloat16*)(ws + L.U) + rec * C * D;
+    __nv_bfloat16* gA = (__nv_bfloat16*)(ws + L.Aqk) + rec * C * C;
+    __nv_bfloat16* gQt = (__nv_bfloat16*)(ws + L.Qt) + rec * C * D;
+    __nv_bfloat16* gKh = (__nv_bfloat16*)(ws + L.Kh) + rec * C * D;
+    __nv_bfloat16* gT = (__nv_bfloat16*)(ws + L.Tm) + rec * C * C;
+    float* gGam = (float*)(ws + L.gamC) + rec * D;
+    const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+    const __nv_bfloat16* k = (const __nv_bfloat16*)p.k;
+    const __nv_bfloat16* v = (const __nv_bfloat16*)p.v;
+    const __nv_bfloat16* g = (const __nv_bfloat16*)p.g;
+    const __nv_bfloat16* beta = (const __nv_bfloat16*)p.beta;
+    const bool l2 = p.flags & KDA_FLAG_QK_L2NORM, gate = p.flags & KDA_FLAG_GATE, sig = p.flags & KDA_FLAG_BETA_SIGMOID;
+
+    if (warp == 0) {
+        tmem_alloc(&tmem_s, TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+
+    // ---- 0a: gate, channel-wise: thread (half, d) owns rows 32*half .. 32*half+31 of channel d
+    {
+        const int half = tid >> 7, d = tid & 127;
+        const float negA = gate ? -expf(p.A_log[h]) : 0.f;
+        const float bias = (gate && p.dt_bias) ? p.dt_bias[h * D + d] : 0.f;
+        float x[32];
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const int i = 32 * half + r;
+            x[r] = i < ci.len ? __bfloat162float(g[((size_t)(ci.tok0 + i) * p.H + h) * D + d]) : 0.f;
+        }
+        float run = 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const int i = 32 * half + r;
+            float gl = 0.f;
+            if (i < ci.len) gl = gate ? negA * softplus_f(x[r] + bias) : x[r];
+            run += gl * LOG2E;
+            sG[i * D + d] = run;
+        }
+        if (half == 0) stot[d] = run;
+    }
+    // ---- 0b: q, k, v, beta row-wise: half warp hw owns rows hw + 16 m, lane c8 the channels 8 c8 ..
+    {
+        const int hw = tid >> 4, c8 = (tid & 15) * 8;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int i = hw + 16 * m;
+            const bool valid = i < ci.len;
+            const size_t row = (size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h;
+            float qf[8], kf[8], vf[8];
+            uint4 z = make_uint4(0, 0, 0, 0);
+            bf16x8_to_f32(valid ? *reinterpret_cast<const uint4*>(q + row * D + c8) : z, qf);
+            bf16x8_to_f32(valid ? *reinterpret_cast<const uint4*>(k + row * D + c8) : z, kf);
+            bf16x8_to_f32(valid ? *reinterpret_cast<const uint4*>(v + row * D + c8) : z, vf);
+            float b = 0.f;
+            if ((tid & 15) == 0 && valid) {
+                b = __bfloat162float(beta[row]);
+                if (sig) b = sigmoid_f(b);
+            }
+            b = __shfl_sync(0xffffffffu, b, lane & 16);
+            if (l2) {
+                float ssq = 0.f, ssk = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    ssq += qf[j] * qf[j];
+                    ssk += kf[j] * kf[j];
+                }
+                ssq = half_warp_sum(ssq);
+                ssk = half_warp_sum(ssk);
+                const float rq = 1.f / fmaxf(sqrtf(ssq), 1e-6f), rk = 1.f / fmaxf(sqrtf(ssk), 1e-6f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    qf[j] *= rq;
+                    kf[j] *= rk;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vf[j] *= b;
+            *reinterpret_cast<uint4*>(sQ + i * D + c8) = f32_to_bf16x8(qf);
+            *reinterpret_cast<uint4*>(sK + i * D + c8) = f32_to_bf16x8(kf);
+            *reinterpret_cast<uint4*>(sBV + cm_idx(i, c8, D)) = f32_to_bf16x8(vf);
+            if ((tid & 15) == 0) sbeta[i] = b;
+        }
+    }
+    for (int idx = tid; idx < C * 65; idx += NTHR) {
+        sA[idx] = 0.f;
+        sL[idx] = 0.f;
+        sT[idx] = 0.f;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem0 = tmem_s;
+    if (tid >= 128) {  // second half of the cumulative sum picks up the first half's total
+        const int d = tid & 127;
+        const float t = stot[d];
+#pragma unroll 8
+        for (int i = 32; i < C; ++i) sG[i * D + d] += t;
+    }
+    __syncthreads();
+
+    // ---- 1: decay-scaled operands
+    {
+        const int hw = tid >> 4, c8 = (tid & 15) * 8;
+        float gl[8];
+        {
+            const float4 a = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8);
+            const float4 b = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8 + 4);
+            gl[0] = a.x; gl[1] = a.y; gl[2] = a.z; gl[3] = a.w; gl[4] = b.x; gl[5] = b.y; gl[6] = b.z; gl[7] = b.w;
+        }
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int i = hw + 16 * m;  // block index of this row == m
+            float G8[8], qf[8], kf[8], o8[8];
+            {
+                const float4 a = *reinterpret_cast<const float4*>(sG + i * D + c8);
+                const float4 b = *reinterpret_cast<const float4*>(sG + i * D + c8 + 4);
+                G8[0] = a.x; G8[1] = a.y; G8[2] = a.z; G8[3] = a.w; G8[4] = b.x; G8[5] = b.y; G8[6] = b.z; G8[7] = b.w;
+            }
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sQ + i * D + c8), qf);
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sK + i * D + c8), kf);
+            const float bi = sbeta[i];
+            float eg[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) eg[j] = exp2f(G8[j]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o8[j] = p.scale * qf[j] * eg[j];
+            *reinterpret_cast<uint4*>(gQt + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o8[j] = bi * kf[j] * eg[j];
+            *reinterpret_cast<uint4*>(sKB + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o8[j] = kf[j] * exp2f(gl[j] - G8[j]);
+            *reinterpret_cast<uint4*>(gKh + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
+            if (m >= 1) {  // rows of block m as the N operand of block m's products
+                const float* r = sG + (16 * m) * D + c8;
+                __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(dyn + XSC + (m - 1) * 8192);
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = exp2f(G8[j] - r[j]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o8[j] = qf[j] * f[j];
+                *reinterpret_cast<uint4*>(xs + cm_idx(i - 16 * m, c8, D)) = f32_to_bf16x8(o8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o8[j] = kf[j] * f[j];
+                *reinterpret_cast<uint4*>(xs + cm_idx(16 + i - 16 * m, c8, D)) = f32_to_bf16x8(o8);
+            }
+#pragma unroll
+            for (int I = 1; I <= 3; ++I) {  // keys scaled for the later blocks
+                __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(dyn + KSC + (I - 1) * 16384);
+                if (m < I) {
+                    const float* r = sG + (16 * I) * D + c8;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o8[j] = kf[j] * exp2f(r[j] - G8[j]);
+                    *reinterpret_cast<uint4*>(ks + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
+                } else {
+                    *reinterpret_cast<uint4*>(ks + cm_idx(i, c8, D)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- 2: off-diagonal blocks on the tensor cores, diagonal blocks exactly on the CUDA cores
+    if (tid == 0) {
+        tc_fence_after();
+        const uint32_t sb = smem_u32(dyn);
+        constexpr uint32_t id = make_idesc(64, 32, false, false);
+#pragma unroll
+        for (int I = 1; I <= 3; ++I)
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                mma_ss(tmem0 + T_D + 32 * (I - 1), make_desc(sb + KSC + (I - 1) * 16384 + s * 256, 128, 2048),
+                       make_desc(sb + XSC + (I - 1) * 8192 + s * 256, 128, 2048), id, s > 0);
+        mma_commit(&bar);
+    }
+    for (int i = warp; i < C; i += NTHR / 32) {
+        float qi[4], ki[4], gi[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            qi[t] = __bfloat162float(sQ[i * D + lane + 32 * t]);
+            ki[t] = __bfloat162float(sK[i * D + lane + 32 * t]);
+            gi[t] = sG[i * D + lane + 32 * t];
+        }
+        for (int j = i & ~15; j <= i; ++j) {
+            float a = 0.f, l = 0.f;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float kd = __bfloat162float(sK[j * D + lane + 32 * t]) * exp2f(gi[t] - sG[j * D + lane + 32 * t]);
+                a = fmaf(qi[t], kd, a);
+                l = fmaf(ki[t], kd, l);
+            }
+            a = warp_sum(a);
+            l = warp_sum(l);
+            if (lane == 0) {
+                sA[i * 65 + j] = a * p.scale;
+                if (j < i) sL[i * 65 + j] = l;
+            }
+        }
+    }
+    bool ok = mbar_wait(&bar, 0, p.status, 8);
+    tc_fence_after();
+    if (ok) {
+        const int qd = warp & 3, cbase = warp < 4 ? 0 : 48;
+        const int j = 16 * qd + (lane & 15);
+#pragma unroll
+        for (int cc = 0; cc < 48; cc += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem0 + ((uint32_t)(32 * qd) << 16) + T_D + cbase + cc, r);
+            tmem_wait_ld();
+            if (lane < 16) {
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    const int col = cbase + cc + u, I = (col >> 5) + 1, nn = col & 31;
+                    if (j < 16 * I) {
+                        const float val = __uint_as_float(r[u]);
+                        if (nn < 16) sA[(16 * I + nn) * 65 + j] = val * p.scale;
+                        else sL[(16 * I + nn - 16) * 65 + j] = val;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- 3: T = (I + diag(beta) L)^-1
+    if (warp < 4) {  // diagonal blocks, one warp each
+        const int b0 = 16 * warp, cc = lane & 15, hf = lane >> 4;
+        for (int r = 0; r < 16; ++r) {
+            float s = 0.f;
+            for (int j = hf; j < r; j += 2) s = fmaf(sL[(b0 + r) * 65 + b0 + j], sT[(b0 + j) * 65 + b0 + cc], s);
+            s += __shfl_xor_sync(0xffffffffu, s, 16);
+            if (hf == 0 && cc <= r) sT[(b0 + r) * 65 + b0 + cc] = (cc == r ? 1.f : 0.f) - sbeta[b0 + r] * s;
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    {
+        const int r = tid >> 4, cc = tid & 15;
+        for (int lvl = 1; lvl <= 3; ++lvl) {
+            for (int J = 0; J + lvl <= 3; ++J) {  // P = sum_K (beta L)_IK T_KJ
+                const int I = J + lvl;
+                float s = 0.f;
+                for (int K = J; K < I; ++K)
+#pragma unroll
+                    for (int m = 0; m < 16; ++m)
+                        s = fmaf(sL[(16 * I + r) * 65 + 16 * K + m], sT[(16 * K + m) * 65 + 16 * J + cc], s);
+                sP[(J * 16 + r) * 17 + cc] = sbeta[16 * I + r] * s;
+            }
+            __syncthreads();
+            for (int J = 0; J + lvl <= 3; ++J) {  // T_IJ = -T_II P
+                const int I = J + lvl;
+                float s = 0.f;
+#pragma unroll
+                for (int m = 0; m < 16; ++m) s = fmaf(sT[(16 * I + r) * 65 + 16 * I + m], sP[(J * 16 + m) * 17 + cc], s);
+                sT[(16 * I + r) * 65 + 16 * J + cc] = -s;
+            }
+            __syncthreads();
+        }
+    }
+
+    // ---- 4: Aqk and T records; T as the B operand of the WY products
+    {
+        __nv_bfloat16* sTB = reinterpret_cast<__nv_bfloat16*>(dyn + KSC);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int qq = tid + NTHR * u, i = qq >> 3, j8 = (qq & 7) * 8;
+            float a8[8], t8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                a8[j] = sA[i * 65 + j8 + j];
+                t8[j] = sT[i * 65 + j8 + j];
+            }
+            const uint4 tb = f32_to_bf16x8(t8);
+            *reinterpret_cast<uint4*>(gA + cm_idx(i, j8, C)) = f32_to_bf16x8(a8);
+            *reinterpret_cast<uint4*>(gT + cm_idx(i, j8, C)) = tb;
+            *reinterpret_cast<uint4*>(sTB + cm_idx(i, j8, C)) = tb;
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- 5: W^T and U^T
+    if (tid == 0) {
+        tc_fence_after();
+        const uint32_t sb = smem_u32(dyn);
+        constexpr uint32_t id = make_idesc(128, 64, true, false);
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+            mma_ss(tmem0 + T_W, make_desc(sb + KB + s * 4096, 2048, 128), make_desc(sb + KSC + s * 256, 128, 1024), id, s > 0);
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+            mma_ss(tmem0 + T_U, make_desc(sb + BV + s * 4096, 2048, 128), make_desc(sb + KSC + s * 256, 128, 1024), id, s > 0);
+        mma_commit(&bar);
+    }
+    if (tid < D) gGam[tid] = exp2f(sG[(C - 1) * D + tid]);
+    ok = mbar_wait(&bar, 1, p.status, 8) && ok;
+    tc_fence_after();
+
+    // ---- 6: W and U records
+    if (ok) {
+        const int qd = warp & 3, dd = 32 * qd + lane;
+        __nv_bfloat16* dst = warp < 4 ? gW : gU;
+        const uint32_t src = tmem0 + ((uint32_t)(32 * qd) << 16) + (warp < 4 ? T_W : T_U);
+#pragma unroll
+        for (int i0 = 0; i0 < C; i0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(src + i0, r);
+            tmem_wait_ld();
+            *reinterpret_cast<uint4*>(dst + cm_idx(dd, i0, C)) =
+                make_uint4(pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1])), pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                           pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5])), pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7])));
+            *reinterpret_cast<uint4*>(dst + cm_idx(dd, i0 + 8, C)) =
+                make_uint4(pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9])), pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11])),
+                           pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13])), pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15])));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
+}
+
+cudaError_t launch_fwd_intra_tc(const KdaParams& p, cudaStream_t s) {
+    cudaError_t e = cudaFuncSetAttribute(kda_fwd_intra_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fi::TOTAL);
+    if (e != cudaSuccess) return e;
+    kda_fwd_intra_tc<<<p.NT * p.H, fi::NTHR, fi::TOTAL, s>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace kda

@@ -53,10 +53,13 @@ def run_device(inp, *, fused=True, h0=None, dht=None, cu=None, state_v_first=Fal
 
 
 def run_oracle(inp, *, fused=True, h0=None, dht=None, cu=None, dtype=torch.float32):
+    # with BF16 activations the reference rounds the normalised q and k back to BF16 before
+    # the recurrence (k3mini/model.py:218-219: ``.to(x.dtype)``); FP32 inputs stay FP32
+    round_to = torch.bfloat16 if (fused and inp["q"].dtype == torch.bfloat16) else None
     return O.kda_oracle_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["do"],
                                 a_log=inp["a_log"] if fused else None, dt_bias=inp["dt_bias"] if fused else None,
                                 scale=inp.get("scale"), initial_state=h0, dht=dht, cu_seqlens=cu, use_qk_l2norm=fused,
-                                use_gate=fused, use_beta_sigmoid=fused, dtype=dtype)
+                                use_gate=fused, use_beta_sigmoid=fused, dtype=dtype, round_qk_to=round_to)
 
 
 def max_abs(a, r):

@@ -62,6 +62,12 @@ def stage_model(name, d, C=64, es=2):
         "fwd_state": (6 * C * d * d + 2 * C * C * d, (4 * t + a + 4 * d) + (2 * t + s)),
         "bwd_state": (6 * C * d * d + 2 * C * C * d, (4 * t + a + 4 * d) + (t + s)),
         "bwd_chunk": (6 * C * d * d + 16 * C * C * d + 4 * C ** 3, (5 * t + C * es) + 2 * t + 2 * s + a + (4 * t + C * es)),
+        # bwd_wy: dAqk, dW, dQt, dKh (K=d), dVb, dKb, Z (K=64), dM; reads dO, v, V', dV', S0, dS, T, W; writes dv, dAqk,
+        # dM and three FP32 [64, d] products
+        "bwd_wy": (8 * C * d * d + 8 * C * C * d, (2 * t) + 3 * t + 2 * s + a + (t + 2 * a + 3 * C * d * 4)),
+        # bwd_intra: 3 pairwise products over the lower triangle (dense-tile count 6 C^2 d); reads q, k, g, beta, dAqk,
+        # dM and the three FP32 products; writes dq, dk, dg, dbeta
+        "bwd_intra": (6 * C * C * d, (3 * t + C * es) + 2 * a + 3 * C * d * 4 + (3 * t + C * es)),
         "param_reduce": (0, 4 * d + 4),
     }
     return m[name]
@@ -260,12 +266,14 @@ def main():
     ms = e0.elapsed_time(e1)
     # per-kernel durations from the events recorded inside the timed region
     names = {0: ["fwd_intra", "fwd_state"], 1: ["bwd_state", "bwd_chunk", "param_reduce"]}
+    names_split = ["bwd_state", "bwd_wy", "bwd_intra", "param_reduce"]
     stage_ms, launches = {}, 0
     buf, kind = (C.c_float * 8)(), C.c_int()
     for call in range(n_calls):
         n = lib.kda_profile_read(call, C.byref(kind), buf, 8)
         for i in range(max(n, 0)):
-            nm = names[kind.value][i] if i < len(names[kind.value]) else f"stage{i}"
+            lst = names_split if (kind.value == 1 and n == 4) else names[kind.value]
+            nm = lst[i] if i < len(lst) else f"stage{i}"
             stage_ms.setdefault(nm, []).append(buf[i])
             launches += 1
     lib.kda_profile_begin(0)

@@ -38,7 +38,7 @@ enum {
     KDA_FLAG_FORCE_SIMT = 16,   /* FP32 CUDA-core arithmetic in every stage (validation mode) */
     /* per-stage variants of the same switch (debugging / A-B measurements) */
     KDA_FLAG_SIMT_FWD_INTRA = 32, KDA_FLAG_SIMT_FWD_STATE = 64,
-    KDA_FLAG_SIMT_BWD_STATE = 128, KDA_FLAG_SIMT_BWD_CHUNK = 256
+    KDA_FLAG_SIMT_BWD_STATE = 128, KDA_FLAG_SIMT_BWD_CHUNK = 256, KDA_FLAG_SIMT_BWD_WY = 512
 };
 
 enum {

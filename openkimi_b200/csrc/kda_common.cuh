@@ -75,7 +75,8 @@ __device__ __forceinline__ void seq_chunks(const KdaParams& p, int n, int& c0, i
 // ---------------------------------------------------------------------------------------
 struct WsLayout {
     size_t W, U, Aqk, Qt, Kh, Tm, S0, gamC, total;      // forward workspace
-    size_t dS, dVn, dA_part, dbias_part, bwd_total;     // backward scratch
+    size_t dS, dVn, dA_part, dbias_part;                // backward scratch
+    size_t dAqk, dM, dQt, dKh, dKb, dbp, gC, bwd_total; // hand-over from bwd_wy to bwd_intra
 };
 
 __host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -99,6 +100,17 @@ __host__ __device__ inline WsLayout ws_layout(int NT, int H, int dk, int dv, int
     w.dVn = off;        off = align256(off + n * C * dv * es);
     w.dA_part = off;    off = align256(off + n * 4);
     w.dbias_part = off; off = align256(off + n * dk * 4);
+    // Two-kernel backward of the BF16 path: bwd_wy leaves dAqk and dM (float [64][64], lower
+    // triangle; FP32 because the gate gradient is a difference of large terms built from them),
+    // the raw products dQt, dKh, d(beta K~) as float [64][dk], the beta gradient collected so
+    // far (float [64]) and dGamma_C * Gamma_C (float [dk]).
+    w.dAqk = off; off = align256(off + n * C * C * 4);
+    w.dM = off;   off = align256(off + n * C * C * 4);
+    w.dQt = off;  off = align256(off + n * C * dk * 4);
+    w.dKh = off;  off = align256(off + n * C * dk * 4);
+    w.dKb = off;  off = align256(off + n * C * dk * 4);
+    w.dbp = off;  off = align256(off + n * C * 4);
+    w.gC = off;   off = align256(off + n * dk * 4);
     w.bwd_total = off;
     return w;
 }

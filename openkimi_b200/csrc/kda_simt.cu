@@ -460,7 +460,9 @@ __global__ void __launch_bounds__(NTHREADS) kda_bwd_state_simt(const KdaParams p
 // bwd_chunk: all chunk-local adjoints, the exact pairwise intra step, the reverse cumulative
 // sum of the gate gradient and the chain rule through gate / L2 norm / sigmoid.
 // ---------------------------------------------------------------------------------------
-template <typename T, int D>
+// SPLIT = true stops after the chunk-level adjoints and leaves them in the scratch buffer for
+// the separate intra kernel of the BF16 path (used to validate the two halves independently).
+template <typename T, int D, bool SPLIT = false>
 __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParams p) {
     extern __shared__ float smem[];
     float* sq = smem;
@@ -484,7 +486,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
     const ChunkInfo ci = chunk_info(p, c);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     const char* ws = (const char*)p.workspace;
-    const char* sc = (const char*)p.bwd_scratch;
+    char* sc = (char*)p.bwd_scratch;
     const size_t rec = (size_t)c * p.H + h;
     const T* gVn = (const T*)(ws + L.U) + rec * C * D;
     const T* gT = (const T*)(ws + L.Tm) + rec * C * C;
@@ -521,6 +523,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
             for (int cc = 0; cc < 4; ++cc) {
                 int i = ty + 16 * r, j = tx + 16 * cc;
                 sdA[i * 65 + j] = (i >= j) ? acc[r][cc] : 0.f;
+                if constexpr (SPLIT)
+                    ((float*)(sc + L.dAqk))[rec * C * C + i * C + j] = sdA[i * 65 + j];
             }
     }
     // 2. dW = -dV' S0^T
@@ -569,6 +573,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
             for (int cc = 0; cc < 4; ++cc) {
                 int i = ty + 16 * r, j = tx + 16 * cc;
                 sdM[i * 65 + j] = (i > j) ? -acc[r][cc] : 0.f;
+                if constexpr (SPLIT)
+                    ((float*)(sc + L.dM))[rec * C * C + i * C + j] = sdM[i * 65 + j];
             }
     }
     // 5. d(beta K~) = T^T dW
@@ -582,6 +588,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
 #pragma unroll
             for (int cc = 0; cc < D / 16; ++cc) {
                 int i = ty + 16 * r, d = tx + 16 * cc;
+                if constexpr (SPLIT) {
+                    ((float*)(sc + L.dKb))[(rec * C + i) * D + d] = acc[r][cc];
+                    continue;
+                }
                 float gam = exp2f(sG[i * D + d]);
                 float kt = sk[i * D + d] * gam;
                 float dkt = sbeta[i] * acc[r][cc];
@@ -619,6 +629,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
 #pragma unroll
             for (int cc = 0; cc < D / 16; ++cc) {
                 int i = ty + 16 * r, d = tx + 16 * cc;
+                if constexpr (SPLIT) {
+                    ((float*)(sc + L.dQt))[(rec * C + i) * D + d] = acc[r][cc];
+                    continue;
+                }
                 float gam = exp2f(sG[i * D + d]);
                 dq_a[r][cc] += scale * acc[r][cc] * gam;
                 dG_a[r][cc] += acc[r][cc] * scale * sq[i * D + d] * gam;
@@ -635,6 +649,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
 #pragma unroll
             for (int cc = 0; cc < D / 16; ++cc) {
                 int i = ty + 16 * r, d = tx + 16 * cc;
+                if constexpr (SPLIT) {
+                    ((float*)(sc + L.dKh))[(rec * C + i) * D + d] = acc[r][cc];
+                    sW[i * D + d] = 0.f;
+                    continue;
+                }
                 float dec = exp2f(sG[(C - 1) * D + d] - sG[i * D + d]);
                 float kh = sk[i * D + d] * dec;
                 dk_a[r][cc] += acc[r][cc] * dec;
@@ -655,6 +674,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
         for (int e = lane; e < D; e += 32) s = fmaf(ldf(gdS + tc::cm_idx(e, d, D)), ldf(gS0 + tc::cm_idx(e, d, D)), s);
         s = warp_sum(s);
         if (lane == 0) scol[d] += s * gGam[d];
+    }
+    if constexpr (SPLIT) {  // hand over: beta gradient so far and dGamma_C * Gamma_C
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            float s = row16_sum(db_r[r]);
+            if (tx == 0) ((float*)(sc + L.dbp))[rec * C + ty + 16 * r] = s;
+        }
+        __syncthreads();
+        for (int d = tid; d < D; d += NTHREADS) ((float*)(sc + L.gC))[rec * D + d] = scol[d];
+        return;
     }
     // 10. intra step with exact pairwise decays
 #pragma unroll
@@ -834,13 +863,17 @@ static cudaError_t launch_stage(const KdaParams& p, int stage, cudaStream_t s) {
             if ((e = set_smem(kda_bwd_chunk_simt<T, D>, smem_bwd_chunk<D>())) != cudaSuccess) return e;
             kda_bwd_chunk_simt<T, D><<<p.NT * p.H, NTHREADS, smem_bwd_chunk<D>(), s>>>(p);
             break;
+        case 5:
+            if ((e = set_smem(kda_bwd_chunk_simt<T, D, true>, smem_bwd_chunk<D>())) != cudaSuccess) return e;
+            kda_bwd_chunk_simt<T, D, true><<<p.NT * p.H, NTHREADS, smem_bwd_chunk<D>(), s>>>(p);
+            break;
         default:
             kda_param_reduce<<<p.H, 128, 0, s>>>(p);
     }
     return cudaGetLastError();
 }
 
-// stage: 0 fwd_intra, 1 fwd_state, 2 bwd_state, 3 bwd_chunk, 4 param_reduce
+// stage: 0 fwd_intra, 1 fwd_state, 2 bwd_state, 3 bwd_chunk, 4 param_reduce, 5 bwd_chunk stopped after the adjoints
 cudaError_t simt_stage(const KdaParams& p, int stage, cudaStream_t s) {
     if (p.dtype == KDA_DTYPE_F32)
         return p.dk == 64 ? launch_stage<float, 64>(p, stage, s) : launch_stage<float, 128>(p, stage, s);

@@ -489,6 +489,8 @@ __global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
 
 cudaError_t simt_stage(const KdaParams& p, int stage, cudaStream_t s);
 cudaError_t launch_fwd_intra_tc(const KdaParams& p, cudaStream_t s);
+cudaError_t launch_bwd_intra(const KdaParams& p, cudaStream_t s);
+cudaError_t launch_bwd_wy_tc(const KdaParams& p, cudaStream_t s);
 void prof_mark(cudaStream_t s);
 
 enum { ST_FWD_INTRA = 0, ST_FWD_STATE = 1, ST_BWD_STATE = 2, ST_BWD_CHUNK = 3, ST_PARAM_REDUCE = 4 };
@@ -524,8 +526,15 @@ cudaError_t tc_bwd(const KdaParams& p, cudaStream_t s) {
         kda_bwd_state_tc<<<dim3(p.H, p.N), 128, smem, s>>>(p);
     }
     prof_mark(s);
-    if ((e = simt_stage(p, ST_BWD_CHUNK, s)) != cudaSuccess) return e;
-    prof_mark(s);
+    if (stage_simt(p, ST_BWD_CHUNK)) {  // fused FP32-math kernel
+        if ((e = simt_stage(p, ST_BWD_CHUNK, s)) != cudaSuccess) return e;
+        prof_mark(s);
+    } else {  // chunk-level adjoints, then the guarded intra kernel
+        if ((e = stage_simt(p, 4) ? simt_stage(p, 5, s) : launch_bwd_wy_tc(p, s)) != cudaSuccess) return e;
+        prof_mark(s);
+        if ((e = launch_bwd_intra(p, s)) != cudaSuccess) return e;
+        prof_mark(s);
+    }
     if (p.flags & KDA_FLAG_GATE) {
         if ((e = simt_stage(p, ST_PARAM_REDUCE, s)) != cudaSuccess) return e;
     }

@@ -1,0 +1,313 @@
+// bwd_wy on tensor cores (BF16 path, d = 128): the chunk-level adjoints of the WY / state
+// products, one CTA per (chunk, head), every [64 x d] result computed TRANSPOSED so that the
+// accumulator rows (TMEM lanes) are the 128 channels:
+//
+//   S1   dAqk = dO V'^T (M = 64)        dWn^T = S0 dV'^T        dQt^T = S0 dO^T
+//        dKh^T = dS V'^T                dVb^T = dV'^T T
+//   S2   dKb^T = -dWn^T T               Z^T   = -dWn^T T + S0 dVb^T
+//   S3   dMn   = Z W^T + dVb V'^T (M = 64);   dM = -strict_lower(dMn)
+//
+// (dWn = dV' S0^T = -dW.  With M = I + diag(beta) L, T = M^-1, W = T (beta K~), U = T (beta V) =
+// V' + W S0, the gradient of M is -(T^T dW)(beta K~)^T T^T - (T^T dV')(beta V)^T T^T
+// = -(dKb W^T + dVb U^T) = -((dKb + dVb S0^T) W^T + dVb V'^T); only its strictly lower part is
+// used, for which masking the intermediate T-gradient is irrelevant.)
+//
+// Outputs: dv, the beta gradient collected so far, dGamma_C * Gamma_C, and the hand-over
+// records of bwd_intra (dAqk, dM, dQt, dKh, dKb, all FP32).
+#include "kda_common.cuh"
+#include "kda_tc.cuh"
+
+namespace kda {
+
+using namespace tc;
+
+namespace bw {
+constexpr int D = 128, NTHR = 128;
+constexpr uint32_t VT = 0;                  // V'^T  cm(e, i; 64)
+constexpr uint32_t DVT = VT + 16384;        // dV'^T cm(e, i; 64);   later Z^T  cm(d, i; 64)
+constexpr uint32_t S0T = DVT + 16384;       // S0^T  cm(e, d; 128)
+constexpr uint32_t DST = S0T + 32768;       // dS^T  cm(e, d; 128)
+constexpr uint32_t TT = DST + 32768;        // T     cm(i, j; 64)
+constexpr uint32_t WT = TT + 8192;          // W^T   cm(d, j; 64)
+constexpr uint32_t TMA_BYTES = WT + 16384;  // everything above arrives by bulk TMA
+constexpr uint32_t DOT = TMA_BYTES;         // dO    cm(i, e; 128);  later dVb^T cm(e, i; 64)
+constexpr uint32_t STG = DOT + 16384;       // f32 [64][128] staging for the beta row sums
+constexpr uint32_t SBETA = STG + 32768;     // f32 [64] beta, f32 [64] row sums
+constexpr uint32_t TOTAL = SBETA + 512;
+constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
+}  // namespace bw
+
+__device__ __forceinline__ void cp_async16_z(void* dst_smem, const void* src, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(valid ? 16 : 0)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) {
+    using namespace bw;
+    extern __shared__ __align__(128) unsigned char dyn[];
+    __shared__ uint64_t full, mmabar;
+    __shared__ uint32_t tmem_s;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int c = blockIdx.x / p.H, h = blockIdx.x % p.H;
+    const ChunkInfo ci = chunk_info(p, c);
+    const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
+    const char* ws = (const char*)p.workspace;
+    char* sc = (char*)p.bwd_scratch;
+    const size_t rec = (size_t)c * p.H + h;
+    float* stg = reinterpret_cast<float*>(dyn + STG);
+    float* sbeta = reinterpret_cast<float*>(dyn + SBETA);
+    float* srow = sbeta + 64;
+    const __nv_bfloat16* dO = (const __nv_bfloat16*)p.grad_o;
+    const __nv_bfloat16* v = (const __nv_bfloat16*)p.v;
+    auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
+
+    if (warp == 0) {
+        tmem_alloc(&tmem_s, TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        mbar_init(&full, 1);
+        mbar_init(&mmabar, 1);
+        mbar_fence_init();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem0 = tmem_s;
+    const uint32_t tmem = tmem0 + ((uint32_t)(warp * 32) << 16);
+
+    if (tid == 0) {
+        mbar_expect_tx(&full, TMA_BYTES);
+        tma_load_1d(dyn + VT, (const __nv_bfloat16*)(ws + L.U) + rec * C * D, 16384, &full);
+        tma_load_1d(dyn + DVT, (const __nv_bfloat16*)(sc + L.dVn) + rec * C * D, 16384, &full);
+        tma_load_1d(dyn + S0T, (const __nv_bfloat16*)(ws + L.S0) + rec * D * D, 32768, &full);
+        tma_load_1d(dyn + DST, (const __nv_bfloat16*)(sc + L.dS) + rec * D * D, 32768, &full);
+        tma_load_1d(dyn + TT, (const __nv_bfloat16*)(ws + L.Tm) + rec * C * C, 8192, &full);
+        tma_load_1d(dyn + WT, (const __nv_bfloat16*)(ws + L.W) + rec * C * D, 16384, &full);
+    }
+    {
+        __nv_bfloat16* sdo = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
+        for (int qq = tid; qq < C * (D / 8); qq += NTHR) {
+            const int i = qq >> 4, e8 = (qq & 15) * 8;
+            const bool valid = i < ci.len;
+            cp_async16_z(sdo + cm_idx(i, e8, D), dO + tok(valid ? i : 0) * D + e8, valid);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (tid < C) {
+            float b = 0.f;
+            if (tid < ci.len) {
+                b = __bfloat162float(((const __nv_bfloat16*)p.beta)[tok(tid)]);
+                if (p.flags & KDA_FLAG_BETA_SIGMOID) b = sigmoid_f(b);
+            }
+            sbeta[tid] = b;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        fence_async_smem();
+    }
+    bool ok = mbar_wait(&full, 0, p.status, 16);
+    tc_fence_before();
+    __syncthreads();
+
+    const uint32_t sb = smem_u32(dyn);
+    // ---- S1
+    if (tid == 0) {
+        tc_fence_after();
+        constexpr uint32_t id_aqk = make_idesc(64, 64, false, true);
+        constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
+        constexpr uint32_t id_mk = make_idesc(128, 64, true, false);
+        constexpr uint32_t id_km = make_idesc(128, 64, false, true);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)  // dAqk = dO (K-major) * V' (MN-major view of V'^T)
+            mma_ss(tmem0 + DAQK, make_desc(sb + DOT + s * 256, 128, 2048), make_desc(sb + VT + s * 2048, 1024, 128), id_aqk, s > 0);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)  // dWn^T = S0 (MN-major view of S0^T) * dV'^T (MN-major)
+            mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DVT + s * 2048, 1024, 128), id_mm, s > 0);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)  // dQt^T = S0 * dO^T (K-major, rows = i)
+            mma_ss(tmem0 + DQT, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 256, 128, 2048), id_mk, s > 0);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)  // dKh^T = dS * V'^T
+            mma_ss(tmem0 + DKH, make_desc(sb + DST + s * 4096, 2048, 128), make_desc(sb + VT + s * 2048, 1024, 128), id_mm, s > 0);
+#pragma unroll
+        for (int s = 0; s < 4; ++s)  // dVb^T = dV'^T (K-major, rows = e) * T (MN-major, rows = j)
+            mma_ss(tmem0 + DVB, make_desc(sb + DVT + s * 256, 128, 1024), make_desc(sb + TT + s * 2048, 1024, 128), id_km, s > 0);
+        mma_commit(&mmabar);
+    }
+    ok = mbar_wait(&mmabar, 0, p.status, 32) && ok;
+    tc_fence_after();
+
+    // ---- conversions after S1
+    {
+        float* gdQt = (float*)(sc + L.dQt) + rec * C * D;
+        float* gdKh = (float*)(sc + L.dKh) + rec * C * D;
+        __nv_bfloat16* dv = (__nv_bfloat16*)p.grad_v;
+        __nv_bfloat16* sdvb = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
+#pragma unroll 1
+        for (int i0 = 0; i0 < C; i0 += 16) {
+            uint32_t r[16], pk[8];
+            tmem_ld16(tmem + DWN + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            tmem_st8(tmem + WBF + i0 / 2, pk);
+            tmem_ld16(tmem + DQT + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) gdQt[(i0 + j) * D + tid] = __uint_as_float(r[j]);
+            tmem_ld16(tmem + DKH + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) gdKh[(i0 + j) * D + tid] = __uint_as_float(r[j]);
+            tmem_ld16(tmem + DVB + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            *reinterpret_cast<uint4*>(sdvb + cm_idx(tid, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(sdvb + cm_idx(tid, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int i = i0 + j;
+                const float x = __uint_as_float(r[j]);
+                float vv = 0.f;
+                if (i < ci.len) {
+                    const size_t off = tok(i) * D + tid;
+                    vv = __bfloat162float(v[off]);
+                    dv[off] = __float2bfloat16_rn(sbeta[i] * x);
+                }
+                stg[i * D + tid] = x * vv;
+            }
+        }
+        // dAqk: rows of the M = 64 accumulator sit in lanes 0..15 of every warp's quadrant
+        {
+            float* gdA = (float*)(sc + L.dAqk) + rec * C * C;
+            const int i = 16 * warp + (lane & 15);
+#pragma unroll 1
+            for (int j0 = 0; j0 < C; j0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(tmem + DAQK + j0, r);
+                tmem_wait_ld();
+                if (lane < 16) {
+                    float f[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) f[j] = (j0 + j <= i) ? __uint_as_float(r[j]) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        *reinterpret_cast<float4*>(gdA + i * C + j0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                }
+            }
+        }
+        tmem_wait_st();
+        fence_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- S2
+    if (tid == 0) {
+        tc_fence_after();
+        constexpr uint32_t id_neg = make_idesc(128, 64, false, true, true);  // -WBF (TMEM) * T (MN-major)
+        constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DKB, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DWN, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)  // Z^T += S0 * dVb^T (MN-major B from cm(e, i; 64))
+            mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 2048, 1024, 128), id_mm, true);
+        mma_commit(&mmabar);
+    }
+    // meanwhile: beta row sums and dGamma_C * Gamma_C on the CUDA cores
+    {
+        const int hw = tid >> 4, c8 = (tid & 15) * 8;
+        for (int m = 0; m < 8; ++m) {
+            const int i = hw + 8 * m;
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s += stg[i * D + c8 + j];
+            s = half_warp_sum(s);
+            if ((tid & 15) == 0) srow[i] = s;
+        }
+        const __nv_bfloat16* s0 = reinterpret_cast<const __nv_bfloat16*>(dyn + S0T);
+        const __nv_bfloat16* ds = reinterpret_cast<const __nv_bfloat16*>(dyn + DST);
+        float acc = 0.f;
+#pragma unroll 8
+        for (int e = 0; e < D; ++e)
+            acc = fmaf(__bfloat162float(ds[cm_idx(e, tid, D)]), __bfloat162float(s0[cm_idx(e, tid, D)]), acc);
+        ((float*)(sc + L.gC))[rec * D + tid] = acc * ((const float*)(ws + L.gamC))[rec * D + tid];
+    }
+    ok = mbar_wait(&mmabar, 1, p.status, 32) && ok;
+    tc_fence_after();
+    __syncthreads();
+    if (tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
+
+    // ---- conversions after S2
+    {
+        float* gdKb = (float*)(sc + L.dKb) + rec * C * D;
+        __nv_bfloat16* sz = reinterpret_cast<__nv_bfloat16*>(dyn + DVT);
+#pragma unroll 1
+        for (int i0 = 0; i0 < C; i0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem + DKB + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) gdKb[(i0 + j) * D + tid] = __uint_as_float(r[j]);
+            tmem_ld16(tmem + DWN + i0, r);
+            tmem_wait_ld();
+            *reinterpret_cast<uint4*>(sz + cm_idx(tid, i0, C)) =
+                make_uint4(pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1])), pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                           pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5])), pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7])));
+            *reinterpret_cast<uint4*>(sz + cm_idx(tid, i0 + 8, C)) =
+                make_uint4(pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9])), pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11])),
+                           pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13])), pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15])));
+        }
+        fence_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- S3
+    if (tid == 0) {
+        tc_fence_after();
+        constexpr uint32_t id = make_idesc(64, 64, true, true);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)  // Z (MN-major view of Z^T) * W^T (MN-major view of the W^T record)
+            mma_ss(tmem0 + DMN, make_desc(sb + DVT + s * 2048, 1024, 128), make_desc(sb + WT + s * 2048, 1024, 128), id, s > 0);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)  // dVb * V'^T
+            mma_ss(tmem0 + DMN, make_desc(sb + DOT + s * 2048, 1024, 128), make_desc(sb + VT + s * 2048, 1024, 128), id, true);
+        mma_commit(&mmabar);
+    }
+    ok = mbar_wait(&mmabar, 0, p.status, 32) && ok;
+    tc_fence_after();
+    {
+        float* gdM = (float*)(sc + L.dM) + rec * C * C;
+        const int i = 16 * warp + (lane & 15);
+#pragma unroll 1
+        for (int j0 = 0; j0 < C; j0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem + DMN + j0, r);
+            tmem_wait_ld();
+            if (lane < 16) {
+                float f[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) f[j] = (j0 + j < i) ? -__uint_as_float(r[j]) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; j += 4)
+                    *reinterpret_cast<float4*>(gdM + i * C + j0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            }
+        }
+    }
+    (void)ok;
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
+}
+
+cudaError_t launch_bwd_wy_tc(const KdaParams& p, cudaStream_t s) {
+    cudaError_t e = cudaFuncSetAttribute(kda_bwd_wy_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bw::TOTAL);
+    if (e != cudaSuccess) return e;
+    kda_bwd_wy_tc<<<p.NT * p.H, bw::NTHR, bw::TOTAL, s>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace kda

@@ -243,7 +243,8 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     if fp32_math or os.environ.get("OPENKIMI_B200_FP32_MATH") == "1":
         flags |= _lib.FLAG_FORCE_SIMT
     # debugging / A-B measurement: bit s of this mask runs stage s (0 fwd_intra, 1 fwd_state,
-    # 2 bwd_state, 3 bwd_chunk) with FP32 CUDA-core arithmetic instead of tensor cores
-    flags |= (int(os.environ.get("OPENKIMI_B200_FP32_STAGES", "0")) & 15) << 5
+    # 2 bwd_state, 3 bwd_chunk as one fused kernel, 4 bwd_wy) with FP32 CUDA-core arithmetic
+    # instead of tensor cores
+    flags |= (int(os.environ.get("OPENKIMI_B200_FP32_STAGES", "0")) & 31) << 5
     return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, initial_state, float(scale), flags,
                                   bool(output_final_state), cu_seqlens, cu_seqlens_cpu, bool(disable_recompute))

@@ -23,19 +23,27 @@ namespace kda {
 using namespace tc;
 
 namespace bi {
-constexpr int D = 128, NTHR = 128, B = 16;
+constexpr int D = 128, NTHR = 256, B = 16;
 constexpr uint32_t SQ = 0;                   // q^ bf16 [64][128]
 constexpr uint32_t SK = SQ + 16384;          // k^ bf16 [64][128]
 constexpr uint32_t SG = SK + 16384;          // G f32 [64][128]
 constexpr uint32_t SDA = SG + 32768;         // dAqk f32 [64][64]
 constexpr uint32_t SDM = SDA + 16384;        // dM   f32 [64][64]
 constexpr uint32_t SC1 = SDM + 16384;        // c1 f32 [64][128]
-constexpr uint32_t STG = SC1 + 32768;        // staging f32 [3][16][128]: dq, dk, dbeta terms
-constexpr uint32_t SBETA = STG + 24576;      // f32 [64] beta, [64] 1/|q|, [64] 1/|k|, [64] dbeta
-constexpr uint32_t SRED = SBETA + 1024;      // f32 [8]
+constexpr uint32_t STG = SC1 + 32768;        // staging f32 [3][16][128]: dq, dk, dbeta terms of one block
+constexpr uint32_t PF = STG + 24576;         // prefetch f32 [3][16][128]: dQt, dKh, dKb rows of one block
+constexpr uint32_t SBETA = PF + 24576;       // f32 [64] beta, [64] 1/|q|, [64] 1/|k|, [64] dbeta
+constexpr uint32_t SRUN = SBETA + 1024;      // f32 [128] last-row term, f32 [128] half totals of the cumulative sum
+constexpr uint32_t SRED = SRUN + 1024;       // f32 [8]
 constexpr uint32_t TOTAL = SRED + 64;
 }  // namespace bi
 
+__device__ __forceinline__ void cpa16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+
+// Threads 0..127 (group A) accumulate the column sums c1, threads 128..255 (group B) the row
+// sums a1, a2 and assemble the gradients; both own channel d = tid % 128.
 __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) {
     using namespace bi;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -46,13 +54,17 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     float* sdM = reinterpret_cast<float*>(dyn + SDM);
     float* sC1 = reinterpret_cast<float*>(dyn + SC1);
     float* stg = reinterpret_cast<float*>(dyn + STG);
+    float* spf = reinterpret_cast<float*>(dyn + PF);
     float* sbeta = reinterpret_cast<float*>(dyn + SBETA);
     float* srq = sbeta + 64;
     float* srk = sbeta + 128;
     float* sdb = sbeta + 192;
+    float* srun = reinterpret_cast<float*>(dyn + SRUN);
+    float* stot = srun + 128;
     float* sred = reinterpret_cast<float*>(dyn + SRED);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid & 127;
+    const bool grpA = tid < 128;
     const int c = blockIdx.x / p.H, h = blockIdx.x % p.H;
     const ChunkInfo ci = chunk_info(p, c);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
@@ -67,15 +79,27 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     const float* gdKb = (const float*)(sc + L.dKb) + rec * C * D;
     const bool l2 = p.flags & KDA_FLAG_QK_L2NORM, gate = p.flags & KDA_FLAG_GATE, sig = p.flags & KDA_FLAG_BETA_SIGMOID;
     const float scale = p.scale;
-    const float negA = gate ? -expf(p.A_log[h]) : 0.f;
+    const float expA = gate ? expf(p.A_log[h]) : 1.f;
+    const float negA = -expA, rcpA = 1.f / expA;
     const float bias = (gate && p.dt_bias) ? p.dt_bias[h * D + d] : 0.f;
     auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
+    // rows 16 I .. 16 I + 15 of dQt, dKh, dKb -> spf (16-byte asynchronous copies)
+    auto prefetch = [&](int I) {
+        for (int qq = tid; qq < 3 * B * (D / 4); qq += NTHR) {
+            const int t = qq / (B * (D / 4)), rem = qq % (B * (D / 4));
+            const float* src = (t == 0 ? gdQt : (t == 1 ? gdKh : gdKb)) + (size_t)(B * I) * D + rem * 4;
+            cpa16(spf + t * B * D + rem * 4, src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    prefetch(3);
 
     // ---- 0a: q, k row-wise (half warp per row): L2 norm, BF16 copies; beta
     {
         const int hw = tid >> 4, c8 = (tid & 15) * 8;
-        for (int m = 0; m < 8; ++m) {
-            const int i = hw + 8 * m;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int i = hw + 16 * m;
             const bool valid = i < ci.len;
             const size_t row = tok(valid ? i : 0);
             float qf[8], kf[8];
@@ -114,19 +138,25 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         }
     }
-    // ---- 0b: gate channel-wise -> cumulative log2 decay G
+    // ---- 0b: gate channel-wise -> cumulative log2 decay G (two halves of 32 rows)
     {
+        const int half = tid >> 7;
+        float x[32];
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const int i = 32 * half + r;
+            x[r] = i < ci.len ? __bfloat162float(g[tok(i) * D + d]) : 0.f;
+        }
         float run = 0.f;
-#pragma unroll 8
-        for (int i = 0; i < C; ++i) {
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const int i = 32 * half + r;
             float gl = 0.f;
-            if (i < ci.len) {
-                const float x = __bfloat162float(g[tok(i) * D + d]);
-                gl = gate ? negA * softplus_f(x + bias) : x;
-            }
+            if (i < ci.len) gl = gate ? negA * softplus_f(x[r] + bias) : x[r];
             run += gl * LOG2E;
             sG[i * D + d] = run;
         }
+        if (half == 0) stot[d] = run;
     }
     // ---- 0c: dAqk, dM (FP32 row-major) and the beta gradient collected by bwd_wy
     {
@@ -137,6 +167,12 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             reinterpret_cast<float4*>(sdM)[qq] = gdM[qq];
         }
         if (tid < C) sdb[tid] = ((const float*)(sc + L.dbp))[rec * C + tid];
+    }
+    __syncthreads();
+    if (!grpA) {
+        const float t = stot[d];
+#pragma unroll 8
+        for (int i = 32; i < C; ++i) sG[i * D + d] += t;
     }
     __syncthreads();
 
@@ -163,10 +199,8 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             if (pass) guard_mask |= 1u << I;
         }
     }
-
-    // decays of one diagonal block: e[i][j] for j < i, i.e. e_idx(i, j) = i (i - 1) / 2 + j
-    // (kept implicit: the two passes below recompute them the same way)
-    auto diag_factors = [&](int I, const float (&Gb)[B], float (&P)[B], float (&N)[B]) {
+    // midpoint factors of one diagonal block: P_r = 2^(G_r - m), N_r = 2^(m - G_r)
+    auto diag_factors = [&](const float (&Gb)[B], float (&P)[B], float (&N)[B]) {
         float gmax = Gb[0], gmin = Gb[0];
 #pragma unroll
         for (int r = 1; r < B; ++r) {
@@ -179,11 +213,10 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             P[r] = exp2f(Gb[r] - m);
             N[r] = exp2f(m - Gb[r]);
         }
-        (void)I;
     };
 
-    // ---- pass C: column sums c1_j, block by block
-    for (int J = 0; J < 4; ++J) {
+    // ---- group A: column sums of block J -> sC1
+    auto col_pass = [&](int J) {
         float c1[B], Gj[B];
 #pragma unroll
         for (int j = 0; j < B; ++j) {
@@ -198,15 +231,19 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 kb[i] = sbeta[B * J + i] * __bfloat162float(sK[(B * J + i) * D + d]);
             }
             if ((guard_mask >> J) & 1) {
-                float P[B], N[B];
-                diag_factors(J, Gj, P, N);
+                float P[B], N[B], u[B];
+                diag_factors(Gj, P, N);
 #pragma unroll
-                for (int i = 1; i < B; ++i)
+                for (int j = 0; j < B; ++j) u[j] = 0.f;
 #pragma unroll
-                    for (int j = 0; j < i; ++j) {
-                        const float t = sdA[(B * J + i) * C + B * J + j] * qs[i] + sdM[(B * J + i) * C + B * J + j] * kb[i];
-                        c1[j] = fmaf(t, P[i] * N[j], c1[j]);
-                    }
+                for (int i = 1; i < B; ++i) {
+                    const float qp = qs[i] * P[i], kp = kb[i] * P[i];
+#pragma unroll
+                    for (int j = 0; j < i; ++j)
+                        u[j] = fmaf(sdA[(B * J + i) * C + B * J + j], qp, fmaf(sdM[(B * J + i) * C + B * J + j], kp, u[j]));
+                }
+#pragma unroll
+                for (int j = 0; j < B; ++j) c1[j] = N[j] * u[j];
             } else {
 #pragma unroll
                 for (int i = 1; i < B; ++i)
@@ -219,173 +256,201 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         }
         for (int I = J + 1; I < 4; ++I) {  // later blocks, reference r = G at their first row
             const float r = sG[(B * I) * D + d];
-            float N[B];
+            float u[B];
 #pragma unroll
-            for (int j = 0; j < B; ++j) N[j] = exp2f(r - Gj[j]);
+            for (int j = 0; j < B; ++j) u[j] = 0.f;
 #pragma unroll
             for (int i = 0; i < B; ++i) {
                 const int ii = B * I + i;
                 const float Pi = exp2f(sG[ii * D + d] - r);
-                const float qs = scale * __bfloat162float(sQ[ii * D + d]) * Pi;
-                const float kb = sbeta[ii] * __bfloat162float(sK[ii * D + d]) * Pi;
+                const float qp = scale * __bfloat162float(sQ[ii * D + d]) * Pi;
+                const float kp = sbeta[ii] * __bfloat162float(sK[ii * D + d]) * Pi;
 #pragma unroll
-                for (int j = 0; j < B; ++j) {
-                    const float t = sdA[ii * C + B * J + j] * qs + sdM[ii * C + B * J + j] * kb;
-                    c1[j] = fmaf(t, N[j], c1[j]);
+                for (int j4 = 0; j4 < B; j4 += 4) {
+                    const float4 a = *reinterpret_cast<const float4*>(sdA + ii * C + B * J + j4);
+                    const float4 m = *reinterpret_cast<const float4*>(sdM + ii * C + B * J + j4);
+                    u[j4 + 0] = fmaf(a.x, qp, fmaf(m.x, kp, u[j4 + 0]));
+                    u[j4 + 1] = fmaf(a.y, qp, fmaf(m.y, kp, u[j4 + 1]));
+                    u[j4 + 2] = fmaf(a.z, qp, fmaf(m.z, kp, u[j4 + 2]));
+                    u[j4 + 3] = fmaf(a.w, qp, fmaf(m.w, kp, u[j4 + 3]));
                 }
             }
+#pragma unroll
+            for (int j = 0; j < B; ++j) c1[j] = fmaf(exp2f(r - Gj[j]), u[j], c1[j]);
         }
 #pragma unroll
         for (int j = 0; j < B; ++j) sC1[(B * J + j) * D + d] = c1[j];
-    }
+    };
 
-    // ---- term of the last row: sum_i dKh_i Kh_i + dGamma_C Gamma_C
     const float gl = sG[(C - 1) * D + d];
-    float run = ((const float*)(sc + L.gC))[rec * D + d];
-    {
-        float s = 0.f;
-#pragma unroll 8
-        for (int i = 0; i < C; ++i)
-            s = fmaf(gdKh[i * D + d], __bfloat162float(sK[i * D + d]) * exp2f(gl - sG[i * D + d]), s);
-        run += s;
-    }
-
-    // ---- pass R: row sums a1_i, a2_i per block (last block first) and the final assembly
-    float dA_acc = 0.f, dbias_acc = 0.f;
+    float run = 0.f, dA_acc = 0.f, dbias_acc = 0.f;
     __nv_bfloat16* dq_out = (__nv_bfloat16*)p.grad_q;
     __nv_bfloat16* dk_out = (__nv_bfloat16*)p.grad_k;
     __nv_bfloat16* dg_out = (__nv_bfloat16*)p.grad_g;
+
     for (int I = 3; I >= 0; --I) {
         float a1[B], a2[B], Gi[B];
+        // ---- X: group A finishes the column sums this block needs, group B sums its rows
+        if (grpA) {
+            if (I == 3) {
+                // term of the last row: dGamma_C Gamma_C + sum_i dKh_i Kh_i
+                float s = ((const float*)(sc + L.gC))[rec * D + d];
+#pragma unroll 8
+                for (int i = 0; i < C; ++i)
+                    s = fmaf(gdKh[i * D + d], __bfloat162float(sK[i * D + d]) * exp2f(gl - sG[i * D + d]), s);
+                srun[d] = s;
+                col_pass(3);
+            }
+        } else {
 #pragma unroll
-        for (int i = 0; i < B; ++i) {
-            a1[i] = 0.f;
-            a2[i] = 0.f;
-            Gi[i] = sG[(B * I + i) * D + d];
-        }
-        {  // earlier blocks
-            float P[B];
-#pragma unroll
-            for (int i = 0; i < B; ++i) P[i] = exp2f(Gi[i] - Gi[0]);
-            for (int J = 0; J < I; ++J) {
+            for (int i = 0; i < B; ++i) {
+                a1[i] = 0.f;
+                a2[i] = 0.f;
+                Gi[i] = sG[(B * I + i) * D + d];
+            }
+            for (int J = 0; J < I; ++J) {  // earlier blocks: k_j 2^(r - G_j), r = G at this block's first row
+                float kd[B], u1[B], u2[B];
 #pragma unroll
                 for (int j = 0; j < B; ++j) {
                     const int jj = B * J + j;
-                    const float kd = __bfloat162float(sK[jj * D + d]) * exp2f(Gi[0] - sG[jj * D + d]);
+                    kd[j] = __bfloat162float(sK[jj * D + d]) * exp2f(Gi[0] - sG[jj * D + d]);
+                }
 #pragma unroll
-                    for (int i = 0; i < B; ++i) {
-                        const float kp = kd * P[i];
-                        a1[i] = fmaf(sdA[(B * I + i) * C + jj], kp, a1[i]);
-                        a2[i] = fmaf(sdM[(B * I + i) * C + jj], kp, a2[i]);
+                for (int i = 0; i < B; ++i) {
+                    u1[i] = 0.f;
+                    u2[i] = 0.f;
+#pragma unroll
+                    for (int j4 = 0; j4 < B; j4 += 4) {
+                        const float4 a = *reinterpret_cast<const float4*>(sdA + (B * I + i) * C + B * J + j4);
+                        const float4 m = *reinterpret_cast<const float4*>(sdM + (B * I + i) * C + B * J + j4);
+                        u1[i] = fmaf(a.x, kd[j4], fmaf(a.y, kd[j4 + 1], fmaf(a.z, kd[j4 + 2], fmaf(a.w, kd[j4 + 3], u1[i]))));
+                        u2[i] = fmaf(m.x, kd[j4], fmaf(m.y, kd[j4 + 1], fmaf(m.z, kd[j4 + 2], fmaf(m.w, kd[j4 + 3], u2[i]))));
                     }
+                }
+#pragma unroll
+                for (int i = 0; i < B; ++i) {
+                    const float Pi = exp2f(Gi[i] - Gi[0]);
+                    a1[i] = fmaf(Pi, u1[i], a1[i]);
+                    a2[i] = fmaf(Pi, u2[i], a2[i]);
+                }
+            }
+            {  // diagonal block: pairs j < i
+                float kj[B];
+#pragma unroll
+                for (int j = 0; j < B; ++j) kj[j] = __bfloat162float(sK[(B * I + j) * D + d]);
+                if ((guard_mask >> I) & 1) {
+                    float P[B], N[B];
+                    diag_factors(Gi, P, N);
+#pragma unroll
+                    for (int j = 0; j < B; ++j) kj[j] *= N[j];
+#pragma unroll
+                    for (int i = 1; i < B; ++i) {
+                        float u1 = 0.f, u2 = 0.f;
+#pragma unroll
+                        for (int j = 0; j < i; ++j) {
+                            u1 = fmaf(sdA[(B * I + i) * C + B * I + j], kj[j], u1);
+                            u2 = fmaf(sdM[(B * I + i) * C + B * I + j], kj[j], u2);
+                        }
+                        a1[i] = fmaf(P[i], u1, a1[i]);
+                        a2[i] = fmaf(P[i], u2, a2[i]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 1; i < B; ++i)
+#pragma unroll
+                        for (int j = 0; j < i; ++j) {
+                            const float kp = kj[j] * exp2f(Gi[i] - Gi[j]);
+                            a1[i] = fmaf(sdA[(B * I + i) * C + B * I + j], kp, a1[i]);
+                            a2[i] = fmaf(sdM[(B * I + i) * C + B * I + j], kp, a2[i]);
+                        }
                 }
             }
         }
-        {  // diagonal block: pairs j < i
-            float kj[B];
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+
+        // ---- Y: group B assembles the 16 tokens of block I (last token first: running suffix
+        //         sum of dG); group A already works on the next block's column sums
+        if (grpA) {
+            if (I > 0) col_pass(I - 1);
+        } else {
+            if (I == 3) run = srun[d];
 #pragma unroll
-            for (int j = 0; j < B; ++j) kj[j] = __bfloat162float(sK[(B * I + j) * D + d]);
-            if ((guard_mask >> I) & 1) {
-                float P[B], N[B];
-                diag_factors(I, Gi, P, N);
-#pragma unroll
-                for (int i = 1; i < B; ++i)
-#pragma unroll
-                    for (int j = 0; j < i; ++j) {
-                        const float kp = kj[j] * (P[i] * N[j]);
-                        a1[i] = fmaf(sdA[(B * I + i) * C + B * I + j], kp, a1[i]);
-                        a2[i] = fmaf(sdM[(B * I + i) * C + B * I + j], kp, a2[i]);
+            for (int i = B - 1; i >= 0; --i) {
+                const int ii = B * I + i;
+                const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
+                const float bi_ = sbeta[ii];
+                const float gam = exp2f(Gi[i]), eta = exp2f(gl - Gi[i]);
+                const float dQt = spf[(0 * B + i) * D + d], dKh = spf[(1 * B + i) * D + d], dKb = spf[(2 * B + i) * D + d];
+                const float c1 = sC1[ii * D + d];
+                const float diag = scale * sdA[ii * C + ii];
+                const float dq_in = scale * a1[i], dk_row = bi_ * a2[i], dKt = bi_ * dKb;
+                stg[(0 * B + i) * D + d] = dq_in + diag * ki + scale * dQt * gam;
+                stg[(1 * B + i) * D + d] = dk_row + c1 + diag * qi + dKt * gam + dKh * eta;
+                stg[(2 * B + i) * D + d] = ki * a2[i] + dKb * (ki * gam);
+                run += qi * dq_in + ki * dk_row - ki * c1 + dQt * (scale * qi * gam) + dKt * (ki * gam) - dKh * (ki * eta);
+                if (ii < ci.len) {
+                    const size_t off = tok(ii) * D + d;
+                    if (gate) {
+                        // per-token log decay g = (G_i - G_{i-1}) ln 2; sigmoid(x + b) = 1 - exp(-softplus) = -expm1(g / e^A)
+                        const float gprev = ii > 0 ? sG[(ii - 1) * D + d] : 0.f;
+                        const float gnat = (Gi[i] - gprev) * 0.6931471805599453f;
+                        dA_acc = fmaf(run, gnat, dA_acc);
+                        const float dx = run * negA * (-expm1f(gnat * rcpA));
+                        dbias_acc += dx;
+                        dg_out[off] = __float2bfloat16_rn(dx);
+                    } else {
+                        dg_out[off] = __float2bfloat16_rn(run);
                     }
-            } else {
-#pragma unroll
-                for (int i = 1; i < B; ++i)
-#pragma unroll
-                    for (int j = 0; j < i; ++j) {
-                        const float kp = kj[j] * exp2f(Gi[i] - Gi[j]);
-                        a1[i] = fmaf(sdA[(B * I + i) * C + B * I + j], kp, a1[i]);
-                        a2[i] = fmaf(sdM[(B * I + i) * C + B * I + j], kp, a2[i]);
-                    }
-            }
-        }
-        // assembly of the 16 tokens of this block, last token first (running suffix sum of dG)
-#pragma unroll
-        for (int i = B - 1; i >= 0; --i) {
-            const int ii = B * I + i;
-            const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
-            const float bi_ = sbeta[ii];
-            const float gam = exp2f(Gi[i]), eta = exp2f(gl - Gi[i]);
-            const float dQt = gdQt[ii * D + d], dKh = gdKh[ii * D + d], dKb = gdKb[ii * D + d];
-            const float c1 = sC1[ii * D + d];
-            const float diag = scale * sdA[ii * C + ii];
-            const float dq_in = scale * a1[i], dk_row = bi_ * a2[i], dKt = bi_ * dKb;
-            const float dqv = dq_in + diag * ki + scale * dQt * gam;
-            const float dkv = dk_row + c1 + diag * qi + dKt * gam + dKh * eta;
-            const float dG = qi * dq_in + ki * dk_row - ki * c1 + dQt * (scale * qi * gam) + dKt * (ki * gam) - dKh * (ki * eta);
-            stg[(0 * B + i) * D + d] = dqv;
-            stg[(1 * B + i) * D + d] = dkv;
-            stg[(2 * B + i) * D + d] = ki * a2[i] + dKb * (ki * gam);
-            run += dG;
-            if (ii < ci.len) {
-                const size_t off = tok(ii) * D + d;
-                if (gate) {
-                    const float z = __bfloat162float(g[off]) + bias;
-                    dA_acc = fmaf(run, negA * softplus_f(z), dA_acc);
-                    const float dx = run * negA * sigmoid_f(z);
-                    dbias_acc += dx;
-                    dg_out[off] = __float2bfloat16_rn(dx);
-                } else {
-                    dg_out[off] = __float2bfloat16_rn(run);
                 }
             }
         }
         __syncthreads();
-        {  // row-wise: L2-norm chain, beta gradient, 16-byte stores
-            const int hw = tid >> 4, c8 = (tid & 15) * 8;
+        // ---- Z: row-wise (one half warp per token): L2-norm chain, beta gradient, 16-byte stores
+        if (I > 0) prefetch(I - 1);
+        {
+            const int i = tid >> 4, c8 = (tid & 15) * 8, ii = B * I + i;
+            float dq8[8], dk8[8], q8[8], k8[8], db = 0.f, dotq = 0.f, dotk = 0.f;
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sQ + ii * D + c8), q8);
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sK + ii * D + c8), k8);
 #pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                const int i = hw + 8 * m, ii = B * I + i;
-                float dq8[8], dk8[8], q8[8], k8[8], db = 0.f, dotq = 0.f, dotk = 0.f;
-                bf16x8_to_f32(*reinterpret_cast<const uint4*>(sQ + ii * D + c8), q8);
-                bf16x8_to_f32(*reinterpret_cast<const uint4*>(sK + ii * D + c8), k8);
+            for (int j = 0; j < 8; ++j) {
+                dq8[j] = stg[(0 * B + i) * D + c8 + j];
+                dk8[j] = stg[(1 * B + i) * D + c8 + j];
+                db += stg[(2 * B + i) * D + c8 + j];
+                dotq = fmaf(q8[j], dq8[j], dotq);
+                dotk = fmaf(k8[j], dk8[j], dotk);
+            }
+            db = half_warp_sum(db);
+            if (l2) {
+                dotq = half_warp_sum(dotq);
+                dotk = half_warp_sum(dotk);
+                const float rq = srq[ii], rk = srk[ii];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    dq8[j] = stg[(0 * B + i) * D + c8 + j];
-                    dk8[j] = stg[(1 * B + i) * D + c8 + j];
-                    db += stg[(2 * B + i) * D + c8 + j];
-                    dotq = fmaf(q8[j], dq8[j], dotq);
-                    dotk = fmaf(k8[j], dk8[j], dotk);
+                    dq8[j] = (dq8[j] - q8[j] * dotq) * rq;
+                    dk8[j] = (dk8[j] - k8[j] * dotk) * rk;
                 }
-                db = half_warp_sum(db);
-                if (l2) {
-                    dotq = half_warp_sum(dotq);
-                    dotk = half_warp_sum(dotk);
-                    const float rq = srq[ii], rk = srk[ii];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        dq8[j] = (dq8[j] - q8[j] * dotq) * rq;
-                        dk8[j] = (dk8[j] - k8[j] * dotk) * rk;
-                    }
-                }
-                if (ii < ci.len) {
-                    const size_t row = tok(ii);
-                    *reinterpret_cast<uint4*>(dq_out + row * D + c8) = f32_to_bf16x8(dq8);
-                    *reinterpret_cast<uint4*>(dk_out + row * D + c8) = f32_to_bf16x8(dk8);
-                    if ((tid & 15) == 0) {
-                        float b = sbeta[ii], v = sdb[ii] + db;
-                        if (sig) v *= b * (1.f - b);
-                        ((__nv_bfloat16*)p.grad_beta)[row] = __float2bfloat16_rn(v);
-                    }
+            }
+            if (ii < ci.len) {
+                const size_t row = tok(ii);
+                *reinterpret_cast<uint4*>(dq_out + row * D + c8) = f32_to_bf16x8(dq8);
+                *reinterpret_cast<uint4*>(dk_out + row * D + c8) = f32_to_bf16x8(dk8);
+                if ((tid & 15) == 0) {
+                    float b = sbeta[ii], v = sdb[ii] + db;
+                    if (sig) v *= b * (1.f - b);
+                    ((__nv_bfloat16*)p.grad_beta)[row] = __float2bfloat16_rn(v);
                 }
             }
         }
         __syncthreads();
     }
     if (gate) {
-        ((float*)(sc + L.dbias_part))[rec * D + d] = dbias_acc;
+        if (!grpA) ((float*)(sc + L.dbias_part))[rec * D + d] = dbias_acc;
         dA_acc = warp_sum(dA_acc);
         if (lane == 0) sred[warp] = dA_acc;
         __syncthreads();
-        if (tid == 0) ((float*)(sc + L.dA_part))[rec] = sred[0] + sred[1] + sred[2] + sred[3];
+        if (tid == 0) ((float*)(sc + L.dA_part))[rec] = sred[4] + sred[5] + sred[6] + sred[7];
     }
 }
 

@@ -30,10 +30,10 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, extra_flags=(), lib_path: str = LIB) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(os.path.dirname(PKG), "include", "kda_b200.h"))
-    objdir = os.path.join(PKG, "build")
+    objdir = os.path.join(PKG, "build" if not extra_flags else "build_" + "_".join(f.strip("-") for f in extra_flags))
     os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()
 
@@ -41,7 +41,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
         path = os.path.join(CSRC, src)
         if force or _stale(obj, [path] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", path, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
+            cmd = [nvcc, *NVCC_FLAGS, *extra_flags, "-c", path, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
             r = subprocess.run(cmd, capture_output=True, text=True)
             if verbose:
                 sys.stderr.write(r.stderr)
@@ -51,11 +51,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    if force or _stale(LIB, objs):
-        r = subprocess.run([nvcc, "-shared", "-o", LIB, *objs, "-lcudart"], capture_output=True, text=True)
+    if force or _stale(lib_path, objs):
+        r = subprocess.run([nvcc, "-shared", "-o", lib_path, *objs, "-lcudart"], capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib_path
 
 
 if __name__ == "__main__":

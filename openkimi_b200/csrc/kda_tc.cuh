@@ -171,6 +171,39 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }  // namespace kda
 
 // ---------------------------------------------------------------------------------------
+// Optional phase timing (compiled in only with -DKDA_PHASE_TIMING; development aid).  Thread 0
+// of every CTA adds the nanoseconds since its previous mark to slot n of a per-file counter
+// array; KDA_PHASE_EXPORT(name) defines the C entry point that reads and clears it.
+// ---------------------------------------------------------------------------------------
+#ifdef KDA_PHASE_TIMING
+static __device__ unsigned long long g_phase_ns[32];
+__device__ __forceinline__ unsigned long long kda_phase_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define KDA_PHASE_BEGIN() unsigned long long _ph_t = kda_phase_now()
+#define KDA_PHASE(n)                                               \
+    do {                                                           \
+        if (threadIdx.x == 0) {                                    \
+            unsigned long long _now = kda_phase_now();             \
+            atomicAdd(&g_phase_ns[n], _now - _ph_t);               \
+            _ph_t = _now;                                          \
+        }                                                          \
+    } while (0)
+#define KDA_PHASE_EXPORT(name)                                                            \
+    extern "C" int name(unsigned long long* out) {                                        \
+        unsigned long long z[32] = {0};                                                   \
+        if (cudaMemcpyFromSymbol(out, g_phase_ns, sizeof(z)) != cudaSuccess) return 1;    \
+        return cudaMemcpyToSymbol(g_phase_ns, z, sizeof(z)) == cudaSuccess ? 0 : 1;       \
+    }
+#else
+#define KDA_PHASE_BEGIN() do {} while (0)
+#define KDA_PHASE(n) do {} while (0)
+#define KDA_PHASE_EXPORT(name)
+#endif
+
+// ---------------------------------------------------------------------------------------
 // small vector helpers
 // ---------------------------------------------------------------------------------------
 namespace kda {

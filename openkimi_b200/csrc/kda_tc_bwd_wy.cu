@@ -32,7 +32,8 @@ constexpr uint32_t WT = TT + 8192;          // W^T   cm(d, j; 64)
 constexpr uint32_t TMA_BYTES = WT + 16384;  // everything above arrives by bulk TMA
 constexpr uint32_t DOT = TMA_BYTES;         // dO    cm(i, e; 128);  later dVb^T cm(e, i; 64)
 constexpr uint32_t STG = DOT + 16384;       // f32 [64][128] staging for the beta row sums
-constexpr uint32_t SBETA = STG + 32768;     // f32 [64] beta, f32 [64] row sums
+constexpr uint32_t SV = STG + 32768;        // v bf16 [64][128] row-major (prefetched with cp.async)
+constexpr uint32_t SBETA = SV + 16384;      // f32 [64] beta, f32 [64] row sums
 constexpr uint32_t TOTAL = SBETA + 512;
 constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bw
@@ -61,6 +62,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     const __nv_bfloat16* v = (const __nv_bfloat16*)p.v;
     auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
 
+    KDA_PHASE_BEGIN();
     if (warp == 0) {
         tmem_alloc(&tmem_s, TMEM_COLS);
         tmem_relinquish();
@@ -87,10 +89,12 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     }
     {
         __nv_bfloat16* sdo = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
+        __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(dyn + SV);
         for (int qq = tid; qq < C * (D / 8); qq += NTHR) {
             const int i = qq >> 4, e8 = (qq & 15) * 8;
             const bool valid = i < ci.len;
             cp_async16_z(sdo + cm_idx(i, e8, D), dO + tok(valid ? i : 0) * D + e8, valid);
+            cp_async16_z(sv + i * D + e8, v + tok(valid ? i : 0) * D + e8, valid);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         if (tid < C) {
@@ -104,9 +108,11 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         fence_async_smem();
     }
+    KDA_PHASE(0);
     bool ok = mbar_wait(&full, 0, p.status, 16);
     tc_fence_before();
     __syncthreads();
+    KDA_PHASE(1);
 
     const uint32_t sb = smem_u32(dyn);
     // ---- S1
@@ -135,6 +141,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     }
     ok = mbar_wait(&mmabar, 0, p.status, 32) && ok;
     tc_fence_after();
+    KDA_PHASE(2);
 
     // ---- conversions after S1
     {
@@ -142,6 +149,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         float* gdKh = (float*)(sc + L.dKh) + rec * C * D;
         __nv_bfloat16* dv = (__nv_bfloat16*)p.grad_v;
         __nv_bfloat16* sdvb = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
+        const __nv_bfloat16* sv = reinterpret_cast<const __nv_bfloat16*>(dyn + SV);
 #pragma unroll 1
         for (int i0 = 0; i0 < C; i0 += 16) {
             uint32_t r[16], pk[8];
@@ -168,12 +176,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             for (int j = 0; j < 16; ++j) {
                 const int i = i0 + j;
                 const float x = __uint_as_float(r[j]);
-                float vv = 0.f;
-                if (i < ci.len) {
-                    const size_t off = tok(i) * D + tid;
-                    vv = __bfloat162float(v[off]);
-                    dv[off] = __float2bfloat16_rn(sbeta[i] * x);
-                }
+                const float vv = __bfloat162float(sv[i * D + tid]);  // zero on padding rows
+                if (i < ci.len) dv[tok(i) * D + tid] = __float2bfloat16_rn(sbeta[i] * x);
                 stg[i * D + tid] = x * vv;
             }
         }
@@ -201,6 +205,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     }
     tc_fence_before();
     __syncthreads();
+    KDA_PHASE(3);
 
     // ---- S2
     if (tid == 0) {
@@ -235,9 +240,11 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             acc = fmaf(__bfloat162float(ds[cm_idx(e, tid, D)]), __bfloat162float(s0[cm_idx(e, tid, D)]), acc);
         ((float*)(sc + L.gC))[rec * D + tid] = acc * ((const float*)(ws + L.gamC))[rec * D + tid];
     }
+    KDA_PHASE(4);
     ok = mbar_wait(&mmabar, 1, p.status, 32) && ok;
     tc_fence_after();
     __syncthreads();
+    KDA_PHASE(5);
     if (tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
 
     // ---- conversions after S2
@@ -264,6 +271,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     }
     tc_fence_before();
     __syncthreads();
+    KDA_PHASE(6);
 
     // ---- S3
     if (tid == 0) {
@@ -279,6 +287,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     }
     ok = mbar_wait(&mmabar, 0, p.status, 32) && ok;
     tc_fence_after();
+    KDA_PHASE(7);
     {
         float* gdM = (float*)(sc + L.dM) + rec * C * C;
         const int i = 16 * warp + (lane & 15);
@@ -300,6 +309,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     (void)ok;
     tc_fence_before();
     __syncthreads();
+    KDA_PHASE(8);
     if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
 }
 
@@ -311,3 +321,5 @@ cudaError_t launch_bwd_wy_tc(const KdaParams& p, cudaStream_t s) {
 }
 
 }  // namespace kda
+
+KDA_PHASE_EXPORT(kda_debug_phases_bwd_wy)

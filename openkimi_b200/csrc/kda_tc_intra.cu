@@ -75,6 +75,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     const __nv_bfloat16* beta = (const __nv_bfloat16*)p.beta;
     const bool l2 = p.flags & KDA_FLAG_QK_L2NORM, gate = p.flags & KDA_FLAG_GATE, sig = p.flags & KDA_FLAG_BETA_SIGMOID;
 
+    KDA_PHASE_BEGIN();
     if (warp == 0) {
         tmem_alloc(&tmem_s, TMEM_COLS);
         tmem_relinquish();
@@ -106,6 +107,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         }
         if (half == 0) stot[d] = run;
     }
+    KDA_PHASE(0);
     // ---- 0b: q, k, v, beta row-wise: half warp hw owns rows hw + 16 m, lane c8 the channels 8 c8 ..
     {
         const int hw = tid >> 4, c8 = (tid & 15) * 8;
@@ -149,6 +151,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             if ((tid & 15) == 0) sbeta[i] = b;
         }
     }
+    KDA_PHASE(1);
     for (int idx = tid; idx < C * 65; idx += NTHR) {
         sA[idx] = 0.f;
         sL[idx] = 0.f;
@@ -165,6 +168,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         for (int i = 32; i < C; ++i) sG[i * D + d] += t;
     }
     __syncthreads();
+    KDA_PHASE(2);
 
     // ---- 1: decay-scaled operands
     {
@@ -230,6 +234,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     tc_fence_before();
     __syncthreads();
 
+    KDA_PHASE(3);
     // ---- 2: off-diagonal blocks on the tensor cores, diagonal blocks exactly on the CUDA cores
     if (tid == 0) {
         tc_fence_after();
@@ -267,6 +272,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             }
         }
     }
+    KDA_PHASE(4);
     bool ok = mbar_wait(&bar, 0, p.status, 8);
     tc_fence_after();
     if (ok) {
@@ -293,6 +299,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     tc_fence_before();
     __syncthreads();
 
+    KDA_PHASE(5);
     // ---- 3: T = (I + diag(beta) L)^-1
     if (warp < 4) {  // diagonal blocks, one warp each
         const int b0 = 16 * warp, cc = lane & 15, hf = lane >> 4;
@@ -329,6 +336,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         }
     }
 
+    KDA_PHASE(6);
     // ---- 4: Aqk and T records; T as the B operand of the WY products
     {
         __nv_bfloat16* sTB = reinterpret_cast<__nv_bfloat16*>(dyn + KSC);
@@ -351,6 +359,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     tc_fence_before();
     __syncthreads();
 
+    KDA_PHASE(7);
     // ---- 5: W^T and U^T
     if (tid == 0) {
         tc_fence_after();
@@ -368,6 +377,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     ok = mbar_wait(&bar, 1, p.status, 8) && ok;
     tc_fence_after();
 
+    KDA_PHASE(8);
     // ---- 6: W and U records
     if (ok) {
         const int qd = warp & 3, dd = 32 * qd + lane;
@@ -388,6 +398,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     }
     tc_fence_before();
     __syncthreads();
+    KDA_PHASE(9);
     if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
 }
 
@@ -399,3 +410,5 @@ cudaError_t launch_fwd_intra_tc(const KdaParams& p, cudaStream_t s) {
 }
 
 }  // namespace kda
+
+KDA_PHASE_EXPORT(kda_debug_phases_fwd_intra)

@@ -50,7 +50,8 @@ enum {
     KDA_ERR_ALIGN = 5,       /* a tensor pointer is not 16-byte aligned */
     KDA_ERR_LAUNCH = 6,      /* the CUDA runtime refused a launch (see kda_last_cuda_error) */
     KDA_ERR_DEVICE_WAIT = 7, /* a bounded device-side wait gave up (read from the status word) */
-    KDA_ERR_GUARD = 8        /* guard span is not a finite value <= 232 (or negative = exact) */
+    KDA_ERR_GUARD = 8,       /* guard span is not a finite value <= 232 (or negative = exact) */
+    KDA_ERR_STATIC_LIMIT = 9 /* size beyond the built-in scratch of an allocation-free entry point */
 };
 
 /* One call's description.  Replaces the keyword arguments of chunk_kda
@@ -112,6 +113,25 @@ int kda_short_conv_fwd(const void *x, const float *weight, void *y, int32_t B, i
 int kda_short_conv_bwd(const void *x, const float *weight, const void *dy, void *dx, float *dweight,
                        float *partial, int32_t n_partial, int32_t B, int32_t T, int32_t C, int32_t ksize,
                        int32_t dtype, const int64_t *cu_seqlens, int32_t N, void *cuda_stream);
+
+/* Allocation-free variant of kda_short_conv_bwd.  It has no counterpart in the reference; it
+ * exists for hosts that may not create device memory at call time: a plugin running under a
+ * memory plan that was frozen at start-up, a real-time loop that forbids allocator calls, a
+ * process whose memory pool is owned by another runtime.  Such a caller still passes its input
+ * and output tensors, but no scratch: the per-token-group partial sums of dweight live in a
+ * 2 MiB array that is part of the library image on every GPU that loads it.
+ *   - Limit: C * ksize <= 8192 (e.g. 2048 channels with 4 taps); larger sizes return
+ *     KDA_ERR_STATIC_LIMIT and launch nothing.
+ *   - The first call on each device looks up that device's address of the array (the device
+ *     must be current); make that first call outside any stream capture.  Later calls do no
+ *     set-up.  No call allocates or frees device memory.
+ *   - All calls on a device share the one array.  Every element that is read is rewritten by
+ *     the same call first, so nothing needs clearing, but two calls that overlap on the GPU
+ *     (different streams) race on it: serialise them.
+ *   - Results equal kda_short_conv_bwd with n_partial = 64 bit for bit. */
+int kda_short_conv_bwd_static(const void *x, const float *weight, const void *dy, void *dx, float *dweight,
+                              int32_t B, int32_t T, int32_t C, int32_t ksize, int32_t dtype,
+                              const int64_t *cu_seqlens, int32_t N, void *cuda_stream);
 
 /* Headwise RMSNorm(x) * sigmoid(gate) over [rows, dim] (k3mini/model.py:91-98; the fast
  * path's fla.modules.FusedRMSNormGated at k3mini/model.py:171-175). */

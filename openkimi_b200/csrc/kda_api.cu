@@ -99,6 +99,7 @@ const char* kda_status_string(int s) {
         case KDA_ERR_LAUNCH: return "CUDA launch failed";
         case KDA_ERR_DEVICE_WAIT: return "a bounded device-side wait gave up";
         case KDA_ERR_GUARD: return "guard span must be negative (exact) or a finite value <= 232";
+        case KDA_ERR_STATIC_LIMIT: return "size exceeds the built-in scratch of the allocation-free entry point (C * ksize <= 8192)";
         default: return "unknown status";
     }
 }

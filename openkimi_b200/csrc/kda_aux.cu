@@ -2,9 +2,19 @@
 // causal depthwise short convolution + SiLU (k3mini/model.py:76-88) and the headwise
 // RMSNorm * sigmoid(gate) output stage (k3mini/model.py:91-98).  Both are single passes
 // with 16-byte vector accesses; parameter gradients are reduced in a fixed order.
+#include <mutex>
+
 #include "kda_common.cuh"
 
 namespace kda {
+
+// Scratch of kda_short_conv_bwd_static: the per-token-group partial sums of the filter
+// gradient, [CONV_STATIC_PARTIALS][C * ksize] floats, resident in every GPU that loads the
+// library (2 MiB) from load until exit.  In host code this name is only a handle for
+// cudaGetSymbolAddress -- it is not a device address and must never be handed to a kernel.
+constexpr int CONV_STATIC_PARTIALS = 64;
+constexpr int CONV_STATIC_MAX_WEIGHTS = 8192;  // C * ksize, e.g. 2048 channels with 4 taps
+static __device__ __align__(256) float g_conv_static_partial[CONV_STATIC_PARTIALS * CONV_STATIC_MAX_WEIGHTS];
 
 template <typename T> struct Vec;
 template <> struct Vec<float> {
@@ -384,6 +394,33 @@ int kda_norm_gate_bwd(const void* x, const void* gate, const float* weight, cons
 #undef NG_BWD
     partial_reduce_kernel<<<(dim + 255) / 256, 256, 0, s>>>(partial, dweight, n_partial, dim);
     return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
+
+// The variant of kda_short_conv_bwd for callers that must not allocate: same kernels, same
+// reduction order (so the same bits as kda_short_conv_bwd with n_partial = 64), but the
+// partial sums live in g_conv_static_partial instead of a caller buffer.
+int kda_short_conv_bwd_static(const void* x, const float* weight, const void* dy, void* dx, float* dweight, int32_t B,
+                              int32_t T, int32_t Cch, int32_t ksize, int32_t dtype, const int64_t* cu_seqlens, int32_t N,
+                              void* stream) {
+    if (ksize < 1 || Cch < 1 || (int64_t)Cch * ksize > CONV_STATIC_MAX_WEIGHTS) return KDA_ERR_STATIC_LIMIT;
+    // One-time set-up per device, with that device current: ask the runtime where this
+    // device's copy of the array lives.  The array's name itself is not that address.
+    static std::mutex mu;
+    static float* dev_ptr[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KDA_ERR_LAUNCH;
+    float* part = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!dev_ptr[dev]) {
+            void* ptr = nullptr;
+            if (cudaGetSymbolAddress(&ptr, g_conv_static_partial) != cudaSuccess || !ptr) return KDA_ERR_LAUNCH;
+            dev_ptr[dev] = static_cast<float*>(ptr);
+        }
+        part = dev_ptr[dev];
+    }
+    return kda_short_conv_bwd(x, weight, dy, dx, dweight, part, CONV_STATIC_PARTIALS, B, T, Cch, ksize, dtype, cu_seqlens,
+                              N, stream);
 }
 
 }  // extern "C"

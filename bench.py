@@ -255,6 +255,13 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    # keep the GPU under the same load while the sampler comes up, so that its samples (20 ms
+    # apart) cover loaded clocks even when the timed region itself lasts only tens of ms
+    t_end = time.perf_counter() + 0.4
+    while time.perf_counter() < t_end:
+        step_device(dev_in, w)
+        torch.cuda.synchronize()
+    lib.kda_profile_begin(n_calls)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()

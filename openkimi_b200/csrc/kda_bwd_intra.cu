@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    KDA_PHASE_BEGIN();
     prefetch(3);
 
     // ---- 0a: q, k row-wise (half warp per row): L2 norm, BF16 copies; beta
@@ -138,6 +139,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         }
     }
+    KDA_PHASE(0);
     // ---- 0b: gate channel-wise -> cumulative log2 decay G (two halves of 32 rows)
     {
         const int half = tid >> 7;
@@ -152,12 +154,13 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         for (int r = 0; r < 32; ++r) {
             const int i = 32 * half + r;
             float gl = 0.f;
-            if (i < ci.len) gl = gate ? negA * softplus_f(x[r] + bias) : x[r];
+            if (i < ci.len) gl = gate ? negA * softplus_fast(x[r] + bias) : x[r];
             run += gl * LOG2E;
             sG[i * D + d] = run;
         }
         if (half == 0) stot[d] = run;
     }
+    KDA_PHASE(1);
     // ---- 0c: dAqk, dM (FP32 row-major) and the beta gradient collected by bwd_wy
     {
         const float4* gdA = reinterpret_cast<const float4*>((const float*)(sc + L.dAqk) + rec * C * C);
@@ -176,6 +179,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     }
     __syncthreads();
 
+    KDA_PHASE(2);
     // ---- guard of the four diagonal tiles (one tile = 16 rows x this warp's 32 channels)
     unsigned guard_mask = 0;
     {
@@ -288,6 +292,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     __nv_bfloat16* dk_out = (__nv_bfloat16*)p.grad_k;
     __nv_bfloat16* dg_out = (__nv_bfloat16*)p.grad_g;
 
+    KDA_PHASE(3);
     for (int I = 3; I >= 0; --I) {
         float a1[B], a2[B], Gi[B];
         // ---- X: group A finishes the column sums this block needs, group B sums its rows
@@ -366,8 +371,10 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 }
             }
         }
+        KDA_PHASE(4 + 4 * (3 - I));
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
+        KDA_PHASE(5 + 4 * (3 - I));
 
         // ---- Y: group B assembles the 16 tokens of block I (last token first: running suffix
         //         sum of dG); group A already works on the next block's column sums
@@ -406,6 +413,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         }
         __syncthreads();
+        KDA_PHASE(6 + 4 * (3 - I));
         // ---- Z: row-wise (one half warp per token): L2-norm chain, beta gradient, 16-byte stores
         if (I > 0) prefetch(I - 1);
         {
@@ -444,6 +452,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         }
         __syncthreads();
+        KDA_PHASE(7 + 4 * (3 - I));
     }
     if (gate) {
         if (!grpA) ((float*)(sc + L.dbias_part))[rec * D + d] = dbias_acc;
@@ -462,3 +471,5 @@ cudaError_t launch_bwd_intra(const KdaParams& p, cudaStream_t s) {
 }
 
 }  // namespace kda
+
+KDA_PHASE_EXPORT(kda_debug_phases_bwd_intra)

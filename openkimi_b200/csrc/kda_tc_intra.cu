@@ -85,47 +85,56 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         mbar_fence_init();
     }
 
+    // ---- 0: issue every global load of the chunk first (gate column, q/k/v rows, beta)
+    const int half = tid >> 7, dch = tid & 127;
+    const int hw = tid >> 4, c8 = (tid & 15) * 8;
+    float x[32];
+    uint4 rq4[4], rk4[4], rv4[4];
+    float rb[4];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+        const int i = 32 * half + r;
+        x[r] = i < ci.len ? __bfloat162float(g[((size_t)(ci.tok0 + i) * p.H + h) * D + dch]) : 0.f;
+    }
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const int i = hw + 16 * m;
+        const bool valid = i < ci.len;
+        const size_t row = (size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h;
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        rq4[m] = valid ? *reinterpret_cast<const uint4*>(q + row * D + c8) : z;
+        rk4[m] = valid ? *reinterpret_cast<const uint4*>(k + row * D + c8) : z;
+        rv4[m] = valid ? *reinterpret_cast<const uint4*>(v + row * D + c8) : z;
+        rb[m] = ((tid & 15) == 0 && valid) ? __bfloat162float(beta[row]) : 0.f;
+    }
     // ---- 0a: gate, channel-wise: thread (half, d) owns rows 32*half .. 32*half+31 of channel d
     {
-        const int half = tid >> 7, d = tid & 127;
         const float negA = gate ? -expf(p.A_log[h]) : 0.f;
-        const float bias = (gate && p.dt_bias) ? p.dt_bias[h * D + d] : 0.f;
-        float x[32];
-#pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const int i = 32 * half + r;
-            x[r] = i < ci.len ? __bfloat162float(g[((size_t)(ci.tok0 + i) * p.H + h) * D + d]) : 0.f;
-        }
+        const float bias = (gate && p.dt_bias) ? p.dt_bias[h * D + dch] : 0.f;
         float run = 0.f;
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
             const int i = 32 * half + r;
             float gl = 0.f;
-            if (i < ci.len) gl = gate ? negA * softplus_f(x[r] + bias) : x[r];
+            if (i < ci.len) gl = gate ? negA * softplus_fast(x[r] + bias) : x[r];
             run += gl * LOG2E;
-            sG[i * D + d] = run;
+            sG[i * D + dch] = run;
         }
-        if (half == 0) stot[d] = run;
+        if (half == 0) stot[dch] = run;
     }
     KDA_PHASE(0);
     // ---- 0b: q, k, v, beta row-wise: half warp hw owns rows hw + 16 m, lane c8 the channels 8 c8 ..
     {
-        const int hw = tid >> 4, c8 = (tid & 15) * 8;
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
             const int i = hw + 16 * m;
             const bool valid = i < ci.len;
-            const size_t row = (size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h;
             float qf[8], kf[8], vf[8];
-            uint4 z = make_uint4(0, 0, 0, 0);
-            bf16x8_to_f32(valid ? *reinterpret_cast<const uint4*>(q + row * D + c8) : z, qf);
-            bf16x8_to_f32(valid ? *reinterpret_cast<const uint4*>(k + row * D + c8) : z, kf);
-            bf16x8_to_f32(valid ? *reinterpret_cast<const uint4*>(v + row * D + c8) : z, vf);
-            float b = 0.f;
-            if ((tid & 15) == 0 && valid) {
-                b = __bfloat162float(beta[row]);
-                if (sig) b = sigmoid_f(b);
-            }
+            bf16x8_to_f32(rq4[m], qf);
+            bf16x8_to_f32(rk4[m], kf);
+            bf16x8_to_f32(rv4[m], vf);
+            float b = rb[m];
+            if ((tid & 15) == 0 && valid && sig) b = sigmoid_f(b);
             b = __shfl_sync(0xffffffffu, b, lane & 16);
             if (l2) {
                 float ssq = 0.f, ssk = 0.f;
@@ -172,7 +181,6 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 
     // ---- 1: decay-scaled operands
     {
-        const int hw = tid >> 4, c8 = (tid & 15) * 8;
         float gl[8];
         {
             const float4 a = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8);
@@ -248,29 +256,25 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                        make_desc(sb + XSC + (I - 1) * 8192 + s * 256, 128, 2048), id, s > 0);
         mma_commit(&bar);
     }
-    for (int i = warp; i < C; i += NTHR / 32) {
-        float qi[4], ki[4], gi[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            qi[t] = __bfloat162float(sQ[i * D + lane + 32 * t]);
-            ki[t] = __bfloat162float(sK[i * D + lane + 32 * t]);
-            gi[t] = sG[i * D + lane + 32 * t];
+    // one thread per (i, j) pair of a diagonal block (4 x 136 pairs); every thread walks the 128
+    // channels from its own starting channel, so a warp's shared-memory reads hit 32 banks
+    for (int pr = tid; pr < 4 * 136; pr += NTHR) {
+        const int blk = pr / 136, rr = pr - blk * 136;
+        int i = (int)((sqrtf(8.f * rr + 1.f) - 1.f) * 0.5f);
+        while ((i + 1) * (i + 2) / 2 <= rr) ++i;
+        while (i * (i + 1) / 2 > rr) --i;
+        const int j = rr - i * (i + 1) / 2;
+        const int ri = 16 * blk + i, rj = 16 * blk + j;
+        float a = 0.f, l = 0.f;
+#pragma unroll 4
+        for (int t = 0; t < D; ++t) {
+            const int d = (lane + t) & (D - 1);
+            const float kd = __bfloat162float(sK[rj * D + d]) * exp2f(sG[ri * D + d] - sG[rj * D + d]);
+            a = fmaf(__bfloat162float(sQ[ri * D + d]), kd, a);
+            l = fmaf(__bfloat162float(sK[ri * D + d]), kd, l);
         }
-        for (int j = i & ~15; j <= i; ++j) {
-            float a = 0.f, l = 0.f;
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const float kd = __bfloat162float(sK[j * D + lane + 32 * t]) * exp2f(gi[t] - sG[j * D + lane + 32 * t]);
-                a = fmaf(qi[t], kd, a);
-                l = fmaf(ki[t], kd, l);
-            }
-            a = warp_sum(a);
-            l = warp_sum(l);
-            if (lane == 0) {
-                sA[i * 65 + j] = a * p.scale;
-                if (j < i) sL[i * 65 + j] = l;
-            }
-        }
+        sA[ri * 65 + rj] = a * p.scale;
+        if (j < i) sL[ri * 65 + rj] = l;
     }
     KDA_PHASE(4);
     bool ok = mbar_wait(&bar, 0, p.status, 8);

@@ -23,18 +23,17 @@ namespace kda {
 using namespace tc;
 
 namespace bi {
-constexpr int D = 128, NTHR = 256, B = 16;
+constexpr int D = 128, NTHR = 256, B = 16, HB = 8;
 constexpr uint32_t SQ = 0;                   // q^ bf16 [64][128]
 constexpr uint32_t SK = SQ + 16384;          // k^ bf16 [64][128]
 constexpr uint32_t SG = SK + 16384;          // G f32 [64][128]
 constexpr uint32_t SDA = SG + 32768;         // dAqk f32 [64][64]
 constexpr uint32_t SDM = SDA + 16384;        // dM   f32 [64][64]
-constexpr uint32_t SC1 = SDM + 16384;        // c1 f32 [64][128]
-constexpr uint32_t STG = SC1 + 32768;        // staging f32 [3][16][128]: dq, dk, dbeta terms of one block
+constexpr uint32_t STG = SDM + 16384;        // staging f32 [3][16][128]: dq, dk, dbeta terms of one block
 constexpr uint32_t PF = STG + 24576;         // prefetch f32 [3][16][128]: dQt, dKh, dKb rows of one block
 constexpr uint32_t SBETA = PF + 24576;       // f32 [64] beta, [64] 1/|q|, [64] 1/|k|, [64] dbeta
-constexpr uint32_t SRUN = SBETA + 1024;      // f32 [128] last-row term, f32 [128] half totals of the cumulative sum
-constexpr uint32_t SRED = SRUN + 1024;       // f32 [8]
+constexpr uint32_t SX = SBETA + 1024;        // f32 [2][2][128] block totals of dG, f32 [2][128] scratch
+constexpr uint32_t SRED = SX + 3072;         // f32 [8]
 constexpr uint32_t TOTAL = SRED + 64;
 }  // namespace bi
 
@@ -42,8 +41,9 @@ __device__ __forceinline__ void cpa16(void* dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
 
-// Threads 0..127 (group A) accumulate the column sums c1, threads 128..255 (group B) the row
-// sums a1, a2 and assemble the gradients; both own channel d = tid % 128.
+// 256 threads: thread (gp, d) = (tid / 128, tid % 128) owns channel d and, inside every 16-row
+// block, the 8 tokens 8 gp .. 8 gp + 7: their row sums a1, a2, their column sums c1 and their
+// final assembly all stay in its registers.
 __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) {
     using namespace bi;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -52,19 +52,17 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     float* sG = reinterpret_cast<float*>(dyn + SG);
     float* sdA = reinterpret_cast<float*>(dyn + SDA);
     float* sdM = reinterpret_cast<float*>(dyn + SDM);
-    float* sC1 = reinterpret_cast<float*>(dyn + SC1);
     float* stg = reinterpret_cast<float*>(dyn + STG);
     float* spf = reinterpret_cast<float*>(dyn + PF);
     float* sbeta = reinterpret_cast<float*>(dyn + SBETA);
     float* srq = sbeta + 64;
     float* srk = sbeta + 128;
     float* sdb = sbeta + 192;
-    float* srun = reinterpret_cast<float*>(dyn + SRUN);
-    float* stot = srun + 128;
+    float* stotal = reinterpret_cast<float*>(dyn + SX);  // [parity][gp][d]
+    float* sscr = stotal + 512;                          // [gp][d]
     float* sred = reinterpret_cast<float*>(dyn + SRED);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid & 127;
-    const bool grpA = tid < 128;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid & 127, gp = tid >> 7;
     const int c = blockIdx.x / p.H, h = blockIdx.x % p.H;
     const ChunkInfo ci = chunk_info(p, c);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
@@ -93,93 +91,107 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     KDA_PHASE_BEGIN();
-    prefetch(3);
-
-    // ---- 0a: q, k row-wise (half warp per row): L2 norm, BF16 copies; beta
+    // ---- every global load of the prologue is issued before anything is computed
     {
-        const int hw = tid >> 4, c8 = (tid & 15) * 8;
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            const int i = hw + 16 * m;
-            const bool valid = i < ci.len;
-            const size_t row = tok(valid ? i : 0);
-            float qf[8], kf[8];
-            const uint4 z = make_uint4(0, 0, 0, 0);
-            bf16x8_to_f32(valid ? *reinterpret_cast<const uint4*>(q + row * D + c8) : z, qf);
-            bf16x8_to_f32(valid ? *reinterpret_cast<const uint4*>(k + row * D + c8) : z, kf);
-            float rq = 1.f, rk = 1.f;
-            if (l2) {
-                float ssq = 0.f, ssk = 0.f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    ssq += qf[j] * qf[j];
-                    ssk += kf[j] * kf[j];
-                }
-                ssq = half_warp_sum(ssq);
-                ssk = half_warp_sum(ssk);
-                rq = 1.f / fmaxf(sqrtf(ssq), 1e-6f);
-                rk = 1.f / fmaxf(sqrtf(ssk), 1e-6f);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    qf[j] *= rq;
-                    kf[j] *= rk;
-                }
-            }
-            *reinterpret_cast<uint4*>(sQ + i * D + c8) = f32_to_bf16x8(qf);
-            *reinterpret_cast<uint4*>(sK + i * D + c8) = f32_to_bf16x8(kf);
-            if ((tid & 15) == 0) {
-                float b = 0.f;
-                if (valid) {
-                    b = __bfloat162float(beta[row]);
-                    if (sig) b = sigmoid_f(b);
-                }
-                sbeta[i] = b;
-                srq[i] = rq;
-                srk[i] = rk;
-            }
+        const float* gdA = (const float*)(sc + L.dAqk) + rec * C * C;
+        const float* gdM = (const float*)(sc + L.dM) + rec * C * C;
+        for (int qq = tid; qq < C * C / 4; qq += NTHR) {
+            cpa16(sdA + qq * 4, gdA + qq * 4);
+            cpa16(sdM + qq * 4, gdM + qq * 4);
         }
     }
-    KDA_PHASE(0);
-    // ---- 0b: gate channel-wise -> cumulative log2 decay G (two halves of 32 rows)
-    {
-        const int half = tid >> 7;
-        float x[32];
+    prefetch(3);
+    const int hw = tid >> 4, c8 = (tid & 15) * 8;
+    float x[32], kh[32];
+    uint4 rq4[4], rk4[4];
+    float rb[4];
 #pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const int i = 32 * half + r;
-            x[r] = i < ci.len ? __bfloat162float(g[tok(i) * D + d]) : 0.f;
-        }
+    for (int r = 0; r < 32; ++r) {
+        const int i = 32 * gp + r;
+        x[r] = i < ci.len ? __bfloat162float(g[tok(i) * D + d]) : 0.f;
+        kh[r] = gdKh[i * D + d];
+    }
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const int i = hw + 16 * m;
+        const bool valid = i < ci.len;
+        const size_t row = tok(valid ? i : 0);
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        rq4[m] = valid ? *reinterpret_cast<const uint4*>(q + row * D + c8) : z;
+        rk4[m] = valid ? *reinterpret_cast<const uint4*>(k + row * D + c8) : z;
+        rb[m] = ((tid & 15) == 0 && valid) ? __bfloat162float(beta[row]) : 0.f;
+    }
+    if (tid < C) sdb[tid] = ((const float*)(sc + L.dbp))[rec * C + tid];
+    // ---- 0a: gate channel-wise -> cumulative log2 decay G (two halves of 32 rows)
+    {
         float run = 0.f;
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
-            const int i = 32 * half + r;
+            const int i = 32 * gp + r;
             float gl = 0.f;
             if (i < ci.len) gl = gate ? negA * softplus_fast(x[r] + bias) : x[r];
             run += gl * LOG2E;
             sG[i * D + d] = run;
         }
-        if (half == 0) stot[d] = run;
+        if (gp == 0) sscr[d] = run;
+    }
+    KDA_PHASE(0);
+    // ---- 0b: q, k row-wise (half warp per row): L2 norm, BF16 copies; beta
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const int i = hw + 16 * m;
+        float qf[8], kf[8];
+        bf16x8_to_f32(rq4[m], qf);
+        bf16x8_to_f32(rk4[m], kf);
+        float rq = 1.f, rk = 1.f;
+        if (l2) {
+            float ssq = 0.f, ssk = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                ssq += qf[j] * qf[j];
+                ssk += kf[j] * kf[j];
+            }
+            ssq = half_warp_sum(ssq);
+            ssk = half_warp_sum(ssk);
+            rq = 1.f / fmaxf(sqrtf(ssq), 1e-6f);
+            rk = 1.f / fmaxf(sqrtf(ssk), 1e-6f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                qf[j] *= rq;
+                kf[j] *= rk;
+            }
+        }
+        *reinterpret_cast<uint4*>(sQ + i * D + c8) = f32_to_bf16x8(qf);
+        *reinterpret_cast<uint4*>(sK + i * D + c8) = f32_to_bf16x8(kf);
+        if ((tid & 15) == 0) {
+            float b = rb[m];
+            if (sig && i < ci.len) b = sigmoid_f(b);
+            sbeta[i] = b;
+            srq[i] = rq;
+            srk[i] = rk;
+        }
     }
     KDA_PHASE(1);
-    // ---- 0c: dAqk, dM (FP32 row-major) and the beta gradient collected by bwd_wy
-    {
-        const float4* gdA = reinterpret_cast<const float4*>((const float*)(sc + L.dAqk) + rec * C * C);
-        const float4* gdM = reinterpret_cast<const float4*>((const float*)(sc + L.dM) + rec * C * C);
-        for (int qq = tid; qq < C * C / 4; qq += NTHR) {
-            reinterpret_cast<float4*>(sdA)[qq] = gdA[qq];
-            reinterpret_cast<float4*>(sdM)[qq] = gdM[qq];
-        }
-        if (tid < C) sdb[tid] = ((const float*)(sc + L.dbp))[rec * C + tid];
-    }
     __syncthreads();
-    if (!grpA) {
-        const float t = stot[d];
+    if (gp == 1) {
+        const float t = sscr[d];
 #pragma unroll 8
         for (int i = 32; i < C; ++i) sG[i * D + d] += t;
     }
     __syncthreads();
-
+    // ---- term of the last row: dGamma_C Gamma_C + sum_i dKh_i Kh_i (each group sums its 32 rows)
+    const float gl = sG[(C - 1) * D + d];
+    {
+        float s = 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const int i = 32 * gp + r;
+            s = fmaf(kh[r], __bfloat162float(sK[i * D + d]) * exp2f(gl - sG[i * D + d]), s);
+        }
+        sscr[128 * gp + d] = s;  // group 0's slot was consumed by group 1 before the last barrier
+    }
     KDA_PHASE(2);
+
     // ---- guard of the four diagonal tiles (one tile = 16 rows x this warp's 32 channels)
     unsigned guard_mask = 0;
     {
@@ -190,11 +202,11 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             bool good = true;
 #pragma unroll
             for (int r = 0; r < B; ++r) {
-                const float x = sG[(B * I + r) * D + d];
-                good = good && (x <= prev) && isfinite(x);
-                prev = x;
-                gmax = fmaxf(gmax, x);
-                gmin = fminf(gmin, x);
+                const float xx = sG[(B * I + r) * D + d];
+                good = good && (xx <= prev) && isfinite(xx);
+                prev = xx;
+                gmax = fmaxf(gmax, xx);
+                gmin = fminf(gmin, xx);
             }
             float span = gmax - gmin;
 #pragma unroll
@@ -203,205 +215,193 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             if (pass) guard_mask |= 1u << I;
         }
     }
-    // midpoint factors of one diagonal block: P_r = 2^(G_r - m), N_r = 2^(m - G_r)
-    auto diag_factors = [&](const float (&Gb)[B], float (&P)[B], float (&N)[B]) {
-        float gmax = Gb[0], gmin = Gb[0];
-#pragma unroll
-        for (int r = 1; r < B; ++r) {
-            gmax = fmaxf(gmax, Gb[r]);
-            gmin = fminf(gmin, Gb[r]);
-        }
-        const float m = 0.5f * (gmax + gmin);
-#pragma unroll
-        for (int r = 0; r < B; ++r) {
-            P[r] = exp2f(Gb[r] - m);
-            N[r] = exp2f(m - Gb[r]);
-        }
-    };
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float carry = ((const float*)(sc + L.gC))[rec * D + d] + sscr[d] + sscr[128 + d];
+    float dA_acc = 0.f, dbias_acc = 0.f;
+    __nv_bfloat16* dq_out = (__nv_bfloat16*)p.grad_q;
+    __nv_bfloat16* dk_out = (__nv_bfloat16*)p.grad_k;
+    __nv_bfloat16* dg_out = (__nv_bfloat16*)p.grad_g;
+    const int h0 = HB * gp;  // first of my 8 tokens inside a block
+    KDA_PHASE(3);
 
-    // ---- group A: column sums of block J -> sC1
-    auto col_pass = [&](int J) {
-        float c1[B], Gj[B];
+    for (int I = 3; I >= 0; --I) {
+        float Gb[B], a1[HB], a2[HB], c1[HB], Gm[HB];
 #pragma unroll
-        for (int j = 0; j < B; ++j) {
-            c1[j] = 0.f;
-            Gj[j] = sG[(B * J + j) * D + d];
+        for (int r = 0; r < B; ++r) Gb[r] = sG[(B * I + r) * D + d];
+#pragma unroll
+        for (int i = 0; i < HB; ++i) {
+            a1[i] = 0.f;
+            a2[i] = 0.f;
+            c1[i] = 0.f;
+            Gm[i] = gp ? Gb[HB + i] : Gb[i];
         }
-        {  // diagonal block: pairs i > j
-            float qs[B], kb[B];
+        // ---- row sums of my 8 tokens over the earlier blocks: k_j 2^(r - G_j), r = G at this block's first row
+        for (int J = 0; J < I; ++J) {
+            float kd[B];
 #pragma unroll
-            for (int i = 0; i < B; ++i) {
-                qs[i] = scale * __bfloat162float(sQ[(B * J + i) * D + d]);
-                kb[i] = sbeta[B * J + i] * __bfloat162float(sK[(B * J + i) * D + d]);
+            for (int j = 0; j < B; ++j) {
+                const int jj = B * J + j;
+                kd[j] = __bfloat162float(sK[jj * D + d]) * exp2f(Gb[0] - sG[jj * D + d]);
             }
-            if ((guard_mask >> J) & 1) {
-                float P[B], N[B], u[B];
-                diag_factors(Gj, P, N);
 #pragma unroll
-                for (int j = 0; j < B; ++j) u[j] = 0.f;
-#pragma unroll
-                for (int i = 1; i < B; ++i) {
-                    const float qp = qs[i] * P[i], kp = kb[i] * P[i];
-#pragma unroll
-                    for (int j = 0; j < i; ++j)
-                        u[j] = fmaf(sdA[(B * J + i) * C + B * J + j], qp, fmaf(sdM[(B * J + i) * C + B * J + j], kp, u[j]));
-                }
-#pragma unroll
-                for (int j = 0; j < B; ++j) c1[j] = N[j] * u[j];
-            } else {
-#pragma unroll
-                for (int i = 1; i < B; ++i)
-#pragma unroll
-                    for (int j = 0; j < i; ++j) {
-                        const float t = sdA[(B * J + i) * C + B * J + j] * qs[i] + sdM[(B * J + i) * C + B * J + j] * kb[i];
-                        c1[j] = fmaf(t, exp2f(Gj[i] - Gj[j]), c1[j]);
-                    }
-            }
-        }
-        for (int I = J + 1; I < 4; ++I) {  // later blocks, reference r = G at their first row
-            const float r = sG[(B * I) * D + d];
-            float u[B];
-#pragma unroll
-            for (int j = 0; j < B; ++j) u[j] = 0.f;
-#pragma unroll
-            for (int i = 0; i < B; ++i) {
-                const int ii = B * I + i;
-                const float Pi = exp2f(sG[ii * D + d] - r);
-                const float qp = scale * __bfloat162float(sQ[ii * D + d]) * Pi;
-                const float kp = sbeta[ii] * __bfloat162float(sK[ii * D + d]) * Pi;
+            for (int i = 0; i < HB; ++i) {
+                const int ii = B * I + h0 + i;
+                float u1 = 0.f, u2 = 0.f;
 #pragma unroll
                 for (int j4 = 0; j4 < B; j4 += 4) {
                     const float4 a = *reinterpret_cast<const float4*>(sdA + ii * C + B * J + j4);
                     const float4 m = *reinterpret_cast<const float4*>(sdM + ii * C + B * J + j4);
-                    u[j4 + 0] = fmaf(a.x, qp, fmaf(m.x, kp, u[j4 + 0]));
-                    u[j4 + 1] = fmaf(a.y, qp, fmaf(m.y, kp, u[j4 + 1]));
-                    u[j4 + 2] = fmaf(a.z, qp, fmaf(m.z, kp, u[j4 + 2]));
-                    u[j4 + 3] = fmaf(a.w, qp, fmaf(m.w, kp, u[j4 + 3]));
+                    u1 = fmaf(a.x, kd[j4], fmaf(a.y, kd[j4 + 1], fmaf(a.z, kd[j4 + 2], fmaf(a.w, kd[j4 + 3], u1))));
+                    u2 = fmaf(m.x, kd[j4], fmaf(m.y, kd[j4 + 1], fmaf(m.z, kd[j4 + 2], fmaf(m.w, kd[j4 + 3], u2))));
                 }
+                const float Pi = exp2f(Gm[i] - Gb[0]);
+                a1[i] = fmaf(Pi, u1, a1[i]);
+                a2[i] = fmaf(Pi, u2, a2[i]);
             }
-#pragma unroll
-            for (int j = 0; j < B; ++j) c1[j] = fmaf(exp2f(r - Gj[j]), u[j], c1[j]);
         }
+        // ---- column sums of my 8 tokens over the later blocks: reference r' = G at their first row
+        for (int Ip = I + 1; Ip < 4; ++Ip) {
+            const float r2 = sG[(B * Ip) * D + d];
+            float u[HB];
 #pragma unroll
-        for (int j = 0; j < B; ++j) sC1[(B * J + j) * D + d] = c1[j];
-    };
-
-    const float gl = sG[(C - 1) * D + d];
-    float run = 0.f, dA_acc = 0.f, dbias_acc = 0.f;
-    __nv_bfloat16* dq_out = (__nv_bfloat16*)p.grad_q;
-    __nv_bfloat16* dk_out = (__nv_bfloat16*)p.grad_k;
-    __nv_bfloat16* dg_out = (__nv_bfloat16*)p.grad_g;
-
-    KDA_PHASE(3);
-    for (int I = 3; I >= 0; --I) {
-        float a1[B], a2[B], Gi[B];
-        // ---- X: group A finishes the column sums this block needs, group B sums its rows
-        if (grpA) {
-            if (I == 3) {
-                // term of the last row: dGamma_C Gamma_C + sum_i dKh_i Kh_i
-                float s = ((const float*)(sc + L.gC))[rec * D + d];
-#pragma unroll 8
-                for (int i = 0; i < C; ++i)
-                    s = fmaf(gdKh[i * D + d], __bfloat162float(sK[i * D + d]) * exp2f(gl - sG[i * D + d]), s);
-                srun[d] = s;
-                col_pass(3);
-            }
-        } else {
+            for (int j = 0; j < HB; ++j) u[j] = 0.f;
 #pragma unroll
             for (int i = 0; i < B; ++i) {
-                a1[i] = 0.f;
-                a2[i] = 0.f;
-                Gi[i] = sG[(B * I + i) * D + d];
+                const int ii = B * Ip + i;
+                const float Pi = exp2f(sG[ii * D + d] - r2);
+                const float qp = scale * __bfloat162float(sQ[ii * D + d]) * Pi;
+                const float kp = sbeta[ii] * __bfloat162float(sK[ii * D + d]) * Pi;
+                const float4 a0 = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + h0);
+                const float4 a4 = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + h0 + 4);
+                const float4 m0 = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + h0);
+                const float4 m4 = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + h0 + 4);
+                u[0] = fmaf(a0.x, qp, fmaf(m0.x, kp, u[0]));
+                u[1] = fmaf(a0.y, qp, fmaf(m0.y, kp, u[1]));
+                u[2] = fmaf(a0.z, qp, fmaf(m0.z, kp, u[2]));
+                u[3] = fmaf(a0.w, qp, fmaf(m0.w, kp, u[3]));
+                u[4] = fmaf(a4.x, qp, fmaf(m4.x, kp, u[4]));
+                u[5] = fmaf(a4.y, qp, fmaf(m4.y, kp, u[5]));
+                u[6] = fmaf(a4.z, qp, fmaf(m4.z, kp, u[6]));
+                u[7] = fmaf(a4.w, qp, fmaf(m4.w, kp, u[7]));
             }
-            for (int J = 0; J < I; ++J) {  // earlier blocks: k_j 2^(r - G_j), r = G at this block's first row
-                float kd[B], u1[B], u2[B];
 #pragma unroll
-                for (int j = 0; j < B; ++j) {
-                    const int jj = B * J + j;
-                    kd[j] = __bfloat162float(sK[jj * D + d]) * exp2f(Gi[0] - sG[jj * D + d]);
+            for (int j = 0; j < HB; ++j) c1[j] = fmaf(exp2f(r2 - Gm[j]), u[j], c1[j]);
+        }
+        // ---- diagonal block: pairs (i, j) with j < i, at least one of them mine
+        {
+            float kj[B], qs[B], kb[B];
+#pragma unroll
+            for (int r = 0; r < B; ++r) {
+                const int rr = B * I + r;
+                const float kk = __bfloat162float(sK[rr * D + d]);
+                kj[r] = kk;
+                qs[r] = scale * __bfloat162float(sQ[rr * D + d]);
+                kb[r] = sbeta[rr] * kk;
+            }
+            if ((guard_mask >> I) & 1) {  // midpoint factorisation 2^(G_i - m) 2^(m - G_j)
+                float gmax = Gb[0], gmin = Gb[0];
+#pragma unroll
+                for (int r = 1; r < B; ++r) {
+                    gmax = fmaxf(gmax, Gb[r]);
+                    gmin = fminf(gmin, Gb[r]);
+                }
+                const float mid = 0.5f * (gmax + gmin);
+#pragma unroll
+                for (int r = 0; r < B; ++r) {
+                    const float P = exp2f(Gb[r] - mid), N = exp2f(mid - Gb[r]);
+                    kj[r] *= N;   // key side of the row sums
+                    qs[r] *= P;   // row side of the column sums
+                    kb[r] *= P;
                 }
 #pragma unroll
-                for (int i = 0; i < B; ++i) {
-                    u1[i] = 0.f;
-                    u2[i] = 0.f;
+                for (int i = 0; i < HB; ++i) {
+                    const int li = h0 + i, ii = B * I + li;
+                    float u1 = 0.f, u2 = 0.f;
 #pragma unroll
-                    for (int j4 = 0; j4 < B; j4 += 4) {
-                        const float4 a = *reinterpret_cast<const float4*>(sdA + (B * I + i) * C + B * J + j4);
-                        const float4 m = *reinterpret_cast<const float4*>(sdM + (B * I + i) * C + B * J + j4);
-                        u1[i] = fmaf(a.x, kd[j4], fmaf(a.y, kd[j4 + 1], fmaf(a.z, kd[j4 + 2], fmaf(a.w, kd[j4 + 3], u1[i]))));
-                        u2[i] = fmaf(m.x, kd[j4], fmaf(m.y, kd[j4 + 1], fmaf(m.z, kd[j4 + 2], fmaf(m.w, kd[j4 + 3], u2[i]))));
+                    for (int j = 0; j < B - 1; ++j) {
+                        const bool on = j < li;
+                        u1 = fmaf(on ? sdA[ii * C + B * I + j] : 0.f, kj[j], u1);
+                        u2 = fmaf(on ? sdM[ii * C + B * I + j] : 0.f, kj[j], u2);
                     }
+                    const float Pi = exp2f(Gm[i] - mid);
+                    a1[i] = fmaf(Pi, u1, a1[i]);
+                    a2[i] = fmaf(Pi, u2, a2[i]);
                 }
 #pragma unroll
-                for (int i = 0; i < B; ++i) {
-                    const float Pi = exp2f(Gi[i] - Gi[0]);
-                    a1[i] = fmaf(Pi, u1[i], a1[i]);
-                    a2[i] = fmaf(Pi, u2[i], a2[i]);
-                }
-            }
-            {  // diagonal block: pairs j < i
-                float kj[B];
-#pragma unroll
-                for (int j = 0; j < B; ++j) kj[j] = __bfloat162float(sK[(B * I + j) * D + d]);
-                if ((guard_mask >> I) & 1) {
-                    float P[B], N[B];
-                    diag_factors(Gi, P, N);
-#pragma unroll
-                    for (int j = 0; j < B; ++j) kj[j] *= N[j];
+                for (int j = 0; j < HB; ++j) {
+                    const int lj = h0 + j, jj = B * I + lj;
+                    float u = 0.f;
 #pragma unroll
                     for (int i = 1; i < B; ++i) {
-                        float u1 = 0.f, u2 = 0.f;
-#pragma unroll
-                        for (int j = 0; j < i; ++j) {
-                            u1 = fmaf(sdA[(B * I + i) * C + B * I + j], kj[j], u1);
-                            u2 = fmaf(sdM[(B * I + i) * C + B * I + j], kj[j], u2);
-                        }
-                        a1[i] = fmaf(P[i], u1, a1[i]);
-                        a2[i] = fmaf(P[i], u2, a2[i]);
+                        const bool on = i > lj;
+                        u = fmaf(on ? sdA[(B * I + i) * C + jj] : 0.f, qs[i], fmaf(on ? sdM[(B * I + i) * C + jj] : 0.f, kb[i], u));
                     }
-                } else {
+                    c1[j] = fmaf(exp2f(mid - Gm[j]), u, c1[j]);
+                }
+            } else {  // one exp2 per pair
 #pragma unroll
-                    for (int i = 1; i < B; ++i)
+                for (int i = 0; i < HB; ++i) {
+                    const int li = h0 + i, ii = B * I + li;
 #pragma unroll
-                        for (int j = 0; j < i; ++j) {
-                            const float kp = kj[j] * exp2f(Gi[i] - Gi[j]);
-                            a1[i] = fmaf(sdA[(B * I + i) * C + B * I + j], kp, a1[i]);
-                            a2[i] = fmaf(sdM[(B * I + i) * C + B * I + j], kp, a2[i]);
-                        }
+                    for (int j = 0; j < B - 1; ++j) {
+                        const bool on = j < li;
+                        const float kp = on ? kj[j] * exp2f(Gm[i] - Gb[j]) : 0.f;
+                        a1[i] = fmaf(sdA[ii * C + B * I + j], kp, a1[i]);
+                        a2[i] = fmaf(sdM[ii * C + B * I + j], kp, a2[i]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < HB; ++j) {
+                    const int lj = h0 + j, jj = B * I + lj;
+#pragma unroll
+                    for (int i = 1; i < B; ++i) {
+                        const bool on = i > lj;
+                        const float e = on ? exp2f(Gb[i] - Gm[j]) : 0.f;
+                        const float t = sdA[(B * I + i) * C + jj] * qs[i] + sdM[(B * I + i) * C + jj] * kb[i];
+                        c1[j] = fmaf(t, e, c1[j]);
+                    }
                 }
             }
         }
         KDA_PHASE(4 + 4 * (3 - I));
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
+        __syncthreads();  // prefetched rows of this block are visible; staging buffer is free
         KDA_PHASE(5 + 4 * (3 - I));
 
-        // ---- Y: group B assembles the 16 tokens of block I (last token first: running suffix
-        //         sum of dG); group A already works on the next block's column sums
-        if (grpA) {
-            if (I > 0) col_pass(I - 1);
-        } else {
-            if (I == 3) run = srun[d];
+        // ---- assembly of my 8 tokens, last first; run[i] = dG summed over the tokens >= i of my half
+        float runl[HB];
+        {
+            float acc = 0.f;
 #pragma unroll
-            for (int i = B - 1; i >= 0; --i) {
-                const int ii = B * I + i;
+            for (int i = HB - 1; i >= 0; --i) {
+                const int li = h0 + i, ii = B * I + li;
                 const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
                 const float bi_ = sbeta[ii];
-                const float gam = exp2f(Gi[i]), eta = exp2f(gl - Gi[i]);
-                const float dQt = spf[(0 * B + i) * D + d], dKh = spf[(1 * B + i) * D + d], dKb = spf[(2 * B + i) * D + d];
-                const float c1 = sC1[ii * D + d];
+                const float gam = exp2f(Gm[i]), eta = exp2f(gl - Gm[i]);
+                const float dQt = spf[(0 * B + li) * D + d], dKh = spf[(1 * B + li) * D + d], dKb = spf[(2 * B + li) * D + d];
                 const float diag = scale * sdA[ii * C + ii];
                 const float dq_in = scale * a1[i], dk_row = bi_ * a2[i], dKt = bi_ * dKb;
-                stg[(0 * B + i) * D + d] = dq_in + diag * ki + scale * dQt * gam;
-                stg[(1 * B + i) * D + d] = dk_row + c1 + diag * qi + dKt * gam + dKh * eta;
-                stg[(2 * B + i) * D + d] = ki * a2[i] + dKb * (ki * gam);
-                run += qi * dq_in + ki * dk_row - ki * c1 + dQt * (scale * qi * gam) + dKt * (ki * gam) - dKh * (ki * eta);
+                stg[(0 * B + li) * D + d] = dq_in + diag * ki + scale * dQt * gam;
+                stg[(1 * B + li) * D + d] = dk_row + c1[i] + diag * qi + dKt * gam + dKh * eta;
+                stg[(2 * B + li) * D + d] = ki * a2[i] + dKb * (ki * gam);
+                acc += qi * dq_in + ki * dk_row - ki * c1[i] + dQt * (scale * qi * gam) + dKt * (ki * gam) - dKh * (ki * eta);
+                runl[i] = acc;
+            }
+            stotal[((I & 1) * 2 + gp) * D + d] = acc;
+        }
+        // gate chain for one half: base = everything after my half's last token
+        auto finish = [&](float base) {
+#pragma unroll
+            for (int i = HB - 1; i >= 0; --i) {
+                const int ii = B * I + h0 + i;
                 if (ii < ci.len) {
+                    const float run = base + runl[i];
                     const size_t off = tok(ii) * D + d;
                     if (gate) {
                         // per-token log decay g = (G_i - G_{i-1}) ln 2; sigmoid(x + b) = 1 - exp(-softplus) = -expm1(g / e^A)
-                        const float gprev = ii > 0 ? sG[(ii - 1) * D + d] : 0.f;
-                        const float gnat = (Gi[i] - gprev) * 0.6931471805599453f;
+                        const float gprev = ii > 0 ? (i > 0 ? Gm[i - 1] : sG[(ii - 1) * D + d]) : 0.f;
+                        const float gnat = (Gm[i] - gprev) * 0.6931471805599453f;
                         dA_acc = fmaf(run, gnat, dA_acc);
                         const float dx = run * negA * (-expm1f(gnat * rcpA));
                         dbias_acc += dx;
@@ -411,13 +411,16 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                     }
                 }
             }
-        }
+        };
+        if (gp == 1) finish(carry);
         __syncthreads();
         KDA_PHASE(6 + 4 * (3 - I));
-        // ---- Z: row-wise (one half warp per token): L2-norm chain, beta gradient, 16-byte stores
-        if (I > 0) prefetch(I - 1);
+        const float upper = stotal[((I & 1) * 2 + 1) * D + d];
+        if (gp == 0) finish(carry + upper);
+        carry += upper + stotal[((I & 1) * 2 + 0) * D + d];
+        // ---- row-wise (one half warp per token): L2-norm chain, beta gradient, 16-byte stores
         {
-            const int i = tid >> 4, c8 = (tid & 15) * 8, ii = B * I + i;
+            const int i = tid >> 4, ii = B * I + i;
             float dq8[8], dk8[8], q8[8], k8[8], db = 0.f, dotq = 0.f, dotk = 0.f;
             bf16x8_to_f32(*reinterpret_cast<const uint4*>(sQ + ii * D + c8), q8);
             bf16x8_to_f32(*reinterpret_cast<const uint4*>(sK + ii * D + c8), k8);
@@ -451,15 +454,21 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 }
             }
         }
-        __syncthreads();
+        __syncthreads();  // staging and prefetch buffers may be overwritten
+        if (I > 0) prefetch(I - 1);
         KDA_PHASE(7 + 4 * (3 - I));
     }
     if (gate) {
-        if (!grpA) ((float*)(sc + L.dbias_part))[rec * D + d] = dbias_acc;
+        sscr[128 * gp + d] = dbias_acc;
         dA_acc = warp_sum(dA_acc);
         if (lane == 0) sred[warp] = dA_acc;
         __syncthreads();
-        if (tid == 0) ((float*)(sc + L.dA_part))[rec] = sred[4] + sred[5] + sred[6] + sred[7];
+        if (gp == 0) ((float*)(sc + L.dbias_part))[rec * D + d] = sscr[d] + sscr[128 + d];
+        if (tid == 0) {
+            float t = 0.f;
+            for (int w = 0; w < 8; ++w) t += sred[w];
+            ((float*)(sc + L.dA_part))[rec] = t;
+        }
     }
 }
 

@@ -806,22 +806,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
     }
 }
 
-// deterministic reduction of the per-chunk partial parameter gradients
-__global__ void kda_param_reduce(const KdaParams p) {
+// deterministic reduction of the per-chunk partial parameter gradients: one block per head,
+// 8 groups of 128 threads each sum every 8th chunk in order, then the 8 group sums are added
+// in a fixed order
+__global__ void __launch_bounds__(1024) kda_param_reduce(const KdaParams p) {
+    __shared__ float sb[8][128];
+    __shared__ float sa[8][32];
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     const char* sc = (const char*)p.bwd_scratch;
-    const int h = blockIdx.x, d = threadIdx.x;
+    const int h = blockIdx.x, d = threadIdx.x & 127, grp = threadIdx.x >> 7;
     const float* pb = (const float*)(sc + L.dbias_part);
     const float* pa = (const float*)(sc + L.dA_part);
-    if (d < p.dk && p.grad_dt_bias) {
-        float s = 0.f;
-        for (int c = 0; c < p.NT; ++c) s += pb[((size_t)c * p.H + h) * p.dk + d];
-        p.grad_dt_bias[h * p.dk + d] = s;
-    }
-    if (d == 0 && p.grad_A_log) {
-        float s = 0.f;
-        for (int c = 0; c < p.NT; ++c) s += pa[(size_t)c * p.H + h];
-        p.grad_A_log[h] = s;
+    float s = 0.f;
+    if (d < p.dk)
+        for (int c = grp; c < p.NT; c += 8) s += pb[((size_t)c * p.H + h) * p.dk + d];
+    sb[grp][d] = s;
+    // dA_log: lanes 0..31 of every group take every 32nd of the group's chunks
+    float a = 0.f;
+    if (d < 32)
+        for (int c = grp + 8 * d; c < p.NT; c += 256) a += pa[(size_t)c * p.H + h];
+    if (d < 32) sa[grp][d] = a;
+    __syncthreads();
+    if (grp == 0) {
+        if (d < p.dk && p.grad_dt_bias) {
+            float t = 0.f;
+            for (int gidx = 0; gidx < 8; ++gidx) t += sb[gidx][d];
+            p.grad_dt_bias[h * p.dk + d] = t;
+        }
+        if (d == 0 && p.grad_A_log) {
+            float t = 0.f;
+            for (int gidx = 0; gidx < 8; ++gidx)
+                for (int l = 0; l < 32; ++l) t += sa[gidx][l];
+            p.grad_A_log[h] = t;
+        }
     }
 }
 
@@ -868,7 +885,7 @@ static cudaError_t launch_stage(const KdaParams& p, int stage, cudaStream_t s) {
             kda_bwd_chunk_simt<T, D, true><<<p.NT * p.H, NTHREADS, smem_bwd_chunk<D>(), s>>>(p);
             break;
         default:
-            kda_param_reduce<<<p.H, 128, 0, s>>>(p);
+            kda_param_reduce<<<p.H, 1024, 0, s>>>(p);
     }
     return cudaGetLastError();
 }

@@ -31,7 +31,7 @@ constexpr uint32_t SDA = SG + 32768;         // dAqk f32 [64][64]
 constexpr uint32_t SDM = SDA + 16384;        // dM   f32 [64][64]
 constexpr uint32_t STG = SDM + 16384;        // staging f32 [3][16][128]: dq, dk, dbeta terms of one block
 constexpr uint32_t PF = STG + 24576;         // prefetch f32 [3][16][128]: dQt, dKh, dKb rows of one block
-constexpr uint32_t SBETA = PF + 24576;       // f32 [64] beta, [64] 1/|q|, [64] 1/|k|, [64] dbeta
+constexpr uint32_t SBETA = PF + 24576;       // f32 [64] 1/|q|, [64] 1/|k|, [64] beta, [64] dbeta
 constexpr uint32_t SX = SBETA + 1024;        // f32 [2][2][128] block totals of dG, f32 [2][128] scratch
 constexpr uint32_t SRED = SX + 3072;         // f32 [8]
 constexpr uint32_t TOTAL = SRED + 64;
@@ -54,10 +54,10 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     float* sdM = reinterpret_cast<float*>(dyn + SDM);
     float* stg = reinterpret_cast<float*>(dyn + STG);
     float* spf = reinterpret_cast<float*>(dyn + PF);
-    float* sbeta = reinterpret_cast<float*>(dyn + SBETA);
-    float* srq = sbeta + 64;
-    float* srk = sbeta + 128;
-    float* sdb = sbeta + 192;
+    float* srq = reinterpret_cast<float*>(dyn + SBETA);  // aux record order: 1/|q|, 1/|k|, beta
+    float* srk = srq + 64;
+    float* sbeta = srq + 128;
+    float* sdb = srq + 192;
     float* stotal = reinterpret_cast<float*>(dyn + SX);  // [parity][gp][d]
     float* sscr = stotal + 512;                          // [gp][d]
     float* sred = reinterpret_cast<float*>(dyn + SRED);
@@ -68,10 +68,6 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     char* sc = (char*)p.bwd_scratch;
     const size_t rec = (size_t)c * p.H + h;
-    const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
-    const __nv_bfloat16* k = (const __nv_bfloat16*)p.k;
-    const __nv_bfloat16* g = (const __nv_bfloat16*)p.g;
-    const __nv_bfloat16* beta = (const __nv_bfloat16*)p.beta;
     const float* gdQt = (const float*)(sc + L.dQt) + rec * C * D;
     const float* gdKh = (const float*)(sc + L.dKh) + rec * C * D;
     const float* gdKb = (const float*)(sc + L.dKb) + rec * C * D;
@@ -79,7 +75,6 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     const float scale = p.scale;
     const float expA = gate ? expf(p.A_log[h]) : 1.f;
     const float negA = -expA, rcpA = 1.f / expA;
-    const float bias = (gate && p.dt_bias) ? p.dt_bias[h * D + d] : 0.f;
     auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
     // rows 16 I .. 16 I + 15 of dQt, dKh, dKb -> spf (16-byte asynchronous copies)
     auto prefetch = [&](int I) {
@@ -91,94 +86,37 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     KDA_PHASE_BEGIN();
-    // ---- every global load of the prologue is issued before anything is computed
+    // ---- the forward kept G, the normalised q and k, the row norms and beta: copy them in
+    //      asynchronously together with dAqk, dM and the first block of dQt / dKh / dKb
     {
+        const char* ws = (const char*)p.workspace;
         const float* gdA = (const float*)(sc + L.dAqk) + rec * C * C;
         const float* gdM = (const float*)(sc + L.dM) + rec * C * C;
+        const float* gG = (const float*)(ws + L.Gc) + rec * C * D;
+        const __nv_bfloat16* gQn = (const __nv_bfloat16*)(ws + L.Qn) + rec * C * D;
+        const __nv_bfloat16* gKn = (const __nv_bfloat16*)(ws + L.Kn) + rec * C * D;
+        const float* gaux = (const float*)(ws + L.aux) + rec * 3 * C;
+        for (int qq = tid; qq < C * D / 4; qq += NTHR) cpa16(sG + qq * 4, gG + qq * 4);
+        for (int qq = tid; qq < C * D / 8; qq += NTHR) {
+            cpa16(sQ + qq * 8, gQn + qq * 8);
+            cpa16(sK + qq * 8, gKn + qq * 8);
+        }
         for (int qq = tid; qq < C * C / 4; qq += NTHR) {
             cpa16(sdA + qq * 4, gdA + qq * 4);
             cpa16(sdM + qq * 4, gdM + qq * 4);
         }
+        if (tid < 3 * C / 4) cpa16(srq + tid * 4, gaux + tid * 4);  // 1/|q|, 1/|k|, beta -> srq, srk, sbeta2
     }
     prefetch(3);
-    const int hw = tid >> 4, c8 = (tid & 15) * 8;
-    float x[32], kh[32];
-    uint4 rq4[4], rk4[4];
-    float rb[4];
+    const int c8 = (tid & 15) * 8;
+    float kh[32];
 #pragma unroll
-    for (int r = 0; r < 32; ++r) {
-        const int i = 32 * gp + r;
-        x[r] = i < ci.len ? __bfloat162float(g[tok(i) * D + d]) : 0.f;
-        kh[r] = gdKh[i * D + d];
-    }
-#pragma unroll
-    for (int m = 0; m < 4; ++m) {
-        const int i = hw + 16 * m;
-        const bool valid = i < ci.len;
-        const size_t row = tok(valid ? i : 0);
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        rq4[m] = valid ? *reinterpret_cast<const uint4*>(q + row * D + c8) : z;
-        rk4[m] = valid ? *reinterpret_cast<const uint4*>(k + row * D + c8) : z;
-        rb[m] = ((tid & 15) == 0 && valid) ? __bfloat162float(beta[row]) : 0.f;
-    }
+    for (int r = 0; r < 32; ++r) kh[r] = gdKh[(32 * gp + r) * D + d];
     if (tid < C) sdb[tid] = ((const float*)(sc + L.dbp))[rec * C + tid];
-    // ---- 0a: gate channel-wise -> cumulative log2 decay G (two halves of 32 rows)
-    {
-        float run = 0.f;
-#pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const int i = 32 * gp + r;
-            float gl = 0.f;
-            if (i < ci.len) gl = gate ? negA * softplus_fast(x[r] + bias) : x[r];
-            run += gl * LOG2E;
-            sG[i * D + d] = run;
-        }
-        if (gp == 0) sscr[d] = run;
-    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     KDA_PHASE(0);
-    // ---- 0b: q, k row-wise (half warp per row): L2 norm, BF16 copies; beta
-#pragma unroll
-    for (int m = 0; m < 4; ++m) {
-        const int i = hw + 16 * m;
-        float qf[8], kf[8];
-        bf16x8_to_f32(rq4[m], qf);
-        bf16x8_to_f32(rk4[m], kf);
-        float rq = 1.f, rk = 1.f;
-        if (l2) {
-            float ssq = 0.f, ssk = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                ssq += qf[j] * qf[j];
-                ssk += kf[j] * kf[j];
-            }
-            ssq = half_warp_sum(ssq);
-            ssk = half_warp_sum(ssk);
-            rq = 1.f / fmaxf(sqrtf(ssq), 1e-6f);
-            rk = 1.f / fmaxf(sqrtf(ssk), 1e-6f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                qf[j] *= rq;
-                kf[j] *= rk;
-            }
-        }
-        *reinterpret_cast<uint4*>(sQ + i * D + c8) = f32_to_bf16x8(qf);
-        *reinterpret_cast<uint4*>(sK + i * D + c8) = f32_to_bf16x8(kf);
-        if ((tid & 15) == 0) {
-            float b = rb[m];
-            if (sig && i < ci.len) b = sigmoid_f(b);
-            sbeta[i] = b;
-            srq[i] = rq;
-            srk[i] = rk;
-        }
-    }
+    __syncthreads();
     KDA_PHASE(1);
-    __syncthreads();
-    if (gp == 1) {
-        const float t = sscr[d];
-#pragma unroll 8
-        for (int i = 32; i < C; ++i) sG[i * D + d] += t;
-    }
-    __syncthreads();
     // ---- term of the last row: dGamma_C Gamma_C + sum_i dKh_i Kh_i (each group sums its 32 rows)
     const float gl = sG[(C - 1) * D + d];
     {
@@ -188,7 +126,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             const int i = 32 * gp + r;
             s = fmaf(kh[r], __bfloat162float(sK[i * D + d]) * exp2f(gl - sG[i * D + d]), s);
         }
-        sscr[128 * gp + d] = s;  // group 0's slot was consumed by group 1 before the last barrier
+        sscr[128 * gp + d] = s;
     }
     KDA_PHASE(2);
 
@@ -403,7 +341,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                         const float gprev = ii > 0 ? (i > 0 ? Gm[i - 1] : sG[(ii - 1) * D + d]) : 0.f;
                         const float gnat = (Gm[i] - gprev) * 0.6931471805599453f;
                         dA_acc = fmaf(run, gnat, dA_acc);
-                        const float dx = run * negA * (-expm1f(gnat * rcpA));
+                        const float dx = run * negA * (1.f - exp2f(gnat * rcpA * LOG2E));
                         dbias_acc += dx;
                         dg_out[off] = __float2bfloat16_rn(dx);
                     } else {
@@ -412,11 +350,10 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 }
             }
         };
-        if (gp == 1) finish(carry);
         __syncthreads();
         KDA_PHASE(6 + 4 * (3 - I));
         const float upper = stotal[((I & 1) * 2 + 1) * D + d];
-        if (gp == 0) finish(carry + upper);
+        finish(gp == 0 ? carry + upper : carry);
         carry += upper + stotal[((I & 1) * 2 + 0) * D + d];
         // ---- row-wise (one half warp per token): L2-norm chain, beta gradient, 16-byte stores
         {

@@ -71,10 +71,11 @@ __device__ __forceinline__ void seq_chunks(const KdaParams& p, int n, int& c0, i
 //   W    as W^T   cm(d, i; 64)      U / V'  as V'^T  cm(e, i; 64)     (i = token in chunk)
 //   Aqk, Tm       cm(i, j; 64)      Qt, Kh           cm(i, d; dk)
 //   S0, dS as S^T cm(e, d; dk)      dVn     as dV'^T cm(e, i; 64)
-// gamC is a plain float[dk].
+// gamC is a plain float[dk]; Gc, Qn, Kn, aux are plain row-major arrays.
 // ---------------------------------------------------------------------------------------
 struct WsLayout {
-    size_t W, U, Aqk, Qt, Kh, Tm, S0, gamC, total;      // forward workspace
+    size_t W, U, Aqk, Qt, Kh, Tm, S0, gamC;             // forward workspace
+    size_t Gc, Qn, Kn, aux, total;                      // prologue results kept for the backward
     size_t dS, dVn, dA_part, dbias_part;                // backward scratch
     size_t dAqk, dM, dQt, dKh, dKb, dbp, gC, bwd_total; // hand-over from bwd_wy to bwd_intra
 };
@@ -94,6 +95,13 @@ __host__ __device__ inline WsLayout ws_layout(int NT, int H, int dk, int dv, int
     w.Tm = off;   off = align256(off + n * C * C * es);
     w.S0 = off;   off = align256(off + n * dk * dv * es);
     w.gamC = off; off = align256(off + n * dk * 4);
+    // kept so that the backward does not redo the prologue: cumulative log2 decay G (float
+    // [64][dk]), normalised q and k (element type, [64][dk] row-major), and per row
+    // 1/|q|, 1/|k|, beta after the sigmoid (float [3][64])
+    w.Gc = off;   off = align256(off + n * C * dk * 4);
+    w.Qn = off;   off = align256(off + n * C * dk * es);
+    w.Kn = off;   off = align256(off + n * C * dk * es);
+    w.aux = off;  off = align256(off + n * 3 * C * 4);
     w.total = off;
     off = 0;
     w.dS = off;         off = align256(off + n * dk * dv * es);

@@ -189,6 +189,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_fwd_intra_simt(const KdaParam
     float* gGam = (float*)(ws + L.gamC) + rec * D;
 
     load_prologue<T, D>(p, ci, h, sq, sk, sG, sv, sbeta, srq, srk);
+    {  // prologue results kept for the backward
+        float* gGc = (float*)(ws + L.Gc) + rec * C * D;
+        T* gQn = (T*)(ws + L.Qn) + rec * C * D;
+        T* gKn = (T*)(ws + L.Kn) + rec * C * D;
+        float* gaux = (float*)(ws + L.aux) + rec * 3 * C;
+        for (int idx = tid; idx < C * D; idx += NTHREADS) {
+            gGc[idx] = sG[idx];
+            stf(gQn + idx, sq[idx]);
+            stf(gKn + idx, sk[idx]);
+        }
+        if (tid < C) {
+            gaux[tid] = srq[tid];
+            gaux[C + tid] = srk[tid];
+            gaux[2 * C + tid] = sbeta[tid];
+        }
+    }
 
     // exact pairwise products: one warp per (i, j) pair, lanes over channels
     for (int i = warp; i < C; i += NTHREADS / 32) {

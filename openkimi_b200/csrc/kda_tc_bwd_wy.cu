@@ -97,14 +97,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             cp_async16_z(sv + i * D + e8, v + tok(valid ? i : 0) * D + e8, valid);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        if (tid < C) {
-            float b = 0.f;
-            if (tid < ci.len) {
-                b = __bfloat162float(((const __nv_bfloat16*)p.beta)[tok(tid)]);
-                if (p.flags & KDA_FLAG_BETA_SIGMOID) b = sigmoid_f(b);
-            }
-            sbeta[tid] = b;
-        }
+        if (tid < C) sbeta[tid] = ((const float*)(ws + L.aux))[rec * 3 * C + 2 * C + tid];  // beta kept by the forward
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         fence_async_smem();
     }

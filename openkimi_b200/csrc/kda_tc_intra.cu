@@ -32,8 +32,8 @@ constexpr uint32_t SA = BV + 16384;          // f32 [64][65]
 constexpr uint32_t SL = SA + 16640;
 constexpr uint32_t ST = SL + 16640;
 constexpr uint32_t SP = ST + 16640;          // f32 [3][16][17]
-constexpr uint32_t SBETA = SP + 3328;        // f32 [64]
-constexpr uint32_t STOT = SBETA + 256;       // f32 [128]
+constexpr uint32_t SBETA = SP + 3328;        // f32 [3][64]: 1/|q|, 1/|k|, beta (the aux record)
+constexpr uint32_t STOT = SBETA + 768;       // f32 [128]
 constexpr uint32_t TOTAL = STOT + 512;
 constexpr uint32_t T_D = 0, T_W = 96, T_U = 160, TMEM_COLS = 256;
 }  // namespace fi
@@ -52,7 +52,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     float* sL = reinterpret_cast<float*>(dyn + SL);
     float* sT = reinterpret_cast<float*>(dyn + ST);
     float* sP = reinterpret_cast<float*>(dyn + SP);
-    float* sbeta = reinterpret_cast<float*>(dyn + SBETA);
+    float* saux = reinterpret_cast<float*>(dyn + SBETA);
+    float* sbeta = saux + 2 * C;
     float* stot = reinterpret_cast<float*>(dyn + STOT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -136,6 +137,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             float b = rb[m];
             if ((tid & 15) == 0 && valid && sig) b = sigmoid_f(b);
             b = __shfl_sync(0xffffffffu, b, lane & 16);
+            float rq = 1.f, rk = 1.f;
             if (l2) {
                 float ssq = 0.f, ssk = 0.f;
 #pragma unroll
@@ -145,7 +147,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                 }
                 ssq = half_warp_sum(ssq);
                 ssk = half_warp_sum(ssk);
-                const float rq = 1.f / fmaxf(sqrtf(ssq), 1e-6f), rk = 1.f / fmaxf(sqrtf(ssk), 1e-6f);
+                rq = 1.f / fmaxf(sqrtf(ssq), 1e-6f);
+                rk = 1.f / fmaxf(sqrtf(ssk), 1e-6f);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     qf[j] *= rq;
@@ -157,7 +160,11 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             *reinterpret_cast<uint4*>(sQ + i * D + c8) = f32_to_bf16x8(qf);
             *reinterpret_cast<uint4*>(sK + i * D + c8) = f32_to_bf16x8(kf);
             *reinterpret_cast<uint4*>(sBV + cm_idx(i, c8, D)) = f32_to_bf16x8(vf);
-            if ((tid & 15) == 0) sbeta[i] = b;
+            if ((tid & 15) == 0) {
+                sbeta[i] = b;
+                saux[i] = rq;
+                saux[C + i] = rk;
+            }
         }
     }
     KDA_PHASE(1);
@@ -176,8 +183,16 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 #pragma unroll 8
         for (int i = 32; i < C; ++i) sG[i * D + d] += t;
     }
+    fence_async_smem();
     __syncthreads();
     KDA_PHASE(2);
+    if (tid == 0) {  // prologue results for the backward: three bulk stores straight from shared memory
+        tma_store_1d((float*)(ws + L.Gc) + rec * C * D, sG, C * D * 4);
+        tma_store_1d((__nv_bfloat16*)(ws + L.Qn) + rec * C * D, sQ, C * D * 2);
+        tma_store_1d((__nv_bfloat16*)(ws + L.Kn) + rec * C * D, sK, C * D * 2);
+        tma_store_1d((float*)(ws + L.aux) + rec * 3 * C, saux, 3 * C * 4);
+        tma_store_commit();
+    }
 
     // ---- 1: decay-scaled operands
     {
@@ -400,6 +415,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                            pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13])), pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15])));
         }
     }
+    if (tid == 0) tma_store_wait_all();
     tc_fence_before();
     __syncthreads();
     KDA_PHASE(9);

@@ -38,6 +38,65 @@ constexpr uint32_t TOTAL = STOT + 512;
 constexpr uint32_t T_D = 0, T_W = 96, T_U = 160, TMEM_COLS = 256;
 }  // namespace fi
 
+// One block column of T = (I + diag(beta) L)^-1 (see stage 3 of the kernel).  sL holds L
+// (strictly lower, row stride 65), sT receives T; sT must be zero above the diagonal blocks.
+template <int J>
+__device__ __forceinline__ void solve_block_column(const float* sL, float* sT, const float* sbeta, int warp, int lane) {
+    const int col = 8 * (warp >> 2) + (lane & 7), rq = lane >> 3, gc = 16 * J + col;
+    float t[4 - J][16];
+    // diagonal block: forward substitution down the column (every lane group does all 16 rows)
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < r; j += 2) {
+            s0 = fmaf(sL[(16 * J + r) * 65 + 16 * J + j], t[0][j], s0);
+            if (j + 1 < r) s1 = fmaf(sL[(16 * J + r) * 65 + 16 * J + j + 1], t[0][j + 1], s1);
+        }
+        t[0][r] = (r == col ? 1.f : 0.f) - sbeta[16 * J + r] * (s0 + s1);
+        if (r < col) t[0][r] = 0.f;
+    }
+    if (rq == 0) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) sT[(16 * J + r) * 65 + gc] = t[0][r];
+    }
+    __syncthreads();  // every diagonal block of T is in shared memory
+#pragma unroll
+    for (int I = J + 1; I < 4; ++I) {
+        // y = sum_K (beta L)_IK t_K for my four rows, then all 16 entries from the lane groups
+        float y4[4], y[16];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int r = 16 * I + 4 * rq + q;
+            float s = 0.f;
+#pragma unroll
+            for (int K = J; K < I; ++K)
+#pragma unroll
+                for (int m = 0; m < 16; ++m) s = fmaf(sL[r * 65 + 16 * K + m], t[K - J][m], s);
+            y4[q] = sbeta[r] * s;
+        }
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) y[4 * g4 + q] = __shfl_sync(0xffffffffu, y4[q], (lane & 7) + 8 * g4);
+        // t_I = -T_II y for my four rows, shared the same way
+        float n4[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int r = 16 * I + 4 * rq + q;
+            float s = 0.f;
+#pragma unroll
+            for (int m = 0; m < 16; ++m) s = fmaf(sT[r * 65 + 16 * I + m], y[m], s);
+            n4[q] = -s;
+            sT[r * 65 + gc] = -s;
+        }
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) t[I - J][4 * g4 + q] = __shfl_sync(0xffffffffu, n4[q], (lane & 7) + 8 * g4);
+    }
+}
+
 __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams p) {
     using namespace fi;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -202,7 +261,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             const float4 b = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8 + 4);
             gl[0] = a.x; gl[1] = a.y; gl[2] = a.z; gl[3] = a.w; gl[4] = b.x; gl[5] = b.y; gl[6] = b.z; gl[7] = b.w;
         }
-#pragma unroll
+#pragma unroll 1
         for (int m = 0; m < 4; ++m) {
             const int i = hw + 16 * m;  // block index of this row == m
             float G8[8], qf[8], kf[8], o8[8];
@@ -239,7 +298,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                 for (int j = 0; j < 8; ++j) o8[j] = kf[j] * f[j];
                 *reinterpret_cast<uint4*>(xs + cm_idx(16 + i - 16 * m, c8, D)) = f32_to_bf16x8(o8);
             }
-#pragma unroll
+#pragma unroll 1
             for (int I = 1; I <= 3; ++I) {  // keys scaled for the later blocks
                 __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(dyn + KSC + (I - 1) * 16384);
                 if (m < I) {
@@ -282,11 +341,16 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         const int ri = 16 * blk + i, rj = 16 * blk + j;
         float a = 0.f, l = 0.f;
 #pragma unroll 4
-        for (int t = 0; t < D; ++t) {
-            const int d = (lane + t) & (D - 1);
-            const float kd = __bfloat162float(sK[rj * D + d]) * exp2f(sG[ri * D + d] - sG[rj * D + d]);
-            a = fmaf(__bfloat162float(sQ[ri * D + d]), kd, a);
-            l = fmaf(__bfloat162float(sK[ri * D + d]), kd, l);
+        for (int t = 0; t < D / 2; ++t) {
+            const int d2 = 2 * ((lane + t) & (D / 2 - 1));
+            const float2 gi = *reinterpret_cast<const float2*>(sG + ri * D + d2);
+            const float2 gj = *reinterpret_cast<const float2*>(sG + rj * D + d2);
+            const float2 kj = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sK + rj * D + d2));
+            const float2 qi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sQ + ri * D + d2));
+            const float2 ki = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sK + ri * D + d2));
+            const float kd0 = kj.x * exp2f(gi.x - gj.x), kd1 = kj.y * exp2f(gi.y - gj.y);
+            a = fmaf(qi.x, kd0, fmaf(qi.y, kd1, a));
+            l = fmaf(ki.x, kd0, fmaf(ki.y, kd1, l));
         }
         sA[ri * 65 + rj] = a * p.scale;
         if (j < i) sL[ri * 65 + rj] = l;
@@ -319,41 +383,17 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     __syncthreads();
 
     KDA_PHASE(5);
-    // ---- 3: T = (I + diag(beta) L)^-1
-    if (warp < 4) {  // diagonal blocks, one warp each
-        const int b0 = 16 * warp, cc = lane & 15, hf = lane >> 4;
-        for (int r = 0; r < 16; ++r) {
-            float s = 0.f;
-            for (int j = hf; j < r; j += 2) s = fmaf(sL[(b0 + r) * 65 + b0 + j], sT[(b0 + j) * 65 + b0 + cc], s);
-            s += __shfl_xor_sync(0xffffffffu, s, 16);
-            if (hf == 0 && cc <= r) sT[(b0 + r) * 65 + b0 + cc] = (cc == r ? 1.f : 0.f) - sbeta[b0 + r] * s;
-            __syncwarp();
-        }
+    // ---- 3: T = (I + diag(beta) L)^-1, column by column.  Column c of T depends only on
+    //      column c of the blocks above it, so one lane carries a whole column in registers:
+    //      warp w owns block column J = w % 4, columns 8 (w / 4) + lane % 8, and its four lane
+    //      groups (lane / 8) split the 16 rows of every block below the diagonal.
+    switch (warp & 3) {
+        case 0: solve_block_column<0>(sL, sT, sbeta, warp, lane); break;
+        case 1: solve_block_column<1>(sL, sT, sbeta, warp, lane); break;
+        case 2: solve_block_column<2>(sL, sT, sbeta, warp, lane); break;
+        default: solve_block_column<3>(sL, sT, sbeta, warp, lane); break;
     }
     __syncthreads();
-    {
-        const int r = tid >> 4, cc = tid & 15;
-        for (int lvl = 1; lvl <= 3; ++lvl) {
-            for (int J = 0; J + lvl <= 3; ++J) {  // P = sum_K (beta L)_IK T_KJ
-                const int I = J + lvl;
-                float s = 0.f;
-                for (int K = J; K < I; ++K)
-#pragma unroll
-                    for (int m = 0; m < 16; ++m)
-                        s = fmaf(sL[(16 * I + r) * 65 + 16 * K + m], sT[(16 * K + m) * 65 + 16 * J + cc], s);
-                sP[(J * 16 + r) * 17 + cc] = sbeta[16 * I + r] * s;
-            }
-            __syncthreads();
-            for (int J = 0; J + lvl <= 3; ++J) {  // T_IJ = -T_II P
-                const int I = J + lvl;
-                float s = 0.f;
-#pragma unroll
-                for (int m = 0; m < 16; ++m) s = fmaf(sT[(16 * I + r) * 65 + 16 * I + m], sP[(J * 16 + m) * 17 + cc], s);
-                sT[(16 * I + r) * 65 + 16 * J + cc] = -s;
-            }
-            __syncthreads();
-        }
-    }
 
     KDA_PHASE(6);
     // ---- 4: Aqk and T records; T as the B operand of the WY products

@@ -38,6 +38,10 @@ WORKLOADS = {
                label="kda_fwd_bwd B=4 T=4096 H=6 d=128 bf16 adversarial gate span"),
     "c3": dict(B=1, T=65536, H=6, d=128, x_mean=0.0, a_lo=1.0, a_hi=16.0, beta_mean=0.0, docs=16,
                label="kda_fwd_bwd packed T=65536 16 docs H=6 d=128 bf16 cu_seqlens"),
+    # whole KimiDeltaAttention sublayer (projections, short conv, KDA, gated norm, o-proj), width 768;
+    # the global batch of 64 is split over the ranks (strong scaling)
+    "c4": dict(B=64, T=2048, H=6, d=128, x_mean=0.0, a_lo=1.0, a_hi=16.0, beta_mean=0.0, docs=0, sublayer=True,
+               label="kda_sublayer_fwd_bwd global B=64 T=2048 width=768 H=6 d=128 bf16"),
 }
 METRIC = "kda_fwd_bwd_throughput"
 UNIT = "Mtok/s"
@@ -148,6 +152,29 @@ def step_device(dev_in, w):
     return o, ht, leaves, h0
 
 
+def make_sublayer(w, device, seed=0):
+    """KimiDeltaAttention (k3mini/model.py:132-227) with random-init weights N(0, 0.02), A_log and
+    dt_bias as the reference initialises them, norm weight 1."""
+    from openkimi_b200 import KimiDeltaAttention
+    torch.manual_seed(seed)
+    m = KimiDeltaAttention(w["H"] * w["d"], w["H"], w["d"], conv_kernel=4, disable_recompute=True)
+    with torch.no_grad():
+        for name, prm in m.named_parameters():
+            if name.endswith("proj.weight") or "out_gate" in name or name.endswith("conv.weight"):
+                prm.normal_(0.0, 0.02)
+    return m.to(device)
+
+
+def step_sublayer(model, x, dout):
+    for prm in model.parameters():
+        prm.grad = None
+    x.grad = None
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = model(x)
+    out.backward(dout)
+    return out
+
+
 def to_device(host, device):
     dev = {k: v.to(device, non_blocking=True) for k, v in host.items() if isinstance(v, torch.Tensor)}
     if host.get("cu") is not None:
@@ -241,14 +268,27 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    host = make_workload(w, seed=rank, pin=True)
-    dev_in = to_device(host, device)
+    sub = bool(w.get("sublayer"))
+    if sub:  # strong scaling: the global batch is split over the ranks
+        w["B"] = max(1, w["B"] // world)
+        gen = torch.Generator().manual_seed(100 + rank)
+        width = w["H"] * w["d"]
+        host = {"x": torch.randn(w["B"], w["T"], width, generator=gen).bfloat16().pin_memory(),
+                "dout": torch.randn(w["B"], w["T"], width, generator=gen).bfloat16().pin_memory()}
+        model = make_sublayer(w, device)
+        dev_x = {k: v.to(device) for k, v in host.items()}
+        dev_x["x"].requires_grad_(True)
+        step_device_any = lambda: step_sublayer(model, dev_x["x"], dev_x["dout"])
+    else:
+        host = make_workload(w, seed=rank, pin=True)
+        dev_in = to_device(host, device)
+        step_device_any = lambda: step_device(dev_in, w)
     tokens = w["B"] * w["T"]
     units = None
 
     # ---- device-resident timing -------------------------------------------------------
     for _ in range(args.warmup):
-        step_device(dev_in, w)
+        step_device_any()
     barrier()
     n_calls = 2 * args.steps
     lib.kda_profile_begin(n_calls)
@@ -259,14 +299,14 @@ def main():
     # apart) cover loaded clocks even when the timed region itself lasts only tens of ms
     t_end = time.perf_counter() + 0.4
     while time.perf_counter() < t_end:
-        step_device(dev_in, w)
+        step_device_any()
         torch.cuda.synchronize()
     lib.kda_profile_begin(n_calls)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
     for _ in range(args.steps):
-        step_device(dev_in, w)
+        step_device_any()
     e1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -303,9 +343,16 @@ def main():
     pinned_out = []
 
     def e2e_step():
-        d = to_device(host, device)
-        o, ht, leaves, h0 = step_device(d, w)
-        outs = [o, ht] + [x.grad for x in leaves] + ([h0.grad] if h0 is not None else [])
+        if sub:
+            xd = host["x"].to(device, non_blocking=True).requires_grad_(True)
+            dd = host["dout"].to(device, non_blocking=True)
+            out = step_sublayer(model, xd, dd)
+            outs = [out.detach(), xd.grad]
+            d = None
+        else:
+            d = to_device(host, device)
+            o, ht, leaves, h0 = step_device(d, w)
+            outs = [o, ht] + [x.grad for x in leaves] + ([h0.grad] if h0 is not None else [])
         if not pinned_out:
             pinned_out.extend(torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs)
         for dst, src in zip(pinned_out, outs):
@@ -364,8 +411,8 @@ def main():
              "tflops": op_flops / step_s / 1e12, "flops_per_token": op_flops / tokens}
 
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": "kda_sublayer_fwd_bwd_throughput" if sub else METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if sub else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["label"], "per_gpu_tokens": tokens, "state": "fp32", "chunk": 64,
                    "l2": "inputs + per-chunk records of one step ~1 GB > 126 MB L2, no explicit flush",

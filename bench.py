@@ -61,17 +61,23 @@ def stage_model(name, d, C=64, es=2):
     t = C * d * es          # one [64, d] tile
     a = C * C * es          # one [64, 64] tile
     s = d * d * es          # one state
+    f4 = C * d * 4          # one FP32 [64, d] tile
+    a4 = C * C * 4          # one FP32 [64, 64] tile
     m = {
-        "fwd_intra": (8 * C * C * d + 2 * C ** 3 // 3, 4 * t + C * es + (4 * t + 2 * a + 4 * d)),
+        # reads q, k, v, g, beta; writes W, U, Qt, Kh, Aqk, T, gamC and the kept prologue (G, q^, k^, norms, beta)
+        "fwd_intra": (8 * C * C * d + 2 * C ** 3 // 3, (4 * t + C * es) + (4 * t + 2 * a + 4 * d) + (f4 + 2 * t + 3 * C * 4)),
+        # reads W, U, Qt, Kh, Aqk, gamC; writes V', o, the chunk-entry state
         "fwd_state": (6 * C * d * d + 2 * C * C * d, (4 * t + a + 4 * d) + (2 * t + s)),
+        # reads W, Qt, Kh, Aqk, gamC, dO; writes dV', the chunk-entry dS
         "bwd_state": (6 * C * d * d + 2 * C * C * d, (4 * t + a + 4 * d) + (t + s)),
+        # fused FP32-math backward (validation mode only)
         "bwd_chunk": (6 * C * d * d + 16 * C * C * d + 4 * C ** 3, (5 * t + C * es) + 2 * t + 2 * s + a + (4 * t + C * es)),
-        # bwd_wy: dAqk, dW, dQt, dKh (K=d), dVb, dKb, Z (K=64), dM; reads dO, v, V', dV', S0, dS, T, W; writes dv, dAqk,
-        # dM and three FP32 [64, d] products
-        "bwd_wy": (8 * C * d * d + 8 * C * C * d, (2 * t) + 3 * t + 2 * s + a + (t + 2 * a + 3 * C * d * 4)),
-        # bwd_intra: 3 pairwise products over the lower triangle (dense-tile count 6 C^2 d); reads q, k, g, beta, dAqk,
-        # dM and the three FP32 products; writes dq, dk, dg, dbeta
-        "bwd_intra": (6 * C * C * d, (3 * t + C * es) + 2 * a + 3 * C * d * 4 + (3 * t + C * es)),
+        # dAqk, dWn, dQt, dKh (K=d), dVb, dKb, Z, dMn; reads dO, v, V', dV', S0, dS, T, W; writes dv and the FP32
+        # hand-over (dAqk, dM, dQt, dKh, dKb)
+        "bwd_wy": (10 * C * d * d + 8 * C * C * d, (2 * t) + 3 * t + 2 * s + a + (t + 2 * a4 + 3 * f4)),
+        # three pairwise products over the lower triangle (dense-tile count 6 C^2 d); reads the kept prologue and
+        # the hand-over; writes dq, dk, dg, dbeta
+        "bwd_intra": (6 * C * C * d, (f4 + 2 * t + 3 * C * 4) + 2 * a4 + 3 * f4 + (3 * t + C * es)),
         "param_reduce": (0, 4 * d + 4),
     }
     return m[name]

@@ -51,98 +51,91 @@ template <> struct Vec<__nv_bfloat16> {
 constexpr int CONV_TT = 16;  // tokens per thread tile
 constexpr int CONV_KMAX = 4;
 
-// start of the document that contains flattened token t
-__device__ __forceinline__ long long doc_start(const int64_t* cu, int N, long long t, int T) {
-    if (!cu) return (t / T) * T;
+// index of the document that contains flattened token t (fixed length: t / T)
+__device__ __forceinline__ int doc_of(const int64_t* cu, int N, long long t, int T) {
+    if (!cu) return (int)(t / T);
     int lo = 0, hi = N;  // cu[lo] <= t < cu[hi]
     while (hi - lo > 1) {
         int mid = (lo + hi) >> 1;
         if (cu[mid] <= t) lo = mid; else hi = mid;
     }
-    return cu[lo];
-}
-__device__ __forceinline__ long long doc_end(const int64_t* cu, int N, long long t, int T) {
-    if (!cu) return (t / T + 1) * T;
-    int lo = 0, hi = N;
-    while (hi - lo > 1) {
-        int mid = (lo + hi) >> 1;
-        if (cu[mid] <= t) lo = mid; else hi = mid;
-    }
-    return cu[hi];
+    return lo;
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float dsilu_f(float x) {
-    float s = 1.f / (1.f + expf(-x));
+    const float s = 1.f / (1.f + __expf(-x));
     return s * (1.f + x * (1.f - s));
 }
 
-// y[t, c] = silu(sum_j w[c][j] * x[t - (K-1) + j, c]), taps before the document start are 0
+// the filter padded to four taps: tap j multiplies x[t - 3 + j]
+template <int V>
+__device__ __forceinline__ void load_taps(const float* __restrict__ w, int c0, int K, float (&wt)[CONV_KMAX][V]) {
+#pragma unroll
+    for (int j = 0; j < CONV_KMAX; ++j)
+#pragma unroll
+        for (int i = 0; i < V; ++i) wt[j][i] = (j >= CONV_KMAX - K) ? w[(c0 + i) * K + j - (CONV_KMAX - K)] : 0.f;
+}
+
+// y[t, c] = silu(sum_j w[c][j] * x[t - (K-1) + j, c]); taps before the document start are 0.
+// One thread walks CONV_TT consecutive tokens of one 16-byte channel group with a sliding
+// window held in registers, so every x element is loaded once per thread.
 template <typename T>
-__global__ void short_conv_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
-                                      long long total, int Tlen, int Cch, int K, const int64_t* cu, int N) {
+__global__ void __launch_bounds__(128) short_conv_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w,
+                                                             T* __restrict__ y, long long total, int Tlen, int Cch, int K,
+                                                             const int64_t* cu, int N) {
     constexpr int V = Vec<T>::N;
     const int cgs = Cch / V;
     const long long ntile = (total + CONV_TT - 1) / CONV_TT;
     for (long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x; item < ntile * cgs;
          item += (long long)gridDim.x * blockDim.x) {
-        const int cg = (int)(item % cgs);
+        const int c0 = (int)(item % cgs) * V;
         const long long t0 = (item / cgs) * CONV_TT;
-        const int c0 = cg * V;
-        float wt[V][CONV_KMAX];
+        float wt[CONV_KMAX][V];
+        load_taps<V>(w, c0, K, wt);
+        float x0[V], x1[V], x2[V];
+        int d0, d1, d2;  // document of each window entry (-1: outside the tensor)
+        {
+            const long long ta = t0 - 3, tb = t0 - 2, tc = t0 - 1;
 #pragma unroll
-        for (int i = 0; i < V; ++i)
-#pragma unroll
-            for (int j = 0; j < CONV_KMAX; ++j) wt[i][j] = j < K ? w[(c0 + i) * K + j] : 0.f;
-        float win[CONV_KMAX][V];  // win[j] = x[t - (K-1) + j]
-        long long ds = doc_start(cu, N, t0, Tlen), de = doc_end(cu, N, t0, Tlen);
-#pragma unroll
-        for (int j = 0; j < CONV_KMAX; ++j)
-#pragma unroll
-            for (int i = 0; i < V; ++i) win[j][i] = 0.f;
-        for (int j = 0; j < K - 1; ++j) {
-            long long ts = t0 - (K - 1) + j;
-            if (ts >= ds) Vec<T>::load(x + ts * Cch + c0, win[j]);
+            for (int i = 0; i < V; ++i) x0[i] = x1[i] = x2[i] = 0.f;
+            d0 = d1 = d2 = -1;
+            if (ta >= 0) { Vec<T>::load(x + ta * Cch + c0, x0); d0 = doc_of(cu, N, ta, Tlen); }
+            if (tb >= 0) { Vec<T>::load(x + tb * Cch + c0, x1); d1 = doc_of(cu, N, tb, Tlen); }
+            if (tc >= 0) { Vec<T>::load(x + tc * Cch + c0, x2); d2 = doc_of(cu, N, tc, Tlen); }
         }
+#pragma unroll 4
         for (int tt = 0; tt < CONV_TT; ++tt) {
-            long long t = t0 + tt;
+            const long long t = t0 + tt;
             if (t >= total) break;
-            if (t >= de) {  // entered the next document: forget the window
-                ds = de;
-                de = doc_end(cu, N, t, Tlen);
-#pragma unroll
-                for (int j = 0; j < CONV_KMAX; ++j)
-#pragma unroll
-                    for (int i = 0; i < V; ++i) win[j][i] = 0.f;
-            }
-            Vec<T>::load(x + t * Cch + c0, win[K - 1]);
-            float out[V];
+            float x3[V], out[V];
+            Vec<T>::load(x + t * Cch + c0, x3);
+            const int d3 = doc_of(cu, N, t, Tlen);
+            const float m0 = d0 == d3 ? 1.f : 0.f, m1 = d1 == d3 ? 1.f : 0.f, m2 = d2 == d3 ? 1.f : 0.f;
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-                float s = 0.f;
-#pragma unroll
-                for (int j = 0; j < CONV_KMAX; ++j)
-                    if (j < K) s = fmaf(wt[i][j], win[j][i], s);
-                out[i] = silu_f(s);
+                const float pre = wt[0][i] * (m0 * x0[i]) + wt[1][i] * (m1 * x1[i]) + wt[2][i] * (m2 * x2[i]) + wt[3][i] * x3[i];
+                out[i] = silu_f(pre);
+                x0[i] = x1[i];
+                x1[i] = x2[i];
+                x2[i] = x3[i];
             }
+            d0 = d1; d1 = d2; d2 = d3;
             Vec<T>::store(y + t * Cch + c0, out);
-#pragma unroll
-            for (int j = 0; j + 1 < CONV_KMAX; ++j)
-                if (j + 1 < K) {
-#pragma unroll
-                    for (int i = 0; i < V; ++i) win[j][i] = win[j + 1][i];
-                }
         }
     }
 }
 
-// dx[t] = sum_j w[j] dpre[t + (K-1) - j],  dw[j] = sum_t dpre[t] x[t - (K-1) + j],
-// dpre[s] = dy[s] silu'(pre[s]) with pre recomputed from x.  blockDim = (32 channel groups,
-// 8 token tiles); per-block partial dw in part[blockIdx.y][C][K].
+// dx[t] = sum_j w[j] dpre[t + 3 - j],  dw[j] = sum_t dpre[t] x[t - 3 + j],
+// dpre[s] = dy[s] silu'(pre[s]) with pre recomputed from x (four-tap padded filter).
+// One thread walks CONV_TT tokens (+3 look-ahead) of one channel group with the x and dpre
+// windows in registers.  blockDim = (32 channel groups, 8 token tiles); the block's partial
+// filter gradient goes to part[blockIdx.y][C][K].
 template <typename T>
-__global__ void short_conv_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T* __restrict__ dy,
-                                      T* __restrict__ dx, float* __restrict__ part, long long total, int Tlen, int Cch,
-                                      int K, const int64_t* cu, int N) {
+__global__ void __launch_bounds__(256) short_conv_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w,
+                                                             const T* __restrict__ dy, T* __restrict__ dx,
+                                                             float* __restrict__ part, long long total, int Tlen, int Cch,
+                                                             int K, const int64_t* cu, int N) {
     constexpr int V = Vec<T>::N;
     __shared__ float sred[8][32][V * CONV_KMAX + 1];
     const int cgs = Cch / V;
@@ -150,82 +143,81 @@ __global__ void short_conv_bwd_kernel(const T* __restrict__ x, const float* __re
     const bool active = cg < cgs;
     const int c0 = cg * V;
     const long long ntile = (total + CONV_TT - 1) / CONV_TT;
-    float wt[V][CONV_KMAX], dw[V][CONV_KMAX];
+    float wt[CONV_KMAX][V], dw[CONV_KMAX][V];
 #pragma unroll
-    for (int i = 0; i < V; ++i)
+    for (int j = 0; j < CONV_KMAX; ++j)
 #pragma unroll
-        for (int j = 0; j < CONV_KMAX; ++j) {
-            wt[i][j] = (active && j < K) ? w[(c0 + i) * K + j] : 0.f;
-            dw[i][j] = 0.f;
-        }
+        for (int i = 0; i < V; ++i) dw[j][i] = 0.f;
     if (active) {
+        load_taps<V>(w, c0, K, wt);
         for (long long tile = (long long)blockIdx.y * 8 + threadIdx.y; tile < ntile; tile += (long long)gridDim.y * 8) {
             const long long t0 = tile * CONV_TT;
-            // x window xs[i] = x[t0 - (K-1) + i], i in [0, TT + 2(K-1)); dpre for s in [t0, t0 + TT + K-1)
-            constexpr int XW = CONV_TT + 2 * (CONV_KMAX - 1);
-            constexpr int PW = CONV_TT + CONV_KMAX - 1;
-            float dpre[PW][V];
-            {
-                float xs[XW][V];
-                long long ds0 = doc_start(cu, N, t0, Tlen);
-                for (int i = 0; i < XW; ++i) {
-                    long long ts = t0 - (K - 1) + i;
+            float x0[V], x1[V], x2[V], p0[V], p1[V], p2[V];  // x[s-3..s-1], dpre[s-3..s-1]
+            int d0 = -1, d1 = -1, d2 = -1;                    // their documents (shared by x and dpre entries)
 #pragma unroll
-                    for (int u = 0; u < V; ++u) xs[i][u] = 0.f;
-                    if (ts >= ds0 && ts < total && i < CONV_TT + 2 * (K - 1)) Vec<T>::load(x + ts * Cch + c0, xs[i]);
-                }
-                for (int s = 0; s < PW; ++s) {
-                    long long ts = t0 + s;
+            for (int i = 0; i < V; ++i) x0[i] = x1[i] = x2[i] = p0[i] = p1[i] = p2[i] = 0.f;
+            if (t0 - 3 >= 0) { Vec<T>::load(x + (t0 - 3) * Cch + c0, x0); d0 = doc_of(cu, N, t0 - 3, Tlen); }
+            if (t0 - 2 >= 0) { Vec<T>::load(x + (t0 - 2) * Cch + c0, x1); d1 = doc_of(cu, N, t0 - 2, Tlen); }
+            if (t0 - 1 >= 0) { Vec<T>::load(x + (t0 - 1) * Cch + c0, x2); d2 = doc_of(cu, N, t0 - 1, Tlen); }
+            // dpre of the three tokens before t0 is not needed: dx[t] only looks ahead
+#pragma unroll 2
+            for (int ss = 0; ss < CONV_TT + 3; ++ss) {
+                const long long sidx = t0 + ss;
+                float x3[V], p3[V];
+                int d3 = -2;
 #pragma unroll
-                    for (int u = 0; u < V; ++u) dpre[s][u] = 0.f;
-                    if (ts >= total || s >= CONV_TT + K - 1) continue;
-                    long long ds = doc_start(cu, N, ts, Tlen);
-                    float g[V];
-                    Vec<T>::load(dy + ts * Cch + c0, g);
+                for (int i = 0; i < V; ++i) x3[i] = p3[i] = 0.f;
+                if (sidx < total) {
+                    float gy[V];
+                    Vec<T>::load(x + sidx * Cch + c0, x3);
+                    Vec<T>::load(dy + sidx * Cch + c0, gy);
+                    d3 = doc_of(cu, N, sidx, Tlen);
+                    const float m0 = d0 == d3 ? 1.f : 0.f, m1 = d1 == d3 ? 1.f : 0.f, m2 = d2 == d3 ? 1.f : 0.f;
+                    const bool own = ss < CONV_TT;  // this thread owns token sidx for the filter gradient
 #pragma unroll
-                    for (int u = 0; u < V; ++u) {
-                        float pre = 0.f;
-#pragma unroll
-                        for (int j = 0; j < CONV_KMAX; ++j)
-                            if (j < K && ts - (K - 1) + j >= ds) pre = fmaf(wt[u][j], xs[s + j][u], pre);
-                        dpre[s][u] = g[u] * dsilu_f(pre);
-                    }
-                    if (s < CONV_TT) {  // this thread owns token ts for the weight gradient
-#pragma unroll
-                        for (int u = 0; u < V; ++u)
-#pragma unroll
-                            for (int j = 0; j < CONV_KMAX; ++j)
-                                if (j < K && ts - (K - 1) + j >= ds) dw[u][j] = fmaf(dpre[s][u], xs[s + j][u], dw[u][j]);
+                    for (int i = 0; i < V; ++i) {
+                        const float a0 = m0 * x0[i], a1 = m1 * x1[i], a2 = m2 * x2[i];
+                        const float pre = wt[0][i] * a0 + wt[1][i] * a1 + wt[2][i] * a2 + wt[3][i] * x3[i];
+                        p3[i] = gy[i] * dsilu_f(pre);
+                        if (own) {
+                            dw[0][i] = fmaf(p3[i], a0, dw[0][i]);
+                            dw[1][i] = fmaf(p3[i], a1, dw[1][i]);
+                            dw[2][i] = fmaf(p3[i], a2, dw[2][i]);
+                            dw[3][i] = fmaf(p3[i], x3[i], dw[3][i]);
+                        }
                     }
                 }
-            }
-            for (int tt = 0; tt < CONV_TT; ++tt) {
-                long long t = t0 + tt;
-                if (t >= total) break;
-                long long de = doc_end(cu, N, t, Tlen);
-                float out[V];
+                // dx of token t = sidx - 3 (the oldest window entry), if this thread owns it
+                if (ss >= 3) {
+                    const long long t = sidx - 3;
+                    if (t < total) {
+                        const float m1 = d1 == d0 ? 1.f : 0.f, m2 = d2 == d0 ? 1.f : 0.f, m3 = d3 == d0 ? 1.f : 0.f;
+                        float out[V];
 #pragma unroll
-                for (int u = 0; u < V; ++u) {
-                    float s = 0.f;
-#pragma unroll
-                    for (int j = 0; j < CONV_KMAX; ++j)
-                        if (j < K && t + (K - 1) - j < de) s = fmaf(wt[u][j], dpre[tt + (K - 1) - j][u], s);
-                    out[u] = s;
+                        for (int i = 0; i < V; ++i)
+                            out[i] = wt[3][i] * p0[i] + wt[2][i] * (m1 * p1[i]) + wt[1][i] * (m2 * p2[i]) + wt[0][i] * (m3 * p3[i]);
+                        Vec<T>::store(dx + t * Cch + c0, out);
+                    }
                 }
-                Vec<T>::store(dx + t * Cch + c0, out);
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    x0[i] = x1[i]; x1[i] = x2[i]; x2[i] = x3[i];
+                    p0[i] = p1[i]; p1[i] = p2[i]; p2[i] = p3[i];
+                }
+                d0 = d1; d1 = d2; d2 = d3;
             }
         }
     }
 #pragma unroll
-    for (int i = 0; i < V; ++i)
+    for (int j = 0; j < CONV_KMAX; ++j)
 #pragma unroll
-        for (int j = 0; j < CONV_KMAX; ++j) sred[threadIdx.y][threadIdx.x][i * CONV_KMAX + j] = dw[i][j];
+        for (int i = 0; i < V; ++i) sred[threadIdx.y][threadIdx.x][i * CONV_KMAX + j] = dw[j][i];
     __syncthreads();
     if (threadIdx.y == 0 && active) {
         for (int i = 0; i < V; ++i)
             for (int j = 0; j < K; ++j) {
                 float s = 0.f;
-                for (int yy = 0; yy < 8; ++yy) s += sred[yy][threadIdx.x][i * CONV_KMAX + j];
+                for (int yy = 0; yy < 8; ++yy) s += sred[yy][threadIdx.x][i * CONV_KMAX + j + (CONV_KMAX - K)];
                 part[((size_t)blockIdx.y * Cch + c0 + i) * K + j] = s;
             }
     }

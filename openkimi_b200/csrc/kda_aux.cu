@@ -232,75 +232,104 @@ __global__ void partial_reduce_kernel(const float* __restrict__ part, float* __r
     out[i] = s;
 }
 
-// ---- RMSNorm(x) * w * sigmoid(gate), one warp per row -----------------------------------
+// ---- RMSNorm(x) * w * sigmoid(gate): DIM / 8 (BF16) or DIM / 4 (FP32) lanes per row, 16-byte accesses
 template <typename T, int DIM>
-__global__ void norm_gate_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gate, const float* __restrict__ w,
-                                     T* __restrict__ y, float* __restrict__ rstd, long long rows, float eps) {
-    constexpr int PER = DIM / 32;
-    const int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(256) norm_gate_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gate,
+                                                            const float* __restrict__ w, T* __restrict__ y,
+                                                            float* __restrict__ rstd, long long rows, float eps) {
+    constexpr int V = Vec<T>::N, LPR = DIM / V;  // lanes per row: 16 or 32 (8 for DIM = 64 BF16)
+    const int lane = threadIdx.x & 31, sub = lane % LPR, rsub = lane / LPR;
+    constexpr int RPW = 32 / LPR;  // rows per warp per iteration
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nw = ((long long)gridDim.x * blockDim.x) >> 5;
-    for (long long r = warp; r < rows; r += nw) {
-        float xv[PER], ss = 0.f;
+    float wv[V];
 #pragma unroll
-        for (int m = 0; m < PER; ++m) {
-            xv[m] = ldf(x + r * DIM + lane + 32 * m);
-            ss += xv[m] * xv[m];
+    for (int i = 0; i < V; ++i) wv[i] = w[sub * V + i];
+    for (long long r0 = warp * RPW; r0 < rows; r0 += nw * RPW) {
+        const long long r = r0 + rsub;
+        const bool ok = r < rows;
+        float xv[V], gv[V], out[V], ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) xv[i] = gv[i] = 0.f;
+        if (ok) {
+            Vec<T>::load(x + r * DIM + sub * V, xv);
+            Vec<T>::load(gate + r * DIM + sub * V, gv);
         }
-        ss = warp_sum(ss);
-        float rs = rsqrtf(ss / DIM + eps);
-        if (lane == 0 && rstd) rstd[r] = rs;
 #pragma unroll
-        for (int m = 0; m < PER; ++m) {
-            int d = lane + 32 * m;
-            stf(y + r * DIM + d, xv[m] * rs * w[d] * sigmoid_f(ldf(gate + r * DIM + d)));
+        for (int i = 0; i < V; ++i) ss += xv[i] * xv[i];
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float rs = rsqrtf(ss / DIM + eps);
+        if (ok) {
+            if (sub == 0 && rstd) rstd[r] = rs;
+#pragma unroll
+            for (int i = 0; i < V; ++i) out[i] = xv[i] * rs * wv[i] * sigmoid_f(gv[i]);
+            Vec<T>::store(y + r * DIM + sub * V, out);
         }
     }
 }
 
 template <typename T, int DIM>
-__global__ void norm_gate_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gate, const float* __restrict__ w,
-                                     const T* __restrict__ dy, T* __restrict__ dx, T* __restrict__ dgate,
-                                     float* __restrict__ part, long long rows, float eps) {
-    constexpr int PER = DIM / 32;
-    __shared__ float sred[8][DIM];
-    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+__global__ void __launch_bounds__(256) norm_gate_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gate,
+                                                            const float* __restrict__ w, const T* __restrict__ dy,
+                                                            T* __restrict__ dx, T* __restrict__ dgate,
+                                                            float* __restrict__ part, long long rows, float eps) {
+    constexpr int V = Vec<T>::N, LPR = DIM / V, RPW = 32 / LPR;
+    __shared__ float sred[8][RPW][DIM];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, sub = lane % LPR, rsub = lane / LPR;
     const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + wib;
     const long long nw = (long long)gridDim.x * (blockDim.x >> 5);
-    float dwv[PER];
+    float wv[V], dwv[V];
 #pragma unroll
-    for (int m = 0; m < PER; ++m) dwv[m] = 0.f;
-    for (long long r = warp; r < rows; r += nw) {
-        float xv[PER], dn[PER], ss = 0.f, dot = 0.f;
+    for (int i = 0; i < V; ++i) {
+        wv[i] = w[sub * V + i];
+        dwv[i] = 0.f;
+    }
+    for (long long r0 = warp * RPW; r0 < rows; r0 += nw * RPW) {
+        const long long r = r0 + rsub;
+        const bool ok = r < rows;
+        float xv[V], gv[V], gy[V], dn[V], ss = 0.f, dot = 0.f;
 #pragma unroll
-        for (int m = 0; m < PER; ++m) {
-            xv[m] = ldf(x + r * DIM + lane + 32 * m);
-            ss += xv[m] * xv[m];
+        for (int i = 0; i < V; ++i) xv[i] = gv[i] = gy[i] = 0.f;
+        if (ok) {
+            Vec<T>::load(x + r * DIM + sub * V, xv);
+            Vec<T>::load(gate + r * DIM + sub * V, gv);
+            Vec<T>::load(dy + r * DIM + sub * V, gy);
         }
-        ss = warp_sum(ss);
-        float rs = rsqrtf(ss / DIM + eps);
 #pragma unroll
-        for (int m = 0; m < PER; ++m) {
-            int d = lane + 32 * m;
-            float s = sigmoid_f(ldf(gate + r * DIM + d));
-            float g = ldf(dy + r * DIM + d);
-            float xh = xv[m] * rs;
-            stf(dgate + r * DIM + d, g * xh * w[d] * s * (1.f - s));
-            dn[m] = g * s;
-            dwv[m] += dn[m] * xh;
-            dn[m] *= w[d];
-            dot += dn[m] * xh;
+        for (int i = 0; i < V; ++i) ss += xv[i] * xv[i];
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float rs = rsqrtf(ss / DIM + eps);
+        float dg[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const float sgm = sigmoid_f(gv[i]);
+            const float xh = xv[i] * rs;
+            dg[i] = gy[i] * xh * wv[i] * sgm * (1.f - sgm);
+            dn[i] = gy[i] * sgm;
+            dwv[i] += dn[i] * xh;
+            dn[i] *= wv[i];
+            dot += dn[i] * xh;
         }
-        dot = warp_sum(dot) / DIM;
 #pragma unroll
-        for (int m = 0; m < PER; ++m) stf(dx + r * DIM + lane + 32 * m, rs * (dn[m] - xv[m] * rs * dot));
+        for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        dot /= DIM;
+        if (ok) {
+            float out[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) out[i] = rs * (dn[i] - xv[i] * rs * dot);
+            Vec<T>::store(dx + r * DIM + sub * V, out);
+            Vec<T>::store(dgate + r * DIM + sub * V, dg);
+        }
     }
 #pragma unroll
-    for (int m = 0; m < PER; ++m) sred[wib][lane + 32 * m] = dwv[m];
+    for (int i = 0; i < V; ++i) sred[wib][rsub][sub * V + i] = dwv[i];
     __syncthreads();
     for (int d = threadIdx.x; d < DIM; d += blockDim.x) {
         float s = 0.f;
-        for (int ww = 0; ww < (int)(blockDim.x >> 5); ++ww) s += sred[ww][d];
+        for (int ww = 0; ww < (int)(blockDim.x >> 5); ++ww)
+            for (int rr = 0; rr < RPW; ++rr) s += sred[ww][rr][d];
         part[(size_t)blockIdx.x * DIM + d] = s;
     }
 }
@@ -362,7 +391,7 @@ int kda_norm_gate_fwd(const void* x, const void* gate, const float* weight, void
     if (rows <= 0 || (dim != 64 && dim != 128)) return KDA_ERR_SHAPE;
     if (dtype != KDA_DTYPE_BF16 && dtype != KDA_DTYPE_F32) return KDA_ERR_DTYPE;
     cudaStream_t s = (cudaStream_t)stream;
-    int grid = (int)((rows + 7) / 8 < 148 * 16 ? (rows + 7) / 8 : 148 * 16);
+    int grid = (int)((rows + 15) / 16 < 148 * 8 ? (rows + 15) / 16 : 148 * 8);
 #define NG_FWD(TT, DD) \
     norm_gate_fwd_kernel<TT, DD><<<grid, 256, 0, s>>>((const TT*)x, (const TT*)gate, weight, (TT*)y, rstd, rows, eps)
     if (dtype == KDA_DTYPE_BF16) { if (dim == 64) NG_FWD(__nv_bfloat16, 64); else NG_FWD(__nv_bfloat16, 128); }

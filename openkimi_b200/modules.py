@@ -103,7 +103,7 @@ class _NormGateFn(torch.autograd.Function):
         dy = dy.contiguous()
         dim = x.shape[-1]
         rows = x.numel() // dim
-        n_partial = 296
+        n_partial = 592
         dx, dgate = torch.empty_like(x), torch.empty_like(gate)
         dw = torch.empty(dim, dtype=torch.float32, device=x.device)
         part = torch.empty(n_partial, dim, dtype=torch.float32, device=x.device)

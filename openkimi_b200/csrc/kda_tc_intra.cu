@@ -38,12 +38,13 @@ constexpr uint32_t TOTAL = STOT + 512;
 constexpr uint32_t T_D = 0, T_W = 96, T_U = 160, TMEM_COLS = 256;
 }  // namespace fi
 
-// One block column of T = (I + diag(beta) L)^-1 (see stage 3 of the kernel).  sL holds L
+// One block column J of T = (I + diag(beta) L)^-1 (see stage 3 of the kernel).  sL holds L
 // (strictly lower, row stride 65), sT receives T; sT must be zero above the diagonal blocks.
-template <int J>
-__device__ __forceinline__ void solve_block_column(const float* sL, float* sT, const float* sbeta, int warp, int lane) {
+// J is uniform over the warp; the loops run over all blocks with warp-uniform skips so that the
+// register arrays keep compile-time indices in a single copy of the code.
+__device__ __forceinline__ void solve_block_column(const float* sL, float* sT, const float* sbeta, int J, int warp, int lane) {
     const int col = 8 * (warp >> 2) + (lane & 7), rq = lane >> 3, gc = 16 * J + col;
-    float t[4 - J][16];
+    float t[4][16];
     // diagonal block: forward substitution down the column (every lane group does all 16 rows)
 #pragma unroll
     for (int r = 0; r < 16; ++r) {
@@ -61,8 +62,11 @@ __device__ __forceinline__ void solve_block_column(const float* sL, float* sT, c
         for (int r = 0; r < 16; ++r) sT[(16 * J + r) * 65 + gc] = t[0][r];
     }
     __syncthreads();  // every diagonal block of T is in shared memory
+    // t[n] is the column restricted to block J + n
 #pragma unroll
-    for (int I = J + 1; I < 4; ++I) {
+    for (int n = 1; n < 4; ++n) {
+        const int I = J + n;
+        if (I > 3) break;
         // y = sum_K (beta L)_IK t_K for my four rows, then all 16 entries from the lane groups
         float y4[4], y[16];
 #pragma unroll
@@ -70,9 +74,9 @@ __device__ __forceinline__ void solve_block_column(const float* sL, float* sT, c
             const int r = 16 * I + 4 * rq + q;
             float s = 0.f;
 #pragma unroll
-            for (int K = J; K < I; ++K)
+            for (int kn = 0; kn < n; ++kn)
 #pragma unroll
-                for (int m = 0; m < 16; ++m) s = fmaf(sL[r * 65 + 16 * K + m], t[K - J][m], s);
+                for (int m = 0; m < 16; ++m) s = fmaf(sL[r * 65 + 16 * (J + kn) + m], t[kn][m], s);
             y4[q] = sbeta[r] * s;
         }
 #pragma unroll
@@ -93,7 +97,7 @@ __device__ __forceinline__ void solve_block_column(const float* sL, float* sT, c
 #pragma unroll
         for (int g4 = 0; g4 < 4; ++g4)
 #pragma unroll
-            for (int q = 0; q < 4; ++q) t[I - J][4 * g4 + q] = __shfl_sync(0xffffffffu, n4[q], (lane & 7) + 8 * g4);
+            for (int q = 0; q < 4; ++q) t[n][4 * g4 + q] = __shfl_sync(0xffffffffu, n4[q], (lane & 7) + 8 * g4);
     }
 }
 
@@ -387,12 +391,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     //      column c of the blocks above it, so one lane carries a whole column in registers:
     //      warp w owns block column J = w % 4, columns 8 (w / 4) + lane % 8, and its four lane
     //      groups (lane / 8) split the 16 rows of every block below the diagonal.
-    switch (warp & 3) {
-        case 0: solve_block_column<0>(sL, sT, sbeta, warp, lane); break;
-        case 1: solve_block_column<1>(sL, sT, sbeta, warp, lane); break;
-        case 2: solve_block_column<2>(sL, sT, sbeta, warp, lane); break;
-        default: solve_block_column<3>(sL, sT, sbeta, warp, lane); break;
-    }
+    solve_block_column(sL, sT, sbeta, warp & 3, warp, lane);
     __syncthreads();
 
     KDA_PHASE(6);

@@ -34,7 +34,7 @@ constexpr uint32_t PF = STG + 24576;         // prefetch f32 [3][16][128]: dQt, 
 constexpr uint32_t SBETA = PF + 24576;       // f32 [64] 1/|q|, [64] 1/|k|, [64] beta, [64] dbeta
 constexpr uint32_t SX = SBETA + 1024;        // f32 [2][2][128] block totals of dG, f32 [2][128] scratch
 constexpr uint32_t SRED = SX + 3072;         // f32 [8]
-constexpr uint32_t TOTAL = SRED + 64;
+constexpr uint32_t TOTAL = SRED + 64 + 256;
 }  // namespace bi
 
 __device__ __forceinline__ void cpa16(void* dst_smem, const void* src) {
@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     float* stotal = reinterpret_cast<float*>(dyn + SX);  // [parity][gp][d]
     float* sscr = stotal + 512;                          // [gp][d]
     float* sred = reinterpret_cast<float*>(dyn + SRED);
+    float* sdiag = sred + 8;  // f32 [64]: diagonal of dAqk (cleared in sdA so that the pair loops need no mask)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid & 127, gp = tid >> 7;
     const int c = blockIdx.x / p.H, h = blockIdx.x % p.H;
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     unsigned guard_mask = 0;
     {
         const float thr = p.guard_span;
-#pragma unroll
+#pragma unroll 1
         for (int I = 0; I < 4; ++I) {
             float gmax = -INFINITY, gmin = INFINITY, prev = INFINITY;
             bool good = true;
@@ -154,6 +155,11 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (tid < C) {
+        sdiag[tid] = sdA[tid * C + tid];
+        sdA[tid * C + tid] = 0.f;
+    }
     __syncthreads();
     float carry = ((const float*)(sc + L.gC))[rec * D + d] + sscr[d] + sscr[128 + d];
     float dA_acc = 0.f, dbias_acc = 0.f;
@@ -253,29 +259,42 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                     kb[r] *= P;
                 }
 #pragma unroll
-                for (int i = 0; i < HB; ++i) {
-                    const int li = h0 + i, ii = B * I + li;
+                for (int i = 0; i < HB; ++i) {  // dA, dM vanish for j >= i (the diagonal of dA was moved to sdiag)
+                    const int ii = B * I + h0 + i;
                     float u1 = 0.f, u2 = 0.f;
 #pragma unroll
-                    for (int j = 0; j < B - 1; ++j) {
-                        const bool on = j < li;
-                        u1 = fmaf(on ? sdA[ii * C + B * I + j] : 0.f, kj[j], u1);
-                        u2 = fmaf(on ? sdM[ii * C + B * I + j] : 0.f, kj[j], u2);
+                    for (int j4 = 0; j4 < B; j4 += 4) {
+                        const float4 a = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + j4);
+                        const float4 m = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + j4);
+                        u1 = fmaf(a.x, kj[j4], fmaf(a.y, kj[j4 + 1], fmaf(a.z, kj[j4 + 2], fmaf(a.w, kj[j4 + 3], u1))));
+                        u2 = fmaf(m.x, kj[j4], fmaf(m.y, kj[j4 + 1], fmaf(m.z, kj[j4 + 2], fmaf(m.w, kj[j4 + 3], u2))));
                     }
                     const float Pi = exp2f(Gm[i] - mid);
                     a1[i] = fmaf(Pi, u1, a1[i]);
                     a2[i] = fmaf(Pi, u2, a2[i]);
                 }
+                {  // column side: dA, dM vanish for i <= j
+                    float u[HB];
 #pragma unroll
-                for (int j = 0; j < HB; ++j) {
-                    const int lj = h0 + j, jj = B * I + lj;
-                    float u = 0.f;
+                    for (int j = 0; j < HB; ++j) u[j] = 0.f;
 #pragma unroll
                     for (int i = 1; i < B; ++i) {
-                        const bool on = i > lj;
-                        u = fmaf(on ? sdA[(B * I + i) * C + jj] : 0.f, qs[i], fmaf(on ? sdM[(B * I + i) * C + jj] : 0.f, kb[i], u));
+                        const int ii = B * I + i;
+                        const float4 a0 = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + h0);
+                        const float4 a4 = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + h0 + 4);
+                        const float4 m0 = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + h0);
+                        const float4 m4 = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + h0 + 4);
+                        u[0] = fmaf(a0.x, qs[i], fmaf(m0.x, kb[i], u[0]));
+                        u[1] = fmaf(a0.y, qs[i], fmaf(m0.y, kb[i], u[1]));
+                        u[2] = fmaf(a0.z, qs[i], fmaf(m0.z, kb[i], u[2]));
+                        u[3] = fmaf(a0.w, qs[i], fmaf(m0.w, kb[i], u[3]));
+                        u[4] = fmaf(a4.x, qs[i], fmaf(m4.x, kb[i], u[4]));
+                        u[5] = fmaf(a4.y, qs[i], fmaf(m4.y, kb[i], u[5]));
+                        u[6] = fmaf(a4.z, qs[i], fmaf(m4.z, kb[i], u[6]));
+                        u[7] = fmaf(a4.w, qs[i], fmaf(m4.w, kb[i], u[7]));
                     }
-                    c1[j] = fmaf(exp2f(mid - Gm[j]), u, c1[j]);
+#pragma unroll
+                    for (int j = 0; j < HB; ++j) c1[j] = fmaf(exp2f(mid - Gm[j]), u[j], c1[j]);
                 }
             } else {  // one exp2 per pair
 #pragma unroll
@@ -318,7 +337,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 const float bi_ = sbeta[ii];
                 const float gam = exp2f(Gm[i]), eta = exp2f(gl - Gm[i]);
                 const float dQt = spf[(0 * B + li) * D + d], dKh = spf[(1 * B + li) * D + d], dKb = spf[(2 * B + li) * D + d];
-                const float diag = scale * sdA[ii * C + ii];
+                const float diag = scale * sdiag[ii];
                 const float dq_in = scale * a1[i], dk_row = bi_ * a2[i], dKt = bi_ * dKb;
                 stg[(0 * B + li) * D + d] = dq_in + diag * ki + scale * dQt * gam;
                 stg[(1 * B + li) * D + d] = dk_row + c1[i] + diag * qi + dKt * gam + dKh * eta;

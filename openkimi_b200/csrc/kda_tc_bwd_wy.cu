@@ -22,7 +22,7 @@ namespace kda {
 using namespace tc;
 
 namespace bw {
-constexpr int D = 128, NTHR = 128;
+constexpr int D = 128, NTHR = 256;
 constexpr uint32_t VT = 0;                  // V'^T  cm(e, i; 64)
 constexpr uint32_t DVT = VT + 16384;        // dV'^T cm(e, i; 64);   later Z^T  cm(d, i; 64)
 constexpr uint32_t S0T = DVT + 16384;       // S0^T  cm(e, d; 128)
@@ -33,8 +33,8 @@ constexpr uint32_t TMA_BYTES = WT + 16384;  // everything above arrives by bulk 
 constexpr uint32_t DOT = TMA_BYTES;         // dO    cm(i, e; 128);  later dVb^T cm(e, i; 64)
 constexpr uint32_t STG = DOT + 16384;       // f32 [64][128] staging for the beta row sums
 constexpr uint32_t SV = STG + 32768;        // v bf16 [64][128] row-major (prefetched with cp.async)
-constexpr uint32_t SBETA = SV + 16384;      // f32 [64] beta, f32 [64] row sums
-constexpr uint32_t TOTAL = SBETA + 512;
+constexpr uint32_t SBETA = SV + 16384;      // f32 [64] beta, f32 [64] row sums, f32 [2][128] partial dGamma_C
+constexpr uint32_t TOTAL = SBETA + 512 + 1024;
 constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bw
 
@@ -76,7 +76,9 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem0 = tmem_s;
-    const uint32_t tmem = tmem0 + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tmem = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's lane quadrant
+    const int ch = tid & 127, half = tid >> 7;                            // channel (TMEM lane) and column half
+    float* spart = srow + 64;
 
     if (tid == 0) {
         mbar_expect_tx(&full, TMA_BYTES);
@@ -144,7 +146,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         __nv_bfloat16* sdvb = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
         const __nv_bfloat16* sv = reinterpret_cast<const __nv_bfloat16*>(dyn + SV);
 #pragma unroll 1
-        for (int i0 = 0; i0 < C; i0 += 16) {
+        for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
             uint32_t r[16], pk[8];
             tmem_ld16(tmem + DWN + i0, r);
             tmem_wait_ld();
@@ -154,32 +156,32 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             tmem_ld16(tmem + DQT + i0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) gdQt[(i0 + j) * D + tid] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) gdQt[(i0 + j) * D + ch] = __uint_as_float(r[j]);
             tmem_ld16(tmem + DKH + i0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) gdKh[(i0 + j) * D + tid] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) gdKh[(i0 + j) * D + ch] = __uint_as_float(r[j]);
             tmem_ld16(tmem + DVB + i0, r);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-            *reinterpret_cast<uint4*>(sdvb + cm_idx(tid, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            *reinterpret_cast<uint4*>(sdvb + cm_idx(tid, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            *reinterpret_cast<uint4*>(sdvb + cm_idx(ch, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(sdvb + cm_idx(ch, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const int i = i0 + j;
                 const float x = __uint_as_float(r[j]);
-                const float vv = __bfloat162float(sv[i * D + tid]);  // zero on padding rows
-                if (i < ci.len) dv[tok(i) * D + tid] = __float2bfloat16_rn(sbeta[i] * x);
-                stg[i * D + tid] = x * vv;
+                const float vv = __bfloat162float(sv[i * D + ch]);  // zero on padding rows
+                if (i < ci.len) dv[tok(i) * D + ch] = __float2bfloat16_rn(sbeta[i] * x);
+                stg[i * D + ch] = x * vv;
             }
         }
         // dAqk: rows of the M = 64 accumulator sit in lanes 0..15 of every warp's quadrant
         {
             float* gdA = (float*)(sc + L.dAqk) + rec * C * C;
-            const int i = 16 * warp + (lane & 15);
+            const int i = 16 * (warp & 3) + (lane & 15);
 #pragma unroll 1
-            for (int j0 = 0; j0 < C; j0 += 16) {
+            for (int j0 = 32 * half; j0 < 32 * half + 32; j0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(tmem + DAQK + j0, r);
                 tmem_wait_ld();
@@ -217,21 +219,41 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     // meanwhile: beta row sums and dGamma_C * Gamma_C on the CUDA cores
     {
         const int hw = tid >> 4, c8 = (tid & 15) * 8;
-        for (int m = 0; m < 8; ++m) {
-            const int i = hw + 8 * m;
+        for (int m = 0; m < 4; ++m) {
+            const int i = hw + 16 * m;
             float s = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) s += stg[i * D + c8 + j];
             s = half_warp_sum(s);
             if ((tid & 15) == 0) srow[i] = s;
         }
+        // dGamma_C[d] = sum_e dS[d][e] S0[d][e].  Both records are cm(e, d; 128): a warp reads, for one
+        // octet of e, 8 rows x 4 channel groups = four contiguous 128-byte core matrices per load.
         const __nv_bfloat16* s0 = reinterpret_cast<const __nv_bfloat16*>(dyn + S0T);
         const __nv_bfloat16* ds = reinterpret_cast<const __nv_bfloat16*>(dyn + DST);
-        float acc = 0.f;
-#pragma unroll 8
-        for (int e = 0; e < D; ++e)
-            acc = fmaf(__bfloat162float(ds[cm_idx(e, tid, D)]), __bfloat162float(s0[cm_idx(e, tid, D)]), acc);
-        ((float*)(sc + L.gC))[rec * D + tid] = acc * ((const float*)(ws + L.gamC))[rec * D + tid];
+        const int e7 = lane & 7, d8 = 8 * (4 * (warp & 3) + (lane >> 3)), eh = warp >> 2;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 2
+        for (int eo = 0; eo < 8; ++eo) {
+            const int e = 8 * (8 * eh + eo) + e7;
+            float a[8], b[8];
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(ds + cm_idx(e, d8, D)), a);
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(s0 + cm_idx(e, d8, D)), b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = fmaf(a[j], b[j], acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 1);
+            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 2);
+            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 4);
+        }
+        if (e7 == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) spart[128 * eh + d8 + j] = acc[j];
+        }
     }
     KDA_PHASE(4);
     ok = mbar_wait(&mmabar, 1, p.status, 32) && ok;
@@ -239,24 +261,25 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     __syncthreads();
     KDA_PHASE(5);
     if (tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
+    if (tid < D) ((float*)(sc + L.gC))[rec * D + tid] = (spart[tid] + spart[128 + tid]) * ((const float*)(ws + L.gamC))[rec * D + tid];
 
     // ---- conversions after S2
     {
         float* gdKb = (float*)(sc + L.dKb) + rec * C * D;
         __nv_bfloat16* sz = reinterpret_cast<__nv_bfloat16*>(dyn + DVT);
 #pragma unroll 1
-        for (int i0 = 0; i0 < C; i0 += 16) {
+        for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
             uint32_t r[16];
             tmem_ld16(tmem + DKB + i0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) gdKb[(i0 + j) * D + tid] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) gdKb[(i0 + j) * D + ch] = __uint_as_float(r[j]);
             tmem_ld16(tmem + DWN + i0, r);
             tmem_wait_ld();
-            *reinterpret_cast<uint4*>(sz + cm_idx(tid, i0, C)) =
+            *reinterpret_cast<uint4*>(sz + cm_idx(ch, i0, C)) =
                 make_uint4(pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1])), pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3])),
                            pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5])), pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7])));
-            *reinterpret_cast<uint4*>(sz + cm_idx(tid, i0 + 8, C)) =
+            *reinterpret_cast<uint4*>(sz + cm_idx(ch, i0 + 8, C)) =
                 make_uint4(pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9])), pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11])),
                            pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13])), pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15])));
         }
@@ -283,9 +306,9 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     KDA_PHASE(7);
     {
         float* gdM = (float*)(sc + L.dM) + rec * C * C;
-        const int i = 16 * warp + (lane & 15);
+        const int i = 16 * (warp & 3) + (lane & 15);
 #pragma unroll 1
-        for (int j0 = 0; j0 < C; j0 += 16) {
+        for (int j0 = 32 * half; j0 < 32 * half + 32; j0 += 16) {
             uint32_t r[16];
             tmem_ld16(tmem + DMN + j0, r);
             tmem_wait_ld();

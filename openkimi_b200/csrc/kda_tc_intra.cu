@@ -257,18 +257,21 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         tma_store_commit();
     }
 
-    // ---- 1: decay-scaled operands
+    // ---- 1: decay-scaled operands.  A warp takes 8 rows x 4 channel groups at a time, so that its
+    //      16-byte stores into the core-matrix tiles cover four whole 128-byte core matrices
+    //      (no bank conflicts; the row-major loads of q^, k^, G take the conflicts instead, and
+    //      there are five times fewer of them)
     {
-        float gl[8];
-        {
-            const float4 a = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8);
-            const float4 b = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8 + 4);
-            gl[0] = a.x; gl[1] = a.y; gl[2] = a.z; gl[3] = a.w; gl[4] = b.x; gl[5] = b.y; gl[6] = b.z; gl[7] = b.w;
-        }
 #pragma unroll 1
-        for (int m = 0; m < 4; ++m) {
-            const int i = hw + 16 * m;  // block index of this row == m
-            float G8[8], qf[8], kf[8], o8[8];
+        for (int it = 0; it < 4; ++it) {
+            const int combo = 4 * warp + it;
+            const int i = 8 * (combo >> 2) + (lane & 7), c8 = 8 * (4 * (combo & 3) + (lane >> 3)), m = i >> 4;
+            float G8[8], qf[8], kf[8], o8[8], gl[8];
+            {
+                const float4 a = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8);
+                const float4 b = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8 + 4);
+                gl[0] = a.x; gl[1] = a.y; gl[2] = a.z; gl[3] = a.w; gl[4] = b.x; gl[5] = b.y; gl[6] = b.z; gl[7] = b.w;
+            }
             {
                 const float4 a = *reinterpret_cast<const float4*>(sG + i * D + c8);
                 const float4 b = *reinterpret_cast<const float4*>(sG + i * D + c8 + 4);

@@ -142,6 +142,16 @@ int kda_norm_gate_bwd(const void *x, const void *gate, const float *weight, cons
                       void *dgate, float *dweight, float *partial, int32_t n_partial, int64_t rows,
                       int32_t dim, float eps, int32_t dtype, void *cuda_stream);
 
+/* The guarded diagonal tile with the interface of the reference's device-independent contract
+ * (experiments/kda_sm90/guarded_diagonal_oracle.py:110-180, reference_policy="midpoint"):
+ * float tensors gate, q, k [n_tiles,16,32], beta [n_tiles,16], dAqk, dAkk [n_tiles,16,16] ->
+ * dq, dk, dkt [n_tiles,16,32] and hits [n_tiles] (1 = midpoint factorisation used).  Same
+ * guard and evaluation rules as the intra-chunk backward; a negative span rejects every tile.
+ * The oracle accepts spans in (0, 252); this entry also accepts negative values. */
+int kda_guarded_diagonal_tiles(const float *gate, const float *q, const float *k, const float *beta,
+                               const float *dAqk, const float *dAkk, float *dq, float *dk, float *dkt,
+                               int *hits, int n_tiles, float max_log2_span, void *cuda_stream);
+
 /* Guarded-diagonal contract of the reference's backend check (k3mini/backends.py:17-19,
  * 68-109): version 1, "tf32x3"-class precision, span <= 232. */
 int kda_guard_version(void);

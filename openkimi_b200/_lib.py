@@ -46,6 +46,7 @@ EXPORTS = {
     "kda_last_cuda_error": (C.c_char_p, []),
     "kda_profile_begin": (C.c_int, [C.c_int]),
     "kda_profile_read": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float), C.c_int]),
+    "kda_guarded_diagonal_tiles": (C.c_int, [C.c_void_p] * 10 + [C.c_int, C.c_float, C.c_void_p]),
     "kda_selftest_mma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 12 + [C.c_void_p, C.c_void_p]),
     "kda_workspace_bytes": (C.c_int, [C.POINTER(KdaParams), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "kda_fwd": (C.c_int, [C.POINTER(KdaParams), C.c_void_p]),

@@ -133,26 +133,12 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 
     // ---- guard of the four diagonal tiles (one tile = 16 rows x this warp's 32 channels)
     unsigned guard_mask = 0;
-    {
-        const float thr = p.guard_span;
 #pragma unroll 1
-        for (int I = 0; I < 4; ++I) {
-            float gmax = -INFINITY, gmin = INFINITY, prev = INFINITY;
-            bool good = true;
+    for (int I = 0; I < 4; ++I) {
+        float Gt[B], mid_unused;
 #pragma unroll
-            for (int r = 0; r < B; ++r) {
-                const float xx = sG[(B * I + r) * D + d];
-                good = good && (xx <= prev) && isfinite(xx);
-                prev = xx;
-                gmax = fmaxf(gmax, xx);
-                gmin = fminf(gmin, xx);
-            }
-            float span = gmax - gmin;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) span = fmaxf(span, __shfl_xor_sync(0xffffffffu, span, o));
-            const bool pass = __all_sync(0xffffffffu, good) && isfinite(span) && span <= thr;
-            if (pass) guard_mask |= 1u << I;
-        }
+        for (int r = 0; r < B; ++r) Gt[r] = sG[(B * I + r) * D + d];
+        if (guard_tile(Gt, p.guard_span, mid_unused)) guard_mask |= 1u << I;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
@@ -435,6 +421,85 @@ cudaError_t launch_bwd_intra(const KdaParams& p, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Stand-alone form of the guarded diagonal tile with the reference's own interface
+// (experiments/kda_sm90/guarded_diagonal_oracle.py:57-180): gate, q, k [N,16,32], beta [N,16],
+// dAqk, dAkk [N,16,16] -> dq, dk, dkt [N,16,32], hits [N].  One warp per tile, one lane per
+// channel; same guard (guard_tile) and the same two evaluation rules as kda_bwd_intra.
+//   dq[i]  = sum_{j<=i} dAqk[i][j] k[j] 2^(g_i-g_j)       dk[i] = sum_{j<=i} dAkk[i][j] k[j] 2^(g_i-g_j)
+//   dkt[i] = sum_{j>=i} (dAqk[i][j] q[j] + dAkk[i][j] beta[j] k[j]) 2^(g_j-g_i)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32) kda_diag_tile_kernel(const float* __restrict__ gate, const float* __restrict__ q,
+                                                           const float* __restrict__ k, const float* __restrict__ beta,
+                                                           const float* __restrict__ dAqk, const float* __restrict__ dAkk,
+                                                           float* __restrict__ dq, float* __restrict__ dk,
+                                                           float* __restrict__ dkt, int* __restrict__ hits, float limit) {
+    const int n = blockIdx.x, ch = threadIdx.x;
+    float G[16], Q[16], K[16], Bt[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        G[r] = gate[(n * 16 + r) * 32 + ch];
+        Q[r] = q[(n * 16 + r) * 32 + ch];
+        K[r] = k[(n * 16 + r) * 32 + ch];
+        Bt[r] = beta[n * 16 + r];
+    }
+    float mid;
+    const bool pass = guard_tile(G, limit, mid);
+    if (ch == 0) hits[n] = pass ? 1 : 0;
+    const float* A = dAqk + n * 256;
+    const float* M = dAkk + n * 256;
+    float P[16], N[16];
+    if (pass) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            P[r] = exp2f(G[r] - mid);
+            N[r] = exp2f(mid - G[r]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float sq = 0.f, sk = 0.f, st = 0.f;
+        if (pass) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (j <= i) {
+                    sq = fmaf(A[i * 16 + j], K[j] * N[j], sq);
+                    sk = fmaf(M[i * 16 + j], K[j] * N[j], sk);
+                }
+                if (j >= i) st = fmaf(A[i * 16 + j], Q[j] * P[j], fmaf(M[i * 16 + j], Bt[j] * K[j] * P[j], st));
+            }
+            sq *= P[i];
+            sk *= P[i];
+            st *= N[i];
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (j <= i) {
+                    const float kp = K[j] * exp2f(G[i] - G[j]);
+                    sq = fmaf(A[i * 16 + j], kp, sq);
+                    sk = fmaf(M[i * 16 + j], kp, sk);
+                }
+                if (j >= i) st = fmaf(A[i * 16 + j] * Q[j] + M[i * 16 + j] * (Bt[j] * K[j]), exp2f(G[j] - G[i]), st);
+            }
+        }
+        dq[(n * 16 + i) * 32 + ch] = sq;
+        dk[(n * 16 + i) * 32 + ch] = sk;
+        dkt[(n * 16 + i) * 32 + ch] = st;
+    }
+}
+
 }  // namespace kda
+
+extern "C" int kda_guarded_diagonal_tiles(const float* gate, const float* q, const float* k, const float* beta,
+                                          const float* dAqk, const float* dAkk, float* dq, float* dk, float* dkt, int* hits,
+                                          int n_tiles, float max_log2_span, void* stream) {
+    if (!gate || !q || !k || !beta || !dAqk || !dAkk || !dq || !dk || !dkt || !hits) return KDA_ERR_NULL;
+    if (n_tiles <= 0) return KDA_ERR_SHAPE;
+    if (!(max_log2_span < 0.f) && !(isfinite(max_log2_span) && max_log2_span < 252.f)) return KDA_ERR_GUARD;
+    kda::kda_diag_tile_kernel<<<n_tiles, 32, 0, (cudaStream_t)stream>>>(gate, q, k, beta, dAqk, dAkk, dq, dk, dkt, hits,
+                                                                       max_log2_span);
+    return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
 
 KDA_PHASE_EXPORT(kda_debug_phases_bwd_intra)

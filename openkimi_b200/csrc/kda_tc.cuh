@@ -220,6 +220,29 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float (&f)[8]) {
 __device__ __forceinline__ uint4 f32_to_bf16x8(const float (&f)[8]) {
     return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
 }
+// Span guard of one [16 rows x 32 channels] tile of the cumulative log2 gate, evaluated by the
+// warp whose lanes hold the 32 channels (experiments/kda_sm90/patch_fla_guarded_intra.py:35-63;
+// oracle: experiments/kda_sm90/guarded_diagonal_oracle.py:131-141): every channel monotone
+// non-increasing and finite, and the largest per-channel (max - min) <= limit.  A negative
+// limit rejects every tile.  Returns the decision (uniform over the warp) and this lane's
+// midpoint (max + min) / 2.
+__device__ __forceinline__ bool guard_tile(const float (&G)[16], float limit, float& mid) {
+    float gmax = -INFINITY, gmin = INFINITY, prev = INFINITY;
+    bool good = true;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        good = good && (G[r] <= prev) && isfinite(G[r]);
+        prev = G[r];
+        gmax = fmaxf(gmax, G[r]);
+        gmin = fminf(gmin, G[r]);
+    }
+    mid = 0.5f * (gmax + gmin);
+    float span = gmax - gmin;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) span = fmaxf(span, __shfl_xor_sync(0xffffffffu, span, o));
+    return __all_sync(0xffffffffu, good) && isfinite(span) && span <= limit;
+}
+
 // sum over the 16 lanes of a half warp
 __device__ __forceinline__ float half_warp_sum(float v) {
 #pragma unroll

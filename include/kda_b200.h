@@ -51,7 +51,8 @@ enum {
     KDA_ERR_LAUNCH = 6,      /* the CUDA runtime refused a launch (see kda_last_cuda_error) */
     KDA_ERR_DEVICE_WAIT = 7, /* a bounded device-side wait gave up (read from the status word) */
     KDA_ERR_GUARD = 8,       /* guard span is not a finite value <= 232 (or negative = exact) */
-    KDA_ERR_STATIC_LIMIT = 9 /* size beyond the built-in scratch of an allocation-free entry point */
+    KDA_ERR_STATIC_LIMIT = 9, /* size beyond the built-in scratch of an allocation-free entry point */
+    KDA_ERR_UNSUPPORTED = 10 /* the fused short convolution needs the BF16, d = 128 tensor-core path */
 };
 
 /* One call's description.  Replaces the keyword arguments of chunk_kda
@@ -88,6 +89,16 @@ typedef struct KdaParams {
     size_t bwd_scratch_bytes;
     int32_t *status;            /* device word, zero-initialised by the caller; a kernel whose
                                    bounded wait gives up ORs a non-zero code into it */
+    /* Optional: the three causal depthwise short convolutions + SiLU in front of the op
+     * (k3mini/model.py:181-185, conv1d of k3mini/model.py:76-88) fused into the load stage.
+     * When conv_q is non-NULL, q, k, v above are the PRE-convolution projections; the taps are
+     * FP32 [H*dk][conv_ksize] (channel = head * dk + d; tap j multiplies x[t - (ksize-1) + j]),
+     * the window restarts at every sequence start, and the convolved rows are rounded to the
+     * element type exactly as the stand-alone kda_short_conv_fwd does.  grad_q, grad_k, grad_v
+     * are then gradients of the CONVOLVED rows; feed them to kda_short_conv_bwd.  All three or
+     * none; BF16 with dk = 128 only (else KDA_ERR_UNSUPPORTED). */
+    const float *conv_q, *conv_k, *conv_v;
+    int32_t conv_ksize;         /* 1..4 */
 } KdaParams;
 
 /* Bytes of forward workspace (saved for the backward) and of backward scratch for these

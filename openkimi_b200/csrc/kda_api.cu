@@ -63,7 +63,14 @@ static int validate(const KdaParams* p, bool bwd) {
     for (const void* x : ptrs)
         if (!aligned16(x)) return KDA_ERR_ALIGN;
     WsLayout L = ws_layout(p->NT, p->H, p->dk, p->dv, p->dtype);
-    if (p->workspace_bytes < L.total || ((uintptr_t)p->workspace & 255)) return KDA_ERR_WORKSPACE;
+    const bool conv = p->conv_q || p->conv_k || p->conv_v;
+    if (conv) {
+        if (!p->conv_q || !p->conv_k || !p->conv_v) return KDA_ERR_NULL;
+        if (p->conv_ksize < 1 || p->conv_ksize > 4) return KDA_ERR_SHAPE;
+        if ((p->flags & (KDA_FLAG_FORCE_SIMT | KDA_FLAG_SIMT_FWD_INTRA | KDA_FLAG_SIMT_BWD_CHUNK | KDA_FLAG_SIMT_BWD_WY)) || !tc_supported(*p))
+            return KDA_ERR_UNSUPPORTED;
+    }
+    if (p->workspace_bytes < (conv ? L.total_conv : L.total) || ((uintptr_t)p->workspace & 255)) return KDA_ERR_WORKSPACE;
     if (bwd) {
         if (!p->grad_o || !p->grad_q || !p->grad_k || !p->grad_v || !p->grad_g || !p->grad_beta || !p->bwd_scratch) return KDA_ERR_NULL;
         if ((p->flags & KDA_FLAG_GATE) && !p->grad_A_log) return KDA_ERR_NULL;
@@ -80,7 +87,7 @@ using namespace kda;
 
 extern "C" {
 
-int kda_abi_version(void) { return 1; }
+int kda_abi_version(void) { return 2; }
 
 int kda_guard_version(void) { return 1; }
 float kda_guard_max_span(void) { return 232.0f; }
@@ -99,6 +106,7 @@ const char* kda_status_string(int s) {
         case KDA_ERR_LAUNCH: return "CUDA launch failed";
         case KDA_ERR_DEVICE_WAIT: return "a bounded device-side wait gave up";
         case KDA_ERR_GUARD: return "guard span must be negative (exact) or a finite value <= 232";
+        case KDA_ERR_UNSUPPORTED: return "the fused short convolution needs BF16 tensors with dk = dv = 128 and the tensor-core stages";
         case KDA_ERR_STATIC_LIMIT: return "size exceeds the built-in scratch of the allocation-free entry point (C * ksize <= 8192)";
         default: return "unknown status";
     }
@@ -108,7 +116,7 @@ int kda_workspace_bytes(const KdaParams* p, size_t* fwd_bytes, size_t* bwd_bytes
     if (!p) return KDA_ERR_NULL;
     if (p->NT <= 0 || p->H <= 0 || p->dk <= 0 || p->dv <= 0) return KDA_ERR_SHAPE;
     WsLayout L = ws_layout(p->NT, p->H, p->dk, p->dv, p->dtype);
-    if (fwd_bytes) *fwd_bytes = L.total;
+    if (fwd_bytes) *fwd_bytes = p->conv_q ? L.total_conv : L.total;
     if (bwd_bytes) *bwd_bytes = L.bwd_total;
     return KDA_OK;
 }

@@ -62,7 +62,6 @@ __device__ __forceinline__ int doc_of(const int64_t* cu, int N, long long t, int
     return lo;
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float dsilu_f(float x) {
     const float s = 1.f / (1.f + __expf(-x));
     return s * (1.f + x * (1.f - s));
@@ -114,7 +113,7 @@ __global__ void __launch_bounds__(128) short_conv_fwd_kernel(const T* __restrict
             const float m0 = d0 == d3 ? 1.f : 0.f, m1 = d1 == d3 ? 1.f : 0.f, m2 = d2 == d3 ? 1.f : 0.f;
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-                const float pre = wt[0][i] * (m0 * x0[i]) + wt[1][i] * (m1 * x1[i]) + wt[2][i] * (m2 * x2[i]) + wt[3][i] * x3[i];
+                const float pre = conv_pre(wt[0][i], wt[1][i], wt[2][i], wt[3][i], m0 * x0[i], m1 * x1[i], m2 * x2[i], x3[i]);
                 out[i] = silu_f(pre);
                 x0[i] = x1[i];
                 x1[i] = x2[i];
@@ -177,7 +176,7 @@ __global__ void __launch_bounds__(256) short_conv_bwd_kernel(const T* __restrict
 #pragma unroll
                     for (int i = 0; i < V; ++i) {
                         const float a0 = m0 * x0[i], a1 = m1 * x1[i], a2 = m2 * x2[i];
-                        const float pre = wt[0][i] * a0 + wt[1][i] * a1 + wt[2][i] * a2 + wt[3][i] * x3[i];
+                        const float pre = conv_pre(wt[0][i], wt[1][i], wt[2][i], wt[3][i], a0, a1, a2, x3[i]);
                         p3[i] = gy[i] * dsilu_f(pre);
                         if (own) {
                             dw[0][i] = fmaf(p3[i], a0, dw[0][i]);

@@ -76,6 +76,7 @@ __device__ __forceinline__ void seq_chunks(const KdaParams& p, int n, int& c0, i
 struct WsLayout {
     size_t W, U, Aqk, Qt, Kh, Tm, S0, gamC;             // forward workspace
     size_t Gc, Qn, Kn, aux, total;                      // prologue results kept for the backward
+    size_t Vc, total_conv;                              // convolved v rows (fused short convolution only)
     size_t dS, dVn, dA_part, dbias_part;                // backward scratch
     size_t dAqk, dM, dQt, dKh, dKb, dbp, gC, bwd_total; // hand-over from bwd_wy to bwd_intra
 };
@@ -103,6 +104,11 @@ __host__ __device__ inline WsLayout ws_layout(int NT, int H, int dk, int dv, int
     w.Kn = off;   off = align256(off + n * C * dk * es);
     w.aux = off;  off = align256(off + n * 3 * C * 4);
     w.total = off;
+    // with the short convolution fused into the load stage the backward needs the convolved v
+    // rows ([64][dv] row-major per record); the record sits behind everything else so that the
+    // plain call's workspace does not grow
+    w.Vc = off;   off = align256(off + n * C * dv * es);
+    w.total_conv = off;
     off = 0;
     w.dS = off;         off = align256(off + n * dk * dv * es);
     w.dVn = off;        off = align256(off + n * C * dv * es);
@@ -134,6 +140,13 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// SiLU and the four-tap causal filter shared by the stand-alone convolution kernels and the
+// fused load stage; one fixed FMA order so that both produce the same bits
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float conv_pre(float w0, float w1, float w2, float w3, float x0, float x1, float x2, float x3) {
+    return fmaf(w3, x3, fmaf(w2, x2, fmaf(w1, x1, w0 * x0)));
+}
+
 // softplus with torch's threshold of 20 (F.softplus, k3mini/model.py:220)
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
@@ -141,7 +154,7 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-
 // absolute error stays below 1e-7, which is what matters for a log-decay
 __device__ __forceinline__ float softplus_fast(float x) {
     const float t = __expf(-fabsf(x));
-    const float l = t < 1e-3f ? t * (1.f - 0.5f * t + 0.33333334f * t * t) : __logf(1.f + t);
+    const float l = t < 1e-3f ? t * fmaf(t, fmaf(0.33333334f, t, -0.5f), 1.f) : __logf(1.f + t);
     return fmaxf(x, 0.f) + l;
 }
 

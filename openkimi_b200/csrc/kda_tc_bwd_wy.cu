@@ -60,6 +60,9 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     float* srow = sbeta + 64;
     const __nv_bfloat16* dO = (const __nv_bfloat16*)p.grad_o;
     const __nv_bfloat16* v = (const __nv_bfloat16*)p.v;
+    // with the short convolution fused into the forward, p.v is the pre-convolution projection and
+    // the convolved rows come from the forward's record
+    const __nv_bfloat16* vrec = p.conv_q ? (const __nv_bfloat16*)(ws + L.Vc) + rec * C * D : nullptr;
     auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
 
     KDA_PHASE_BEGIN();
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             const int i = qq >> 4, e8 = (qq & 15) * 8;
             const bool valid = i < ci.len;
             cp_async16_z(sdo + cm_idx(i, e8, D), dO + tok(valid ? i : 0) * D + e8, valid);
-            cp_async16_z(sv + i * D + e8, v + tok(valid ? i : 0) * D + e8, valid);
+            cp_async16_z(sv + i * D + e8, vrec ? vrec + (valid ? i : 0) * D + e8 : v + tok(valid ? i : 0) * D + e8, valid);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         if (tid < C) sbeta[tid] = ((const float*)(ws + L.aux))[rec * 3 * C + 2 * C + tid];  // beta kept by the forward

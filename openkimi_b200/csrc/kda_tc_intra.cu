@@ -1,7 +1,10 @@
 // fwd_intra on tensor cores (BF16 operands, d = 128): one CTA per (chunk, head).
 //
 //   0  load q, k, v, beta row-wise with 16-byte accesses: L2 norm, sigmoid, beta*v operand;
-//      load the gate channel-wise: activation and the within-chunk cumulative sum G (log2)
+//      load the gate channel-wise: activation and the within-chunk cumulative sum G (log2).
+//      The CONV instantiation reads the pre-convolution projections instead (three halo rows
+//      before the chunk included) and applies the causal depthwise filter + SiLU of
+//      k3mini/model.py:76-88,181-185 in registers before anything else sees the rows
 //   1  decay-scaled operands: Qt, Kh records; beta*k*2^G; and for every 16-row block I >= 1
 //      the factorised operands  k_j 2^(r_I - G_j) (j < 16 I)  and  x_i 2^(G_i - r_I) (i in I),
 //      r_I = G at the first row of block I, so that every exponent is <= 0
@@ -101,6 +104,7 @@ __device__ __forceinline__ void solve_block_column(const float* sL, float* sT, c
     }
 }
 
+template <bool CONV>
 __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams p) {
     using namespace fi;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -152,24 +156,53 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     // ---- 0: issue every global load of the chunk first (gate column, q/k/v rows, beta)
     const int half = tid >> 7, dch = tid & 127;
     const int hw = tid >> 4, c8 = (tid & 15) * 8;
+    // Rows of a half warp: hw + 16 m without the convolution; 4 hw + m with it, so that the seven
+    // input rows 4 hw - 3 .. 4 hw + 3 serve the four outputs of one thread.
+    constexpr int NROW = CONV ? 7 : 4;
     float x[32];
-    uint4 rq4[4], rk4[4], rv4[4];
+    uint4 rq4[NROW], rk4[NROW], rv4[NROW];
     float rb[4];
+    float4 tap[2];
+    if constexpr (CONV) {  // filter taps of this head, padded to four: entry e = tensor * 128 + channel
+        const int K = p.conv_ksize;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int e = tid + NTHR * u;
+            float t4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (e < 3 * D) {
+                const float* w = (e < D ? p.conv_q : e < 2 * D ? p.conv_k : p.conv_v) + (size_t)(h * D + (e & (D - 1))) * K;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (j >= 4 - K) t4[j] = w[j - (4 - K)];
+            }
+            tap[u] = make_float4(t4[0], t4[1], t4[2], t4[3]);
+        }
+    }
 #pragma unroll
     for (int r = 0; r < 32; ++r) {
         const int i = 32 * half + r;
         x[r] = i < ci.len ? __bfloat162float(g[((size_t)(ci.tok0 + i) * p.H + h) * D + dch]) : 0.f;
     }
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-        const int i = hw + 16 * m;
-        const bool valid = i < ci.len;
+    for (int m = 0; m < NROW; ++m) {
+        // a halo row (i < 0) exists when the chunk is not the first of its sequence
+        const int i = CONV ? 4 * hw - 3 + m : hw + 16 * m;
+        const bool valid = i >= 0 ? i < ci.len : ci.lc > 0;
         const size_t row = (size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h;
         const uint4 z = make_uint4(0, 0, 0, 0);
         rq4[m] = valid ? *reinterpret_cast<const uint4*>(q + row * D + c8) : z;
         rk4[m] = valid ? *reinterpret_cast<const uint4*>(k + row * D + c8) : z;
         rv4[m] = valid ? *reinterpret_cast<const uint4*>(v + row * D + c8) : z;
-        rb[m] = ((tid & 15) == 0 && valid) ? __bfloat162float(beta[row]) : 0.f;
+    }
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const int i = CONV ? 4 * hw + m : hw + 16 * m;
+        rb[m] = ((tid & 15) == 0 && i < ci.len) ? __bfloat162float(beta[(size_t)(ci.tok0 + i) * p.H + h]) : 0.f;
+    }
+    if constexpr (CONV) {  // the taps go through shared memory (operand space that stage 1 fills later)
+        float4* sW = reinterpret_cast<float4*>(dyn + XSC);
+        sW[tid] = tap[0];
+        if (tid + NTHR < 3 * D) sW[tid + NTHR] = tap[1];
     }
     // ---- 0a: gate, channel-wise: thread (half, d) owns rows 32*half .. 32*half+31 of channel d
     {
@@ -181,17 +214,46 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             const int i = 32 * half + r;
             float gl = 0.f;
             if (i < ci.len) gl = gate ? negA * softplus_fast(x[r] + bias) : x[r];
-            run += gl * LOG2E;
+            run = fmaf(gl, LOG2E, run);  // explicit: both instantiations must round alike
             sG[i * D + dch] = run;
         }
         if (half == 0) stot[dch] = run;
     }
     KDA_PHASE(0);
-    // ---- 0b: q, k, v, beta row-wise: half warp hw owns rows hw + 16 m, lane c8 the channels 8 c8 ..
+    if constexpr (CONV) {
+        // ---- 0c: y[i] = silu(sum_j tap[j] x[i - 3 + j]) for the thread's four rows, rounded to
+        //      BF16 like the stand-alone convolution; rq4 / rk4 / rv4[0..3] then hold the convolved
+        //      rows and the rest of the stage does not know the difference
+        __syncthreads();
+        const float4* sW = reinterpret_cast<const float4*>(dyn + XSC);
+        auto conv_rows = [&](uint4(&raw)[NROW], int tensor) {
+            float4 w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[j] = sW[tensor * D + c8 + j];
+            float win[NROW][8];
+#pragma unroll
+            for (int r = 0; r < NROW; ++r) bf16x8_to_f32(raw[r], win[r]);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                float y[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    y[j] = silu_f(conv_pre(w[j].x, w[j].y, w[j].z, w[j].w, win[m][j], win[m + 1][j], win[m + 2][j], win[m + 3][j]));
+                raw[m] = 4 * hw + m < ci.len ? f32_to_bf16x8(y) : make_uint4(0, 0, 0, 0);
+            }
+        };
+        conv_rows(rq4, 0);
+        conv_rows(rk4, 1);
+        conv_rows(rv4, 2);
+        __nv_bfloat16* gVc = (__nv_bfloat16*)(ws + L.Vc) + rec * C * D;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) *reinterpret_cast<uint4*>(gVc + (4 * hw + m) * D + c8) = rv4[m];
+    }
+    // ---- 0b: q, k, v, beta row-wise: a half warp owns four rows, lane c8 the channels 8 c8 ..
     {
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
-            const int i = hw + 16 * m;
+            const int i = CONV ? 4 * hw + m : hw + 16 * m;
             const bool valid = i < ci.len;
             float qf[8], kf[8], vf[8];
             bf16x8_to_f32(rq4[m], qf);
@@ -205,8 +267,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                 float ssq = 0.f, ssk = 0.f;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    ssq += qf[j] * qf[j];
-                    ssk += kf[j] * kf[j];
+                    ssq = fmaf(qf[j], qf[j], ssq);  // explicit: both instantiations must round alike
+                    ssk = fmaf(kf[j], kf[j], ssk);
                 }
                 ssq = half_warp_sum(ssq);
                 ssk = half_warp_sum(ssk);
@@ -465,9 +527,10 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 }
 
 cudaError_t launch_fwd_intra_tc(const KdaParams& p, cudaStream_t s) {
-    cudaError_t e = cudaFuncSetAttribute(kda_fwd_intra_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fi::TOTAL);
+    auto kern = p.conv_q ? kda_fwd_intra_tc<true> : kda_fwd_intra_tc<false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fi::TOTAL);
     if (e != cudaSuccess) return e;
-    kda_fwd_intra_tc<<<p.NT * p.H, fi::NTHR, fi::TOTAL, s>>>(p);
+    kern<<<p.NT * p.H, fi::NTHR, fi::TOTAL, s>>>(p);
     return cudaGetLastError();
 }
 

@@ -57,6 +57,11 @@ class _ShortConvFn(torch.autograd.Function):
         return dx, dw.to(ctx.wdtype), None
 
 
+def short_convolution(x, weight, cu_seqlens=None):
+    """Causal depthwise convolution + SiLU over x [B, T, C] with filter [C, 1, ksize]."""
+    return _ShortConvFn.apply(x, weight, cu_seqlens)
+
+
 class ShortConvolution(nn.Module):
     """Causal depthwise conv1d (kernel <= 4) + SiLU over [B, T, hidden]; the interface the
     reference uses from ``fla.modules.ShortConvolution`` (k3mini/model.py:147-155, 181-185):
@@ -137,10 +142,13 @@ class KimiDeltaAttention(nn.Module):
     gate / sigmoid prologue, gated RMSNorm and the output projection.  Constructor arguments
     replace the reference's ``ModelConfig`` fields (k3mini/config.py:56-59)."""
 
-    def __init__(self, d_model, n_heads, head_dim=128, conv_kernel=4, rms_norm_eps=1e-6, disable_recompute=False):
+    def __init__(self, d_model, n_heads, head_dim=128, conv_kernel=4, rms_norm_eps=1e-6, disable_recompute=False,
+                 fuse_short_conv=True):
         super().__init__()
         self.d_model, self.n_heads, self.head_dim = d_model, n_heads, head_dim
         self.disable_recompute = disable_recompute
+        # True: the three short convolutions run inside the KDA forward's load stage (same bits)
+        self.fuse_short_conv = fuse_short_conv
         proj = n_heads * head_dim
         self.q_proj = nn.Linear(d_model, proj, bias=False)
         self.k_proj = nn.Linear(d_model, proj, bias=False)
@@ -163,16 +171,21 @@ class KimiDeltaAttention(nn.Module):
         return x.view(*x.shape[:2], self.n_heads, self.head_dim)
 
     def forward(self, x, cu_seqlens=None):
-        q = self._heads(self.q_conv(self.q_proj(x), cu_seqlens=cu_seqlens)[0])
-        k = self._heads(self.k_conv(self.k_proj(x), cu_seqlens=cu_seqlens)[0])
-        v = self._heads(self.v_conv(self.v_proj(x), cu_seqlens=cu_seqlens)[0])
+        conv_w = None
+        if self.fuse_short_conv:
+            q, k, v = (self._heads(proj(x)) for proj in (self.q_proj, self.k_proj, self.v_proj))
+            conv_w = (self.q_conv.weight, self.k_conv.weight, self.v_conv.weight)
+        else:
+            q = self._heads(self.q_conv(self.q_proj(x), cu_seqlens=cu_seqlens)[0])
+            k = self._heads(self.k_conv(self.k_proj(x), cu_seqlens=cu_seqlens)[0])
+            v = self._heads(self.v_conv(self.v_proj(x), cu_seqlens=cu_seqlens)[0])
         raw_decay = self._heads(self.f_b_proj(self.f_a_proj(x)))
         beta_logits = self.beta_proj(x)
         out, _ = chunk_kda(q=q, k=k, v=v, g=raw_decay, beta=beta_logits, A_log=self.A_log,
                            dt_bias=self.dt_bias.reshape(-1), scale=self.scale, use_qk_l2norm_in_kernel=True,
                            use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True, safe_gate=False,
                            output_final_state=False, state_v_first=True, cu_seqlens=cu_seqlens,
-                           disable_recompute=self.disable_recompute)
+                           disable_recompute=self.disable_recompute, short_conv_weights=conv_w)
         gate = self._heads(self.out_gate_b(self.out_gate_a(x)))
         out = self.out_norm_gate(out, gate).flatten(2)
         return self.out_proj(out)

@@ -50,7 +50,7 @@ def _chunk_tables(cu_seqlens, cu_seqlens_cpu, device):
 class _Call:
     """Builds the KdaParams block for one forward (+ backward) call."""
 
-    def __init__(self, q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags):
+    def __init__(self, q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags, conv=None):
         B, T, H, dk = q.shape
         self.shape = (B, T, H, dk, v.shape[-1])
         self.dev = q.device
@@ -78,6 +78,9 @@ class _Call:
             p.cu_seqlens = self.cu.data_ptr()
             p.chunk_seq = self.chunk_seq.data_ptr()
             p.seq_chunk_off = self.seq_off.data_ptr()
+        if conv is not None:
+            p.conv_q, p.conv_k, p.conv_v = (w.data_ptr() for w in conv)
+            p.conv_ksize = conv[0].shape[-1]
         self.p = p
         fb, bb = C.c_size_t(0), C.c_size_t(0)
         _lib.check(_lib.load().kda_workspace_bytes(C.byref(p), C.byref(fb), C.byref(bb)), "kda_workspace_bytes")
@@ -92,10 +95,27 @@ def _require_cuda(t):
         raise RuntimeError("chunk_kda runs only on a CUDA device (sm_100a); there is no CPU fallback")
 
 
+def _short_conv_bwd(x, w, dy, cu):
+    """Backward of the causal depthwise convolution + SiLU (k3mini/model.py:76-88) for x, dy
+    [B, T, C] and FP32 taps w [C, ksize]; returns (dx, dw [C, 1, ksize] FP32)."""
+    B, T, Cc = x.shape
+    ks = w.shape[-1]
+    n_partial = 128
+    dx = torch.empty_like(x)
+    dw = torch.empty(Cc, 1, ks, dtype=torch.float32, device=x.device)
+    part = torch.empty(n_partial, Cc, ks, dtype=torch.float32, device=x.device)
+    stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(_lib.load().kda_short_conv_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                                              part.data_ptr(), n_partial, B, T, Cc, ks, _DTYPES[x.dtype],
+                                              None if cu is None else cu.data_ptr(), 0 if cu is None else cu.numel() - 1,
+                                              stream), "kda_short_conv_bwd")
+    return dx, dw
+
+
 class ChunkKDAFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, A_log, dt_bias, h0, scale, flags, output_final_state, cu_seqlens,
-                cu_seqlens_cpu, disable_recompute):
+    def forward(ctx, q, k, v, g, beta, A_log, dt_bias, h0, conv_q, conv_k, conv_v, scale, flags, output_final_state,
+                cu_seqlens, cu_seqlens_cpu, disable_recompute):
         lib = _lib.load()
         in_dtypes = (g.dtype, beta.dtype)
         dt = q.dtype
@@ -103,8 +123,13 @@ class ChunkKDAFunction(torch.autograd.Function):
         A_log = A_log.float().contiguous() if A_log is not None else None
         dt_bias = dt_bias.float().contiguous() if dt_bias is not None else None
         h0 = h0.contiguous() if h0 is not None else None
+        # fused short convolution: q, k, v are the projections, conv_* the [H*K, 1, ksize] filters
+        conv = None
+        if conv_q is not None:
+            conv = tuple(w.float().reshape(w.shape[0], w.shape[-1]).contiguous() for w in (conv_q, conv_k, conv_v))
+            ctx.conv_dtypes = tuple(w.dtype for w in (conv_q, conv_k, conv_v))
         with torch.cuda.device(q.device):
-            call = _Call(q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags)
+            call = _Call(q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags, conv)
             B, T, H, dk, dv = call.shape
             o = torch.empty(B, T, H, dv, dtype=dt, device=q.device)
             state_shape = (call.N, H, dv, dk) if flags & _lib.FLAG_STATE_V_FIRST else (call.N, H, dk, dv)
@@ -118,18 +143,19 @@ class ChunkKDAFunction(torch.autograd.Function):
             elif ht is not None:
                 ht.copy_(h0 if h0 is not None else torch.zeros_like(ht))
         ctx.save_for_backward(q, k, v, g, beta, A_log, dt_bias, h0, cu_seqlens, cu_seqlens_cpu,
-                              ws if disable_recompute else None)
+                              ws if disable_recompute else None, *(conv or ()))
         ctx.meta = (scale, flags, in_dtypes, state_shape)
         return o, ht
 
     @staticmethod
     def backward(ctx, do, dht):
         lib = _lib.load()
-        q, k, v, g, beta, A_log, dt_bias, h0, cu_seqlens, cu_seqlens_cpu, ws = ctx.saved_tensors
+        q, k, v, g, beta, A_log, dt_bias, h0, cu_seqlens, cu_seqlens_cpu, ws, *conv = ctx.saved_tensors
+        conv = tuple(conv) or None
         scale, flags, in_dtypes, state_shape = ctx.meta
         dt = q.dtype
         with torch.cuda.device(q.device):
-            call = _Call(q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags)
+            call = _Call(q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags, conv)
             p = call.p
             B, T, H, dk, dv = call.shape
             if ws is None:  # recompute policy: rebuild the per-chunk records instead of keeping them
@@ -165,7 +191,15 @@ class ChunkKDAFunction(torch.autograd.Function):
                     t.zero_()
                 if dh0 is not None:
                     dh0.copy_(dht if dht is not None else torch.zeros_like(dh0))
-        return (dq, dk_, dv_, dg.to(in_dtypes[0]), dbeta.to(in_dtypes[1]), dA, dbias, dh0,
+            dconv = (None, None, None)
+            if conv is not None:
+                # dq, dk_, dv_ are gradients of the convolved rows: the stand-alone convolution
+                # backward turns them into gradients of the projections and of the filters
+                outs = [_short_conv_bwd(x.view(B, T, H * dk), w, dy.view(B, T, H * dk), call.cu)
+                        for x, w, dy in zip((q, k, v), conv, (dq, dk_, dv_))]
+                dq, dk_, dv_ = (dx.view(B, T, H, dk) for dx, _ in outs)
+                dconv = tuple(dw.to(wd) for (_, dw), wd in zip(outs, ctx.conv_dtypes))
+        return (dq, dk_, dv_, dg.to(in_dtypes[0]), dbeta.to(in_dtypes[1]), dA, dbias, dh0, *dconv,
                 None, None, None, None, None, None)
 
 
@@ -173,7 +207,8 @@ class ChunkKDAFunction(torch.autograd.Function):
 def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
               use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
               cu_seqlens=None, cu_seqlens_cpu=None, safe_gate=False, lower_bound=None, disable_recompute=False,
-              state_v_first=False, A_log=None, dt_bias=None, chunk_size=64, fp32_math=False, **kwargs):
+              state_v_first=False, A_log=None, dt_bias=None, chunk_size=64, fp32_math=False,
+              short_conv_weights=None, **kwargs):
     """Kimi Delta Attention, chunkwise (k3mini/model.py:200-216).
 
     q, k, g: [B, T, H, K]; v: [B, T, H, V]; beta: [B, T, H].  With
@@ -187,6 +222,13 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     records between forward and backward, ``False`` rebuilds them in the backward.
     ``fp32_math=True`` forces FP32 CUDA-core arithmetic in every stage (validation mode;
     FP32 inputs always run that way).  Returns ``(o, final_state or None)``.
+
+    ``short_conv_weights=(wq, wk, wv)`` (each ``[H*K, 1, ksize]``, ksize <= 4; an extension, the
+    reference has no such argument) says that q, k, v are the projections BEFORE the three
+    causal depthwise convolutions + SiLU of k3mini/model.py:181-185.  For BF16 with K = 128 the
+    forward kernel applies the filter while it loads the chunk (three halo rows included, the
+    window restarting at every sequence start); otherwise the stand-alone convolution kernels
+    run first.  Both routes give the same bits as ``ShortConvolution`` followed by ``chunk_kda``.
     """
     state_v_first = bool(kwargs.pop("transpose_state_layout", state_v_first))
     for name in ("return_intermediate_states", "cp_context"):
@@ -246,5 +288,18 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     # 2 bwd_state, 3 bwd_chunk as one fused kernel, 4 bwd_wy) with FP32 CUDA-core arithmetic
     # instead of tensor cores
     flags |= (int(os.environ.get("OPENKIMI_B200_FP32_STAGES", "0")) & 31) << 5
-    return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, initial_state, float(scale), flags,
+    conv = (None, None, None)
+    if short_conv_weights is not None:
+        wq, wk, wv = short_conv_weights
+        for w in (wq, wk, wv):
+            if w.dim() != 3 or w.shape[0] != H * K or w.shape[1] != 1 or not 1 <= w.shape[2] <= 4 or w.shape != wq.shape:
+                raise ValueError(f"short_conv_weights must be three [H*K, 1, ksize<=4] filters, got {tuple(w.shape)}")
+        if q.dtype == torch.bfloat16 and K == 128 and not flags & ~15:
+            conv = (wq, wk, wv)
+        else:  # FP32 validation mode and d = 64: same arithmetic, separate kernels
+            from .modules import short_convolution
+            cu = None if cu_seqlens is None else cu_seqlens.to(device=q.device, dtype=torch.int64).contiguous()
+            q, k, v = (short_convolution(x.reshape(B, T, H * K), w, cu).view(B, T, H, K)
+                       for x, w in zip((q, k, v), (wq, wk, wv)))
+    return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, initial_state, *conv, float(scale), flags,
                                   bool(output_final_state), cu_seqlens, cu_seqlens_cpu, bool(disable_recompute))

@@ -63,7 +63,7 @@ __device__ __forceinline__ int doc_of(const int64_t* cu, int N, long long t, int
 }
 
 __device__ __forceinline__ float dsilu_f(float x) {
-    const float s = 1.f / (1.f + __expf(-x));
+    const float s = __fdividef(1.f, 1.f + __expf(-x));
     return s * (1.f + x * (1.f - s));
 }
 
@@ -127,98 +127,93 @@ __global__ void __launch_bounds__(128) short_conv_fwd_kernel(const T* __restrict
 
 // dx[t] = sum_j w[j] dpre[t + 3 - j],  dw[j] = sum_t dpre[t] x[t - 3 + j],
 // dpre[s] = dy[s] silu'(pre[s]) with pre recomputed from x (four-tap padded filter).
-// One thread walks CONV_TT tokens (+3 look-ahead) of one channel group with the x and dpre
-// windows in registers.  blockDim = (32 channel groups, 8 token tiles); the block's partial
-// filter gradient goes to part[blockIdx.y][C][K].
+// A block owns 512 bytes of channels and walks token tiles of CONV_BT tokens: the x rows (three
+// before the tile, three after) and the dy rows (three after) arrive in shared memory through
+// 16-byte asynchronous copies, then thread = channel runs down the tile with its windows in
+// registers, writes dx over the consumed dy rows, and the tile leaves again in 16-byte stores.
+// The thread's filter gradient stays in registers over all its tiles and goes to
+// part[blockIdx.y][C][K] without any reduction inside the block.
+constexpr int CONV_BT = 32;
 template <typename T>
-__global__ void __launch_bounds__(256) short_conv_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w,
-                                                             const T* __restrict__ dy, T* __restrict__ dx,
-                                                             float* __restrict__ part, long long total, int Tlen, int Cch,
-                                                             int K, const int64_t* cu, int N) {
-    constexpr int V = Vec<T>::N;
-    __shared__ float sred[8][32][V * CONV_KMAX + 1];
-    const int cgs = Cch / V;
-    const int cg = blockIdx.x * 32 + threadIdx.x;
-    const bool active = cg < cgs;
-    const int c0 = cg * V;
-    const long long ntile = (total + CONV_TT - 1) / CONV_TT;
-    float wt[CONV_KMAX][V], dw[CONV_KMAX][V];
+__global__ void __launch_bounds__(512 / sizeof(T)) short_conv_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w,
+                                                                        const T* __restrict__ dy, T* __restrict__ dx,
+                                                                        float* __restrict__ part, long long total, int Tlen,
+                                                                        int Cch, int K, const int64_t* cu, int N) {
+    constexpr int CH = 512 / sizeof(T), V = 16 / sizeof(T), PCS = CH / V, XR = CONV_BT + 6, GR = CONV_BT + 3;
+    __shared__ __align__(16) T sx[XR][CH];
+    __shared__ __align__(16) T sg[GR][CH];
+    __shared__ int sdoc[XR];
+    const int tid = threadIdx.x, cbase = blockIdx.x * CH, c = cbase + tid;
+    const bool act = c < Cch;
+    float wt[CONV_KMAX], dw[CONV_KMAX] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < CONV_KMAX; ++j)
-#pragma unroll
-        for (int i = 0; i < V; ++i) dw[j][i] = 0.f;
-    if (active) {
-        load_taps<V>(w, c0, K, wt);
-        for (long long tile = (long long)blockIdx.y * 8 + threadIdx.y; tile < ntile; tile += (long long)gridDim.y * 8) {
-            const long long t0 = tile * CONV_TT;
-            float x0[V], x1[V], x2[V], p0[V], p1[V], p2[V];  // x[s-3..s-1], dpre[s-3..s-1]
-            int d0 = -1, d1 = -1, d2 = -1;                    // their documents (shared by x and dpre entries)
-#pragma unroll
-            for (int i = 0; i < V; ++i) x0[i] = x1[i] = x2[i] = p0[i] = p1[i] = p2[i] = 0.f;
-            if (t0 - 3 >= 0) { Vec<T>::load(x + (t0 - 3) * Cch + c0, x0); d0 = doc_of(cu, N, t0 - 3, Tlen); }
-            if (t0 - 2 >= 0) { Vec<T>::load(x + (t0 - 2) * Cch + c0, x1); d1 = doc_of(cu, N, t0 - 2, Tlen); }
-            if (t0 - 1 >= 0) { Vec<T>::load(x + (t0 - 1) * Cch + c0, x2); d2 = doc_of(cu, N, t0 - 1, Tlen); }
-            // dpre of the three tokens before t0 is not needed: dx[t] only looks ahead
-#pragma unroll 2
-            for (int ss = 0; ss < CONV_TT + 3; ++ss) {
-                const long long sidx = t0 + ss;
-                float x3[V], p3[V];
-                int d3 = -2;
-#pragma unroll
-                for (int i = 0; i < V; ++i) x3[i] = p3[i] = 0.f;
-                if (sidx < total) {
-                    float gy[V];
-                    Vec<T>::load(x + sidx * Cch + c0, x3);
-                    Vec<T>::load(dy + sidx * Cch + c0, gy);
-                    d3 = doc_of(cu, N, sidx, Tlen);
-                    const float m0 = d0 == d3 ? 1.f : 0.f, m1 = d1 == d3 ? 1.f : 0.f, m2 = d2 == d3 ? 1.f : 0.f;
-                    const bool own = ss < CONV_TT;  // this thread owns token sidx for the filter gradient
-#pragma unroll
-                    for (int i = 0; i < V; ++i) {
-                        const float a0 = m0 * x0[i], a1 = m1 * x1[i], a2 = m2 * x2[i];
-                        const float pre = conv_pre(wt[0][i], wt[1][i], wt[2][i], wt[3][i], a0, a1, a2, x3[i]);
-                        p3[i] = gy[i] * dsilu_f(pre);
-                        if (own) {
-                            dw[0][i] = fmaf(p3[i], a0, dw[0][i]);
-                            dw[1][i] = fmaf(p3[i], a1, dw[1][i]);
-                            dw[2][i] = fmaf(p3[i], a2, dw[2][i]);
-                            dw[3][i] = fmaf(p3[i], x3[i], dw[3][i]);
-                        }
-                    }
+    for (int j = 0; j < CONV_KMAX; ++j) wt[j] = (act && j >= CONV_KMAX - K) ? w[(size_t)c * K + j - (CONV_KMAX - K)] : 0.f;
+    const long long ntile = (total + CONV_BT - 1) / CONV_BT;
+    for (long long tile = blockIdx.y; tile < ntile; tile += gridDim.y) {
+        const long long t0 = tile * CONV_BT;
+        for (int q = tid; q < XR * PCS; q += CH) {
+            const int r = q / PCS, pc = q % PCS;
+            const long long t = t0 - 3 + r;
+            const bool valid = t >= 0 && t < total && cbase + pc * V < Cch;
+            const T* src = x + (valid ? (size_t)t * Cch + cbase + pc * V : 0);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(&sx[r][pc * V])),
+                         "l"(src), "r"(valid ? 16 : 0) : "memory");
+        }
+        for (int q = tid; q < GR * PCS; q += CH) {
+            const int r = q / PCS, pc = q % PCS;
+            const long long t = t0 + r;
+            const bool valid = t < total && cbase + pc * V < Cch;
+            const T* src = dy + (valid ? (size_t)t * Cch + cbase + pc * V : 0);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(&sg[r][pc * V])),
+                         "l"(src), "r"(valid ? 16 : 0) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (tid < XR) {  // document of every row of the tile (-1: outside the tensor; such rows are all zero)
+            const long long t = t0 - 3 + tid;
+            sdoc[tid] = (t >= 0 && t < total) ? doc_of(cu, N, t, Tlen) : -1;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (act) {
+            // window: x and dpre of tokens s-3, s-2, s-1 (a, b, c) and the current one (d)
+            float xa = (float)sx[0][tid], xb = (float)sx[1][tid], xc = (float)sx[2][tid];
+            int da = sdoc[0], db = sdoc[1], dc = sdoc[2];
+            float pa = 0.f, pb = 0.f, pc_ = 0.f;
+#pragma unroll 7
+            for (int sI = 0; sI < GR; ++sI) {
+                const float xd = (float)sx[sI + 3][tid], gy = (float)sg[sI][tid];
+                const int dd = sdoc[sI + 3];
+                const float a0 = da == dd ? xa : 0.f, a1 = db == dd ? xb : 0.f, a2 = dc == dd ? xc : 0.f;
+                const float pd = gy * dsilu_f(conv_pre(wt[0], wt[1], wt[2], wt[3], a0, a1, a2, xd));
+                if (sI < CONV_BT) {  // the tile's own tokens feed the filter gradient
+                    dw[0] = fmaf(pd, a0, dw[0]);
+                    dw[1] = fmaf(pd, a1, dw[1]);
+                    dw[2] = fmaf(pd, a2, dw[2]);
+                    dw[3] = fmaf(pd, xd, dw[3]);
                 }
-                // dx of token t = sidx - 3 (the oldest window entry), if this thread owns it
-                if (ss >= 3) {
-                    const long long t = sidx - 3;
-                    if (t < total) {
-                        const float m1 = d1 == d0 ? 1.f : 0.f, m2 = d2 == d0 ? 1.f : 0.f, m3 = d3 == d0 ? 1.f : 0.f;
-                        float out[V];
-#pragma unroll
-                        for (int i = 0; i < V; ++i)
-                            out[i] = wt[3][i] * p0[i] + wt[2][i] * (m1 * p1[i]) + wt[1][i] * (m2 * p2[i]) + wt[0][i] * (m3 * p3[i]);
-                        Vec<T>::store(dx + t * Cch + c0, out);
-                    }
+                if (sI >= 3) {  // dx of the oldest window entry; its dy row has been consumed
+                    const float out = fmaf(wt[0], dd == da ? pd : 0.f,
+                                           fmaf(wt[1], dc == da ? pc_ : 0.f, fmaf(wt[2], db == da ? pb : 0.f, wt[3] * pa)));
+                    sg[sI - 3][tid] = (T)out;
                 }
-#pragma unroll
-                for (int i = 0; i < V; ++i) {
-                    x0[i] = x1[i]; x1[i] = x2[i]; x2[i] = x3[i];
-                    p0[i] = p1[i]; p1[i] = p2[i]; p2[i] = p3[i];
-                }
-                d0 = d1; d1 = d2; d2 = d3;
+                xa = xb; xb = xc; xc = xd;
+                da = db; db = dc; dc = dd;
+                pa = pb; pb = pc_; pc_ = pd;
             }
         }
+        __syncthreads();
+        for (int q = tid; q < CONV_BT * PCS; q += CH) {
+            const int r = q / PCS, pc = q % PCS;
+            const long long t = t0 + r;
+            if (t < total && cbase + pc * V < Cch)
+                *reinterpret_cast<uint4*>(dx + (size_t)t * Cch + cbase + pc * V) = *reinterpret_cast<const uint4*>(&sg[r][pc * V]);
+        }
+        __syncthreads();
     }
+    if (act) {
 #pragma unroll
-    for (int j = 0; j < CONV_KMAX; ++j)
-#pragma unroll
-        for (int i = 0; i < V; ++i) sred[threadIdx.y][threadIdx.x][i * CONV_KMAX + j] = dw[j][i];
-    __syncthreads();
-    if (threadIdx.y == 0 && active) {
-        for (int i = 0; i < V; ++i)
-            for (int j = 0; j < K; ++j) {
-                float s = 0.f;
-                for (int yy = 0; yy < 8; ++yy) s += sred[yy][threadIdx.x][i * CONV_KMAX + j + (CONV_KMAX - K)];
-                part[((size_t)blockIdx.y * Cch + c0 + i) * K + j] = s;
-            }
+        for (int j = 0; j < CONV_KMAX; ++j)
+            if (j >= CONV_KMAX - K) part[((size_t)blockIdx.y * Cch + c) * K + j - (CONV_KMAX - K)] = dw[j];
     }
 }
 
@@ -370,7 +365,8 @@ int kda_short_conv_bwd(const void* x, const float* weight, const void* dy, void*
     if (Cch % V) return KDA_ERR_SHAPE;
     if (((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dx) & 15) return KDA_ERR_ALIGN;
     long long total = (long long)B * T;
-    dim3 grid((Cch / V + 31) / 32, n_partial), block(32, 8);
+    const int chb = dtype == KDA_DTYPE_BF16 ? 256 : 128;  // channels per block (512 bytes)
+    dim3 grid((Cch + chb - 1) / chb, n_partial), block(chb);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == KDA_DTYPE_BF16)
         short_conv_bwd_kernel<__nv_bfloat16><<<grid, block, 0, s>>>((const __nv_bfloat16*)x, weight, (const __nv_bfloat16*)dy,

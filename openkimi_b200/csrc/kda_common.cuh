@@ -142,7 +142,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // SiLU and the four-tap causal filter shared by the stand-alone convolution kernels and the
 // fused load stage; one fixed FMA order so that both produce the same bits
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+// (branch-free approximate division, 2 ulp: an IEEE division carries a slow-path branch that keeps
+// the compiler from interleaving the independent channels of a thread)
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 __device__ __forceinline__ float conv_pre(float w0, float w1, float w2, float w3, float x0, float x1, float x2, float x3) {
     return fmaf(w3, x3, fmaf(w2, x2, fmaf(w1, x1, w0 * x0)));
 }

@@ -309,14 +309,6 @@ constexpr uint32_t TMA_BYTES = 16384 * 3 + 8192 + 512;
 constexpr uint32_t SACC = 0, SBF = 128, VACC = 192, VBF = 256, TMEM_COLS = 512;
 }  // namespace bs
 
-__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src, bool valid) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(valid ? 16 : 0)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 __global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
     using namespace bs;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -376,7 +368,7 @@ __global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
             const int i = q >> 4, e8 = (q & 15) * 8;
             const bool valid = i < ci.len;
             const size_t row = (size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h;
-            cp_async16(sdo + cm_idx(i, e8, D), dO + row * D + e8, valid);
+            cp_async16_z(sdo + cm_idx(i, e8, D), dO + row * D + e8, valid);
         }
         cp_async_commit();
     };

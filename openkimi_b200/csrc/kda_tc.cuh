@@ -243,6 +243,15 @@ __device__ __forceinline__ bool guard_tile(const float (&G)[16], float limit, fl
     return __all_sync(0xffffffffu, good) && isfinite(span) && span <= limit;
 }
 
+// 16-byte asynchronous copy global -> shared (L2 only); !valid writes zeros and reads nothing
+__device__ __forceinline__ void cp_async16_z(void* dst_smem, const void* src, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(valid ? 16 : 0)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // sum over the 16 lanes of a half warp
 __device__ __forceinline__ float half_warp_sum(float v) {
 #pragma unroll

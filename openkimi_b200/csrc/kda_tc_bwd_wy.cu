@@ -38,11 +38,6 @@ constexpr uint32_t TOTAL = SBETA + 512 + 1024;
 constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bw
 
-__device__ __forceinline__ void cp_async16_z(void* dst_smem, const void* src, bool valid) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(valid ? 16 : 0)
-                 : "memory");
-}
-
 __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) {
     using namespace bw;
     extern __shared__ __align__(128) unsigned char dyn[];

@@ -153,14 +153,17 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         mbar_fence_init();
     }
 
-    // ---- 0: issue every global load of the chunk first (gate column, q/k/v rows, beta)
+    // ---- 0: the chunk's inputs go to shared memory with 16-byte asynchronous copies, two groups:
+    //      the gate tile, then the q, k, v rows.  Staging areas are operand space that stage 1
+    //      fills later: gate rows in KB; q, k, v rows (ROWS each, three halo rows first when the
+    //      convolution is fused) from KSC on; the filter taps behind them.
+    constexpr int HALO = CONV ? 3 : 0, ROWS = C + HALO;
+    constexpr uint32_t RAW = KSC, TAPS = RAW + 3 * ROWS * D * 2;
+    static_assert(TAPS + (CONV ? 3 * D * 16 : 0) <= KB, "staging overruns the operand space");
+    __nv_bfloat16* sRG = reinterpret_cast<__nv_bfloat16*>(dyn + KB);
+    __nv_bfloat16* sRaw = reinterpret_cast<__nv_bfloat16*>(dyn + RAW);
     const int half = tid >> 7, dch = tid & 127;
     const int hw = tid >> 4, c8 = (tid & 15) * 8;
-    // Rows of a half warp: hw + 16 m without the convolution; 4 hw + m with it, so that the seven
-    // input rows 4 hw - 3 .. 4 hw + 3 serve the four outputs of one thread.
-    constexpr int NROW = CONV ? 7 : 4;
-    float x[32];
-    uint4 rq4[NROW], rk4[NROW], rv4[NROW];
     float rb[4];
     float4 tap[2];
     if constexpr (CONV) {  // filter taps of this head, padded to four: entry e = tensor * 128 + channel
@@ -179,31 +182,45 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         }
     }
 #pragma unroll
-    for (int r = 0; r < 32; ++r) {
-        const int i = 32 * half + r;
-        x[r] = i < ci.len ? __bfloat162float(g[((size_t)(ci.tok0 + i) * p.H + h) * D + dch]) : 0.f;
+    for (int m = 0; m < 4; ++m) {
+        const int i = hw + 16 * m;
+        const bool valid = i < ci.len;
+        cp_async16_z(sRG + i * D + c8, g + ((size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h) * D + c8, valid);
     }
+    cp_async_commit();
 #pragma unroll
-    for (int m = 0; m < NROW; ++m) {
-        // a halo row (i < 0) exists when the chunk is not the first of its sequence
-        const int i = CONV ? 4 * hw - 3 + m : hw + 16 * m;
-        const bool valid = i >= 0 ? i < ci.len : ci.lc > 0;
-        const size_t row = (size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h;
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        rq4[m] = valid ? *reinterpret_cast<const uint4*>(q + row * D + c8) : z;
-        rk4[m] = valid ? *reinterpret_cast<const uint4*>(k + row * D + c8) : z;
-        rv4[m] = valid ? *reinterpret_cast<const uint4*>(v + row * D + c8) : z;
+    for (int m = 0; m < 4; ++m) {
+        const int i = hw + 16 * m;
+        const bool valid = i < ci.len;
+        const size_t src = ((size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h) * D + c8;
+        const int dst = (HALO + i) * D + c8;
+        cp_async16_z(sRaw + dst, q + src, valid);
+        cp_async16_z(sRaw + ROWS * D + dst, k + src, valid);
+        cp_async16_z(sRaw + 2 * ROWS * D + dst, v + src, valid);
     }
+    if constexpr (CONV) {  // three rows before the chunk: they exist unless the chunk starts its sequence
+        if (tid < 3 * 3 * 16) {
+            const int t3 = tid / 48, r = (tid % 48) >> 4, x8 = (tid & 15) * 8;
+            const bool valid = ci.lc > 0;
+            const __nv_bfloat16* src = (t3 == 0 ? q : t3 == 1 ? k : v) + ((size_t)(ci.tok0 + (valid ? r - 3 : 0)) * p.H + h) * D + x8;
+            cp_async16_z(sRaw + (t3 * ROWS + r) * D + x8, src, valid);
+        }
+    }
+    cp_async_commit();
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
         const int i = CONV ? 4 * hw + m : hw + 16 * m;
         rb[m] = ((tid & 15) == 0 && i < ci.len) ? __bfloat162float(beta[(size_t)(ci.tok0 + i) * p.H + h]) : 0.f;
     }
-    if constexpr (CONV) {  // the taps go through shared memory (operand space that stage 1 fills later)
-        float4* sW = reinterpret_cast<float4*>(dyn + XSC);
-        sW[tid] = tap[0];
-        if (tid + NTHR < 3 * D) sW[tid + NTHR] = tap[1];
+    if constexpr (CONV) {  // taps: entry (tensor, channel) at [tensor][channel % 8][channel / 8], so that the
+                           // sixteen lanes of a half warp read consecutive 16-byte words
+        float4* sW = reinterpret_cast<float4*>(dyn + TAPS);
+        sW[(tid & ~(D - 1)) + (tid & 7) * 16 + ((tid & (D - 1)) >> 3)] = tap[0];
+        const int e = tid + NTHR;
+        if (e < 3 * D) sW[(e & ~(D - 1)) + (e & 7) * 16 + ((e & (D - 1)) >> 3)] = tap[1];
     }
+    cp_async_wait<1>();
+    __syncthreads();
     // ---- 0a: gate, channel-wise: thread (half, d) owns rows 32*half .. 32*half+31 of channel d
     {
         const float negA = gate ? -expf(p.A_log[h]) : 0.f;
@@ -212,34 +229,39 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
             const int i = 32 * half + r;
+            const float x = __bfloat162float(sRG[i * D + dch]);
             float gl = 0.f;
-            if (i < ci.len) gl = gate ? negA * softplus_fast(x[r] + bias) : x[r];
+            if (i < ci.len) gl = gate ? negA * softplus_fast(x + bias) : x;
             run = fmaf(gl, LOG2E, run);  // explicit: both instantiations must round alike
             sG[i * D + dch] = run;
         }
         if (half == 0) stot[dch] = run;
     }
+    cp_async_wait<0>();
+    __syncthreads();
     KDA_PHASE(0);
+    // Rows of a half warp: hw + 16 m without the convolution; 4 hw + m with it, so that the seven
+    // input rows 4 hw - 3 .. 4 hw + 3 serve the four outputs of one thread.
+    uint4 rq4[4], rk4[4], rv4[4];
     if constexpr (CONV) {
         // ---- 0c: y[i] = silu(sum_j tap[j] x[i - 3 + j]) for the thread's four rows, rounded to
-        //      BF16 like the stand-alone convolution; rq4 / rk4 / rv4[0..3] then hold the convolved
-        //      rows and the rest of the stage does not know the difference
-        __syncthreads();
-        const float4* sW = reinterpret_cast<const float4*>(dyn + XSC);
-        auto conv_rows = [&](uint4(&raw)[NROW], int tensor) {
+        //      BF16 like the stand-alone convolution; the rest of the stage sees only y
+        const float4* sW = reinterpret_cast<const float4*>(dyn + TAPS);
+        auto conv_rows = [&](uint4(&out)[4], int tensor) {
             float4 w[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) w[j] = sW[tensor * D + c8 + j];
-            float win[NROW][8];
+            for (int j = 0; j < 8; ++j) w[j] = sW[tensor * D + j * 16 + (c8 >> 3)];
+            float win[7][8];
 #pragma unroll
-            for (int r = 0; r < NROW; ++r) bf16x8_to_f32(raw[r], win[r]);
+            for (int r = 0; r < 7; ++r)
+                bf16x8_to_f32(*reinterpret_cast<const uint4*>(sRaw + (tensor * ROWS + 4 * hw + r) * D + c8), win[r]);
 #pragma unroll
             for (int m = 0; m < 4; ++m) {
                 float y[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                     y[j] = silu_f(conv_pre(w[j].x, w[j].y, w[j].z, w[j].w, win[m][j], win[m + 1][j], win[m + 2][j], win[m + 3][j]));
-                raw[m] = 4 * hw + m < ci.len ? f32_to_bf16x8(y) : make_uint4(0, 0, 0, 0);
+                out[m] = 4 * hw + m < ci.len ? f32_to_bf16x8(y) : make_uint4(0, 0, 0, 0);
             }
         };
         conv_rows(rq4, 0);
@@ -248,6 +270,14 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         __nv_bfloat16* gVc = (__nv_bfloat16*)(ws + L.Vc) + rec * C * D;
 #pragma unroll
         for (int m = 0; m < 4; ++m) *reinterpret_cast<uint4*>(gVc + (4 * hw + m) * D + c8) = rv4[m];
+    } else {
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int off = (hw + 16 * m) * D + c8;
+            rq4[m] = *reinterpret_cast<const uint4*>(sRaw + off);
+            rk4[m] = *reinterpret_cast<const uint4*>(sRaw + ROWS * D + off);
+            rv4[m] = *reinterpret_cast<const uint4*>(sRaw + 2 * ROWS * D + off);
+        }
     }
     // ---- 0b: q, k, v, beta row-wise: a half warp owns four rows, lane c8 the channels 8 c8 ..
     {

@@ -243,6 +243,14 @@ __device__ __forceinline__ bool guard_tile(const float (&G)[16], float limit, fl
     return __all_sync(0xffffffffu, good) && isfinite(span) && span <= limit;
 }
 
+// 2^x by the hardware approximation alone (results below 2^-126 flush to zero); exp2f wraps the
+// same instruction in a rescaling for denormal results that no decay factor here needs
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // 16-byte asynchronous copy global -> shared (L2 only); !valid writes zeros and reads nothing
 __device__ __forceinline__ void cp_async16_z(void* dst_smem, const void* src, bool valid) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(valid ? 16 : 0)

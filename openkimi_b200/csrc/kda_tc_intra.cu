@@ -429,34 +429,78 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                        make_desc(sb + XSC + (I - 1) * 8192 + s * 256, 128, 2048), id, s > 0);
         mma_commit(&bar);
     }
-    // one thread per (i, j) pair of a diagonal block (4 x 136 pairs); every thread walks the 128
-    // channels from its own starting channel, so a warp's shared-memory reads hit 32 banks
-    for (int pr = tid; pr < 4 * 136; pr += NTHR) {
-        const int blk = pr / 136, rr = pr - blk * 136;
-        int i = (int)((sqrtf(8.f * rr + 1.f) - 1.f) * 0.5f);
-        while ((i + 1) * (i + 2) / 2 <= rr) ++i;
-        while (i * (i + 1) / 2 > rr) --i;
-        const int j = rr - i * (i + 1) / 2;
-        const int ri = 16 * blk + i, rj = 16 * blk + j;
-        float a = 0.f, l = 0.f;
-#pragma unroll 4
-        for (int t = 0; t < D / 2; ++t) {
-            const int d2 = 2 * ((lane + t) & (D / 2 - 1));
-            const float2 gi = *reinterpret_cast<const float2*>(sG + ri * D + d2);
-            const float2 gj = *reinterpret_cast<const float2*>(sG + rj * D + d2);
-            const float2 kj = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sK + rj * D + d2));
-            const float2 qi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sQ + ri * D + d2));
-            const float2 ki = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sK + ri * D + d2));
-            const float kd0 = kj.x * exp2f(gi.x - gj.x), kd1 = kj.y * exp2f(gi.y - gj.y);
-            a = fmaf(qi.x, kd0, fmaf(qi.y, kd1, a));
-            l = fmaf(ki.x, kd0, fmaf(ki.y, kd1, l));
+    KDA_PHASE(10);
+    // Thread = (diagonal block b, row pair rp, channel slice cs): it takes rows rp and 15 - rp of the
+    // block (17 (i, j) pairs together, the same for every thread) and the 16 channels 32 u + 4 cs ..+3,
+    // keeps its own row in registers, walks the rows j <= i, and the eight slices of a pair meet
+    // in three shuffles.  Eight lanes read 128 contiguous bytes of a row: no bank conflicts.
+    {
+        const int cs = lane & 7, rp = (warp & 1) * 4 + (lane >> 3), b = warp >> 1;
+#pragma unroll 1
+        for (int pass = 0; pass < 2; ++pass) {
+            const int i = pass == 0 ? rp : 15 - rp, ri = 16 * b + i;
+            // trip count of the warp: the largest i + 1 among its four row pairs
+            const int nj = pass == 0 ? (warp & 1) * 4 + 4 : 16 - (warp & 1) * 4;
+            float gi[16], qi[16], ki[16];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int d0 = 32 * u + 4 * cs;
+                const float4 g4 = *reinterpret_cast<const float4*>(sG + ri * D + d0);
+                gi[4 * u] = g4.x; gi[4 * u + 1] = g4.y; gi[4 * u + 2] = g4.z; gi[4 * u + 3] = g4.w;
+                const uint2 q2 = *reinterpret_cast<const uint2*>(sQ + ri * D + d0);
+                const uint2 k2 = *reinterpret_cast<const uint2*>(sK + ri * D + d0);
+                const float2 qa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.x));
+                const float2 qb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.y));
+                const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
+                const float2 kb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.y));
+                qi[4 * u] = qa.x; qi[4 * u + 1] = qa.y; qi[4 * u + 2] = qb.x; qi[4 * u + 3] = qb.y;
+                ki[4 * u] = ka.x; ki[4 * u + 1] = ka.y; ki[4 * u + 2] = kb.x; ki[4 * u + 3] = kb.y;
+            }
+            // four rows j at a time (every trip count is a multiple of four): their eight sums (a and l
+            // of each pair) are reduced over the eight slices by a transposing exchange, 7 shuffles
+            // instead of 24, after which lane cs owns sum number cs and stores it
+#pragma unroll 1
+            for (int j0 = 0; j0 < nj; j0 += 4) {
+                float v[8];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int rj = 16 * b + j0 + jj;
+                    float av = 0.f, lv = 0.f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int d0 = 32 * u + 4 * cs;
+                        const float4 g4 = *reinterpret_cast<const float4*>(sG + rj * D + d0);
+                        const uint2 k2 = *reinterpret_cast<const uint2*>(sK + rj * D + d0);
+                        const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
+                        const float2 kb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.y));
+                        // (rows j > i are computed too but never stored; whatever they overflow to is dropped)
+                        const float k0 = ka.x * ex2_approx(gi[4 * u] - g4.x), k1 = ka.y * ex2_approx(gi[4 * u + 1] - g4.y);
+                        const float k2f = kb.x * ex2_approx(gi[4 * u + 2] - g4.z), k3 = kb.y * ex2_approx(gi[4 * u + 3] - g4.w);
+                        av = fmaf(qi[4 * u], k0, fmaf(qi[4 * u + 1], k1, fmaf(qi[4 * u + 2], k2f, fmaf(qi[4 * u + 3], k3, av))));
+                        lv = fmaf(ki[4 * u], k0, fmaf(ki[4 * u + 1], k1, fmaf(ki[4 * u + 2], k2f, fmaf(ki[4 * u + 3], k3, lv))));
+                    }
+                    v[2 * jj] = av;
+                    v[2 * jj + 1] = lv;
+                }
+                const bool b2 = cs & 4, b1 = cs & 2, b0 = cs & 1;
+                float w4[4], w2[2];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) w4[t] = (b2 ? v[t + 4] : v[t]) + __shfl_xor_sync(0xffffffffu, b2 ? v[t] : v[t + 4], 4);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) w2[t] = (b1 ? w4[t + 2] : w4[t]) + __shfl_xor_sync(0xffffffffu, b1 ? w4[t] : w4[t + 2], 2);
+                const float sum = (b0 ? w2[1] : w2[0]) + __shfl_xor_sync(0xffffffffu, b0 ? w2[0] : w2[1], 1);
+                const int j = j0 + (cs >> 1);
+                if (j <= i) {
+                    if (!b0) sA[ri * 65 + 16 * b + j] = sum * p.scale;
+                    else if (j < i) sL[ri * 65 + 16 * b + j] = sum;
+                }
+            }
         }
-        sA[ri * 65 + rj] = a * p.scale;
-        if (j < i) sL[ri * 65 + rj] = l;
     }
     KDA_PHASE(4);
     bool ok = mbar_wait(&bar, 0, p.status, 8);
     tc_fence_after();
+    KDA_PHASE(11);
     if (ok) {
         const int qd = warp & 3, cbase = warp < 4 ? 0 : 48;
         const int j = 16 * qd + (lane & 15);
@@ -478,6 +522,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             }
         }
     }
+    KDA_PHASE(12);
     tc_fence_before();
     __syncthreads();
 

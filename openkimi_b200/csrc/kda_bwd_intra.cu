@@ -44,6 +44,18 @@ __device__ __forceinline__ void cpa16(void* dst_smem, const void* src) {
 // 256 threads: thread (gp, d) = (tid / 128, tid % 128) owns channel d and, inside every 16-row
 // block, the 8 tokens 8 gp .. 8 gp + 7: their row sums a1, a2, their column sums c1 and their
 // final assembly all stay in its registers.
+// u[0..7] += dA[0..7] * qf + dM[0..7] * kf as packed two-wide FP32 FMAs (one issue slot per two
+// products); dA and dM point at eight consecutive floats in shared memory, 16-byte aligned
+__device__ __forceinline__ void col_accumulate(float2 (&u)[4], const float* dA, const float* dM, float qf, float kf) {
+    const float4 a0 = *reinterpret_cast<const float4*>(dA), a4 = *reinterpret_cast<const float4*>(dA + 4);
+    const float4 m0 = *reinterpret_cast<const float4*>(dM), m4 = *reinterpret_cast<const float4*>(dM + 4);
+    const float2 q2 = make_float2(qf, qf), k2 = make_float2(kf, kf);
+    u[0] = __ffma2_rn(make_float2(a0.x, a0.y), q2, __ffma2_rn(make_float2(m0.x, m0.y), k2, u[0]));
+    u[1] = __ffma2_rn(make_float2(a0.z, a0.w), q2, __ffma2_rn(make_float2(m0.z, m0.w), k2, u[1]));
+    u[2] = __ffma2_rn(make_float2(a4.x, a4.y), q2, __ffma2_rn(make_float2(m4.x, m4.y), k2, u[2]));
+    u[3] = __ffma2_rn(make_float2(a4.z, a4.w), q2, __ffma2_rn(make_float2(m4.z, m4.w), k2, u[3]));
+}
+
 __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) {
     using namespace bi;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -125,7 +137,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
             const int i = 32 * gp + r;
-            s = fmaf(kh[r], __bfloat162float(sK[i * D + d]) * exp2f(gl - sG[i * D + d]), s);
+            s = fmaf(kh[r], __bfloat162float(sK[i * D + d]) * ex2_approx(gl - sG[i * D + d]), s);
         }
         sscr[128 * gp + d] = s;
     }
@@ -172,51 +184,41 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 #pragma unroll
             for (int j = 0; j < B; ++j) {
                 const int jj = B * J + j;
-                kd[j] = __bfloat162float(sK[jj * D + d]) * exp2f(Gb[0] - sG[jj * D + d]);
+                kd[j] = __bfloat162float(sK[jj * D + d]) * ex2_approx(Gb[0] - sG[jj * D + d]);
             }
 #pragma unroll
             for (int i = 0; i < HB; ++i) {
                 const int ii = B * I + h0 + i;
-                float u1 = 0.f, u2 = 0.f;
+                float2 u1 = make_float2(0.f, 0.f), u2 = u1;  // even / odd j in the two halves
 #pragma unroll
                 for (int j4 = 0; j4 < B; j4 += 4) {
                     const float4 a = *reinterpret_cast<const float4*>(sdA + ii * C + B * J + j4);
                     const float4 m = *reinterpret_cast<const float4*>(sdM + ii * C + B * J + j4);
-                    u1 = fmaf(a.x, kd[j4], fmaf(a.y, kd[j4 + 1], fmaf(a.z, kd[j4 + 2], fmaf(a.w, kd[j4 + 3], u1))));
-                    u2 = fmaf(m.x, kd[j4], fmaf(m.y, kd[j4 + 1], fmaf(m.z, kd[j4 + 2], fmaf(m.w, kd[j4 + 3], u2))));
+                    const float2 k01 = make_float2(kd[j4], kd[j4 + 1]), k23 = make_float2(kd[j4 + 2], kd[j4 + 3]);
+                    u1 = __ffma2_rn(make_float2(a.x, a.y), k01, __ffma2_rn(make_float2(a.z, a.w), k23, u1));
+                    u2 = __ffma2_rn(make_float2(m.x, m.y), k01, __ffma2_rn(make_float2(m.z, m.w), k23, u2));
                 }
-                const float Pi = exp2f(Gm[i] - Gb[0]);
-                a1[i] = fmaf(Pi, u1, a1[i]);
-                a2[i] = fmaf(Pi, u2, a2[i]);
+                const float Pi = ex2_approx(Gm[i] - Gb[0]);
+                a1[i] = fmaf(Pi, u1.x + u1.y, a1[i]);
+                a2[i] = fmaf(Pi, u2.x + u2.y, a2[i]);
             }
         }
         // ---- column sums of my 8 tokens over the later blocks: reference r' = G at their first row
         for (int Ip = I + 1; Ip < 4; ++Ip) {
             const float r2 = sG[(B * Ip) * D + d];
-            float u[HB];
+            float2 u[HB / 2];
 #pragma unroll
-            for (int j = 0; j < HB; ++j) u[j] = 0.f;
+            for (int j = 0; j < HB / 2; ++j) u[j] = make_float2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < B; ++i) {
                 const int ii = B * Ip + i;
-                const float Pi = exp2f(sG[ii * D + d] - r2);
+                const float Pi = ex2_approx(sG[ii * D + d] - r2);
                 const float qp = scale * __bfloat162float(sQ[ii * D + d]) * Pi;
                 const float kp = sbeta[ii] * __bfloat162float(sK[ii * D + d]) * Pi;
-                const float4 a0 = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + h0);
-                const float4 a4 = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + h0 + 4);
-                const float4 m0 = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + h0);
-                const float4 m4 = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + h0 + 4);
-                u[0] = fmaf(a0.x, qp, fmaf(m0.x, kp, u[0]));
-                u[1] = fmaf(a0.y, qp, fmaf(m0.y, kp, u[1]));
-                u[2] = fmaf(a0.z, qp, fmaf(m0.z, kp, u[2]));
-                u[3] = fmaf(a0.w, qp, fmaf(m0.w, kp, u[3]));
-                u[4] = fmaf(a4.x, qp, fmaf(m4.x, kp, u[4]));
-                u[5] = fmaf(a4.y, qp, fmaf(m4.y, kp, u[5]));
-                u[6] = fmaf(a4.z, qp, fmaf(m4.z, kp, u[6]));
-                u[7] = fmaf(a4.w, qp, fmaf(m4.w, kp, u[7]));
+                col_accumulate(u, sdA + ii * C + B * I + h0, sdM + ii * C + B * I + h0, qp, kp);
             }
 #pragma unroll
-            for (int j = 0; j < HB; ++j) c1[j] = fmaf(exp2f(r2 - Gm[j]), u[j], c1[j]);
+            for (int j = 0; j < HB; ++j) c1[j] = fmaf(ex2_approx(r2 - Gm[j]), j & 1 ? u[j >> 1].y : u[j >> 1].x, c1[j]);
         }
         // ---- diagonal block: pairs (i, j) with j < i, at least one of them mine
         {
@@ -239,7 +241,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 const float mid = 0.5f * (gmax + gmin);
 #pragma unroll
                 for (int r = 0; r < B; ++r) {
-                    const float P = exp2f(Gb[r] - mid), N = exp2f(mid - Gb[r]);
+                    const float P = ex2_approx(Gb[r] - mid), N = ex2_approx(mid - Gb[r]);
                     kj[r] *= N;   // key side of the row sums
                     qs[r] *= P;   // row side of the column sums
                     kb[r] *= P;
@@ -247,40 +249,30 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 #pragma unroll
                 for (int i = 0; i < HB; ++i) {  // dA, dM vanish for j >= i (the diagonal of dA was moved to sdiag)
                     const int ii = B * I + h0 + i;
-                    float u1 = 0.f, u2 = 0.f;
+                    float2 u1 = make_float2(0.f, 0.f), u2 = u1;
 #pragma unroll
                     for (int j4 = 0; j4 < B; j4 += 4) {
                         const float4 a = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + j4);
                         const float4 m = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + j4);
-                        u1 = fmaf(a.x, kj[j4], fmaf(a.y, kj[j4 + 1], fmaf(a.z, kj[j4 + 2], fmaf(a.w, kj[j4 + 3], u1))));
-                        u2 = fmaf(m.x, kj[j4], fmaf(m.y, kj[j4 + 1], fmaf(m.z, kj[j4 + 2], fmaf(m.w, kj[j4 + 3], u2))));
+                        const float2 k01 = make_float2(kj[j4], kj[j4 + 1]), k23 = make_float2(kj[j4 + 2], kj[j4 + 3]);
+                        u1 = __ffma2_rn(make_float2(a.x, a.y), k01, __ffma2_rn(make_float2(a.z, a.w), k23, u1));
+                        u2 = __ffma2_rn(make_float2(m.x, m.y), k01, __ffma2_rn(make_float2(m.z, m.w), k23, u2));
                     }
-                    const float Pi = exp2f(Gm[i] - mid);
-                    a1[i] = fmaf(Pi, u1, a1[i]);
-                    a2[i] = fmaf(Pi, u2, a2[i]);
+                    const float Pi = ex2_approx(Gm[i] - mid);
+                    a1[i] = fmaf(Pi, u1.x + u1.y, a1[i]);
+                    a2[i] = fmaf(Pi, u2.x + u2.y, a2[i]);
                 }
                 {  // column side: dA, dM vanish for i <= j
-                    float u[HB];
+                    float2 u[HB / 2];
 #pragma unroll
-                    for (int j = 0; j < HB; ++j) u[j] = 0.f;
+                    for (int j = 0; j < HB / 2; ++j) u[j] = make_float2(0.f, 0.f);
 #pragma unroll
                     for (int i = 1; i < B; ++i) {
                         const int ii = B * I + i;
-                        const float4 a0 = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + h0);
-                        const float4 a4 = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + h0 + 4);
-                        const float4 m0 = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + h0);
-                        const float4 m4 = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + h0 + 4);
-                        u[0] = fmaf(a0.x, qs[i], fmaf(m0.x, kb[i], u[0]));
-                        u[1] = fmaf(a0.y, qs[i], fmaf(m0.y, kb[i], u[1]));
-                        u[2] = fmaf(a0.z, qs[i], fmaf(m0.z, kb[i], u[2]));
-                        u[3] = fmaf(a0.w, qs[i], fmaf(m0.w, kb[i], u[3]));
-                        u[4] = fmaf(a4.x, qs[i], fmaf(m4.x, kb[i], u[4]));
-                        u[5] = fmaf(a4.y, qs[i], fmaf(m4.y, kb[i], u[5]));
-                        u[6] = fmaf(a4.z, qs[i], fmaf(m4.z, kb[i], u[6]));
-                        u[7] = fmaf(a4.w, qs[i], fmaf(m4.w, kb[i], u[7]));
+                        col_accumulate(u, sdA + ii * C + B * I + h0, sdM + ii * C + B * I + h0, qs[i], kb[i]);
                     }
 #pragma unroll
-                    for (int j = 0; j < HB; ++j) c1[j] = fmaf(exp2f(mid - Gm[j]), u[j], c1[j]);
+                    for (int j = 0; j < HB; ++j) c1[j] = fmaf(ex2_approx(mid - Gm[j]), j & 1 ? u[j >> 1].y : u[j >> 1].x, c1[j]);
                 }
             } else {  // one exp2 per pair
 #pragma unroll
@@ -289,7 +281,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 #pragma unroll
                     for (int j = 0; j < B - 1; ++j) {
                         const bool on = j < li;
-                        const float kp = on ? kj[j] * exp2f(Gm[i] - Gb[j]) : 0.f;
+                        const float kp = on ? kj[j] * ex2_approx(Gm[i] - Gb[j]) : 0.f;
                         a1[i] = fmaf(sdA[ii * C + B * I + j], kp, a1[i]);
                         a2[i] = fmaf(sdM[ii * C + B * I + j], kp, a2[i]);
                     }
@@ -300,7 +292,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 #pragma unroll
                     for (int i = 1; i < B; ++i) {
                         const bool on = i > lj;
-                        const float e = on ? exp2f(Gb[i] - Gm[j]) : 0.f;
+                        const float e = on ? ex2_approx(Gb[i] - Gm[j]) : 0.f;
                         const float t = sdA[(B * I + i) * C + jj] * qs[i] + sdM[(B * I + i) * C + jj] * kb[i];
                         c1[j] = fmaf(t, e, c1[j]);
                     }
@@ -321,7 +313,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 const int li = h0 + i, ii = B * I + li;
                 const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
                 const float bi_ = sbeta[ii];
-                const float gam = exp2f(Gm[i]), eta = exp2f(gl - Gm[i]);
+                const float gam = ex2_approx(Gm[i]), eta = ex2_approx(gl - Gm[i]);
                 const float dQt = spf[(0 * B + li) * D + d], dKh = spf[(1 * B + li) * D + d], dKb = spf[(2 * B + li) * D + d];
                 const float diag = scale * sdiag[ii];
                 const float dq_in = scale * a1[i], dk_row = bi_ * a2[i], dKt = bi_ * dKb;
@@ -346,7 +338,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                         const float gprev = ii > 0 ? (i > 0 ? Gm[i - 1] : sG[(ii - 1) * D + d]) : 0.f;
                         const float gnat = (Gm[i] - gprev) * 0.6931471805599453f;
                         dA_acc = fmaf(run, gnat, dA_acc);
-                        const float dx = run * negA * (1.f - exp2f(gnat * rcpA * LOG2E));
+                        const float dx = run * negA * (1.f - ex2_approx(gnat * rcpA * LOG2E));
                         dbias_acc += dx;
                         dg_out[off] = __float2bfloat16_rn(dx);
                     } else {
@@ -453,8 +445,8 @@ __global__ void __launch_bounds__(32) kda_diag_tile_kernel(const float* __restri
     if (pass) {
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            P[r] = exp2f(G[r] - mid);
-            N[r] = exp2f(mid - G[r]);
+            P[r] = ex2_approx(G[r] - mid);
+            N[r] = ex2_approx(mid - G[r]);
         }
     }
 #pragma unroll
@@ -476,11 +468,11 @@ __global__ void __launch_bounds__(32) kda_diag_tile_kernel(const float* __restri
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 if (j <= i) {
-                    const float kp = K[j] * exp2f(G[i] - G[j]);
+                    const float kp = K[j] * ex2_approx(G[i] - G[j]);
                     sq = fmaf(A[i * 16 + j], kp, sq);
                     sk = fmaf(M[i * 16 + j], kp, sk);
                 }
-                if (j >= i) st = fmaf(A[i * 16 + j] * Q[j] + M[i * 16 + j] * (Bt[j] * K[j]), exp2f(G[j] - G[i]), st);
+                if (j >= i) st = fmaf(A[i * 16 + j] * Q[j] + M[i * 16 + j] * (Bt[j] * K[j]), ex2_approx(G[j] - G[i]), st);
             }
         }
         dq[(n * 16 + i) * 32 + ch] = sq;

@@ -104,6 +104,31 @@ __device__ __forceinline__ void solve_block_column(const float* sL, float* sT, c
     }
 }
 
+// Off-diagonal blocks from tensor memory into sA (Aqk, scaled) and sL: accumulator column
+// 32 (I - 1) + n holds, for key row j (lane), the product with q row n (n < 16) or k row n - 16 of
+// block I.  CBASE is a template argument so that every block / row index is a constant.
+template <int CBASE>
+__device__ __forceinline__ void read_offdiag(uint32_t tmem_d, int qd, int lane, float* sA, float* sL, float scale) {
+    const int j = 16 * qd + (lane & 15);
+#pragma unroll
+    for (int cc = 0; cc < 48; cc += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem_d + ((uint32_t)(32 * qd) << 16) + CBASE + cc, r);
+        tmem_wait_ld();
+        if (lane < 16) {
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int col = CBASE + cc + u, I = (col >> 5) + 1, nn = col & 31;
+                if (j < 16 * I) {
+                    const float val = __uint_as_float(r[u]);
+                    if (nn < 16) sA[(16 * I + nn) * 65 + j] = val * scale;
+                    else sL[(16 * I + nn - 16) * 65 + j] = val;
+                }
+            }
+        }
+    }
+}
+
 template <bool CONV>
 __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams p) {
     using namespace fi;
@@ -374,7 +399,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             const float bi = sbeta[i];
             float eg[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) eg[j] = exp2f(G8[j]);
+            for (int j = 0; j < 8; ++j) eg[j] = ex2_approx(G8[j]);
 #pragma unroll
             for (int j = 0; j < 8; ++j) o8[j] = p.scale * qf[j] * eg[j];
             *reinterpret_cast<uint4*>(gQt + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
@@ -382,14 +407,14 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             for (int j = 0; j < 8; ++j) o8[j] = bi * kf[j] * eg[j];
             *reinterpret_cast<uint4*>(sKB + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o8[j] = kf[j] * exp2f(gl[j] - G8[j]);
+            for (int j = 0; j < 8; ++j) o8[j] = kf[j] * ex2_approx(gl[j] - G8[j]);
             *reinterpret_cast<uint4*>(gKh + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
             if (m >= 1) {  // rows of block m as the N operand of block m's products
                 const float* r = sG + (16 * m) * D + c8;
                 __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(dyn + XSC + (m - 1) * 8192);
                 float f[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = exp2f(G8[j] - r[j]);
+                for (int j = 0; j < 8; ++j) f[j] = ex2_approx(G8[j] - r[j]);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) o8[j] = qf[j] * f[j];
                 *reinterpret_cast<uint4*>(xs + cm_idx(i - 16 * m, c8, D)) = f32_to_bf16x8(o8);
@@ -403,7 +428,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                 if (m < I) {
                     const float* r = sG + (16 * I) * D + c8;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) o8[j] = kf[j] * exp2f(r[j] - G8[j]);
+                    for (int j = 0; j < 8; ++j) o8[j] = kf[j] * ex2_approx(r[j] - G8[j]);
                     *reinterpret_cast<uint4*>(ks + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
                 } else {
                     *reinterpret_cast<uint4*>(ks + cm_idx(i, c8, D)) = make_uint4(0, 0, 0, 0);
@@ -465,7 +490,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {
                     const int rj = 16 * b + j0 + jj;
-                    float av = 0.f, lv = 0.f;
+                    float2 av = make_float2(0.f, 0.f), lv = av;  // packed two-wide FMAs: even / odd channels
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const int d0 = 32 * u + 4 * cs;
@@ -474,13 +499,13 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                         const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
                         const float2 kb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.y));
                         // (rows j > i are computed too but never stored; whatever they overflow to is dropped)
-                        const float k0 = ka.x * ex2_approx(gi[4 * u] - g4.x), k1 = ka.y * ex2_approx(gi[4 * u + 1] - g4.y);
-                        const float k2f = kb.x * ex2_approx(gi[4 * u + 2] - g4.z), k3 = kb.y * ex2_approx(gi[4 * u + 3] - g4.w);
-                        av = fmaf(qi[4 * u], k0, fmaf(qi[4 * u + 1], k1, fmaf(qi[4 * u + 2], k2f, fmaf(qi[4 * u + 3], k3, av))));
-                        lv = fmaf(ki[4 * u], k0, fmaf(ki[4 * u + 1], k1, fmaf(ki[4 * u + 2], k2f, fmaf(ki[4 * u + 3], k3, lv))));
+                        const float2 k01 = __fmul2_rn(ka, make_float2(ex2_approx(gi[4 * u] - g4.x), ex2_approx(gi[4 * u + 1] - g4.y)));
+                        const float2 k23 = __fmul2_rn(kb, make_float2(ex2_approx(gi[4 * u + 2] - g4.z), ex2_approx(gi[4 * u + 3] - g4.w)));
+                        av = __ffma2_rn(make_float2(qi[4 * u], qi[4 * u + 1]), k01, __ffma2_rn(make_float2(qi[4 * u + 2], qi[4 * u + 3]), k23, av));
+                        lv = __ffma2_rn(make_float2(ki[4 * u], ki[4 * u + 1]), k01, __ffma2_rn(make_float2(ki[4 * u + 2], ki[4 * u + 3]), k23, lv));
                     }
-                    v[2 * jj] = av;
-                    v[2 * jj + 1] = lv;
+                    v[2 * jj] = av.x + av.y;
+                    v[2 * jj + 1] = lv.x + lv.y;
                 }
                 const bool b2 = cs & 4, b1 = cs & 2, b0 = cs & 1;
                 float w4[4], w2[2];
@@ -501,26 +526,9 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     bool ok = mbar_wait(&bar, 0, p.status, 8);
     tc_fence_after();
     KDA_PHASE(11);
-    if (ok) {
-        const int qd = warp & 3, cbase = warp < 4 ? 0 : 48;
-        const int j = 16 * qd + (lane & 15);
-#pragma unroll
-        for (int cc = 0; cc < 48; cc += 16) {
-            uint32_t r[16];
-            tmem_ld16(tmem0 + ((uint32_t)(32 * qd) << 16) + T_D + cbase + cc, r);
-            tmem_wait_ld();
-            if (lane < 16) {
-#pragma unroll
-                for (int u = 0; u < 16; ++u) {
-                    const int col = cbase + cc + u, I = (col >> 5) + 1, nn = col & 31;
-                    if (j < 16 * I) {
-                        const float val = __uint_as_float(r[u]);
-                        if (nn < 16) sA[(16 * I + nn) * 65 + j] = val * p.scale;
-                        else sL[(16 * I + nn - 16) * 65 + j] = val;
-                    }
-                }
-            }
-        }
+    if (ok) {  // warps 0-3 take accumulator columns 0..47, warps 4-7 columns 48..95
+        if (warp < 4) read_offdiag<0>(tmem0 + T_D, warp & 3, lane, sA, sL, p.scale);
+        else read_offdiag<48>(tmem0 + T_D, warp & 3, lane, sA, sL, p.scale);
     }
     KDA_PHASE(12);
     tc_fence_before();
@@ -571,7 +579,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             mma_ss(tmem0 + T_U, make_desc(sb + BV + s * 4096, 2048, 128), make_desc(sb + KSC + s * 256, 128, 1024), id, s > 0);
         mma_commit(&bar);
     }
-    if (tid < D) gGam[tid] = exp2f(sG[(C - 1) * D + tid]);
+    if (tid < D) gGam[tid] = ex2_approx(sG[(C - 1) * D + tid]);
     ok = mbar_wait(&bar, 1, p.status, 8) && ok;
     tc_fence_after();
 

@@ -432,7 +432,14 @@ def main():
     else:
         ach = flops * units / (avg[dom] / 1e3) / 1e12
         roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"]}
-    roof.update({"kernel": dom, "kernel_ms": avg[dom], "peak_source": peaks["source"], "traffic": None,
+    # DRAM bytes per (chunk, head) unit from the committed ncu capture of the batch-4 case
+    # (dram__bytes_read.sum + dram__bytes_write.sum over 768 units, profiles/kda_bf16_kernels_c1_batch4.md);
+    # traffic grows in proportion to the units, so a full launch is that figure times its units
+    ncu_bytes_per_unit = {"fwd_intra": 140.2e3, "fwd_state": 84.5e3, "bwd_state": 87.2e3, "bwd_wy": 241.4e3,
+                          "bwd_intra": 227.2e3}
+    traffic = ncu_bytes_per_unit[dom] * units if (dom in ncu_bytes_per_unit and w["d"] == 128 and not sub) else None
+    roof.update({"kernel": dom, "kernel_ms": avg[dom], "peak_source": peaks["source"], "traffic": traffic,
+                 "traffic_source": "ncu capture of 768 units, scaled by units" if traffic else None,
                  "units_per_launch": units, "algorithmic_bytes_per_unit": byts, "algorithmic_flops_per_unit": flops})
     # whole-op fractions: dense-tile FLOPs 3*(10*C*d + 6*d^2) per (token, head); minimal HBM bytes
     d = w["d"]

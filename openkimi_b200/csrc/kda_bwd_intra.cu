@@ -30,8 +30,8 @@ constexpr uint32_t SG = SK + 16384;          // G f32 [64][128]
 constexpr uint32_t SDA = SG + 32768;         // dAqk f32 [64][64]
 constexpr uint32_t SDM = SDA + 16384;        // dM   f32 [64][64]
 constexpr uint32_t STG = SDM + 16384;        // staging f32 [3][16][128]: dq, dk, dbeta terms of one block
-constexpr uint32_t PF = STG + 24576;         // prefetch f32 [3][16][128]: dQt, dKh, dKb rows of one block
-constexpr uint32_t SBETA = PF + 24576;       // f32 [64] 1/|q|, [64] 1/|k|, [64] beta, [64] dbeta
+constexpr uint32_t PF = STG + 24576;         // f32 [3][64][128]: dQt, dKh, dKb of the whole chunk
+constexpr uint32_t SBETA = PF + 98304;       // f32 [64] 1/|q|, [64] 1/|k|, [64] beta, [64] dbeta
 constexpr uint32_t SX = SBETA + 1024;        // f32 [2][2][128] block totals of dG, f32 [2][128] scratch
 constexpr uint32_t SRED = SX + 3072;         // f32 [8]
 constexpr uint32_t TOTAL = SRED + 64 + 256;
@@ -59,6 +59,7 @@ __device__ __forceinline__ void col_accumulate(float2 (&u)[4], const float* dA, 
 __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) {
     using namespace bi;
     extern __shared__ __align__(128) unsigned char dyn[];
+    __shared__ uint64_t barA, barB;
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dyn + SQ);
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(dyn + SK);
     float* sG = reinterpret_cast<float*>(dyn + SG);
@@ -89,58 +90,34 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     const float expA = gate ? expf(p.A_log[h]) : 1.f;
     const float negA = -expA, rcpA = 1.f / expA;
     auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
-    // rows 16 I .. 16 I + 15 of dQt, dKh, dKb -> spf (16-byte asynchronous copies)
-    auto prefetch = [&](int I) {
-        for (int qq = tid; qq < 3 * B * (D / 4); qq += NTHR) {
-            const int t = qq / (B * (D / 4)), rem = qq % (B * (D / 4));
-            const float* src = (t == 0 ? gdQt : (t == 1 ? gdKh : gdKb)) + (size_t)(B * I) * D + rem * 4;
-            cpa16(spf + t * B * D + rem * 4, src);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
     KDA_PHASE_BEGIN();
-    // ---- the forward kept G, the normalised q and k, the row norms and beta: copy them in
-    //      asynchronously together with dAqk, dM and the first block of dQt / dKh / dKb
-    {
+    // ---- everything the kernel reads arrives by bulk TMA: on barA what the pair sums need (G, the
+    //      normalised q and k, the row norms and beta kept by the forward; dAqk and dM from bwd_wy),
+    //      on barB the three [64][128] hand-over arrays that only the assembly needs
+    if (tid == 0) {
+        mbar_init(&barA, 1);
+        mbar_init(&barB, 1);
+        mbar_fence_init();
         const char* ws = (const char*)p.workspace;
-        const float* gdA = (const float*)(sc + L.dAqk) + rec * C * C;
-        const float* gdM = (const float*)(sc + L.dM) + rec * C * C;
-        const float* gG = (const float*)(ws + L.Gc) + rec * C * D;
-        const __nv_bfloat16* gQn = (const __nv_bfloat16*)(ws + L.Qn) + rec * C * D;
-        const __nv_bfloat16* gKn = (const __nv_bfloat16*)(ws + L.Kn) + rec * C * D;
-        const float* gaux = (const float*)(ws + L.aux) + rec * 3 * C;
-        for (int qq = tid; qq < C * D / 4; qq += NTHR) cpa16(sG + qq * 4, gG + qq * 4);
-        for (int qq = tid; qq < C * D / 8; qq += NTHR) {
-            cpa16(sQ + qq * 8, gQn + qq * 8);
-            cpa16(sK + qq * 8, gKn + qq * 8);
-        }
-        for (int qq = tid; qq < C * C / 4; qq += NTHR) {
-            cpa16(sdA + qq * 4, gdA + qq * 4);
-            cpa16(sdM + qq * 4, gdM + qq * 4);
-        }
-        if (tid < 3 * C / 4) cpa16(srq + tid * 4, gaux + tid * 4);  // 1/|q|, 1/|k|, beta -> srq, srk, sbeta2
+        mbar_expect_tx(&barA, C * D * 4 + 2 * C * D * 2 + 2 * C * C * 4 + 3 * C * 4);
+        tma_load_1d(sG, (const float*)(ws + L.Gc) + rec * C * D, C * D * 4, &barA);
+        tma_load_1d(sQ, (const __nv_bfloat16*)(ws + L.Qn) + rec * C * D, C * D * 2, &barA);
+        tma_load_1d(sK, (const __nv_bfloat16*)(ws + L.Kn) + rec * C * D, C * D * 2, &barA);
+        tma_load_1d(sdA, (const float*)(sc + L.dAqk) + rec * C * C, C * C * 4, &barA);
+        tma_load_1d(sdM, (const float*)(sc + L.dM) + rec * C * C, C * C * 4, &barA);
+        tma_load_1d(srq, (const float*)(ws + L.aux) + rec * 3 * C, 3 * C * 4, &barA);  // 1/|q|, 1/|k|, beta
+        mbar_expect_tx(&barB, 3 * C * D * 4);
+        tma_load_1d(spf, gdQt, C * D * 4, &barB);
+        tma_load_1d(spf + C * D, gdKh, C * D * 4, &barB);
+        tma_load_1d(spf + 2 * C * D, gdKb, C * D * 4, &barB);
     }
-    prefetch(3);
     const int c8 = (tid & 15) * 8;
-    float kh[32];
-#pragma unroll
-    for (int r = 0; r < 32; ++r) kh[r] = gdKh[(32 * gp + r) * D + d];
     if (tid < C) sdb[tid] = ((const float*)(sc + L.dbp))[rec * C + tid];
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // barrier initialisation is visible
+    if (!mbar_wait(&barA, 0, p.status, 64)) return;  // uniform: every thread polls the same barrier
     KDA_PHASE(0);
-    __syncthreads();
-    KDA_PHASE(1);
-    // ---- term of the last row: dGamma_C Gamma_C + sum_i dKh_i Kh_i (each group sums its 32 rows)
     const float gl = sG[(C - 1) * D + d];
-    {
-        float s = 0.f;
-#pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const int i = 32 * gp + r;
-            s = fmaf(kh[r], __bfloat162float(sK[i * D + d]) * ex2_approx(gl - sG[i * D + d]), s);
-        }
-        sscr[128 * gp + d] = s;
-    }
+    KDA_PHASE(1);
     KDA_PHASE(2);
 
     // ---- guard of the four diagonal tiles (one tile = 16 rows x this warp's 32 channels)
@@ -152,14 +129,12 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         for (int r = 0; r < B; ++r) Gt[r] = sG[(B * I + r) * D + d];
         if (guard_tile(Gt, p.guard_span, mid_unused)) guard_mask |= 1u << I;
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
     if (tid < C) {
         sdiag[tid] = sdA[tid * C + tid];
         sdA[tid * C + tid] = 0.f;
     }
     __syncthreads();
-    float carry = ((const float*)(sc + L.gC))[rec * D + d] + sscr[d] + sscr[128 + d];
+    float carry = ((const float*)(sc + L.gC))[rec * D + d];
     float dA_acc = 0.f, dbias_acc = 0.f;
     __nv_bfloat16* dq_out = (__nv_bfloat16*)p.grad_q;
     __nv_bfloat16* dk_out = (__nv_bfloat16*)p.grad_k;
@@ -300,8 +275,18 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         }
         KDA_PHASE(4 + 4 * (3 - I));
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();  // prefetched rows of this block are visible; staging buffer is free
+        if (I == 3) {
+            if (!mbar_wait(&barB, 0, p.status, 64)) return;
+            // term of the last row: dGamma_C Gamma_C + sum_i dKh_i Kh_i (each group sums its 32 rows);
+            // it joins the carry after the barrier that follows the assembly
+            float s = 0.f;
+#pragma unroll 8
+            for (int r = 0; r < 32; ++r) {
+                const int i = 32 * gp + r;
+                s = fmaf(spf[(C + i) * D + d], __bfloat162float(sK[i * D + d]) * ex2_approx(gl - sG[i * D + d]), s);
+            }
+            sscr[128 * gp + d] = s;
+        }
         KDA_PHASE(5 + 4 * (3 - I));
 
         // ---- assembly of my 8 tokens, last first; run[i] = dG summed over the tokens >= i of my half
@@ -314,7 +299,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
                 const float bi_ = sbeta[ii];
                 const float gam = ex2_approx(Gm[i]), eta = ex2_approx(gl - Gm[i]);
-                const float dQt = spf[(0 * B + li) * D + d], dKh = spf[(1 * B + li) * D + d], dKb = spf[(2 * B + li) * D + d];
+                const float dQt = spf[ii * D + d], dKh = spf[(C + ii) * D + d], dKb = spf[(2 * C + ii) * D + d];
                 const float diag = scale * sdiag[ii];
                 const float dq_in = scale * a1[i], dk_row = bi_ * a2[i], dKt = bi_ * dKb;
                 stg[(0 * B + li) * D + d] = dq_in + diag * ki + scale * dQt * gam;
@@ -349,6 +334,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         };
         __syncthreads();
         KDA_PHASE(6 + 4 * (3 - I));
+        if (I == 3) carry += sscr[d] + sscr[128 + d];
         const float upper = stotal[((I & 1) * 2 + 1) * D + d];
         finish(gp == 0 ? carry + upper : carry);
         carry += upper + stotal[((I & 1) * 2 + 0) * D + d];
@@ -388,8 +374,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 }
             }
         }
-        __syncthreads();  // staging and prefetch buffers may be overwritten
-        if (I > 0) prefetch(I - 1);
+        __syncthreads();  // the staging buffer may be overwritten
         KDA_PHASE(7 + 4 * (3 - I));
     }
     if (gate) {

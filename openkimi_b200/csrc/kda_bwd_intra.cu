@@ -37,10 +37,6 @@ constexpr uint32_t SRED = SX + 3072;         // f32 [8]
 constexpr uint32_t TOTAL = SRED + 64 + 256;
 }  // namespace bi
 
-__device__ __forceinline__ void cpa16(void* dst_smem, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-
 // 256 threads: thread (gp, d) = (tid / 128, tid % 128) owns channel d and, inside every 16-row
 // block, the 8 tokens 8 gp .. 8 gp + 7: their row sums a1, a2, their column sums c1 and their
 // final assembly all stay in its registers.

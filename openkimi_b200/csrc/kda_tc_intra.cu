@@ -34,8 +34,7 @@ constexpr uint32_t BV = KB + 16384;          // beta v      cm(j, e; 128)
 constexpr uint32_t SA = BV + 16384;          // f32 [64][65]
 constexpr uint32_t SL = SA + 16640;
 constexpr uint32_t ST = SL + 16640;
-constexpr uint32_t SP = ST + 16640;          // f32 [3][16][17]
-constexpr uint32_t SBETA = SP + 3328;        // f32 [3][64]: 1/|q|, 1/|k|, beta (the aux record)
+constexpr uint32_t SBETA = ST + 16640;        // f32 [3][64]: 1/|q|, 1/|k|, beta (the aux record)
 constexpr uint32_t STOT = SBETA + 768;       // f32 [128]
 constexpr uint32_t TOTAL = STOT + 512;
 constexpr uint32_t T_D = 0, T_W = 96, T_U = 160, TMEM_COLS = 256;
@@ -143,7 +142,6 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     float* sA = reinterpret_cast<float*>(dyn + SA);
     float* sL = reinterpret_cast<float*>(dyn + SL);
     float* sT = reinterpret_cast<float*>(dyn + ST);
-    float* sP = reinterpret_cast<float*>(dyn + SP);
     float* saux = reinterpret_cast<float*>(dyn + SBETA);
     float* sbeta = saux + 2 * C;
     float* stot = reinterpret_cast<float*>(dyn + STOT);

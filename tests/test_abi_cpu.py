@@ -66,6 +66,37 @@ def test_validation_rejects_bad_arguments_without_a_gpu():
     assert fb.value > 0 and bb.value > 0 and fb.value % 256 == 0
 
 
+def test_fused_convolution_arguments_are_validated_without_a_gpu():
+    """The fused short convolution (KdaParams.conv_*): all three filters or none, 1..4 taps, BF16 with
+    dk = 128 only, and a larger workspace.  Every case fails before any launch, so fake (aligned,
+    never dereferenced) addresses stand in for the tensors."""
+    from openkimi_b200 import _lib
+
+    lib = _lib.load()
+    p = _lib.KdaParams()
+    p.B, p.T, p.H, p.N, p.NT, p.dk, p.dv = 1, 64, 1, 1, 1, 128, 128
+    p.dtype, p.guard_span = _lib.DTYPE_BF16, 232.0
+    for name in ("q", "k", "v", "g", "beta", "o", "workspace"):
+        setattr(p, name, 4096)
+    fb0, fb1, bb = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    assert lib.kda_workspace_bytes(C.byref(p), C.byref(fb0), C.byref(bb)) == 0
+    p.conv_q = 4096
+    assert lib.kda_fwd(C.byref(p), None) == 1            # conv_k, conv_v missing
+    p.conv_k = p.conv_v = 4096
+    p.conv_ksize = 5
+    assert lib.kda_fwd(C.byref(p), None) == 2
+    p.conv_ksize = 4
+    assert lib.kda_workspace_bytes(C.byref(p), C.byref(fb1), C.byref(bb)) == 0
+    assert fb1.value == fb0.value + 64 * 128 * 2         # one BF16 [64][dv] record per unit more
+    p.workspace_bytes = fb0.value
+    assert lib.kda_fwd(C.byref(p), None) == 4            # workspace too small for the fused call
+    p.dtype = _lib.DTYPE_F32
+    assert lib.kda_fwd(C.byref(p), None) == 10           # FP32 has no fused convolution
+    p.dtype, p.flags = _lib.DTYPE_BF16, _lib.FLAG_FORCE_SIMT
+    assert lib.kda_fwd(C.byref(p), None) == 10
+    assert b"short convolution" in lib.kda_status_string(10)
+
+
 def _patched(version=1, span=232.0, precision="tf32x3"):
     m = ModuleType("chunk_intra")
     m.OPENKIMI_KDA_GUARDED_DIAGONAL_VERSION = version

@@ -109,6 +109,7 @@ mma_selftest_kernel(const float* __restrict__ A, const float* __restrict__ B, fl
 namespace fs {
 constexpr int D = 128;
 constexpr uint32_t WT = 0, QT = 16384, KH = 32768, UT = 49152, AQ = 65536, GAM = 73728, STAGE = 74240;
+constexpr uint32_t OUT = 2 * STAGE, TOTAL = OUT + 16384;  // output tile bf16 [64][128] behind the two stages
 constexpr uint32_t SACC = 0, SBF = 128, WSACC = 192, OACC = 256, VBF = 320, TMEM_COLS = 512;
 }  // namespace fs
 
@@ -174,15 +175,17 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
 
     uint32_t mma_phase = 0;
     bool ok = true;
+    KDA_PHASE_BEGIN();
     __nv_bfloat16* o = (__nv_bfloat16*)p.o;
     for (int lc = 0; lc < nc; ++lc) {
         const int stage = lc & 1;
         unsigned char* b = dyn + stage * STAGE;
         const ChunkInfo ci = chunk_info(p, c0 + lc);
         const size_t rec = (size_t)(c0 + lc) * p.H + h;
-        if (tid == 0 && lc + 1 < nc) issue_loads(lc + 1, stage ^ 1);
+        tma_store_wait_read();  // the previous chunk's output rows have left the staging tile
         ok = mbar_wait(&full[stage], (lc >> 1) & 1, p.status, 2);
         if (!__syncthreads_and(ok)) { ok = false; break; }
+        KDA_PHASE(0);
 
         // ---- A: BF16 copy of the entering state, checkpoint, decay
         {
@@ -203,6 +206,7 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
             }
             tmem_wait_st();
         }
+        KDA_PHASE(1);
         tc_fence_before();
         __syncthreads();
         if (tid == 0) {
@@ -218,10 +222,14 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
                 mma_ts(tmem0 + OACC, tmem0 + SBF + s * 8, make_desc(sb + QT + s * 256, 128, 2048), id_k, s > 0);
             mma_commit(&mmabar);
         }
+        // the next chunk's records are requested while the first MMA group runs (the other stage was
+        // last read by the previous chunk's MMAs, which have completed)
+        if (tid == 32 && lc + 1 < nc) issue_loads(lc + 1, stage ^ 1);
         ok = mbar_wait(&mmabar, mma_phase, p.status, 4);
         mma_phase ^= 1;
         tc_fence_after();
         if (!__syncthreads_and(ok)) { ok = false; break; }
+        KDA_PHASE(2);
 
         // ---- B: V'^T = U^T - (W S)^T
         {
@@ -250,6 +258,7 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
             }
             tmem_wait_st();
         }
+        KDA_PHASE(3);
         tc_fence_before();
         __syncthreads();
         if (tid == 0) {
@@ -269,17 +278,28 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
         mma_phase ^= 1;
         tc_fence_after();
         if (!__syncthreads_and(ok)) { ok = false; break; }
+        KDA_PHASE(4);
 
-        // ---- C: output rows
-        for (int i0 = 0; i0 < C; i0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(tmem + OACC + i0, r);
-            tmem_wait_ld();
+        // ---- C: output rows.  The accumulator holds O^T (lane = channel), so the tile is transposed
+        //      through shared memory and every valid row leaves as one 256-byte bulk store
+        {
+            __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(dyn + OUT);
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (i0 + j < ci.len)
-                    o[((size_t)(ci.tok0 + i0 + j) * p.H + h) * D + tid] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            for (int i0 = 0; i0 < C; i0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(tmem + OACC + i0, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) sO[(i0 + j) * D + tid] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+            fence_async_smem();
+            __syncthreads();
+            if (tid < ci.len) {
+                tma_store_1d(o + ((size_t)(ci.tok0 + tid) * p.H + h) * D, sO + tid * D, D * 2);
+                tma_store_commit();
+            }
         }
+        KDA_PHASE(5);
     }
     if (ok && p.ht) {
         for (int d0 = 0; d0 < D; d0 += 16) {
@@ -290,6 +310,7 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
             for (int j = 0; j < 16; ++j) p.ht[sbase + state_idx(p, d0 + j, tid)] = __uint_as_float(r[j]);
         }
     }
+    tma_store_wait_all();
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
@@ -498,7 +519,7 @@ cudaError_t tc_fwd(const KdaParams& p, cudaStream_t s) {
     if (stage_simt(p, ST_FWD_STATE)) {
         if ((e = simt_stage(p, ST_FWD_STATE, s)) != cudaSuccess) return e;
     } else {
-        constexpr int smem = 2 * fs::STAGE;
+        constexpr int smem = fs::TOTAL;
         if ((e = cudaFuncSetAttribute(kda_fwd_state_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return e;
         kda_fwd_state_tc<<<dim3(p.H, p.N), 128, smem, s>>>(p);
@@ -551,3 +572,5 @@ extern "C" int kda_selftest_mma(const float* A, const float* B, float* D, int N,
                                                                      lbo_b, sbo_b, step_b, neg_a, m_rows, status);
     return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
+
+KDA_PHASE_EXPORT(kda_debug_phases_state)

@@ -132,7 +132,7 @@ template <bool CONV>
 __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams p) {
     using namespace fi;
     extern __shared__ __align__(128) unsigned char dyn[];
-    __shared__ uint64_t bar;
+    __shared__ uint64_t bar, bar2;
     __shared__ uint32_t tmem_s;
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dyn + SQ);
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(dyn + SK);
@@ -172,7 +172,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         tmem_relinquish();
     }
     if (tid == 0) {
-        mbar_init(&bar, 1);
+        mbar_init(&bar, 3);   // three issuing threads commit the off-diagonal products
+        mbar_init(&bar2, 1);
         mbar_fence_init();
     }
 
@@ -440,16 +441,17 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 
     KDA_PHASE(3);
     // ---- 2: off-diagonal blocks on the tensor cores, diagonal blocks exactly on the CUDA cores
-    if (tid == 0) {
+    // (lane 0 of warps 0, 1, 2 issues the eight MMAs of block I = warp + 1: the accumulators are
+    //  independent, and no warp starts its share of the diagonal work a whole issue sequence late)
+    if (warp < 3 && lane == 0) {
         tc_fence_after();
         const uint32_t sb = smem_u32(dyn);
         constexpr uint32_t id = make_idesc(64, 32, false, false);
+        const int I = warp + 1;
 #pragma unroll
-        for (int I = 1; I <= 3; ++I)
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-                mma_ss(tmem0 + T_D + 32 * (I - 1), make_desc(sb + KSC + (I - 1) * 16384 + s * 256, 128, 2048),
-                       make_desc(sb + XSC + (I - 1) * 8192 + s * 256, 128, 2048), id, s > 0);
+        for (int s = 0; s < 8; ++s)
+            mma_ss(tmem0 + T_D + 32 * (I - 1), make_desc(sb + KSC + (I - 1) * 16384 + s * 256, 128, 2048),
+                   make_desc(sb + XSC + (I - 1) * 8192 + s * 256, 128, 2048), id, s > 0);
         mma_commit(&bar);
     }
     KDA_PHASE(10);
@@ -575,10 +577,10 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 #pragma unroll
         for (int s = 0; s < 4; ++s)
             mma_ss(tmem0 + T_U, make_desc(sb + BV + s * 4096, 2048, 128), make_desc(sb + KSC + s * 256, 128, 1024), id, s > 0);
-        mma_commit(&bar);
+        mma_commit(&bar2);
     }
     if (tid < D) gGam[tid] = ex2_approx(sG[(C - 1) * D + tid]);
-    ok = mbar_wait(&bar, 1, p.status, 8) && ok;
+    ok = mbar_wait(&bar2, 0, p.status, 8) && ok;
     tc_fence_after();
 
     KDA_PHASE(8);

@@ -34,7 +34,8 @@ constexpr uint32_t DOT = TMA_BYTES;         // dO    cm(i, e; 128);  later dVb^T
 constexpr uint32_t STG = DOT + 16384;       // f32 [64][128] staging for the beta row sums
 constexpr uint32_t SV = STG + 32768;        // v bf16 [64][128] row-major (prefetched with cp.async)
 constexpr uint32_t SBETA = SV + 16384;      // f32 [64] beta, f32 [64] row sums, f32 [2][128] partial dGamma_C
-constexpr uint32_t TOTAL = SBETA + 512 + 1024;
+constexpr uint32_t SKH = SBETA + 512 + 1024;   // f32 [64][128] staging of dKh (dQt and dKb are staged in DST once dS is dead)
+constexpr uint32_t TOTAL = SKH + 32768;
 constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bw
 
@@ -132,99 +133,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             mma_ss(tmem0 + DVB, make_desc(sb + DVT + s * 256, 128, 1024), make_desc(sb + TT + s * 2048, 1024, 128), id_km, s > 0);
         mma_commit(&mmabar);
     }
-    ok = mbar_wait(&mmabar, 0, p.status, 32) && ok;
-    tc_fence_after();
-    KDA_PHASE(2);
-
-    // ---- conversions after S1
-    {
-        float* gdQt = (float*)(sc + L.dQt) + rec * C * D;
-        float* gdKh = (float*)(sc + L.dKh) + rec * C * D;
-        __nv_bfloat16* dv = (__nv_bfloat16*)p.grad_v;
-        __nv_bfloat16* sdvb = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
-        const __nv_bfloat16* sv = reinterpret_cast<const __nv_bfloat16*>(dyn + SV);
-#pragma unroll 1
-        for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
-            uint32_t r[16], pk[8];
-            tmem_ld16(tmem + DWN + i0, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-            tmem_st8(tmem + WBF + i0 / 2, pk);
-            tmem_ld16(tmem + DQT + i0, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) gdQt[(i0 + j) * D + ch] = __uint_as_float(r[j]);
-            tmem_ld16(tmem + DKH + i0, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) gdKh[(i0 + j) * D + ch] = __uint_as_float(r[j]);
-            tmem_ld16(tmem + DVB + i0, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-            *reinterpret_cast<uint4*>(sdvb + cm_idx(ch, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            *reinterpret_cast<uint4*>(sdvb + cm_idx(ch, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int i = i0 + j;
-                const float x = __uint_as_float(r[j]);
-                const float vv = __bfloat162float(sv[i * D + ch]);  // zero on padding rows
-                if (i < ci.len) dv[tok(i) * D + ch] = __float2bfloat16_rn(sbeta[i] * x);
-                stg[i * D + ch] = x * vv;
-            }
-        }
-        // dAqk: rows of the M = 64 accumulator sit in lanes 0..15 of every warp's quadrant
-        {
-            float* gdA = (float*)(sc + L.dAqk) + rec * C * C;
-            const int i = 16 * (warp & 3) + (lane & 15);
-#pragma unroll 1
-            for (int j0 = 32 * half; j0 < 32 * half + 32; j0 += 16) {
-                uint32_t r[16];
-                tmem_ld16(tmem + DAQK + j0, r);
-                tmem_wait_ld();
-                if (lane < 16) {
-                    float f[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) f[j] = (j0 + j <= i) ? __uint_as_float(r[j]) : 0.f;
-#pragma unroll
-                    for (int j = 0; j < 16; j += 4)
-                        *reinterpret_cast<float4*>(gdA + i * C + j0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-                }
-            }
-        }
-        tmem_wait_st();
-        fence_async_smem();
-    }
-    tc_fence_before();
-    __syncthreads();
-    KDA_PHASE(3);
-
-    // ---- S2
-    if (tid == 0) {
-        tc_fence_after();
-        constexpr uint32_t id_neg = make_idesc(128, 64, false, true, true);  // -WBF (TMEM) * T (MN-major)
-        constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
-#pragma unroll
-        for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DKB, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
-#pragma unroll
-        for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DWN, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
-#pragma unroll
-        for (int s = 0; s < 8; ++s)  // Z^T += S0 * dVb^T (MN-major B from cm(e, i; 64))
-            mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 2048, 1024, 128), id_mm, true);
-        mma_commit(&mmabar);
-    }
-    // meanwhile: beta row sums and dGamma_C * Gamma_C on the CUDA cores
-    {
-        const int hw = tid >> 4, c8 = (tid & 15) * 8;
-        for (int m = 0; m < 4; ++m) {
-            const int i = hw + 16 * m;
-            float s = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s += stg[i * D + c8 + j];
-            s = half_warp_sum(s);
-            if ((tid & 15) == 0) srow[i] = s;
-        }
+    {   // while the first MMA group runs:
         // dGamma_C[d] = sum_e dS[d][e] S0[d][e].  Both records are cm(e, d; 128): a warp reads, for one
         // octet of e, 8 rows x 4 channel groups = four contiguous 128-byte core matrices per load.
         const __nv_bfloat16* s0 = reinterpret_cast<const __nv_bfloat16*>(dyn + S0T);
@@ -252,10 +161,116 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
 #pragma unroll
             for (int j = 0; j < 8; ++j) spart[128 * eh + d8 + j] = acc[j];
         }
+        }
+    ok = mbar_wait(&mmabar, 0, p.status, 32) && ok;
+    tc_fence_after();
+    __syncthreads();  // every warp is done reading dS: its tile becomes the staging area of dQt
+    KDA_PHASE(2);
+
+    // ---- conversions after S1
+    {
+        // dQt, dKh (FP32 [64][128] records) and dv (BF16 rows) are transposed through shared memory
+        // (lane = channel, so every store is conflict-free) and leave as bulk copies after the barrier
+        float* sdq = reinterpret_cast<float*>(dyn + DST);
+        float* sdkh = reinterpret_cast<float*>(dyn + SKH);
+        __nv_bfloat16* sdvb = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
+        __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(dyn + SV);
+#pragma unroll 1
+        for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
+            uint32_t r[16], pk[8];
+            tmem_ld16(tmem + DWN + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            tmem_st8(tmem + WBF + i0 / 2, pk);
+            tmem_ld16(tmem + DQT + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sdq[(i0 + j) * D + ch] = __uint_as_float(r[j]);
+            tmem_ld16(tmem + DKH + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sdkh[(i0 + j) * D + ch] = __uint_as_float(r[j]);
+            tmem_ld16(tmem + DVB + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            *reinterpret_cast<uint4*>(sdvb + cm_idx(ch, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(sdvb + cm_idx(ch, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int i = i0 + j;
+                const float x = __uint_as_float(r[j]);
+                const float vv = __bfloat162float(sv[i * D + ch]);  // zero on padding rows
+                sv[i * D + ch] = __float2bfloat16_rn(sbeta[i] * x);  // dv takes the place of v
+                stg[i * D + ch] = x * vv;
+            }
+        }
+        // dAqk: rows of the M = 64 accumulator sit in lanes 0..15 of every warp's quadrant
+        {
+            float* gdA = (float*)(sc + L.dAqk) + rec * C * C;
+            const int i = 16 * (warp & 3) + (lane & 15);
+#pragma unroll 1
+            for (int j0 = 32 * half; j0 < 32 * half + 32; j0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(tmem + DAQK + j0, r);
+                tmem_wait_ld();
+                if (lane < 16) {
+                    float f[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) f[j] = (j0 + j <= i) ? __uint_as_float(r[j]) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        *reinterpret_cast<float4*>(gdA + i * C + j0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                }
+            }
+        }
+        tmem_wait_st();
+        fence_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+        tma_store_1d((float*)(sc + L.dQt) + rec * C * D, dyn + DST, C * D * 4);
+        tma_store_1d((float*)(sc + L.dKh) + rec * C * D, dyn + SKH, C * D * 4);
+        tma_store_commit();
+    } else if (tid >= 64 && tid - 64 < ci.len) {
+        const int i = tid - 64;
+        tma_store_1d((__nv_bfloat16*)p.grad_v + tok(i) * D, dyn + SV + i * D * 2, D * 2);
+        tma_store_commit();
+    }
+    KDA_PHASE(3);
+
+    // ---- S2
+    if (tid == 0) {
+        tc_fence_after();
+        constexpr uint32_t id_neg = make_idesc(128, 64, false, true, true);  // -WBF (TMEM) * T (MN-major)
+        constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DKB, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DWN, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)  // Z^T += S0 * dVb^T (MN-major B from cm(e, i; 64))
+            mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 2048, 1024, 128), id_mm, true);
+        mma_commit(&mmabar);
+    }
+    // meanwhile: beta row sums and dGamma_C * Gamma_C on the CUDA cores
+    {
+        const int hw = tid >> 4, c8 = (tid & 15) * 8;
+        for (int m = 0; m < 4; ++m) {
+            const int i = hw + 16 * m;
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s += stg[i * D + c8 + j];
+            s = half_warp_sum(s);
+            if ((tid & 15) == 0) srow[i] = s;
+        }
     }
     KDA_PHASE(4);
     ok = mbar_wait(&mmabar, 1, p.status, 32) && ok;
     tc_fence_after();
+    if (tid == 0) tma_store_wait_read();  // dQt has left the staging tile: dKb may take it
     __syncthreads();
     KDA_PHASE(5);
     if (tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
@@ -263,7 +278,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
 
     // ---- conversions after S2
     {
-        float* gdKb = (float*)(sc + L.dKb) + rec * C * D;
+        float* sdkb = reinterpret_cast<float*>(dyn + DST);
         __nv_bfloat16* sz = reinterpret_cast<__nv_bfloat16*>(dyn + DVT);
 #pragma unroll 1
         for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
@@ -271,7 +286,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             tmem_ld16(tmem + DKB + i0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) gdKb[(i0 + j) * D + ch] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) sdkb[(i0 + j) * D + ch] = __uint_as_float(r[j]);
             tmem_ld16(tmem + DWN + i0, r);
             tmem_wait_ld();
             *reinterpret_cast<uint4*>(sz + cm_idx(ch, i0, C)) =
@@ -285,6 +300,10 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     }
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) {
+        tma_store_1d((float*)(sc + L.dKb) + rec * C * D, dyn + DST, C * D * 4);
+        tma_store_commit();
+    }
     KDA_PHASE(6);
 
     // ---- S3
@@ -321,6 +340,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         }
     }
     (void)ok;
+    tma_store_wait_all();
     tc_fence_before();
     __syncthreads();
     KDA_PHASE(8);

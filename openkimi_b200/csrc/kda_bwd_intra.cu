@@ -30,8 +30,8 @@ constexpr uint32_t SG = SK + 16384;          // G f32 [64][128]
 constexpr uint32_t SDA = SG + 32768;         // dAqk f32 [64][64]
 constexpr uint32_t SDM = SDA + 16384;        // dM   f32 [64][64]
 constexpr uint32_t STG = SDM + 16384;        // staging f32 [3][16][128]: dq, dk, dbeta terms of one block
-constexpr uint32_t PF = STG + 24576;         // f32 [3][64][128]: dQt, dKh, dKb of the whole chunk
-constexpr uint32_t SBETA = PF + 98304;       // f32 [64] 1/|q|, [64] 1/|k|, [64] beta, [64] dbeta
+constexpr uint32_t PF = STG + 24576;         // bf16 [3][64][128]: dQt, dKh, dKb of the whole chunk
+constexpr uint32_t SBETA = PF + 49152;       // f32 [64] 1/|q|, [64] 1/|k|, [64] beta, [64] dbeta
 constexpr uint32_t SX = SBETA + 1024;        // f32 [2][2][128] block totals of dG, f32 [2][128] scratch
 constexpr uint32_t SRED = SX + 3072;         // f32 [8]
 constexpr uint32_t TOTAL = SRED + 64 + 256;
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     float* sdA = reinterpret_cast<float*>(dyn + SDA);
     float* sdM = reinterpret_cast<float*>(dyn + SDM);
     float* stg = reinterpret_cast<float*>(dyn + STG);
-    float* spf = reinterpret_cast<float*>(dyn + PF);
+    const __nv_bfloat16* spf = reinterpret_cast<const __nv_bfloat16*>(dyn + PF);
     float* srq = reinterpret_cast<float*>(dyn + SBETA);  // aux record order: 1/|q|, 1/|k|, beta
     float* srk = srq + 64;
     float* sbeta = srq + 128;
@@ -78,9 +78,9 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     char* sc = (char*)p.bwd_scratch;
     const size_t rec = (size_t)c * p.H + h;
-    const float* gdQt = (const float*)(sc + L.dQt) + rec * C * D;
-    const float* gdKh = (const float*)(sc + L.dKh) + rec * C * D;
-    const float* gdKb = (const float*)(sc + L.dKb) + rec * C * D;
+    const __nv_bfloat16* gdQt = (const __nv_bfloat16*)(sc + L.dQt) + rec * C * D;
+    const __nv_bfloat16* gdKh = (const __nv_bfloat16*)(sc + L.dKh) + rec * C * D;
+    const __nv_bfloat16* gdKb = (const __nv_bfloat16*)(sc + L.dKb) + rec * C * D;
     const bool l2 = p.flags & KDA_FLAG_QK_L2NORM, gate = p.flags & KDA_FLAG_GATE, sig = p.flags & KDA_FLAG_BETA_SIGMOID;
     const float scale = p.scale;
     const float expA = gate ? expf(p.A_log[h]) : 1.f;
@@ -102,10 +102,10 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         tma_load_1d(sdA, (const float*)(sc + L.dAqk) + rec * C * C, C * C * 4, &barA);
         tma_load_1d(sdM, (const float*)(sc + L.dM) + rec * C * C, C * C * 4, &barA);
         tma_load_1d(srq, (const float*)(ws + L.aux) + rec * 3 * C, 3 * C * 4, &barA);  // 1/|q|, 1/|k|, beta
-        mbar_expect_tx(&barB, 3 * C * D * 4);
-        tma_load_1d(spf, gdQt, C * D * 4, &barB);
-        tma_load_1d(spf + C * D, gdKh, C * D * 4, &barB);
-        tma_load_1d(spf + 2 * C * D, gdKb, C * D * 4, &barB);
+        mbar_expect_tx(&barB, 3 * C * D * 2);
+        tma_load_1d(dyn + PF, gdQt, C * D * 2, &barB);
+        tma_load_1d(dyn + PF + C * D * 2, gdKh, C * D * 2, &barB);
+        tma_load_1d(dyn + PF + 2 * C * D * 2, gdKb, C * D * 2, &barB);
     }
     const int c8 = (tid & 15) * 8;
     if (tid < C) sdb[tid] = ((const float*)(sc + L.dbp))[rec * C + tid];
@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 #pragma unroll 8
             for (int r = 0; r < 32; ++r) {
                 const int i = 32 * gp + r;
-                s = fmaf(spf[(C + i) * D + d], __bfloat162float(sK[i * D + d]) * ex2_approx(gl - sG[i * D + d]), s);
+                s = fmaf(__bfloat162float(spf[(C + i) * D + d]), __bfloat162float(sK[i * D + d]) * ex2_approx(gl - sG[i * D + d]), s);
             }
             sscr[128 * gp + d] = s;
         }
@@ -295,7 +295,8 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
                 const float bi_ = sbeta[ii];
                 const float gam = ex2_approx(Gm[i]), eta = ex2_approx(gl - Gm[i]);
-                const float dQt = spf[ii * D + d], dKh = spf[(C + ii) * D + d], dKb = spf[(2 * C + ii) * D + d];
+                const float dQt = __bfloat162float(spf[ii * D + d]), dKh = __bfloat162float(spf[(C + ii) * D + d]),
+                            dKb = __bfloat162float(spf[(2 * C + ii) * D + d]);
                 const float diag = scale * sdiag[ii];
                 const float dq_in = scale * a1[i], dk_row = bi_ * a2[i], dKt = bi_ * dKb;
                 stg[(0 * B + li) * D + d] = dq_in + diag * ki + scale * dQt * gam;

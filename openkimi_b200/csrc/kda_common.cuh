@@ -116,13 +116,15 @@ __host__ __device__ inline WsLayout ws_layout(int NT, int H, int dk, int dv, int
     w.dbias_part = off; off = align256(off + n * dk * 4);
     // Two-kernel backward of the BF16 path: bwd_wy leaves dAqk and dM (float [64][64], lower
     // triangle; FP32 because the gate gradient is a difference of large terms built from them),
-    // the raw products dQt, dKh, d(beta K~) as float [64][dk], the beta gradient collected so
-    // far (float [64]) and dGamma_C * Gamma_C (float [dk]).
+    // the raw products dQt, dKh, d(beta K~) as [64][dk] in the element type (BF16 on the BF16 path:
+    // rounding them moves no gradient by more than 3e-4 relative L2, and they are half of the
+    // backward's hand-over traffic), the beta gradient collected so far (float [64]) and
+    // dGamma_C * Gamma_C (float [dk]).
     w.dAqk = off; off = align256(off + n * C * C * 4);
     w.dM = off;   off = align256(off + n * C * C * 4);
-    w.dQt = off;  off = align256(off + n * C * dk * 4);
-    w.dKh = off;  off = align256(off + n * C * dk * 4);
-    w.dKb = off;  off = align256(off + n * C * dk * 4);
+    w.dQt = off;  off = align256(off + n * C * dk * es);
+    w.dKh = off;  off = align256(off + n * C * dk * es);
+    w.dKb = off;  off = align256(off + n * C * dk * es);
     w.dbp = off;  off = align256(off + n * C * 4);
     w.gC = off;   off = align256(off + n * dk * 4);
     w.bwd_total = off;

@@ -13,7 +13,7 @@
 // used, for which masking the intermediate T-gradient is irrelevant.)
 //
 // Outputs: dv, the beta gradient collected so far, dGamma_C * Gamma_C, and the hand-over
-// records of bwd_intra (dAqk, dM, dQt, dKh, dKb, all FP32).
+// records of bwd_intra (dAqk, dM in FP32; dQt, dKh, dKb in BF16).
 #include "kda_common.cuh"
 #include "kda_tc.cuh"
 
@@ -34,8 +34,8 @@ constexpr uint32_t DOT = TMA_BYTES;         // dO    cm(i, e; 128);  later dVb^T
 constexpr uint32_t STG = DOT + 16384;       // f32 [64][128] staging for the beta row sums
 constexpr uint32_t SV = STG + 32768;        // v bf16 [64][128] row-major (prefetched with cp.async)
 constexpr uint32_t SBETA = SV + 16384;      // f32 [64] beta, f32 [64] row sums, f32 [2][128] partial dGamma_C
-constexpr uint32_t SKH = SBETA + 512 + 1024;   // f32 [64][128] staging of dKh (dQt and dKb are staged in DST once dS is dead)
-constexpr uint32_t TOTAL = SKH + 32768;
+constexpr uint32_t SKH = SBETA + 512 + 1024;   // bf16 [64][128] staging of dKh (dQt and dKb are staged in the two halves of DST once dS is dead)
+constexpr uint32_t TOTAL = SKH + 16384;
 constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bw
 
@@ -169,10 +169,10 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
 
     // ---- conversions after S1
     {
-        // dQt, dKh (FP32 [64][128] records) and dv (BF16 rows) are transposed through shared memory
+        // dQt, dKh (BF16 [64][128] records) and dv (BF16 rows) are transposed through shared memory
         // (lane = channel, so every store is conflict-free) and leave as bulk copies after the barrier
-        float* sdq = reinterpret_cast<float*>(dyn + DST);
-        float* sdkh = reinterpret_cast<float*>(dyn + SKH);
+        __nv_bfloat16* sdq = reinterpret_cast<__nv_bfloat16*>(dyn + DST);
+        __nv_bfloat16* sdkh = reinterpret_cast<__nv_bfloat16*>(dyn + SKH);
         __nv_bfloat16* sdvb = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
         __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(dyn + SV);
 #pragma unroll 1
@@ -186,11 +186,11 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             tmem_ld16(tmem + DQT + i0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) sdq[(i0 + j) * D + ch] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) sdq[(i0 + j) * D + ch] = __float2bfloat16_rn(__uint_as_float(r[j]));
             tmem_ld16(tmem + DKH + i0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) sdkh[(i0 + j) * D + ch] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) sdkh[(i0 + j) * D + ch] = __float2bfloat16_rn(__uint_as_float(r[j]));
             tmem_ld16(tmem + DVB + i0, r);
             tmem_wait_ld();
 #pragma unroll
@@ -231,8 +231,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
-        tma_store_1d((float*)(sc + L.dQt) + rec * C * D, dyn + DST, C * D * 4);
-        tma_store_1d((float*)(sc + L.dKh) + rec * C * D, dyn + SKH, C * D * 4);
+        tma_store_1d((__nv_bfloat16*)(sc + L.dQt) + rec * C * D, dyn + DST, C * D * 2);
+        tma_store_1d((__nv_bfloat16*)(sc + L.dKh) + rec * C * D, dyn + SKH, C * D * 2);
         tma_store_commit();
     } else if (tid >= 64 && tid - 64 < ci.len) {
         const int i = tid - 64;
@@ -270,7 +270,6 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     KDA_PHASE(4);
     ok = mbar_wait(&mmabar, 1, p.status, 32) && ok;
     tc_fence_after();
-    if (tid == 0) tma_store_wait_read();  // dQt has left the staging tile: dKb may take it
     __syncthreads();
     KDA_PHASE(5);
     if (tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
@@ -278,7 +277,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
 
     // ---- conversions after S2
     {
-        float* sdkb = reinterpret_cast<float*>(dyn + DST);
+        __nv_bfloat16* sdkb = reinterpret_cast<__nv_bfloat16*>(dyn + DST + 16384);  // second half: dQt may still be leaving the first
         __nv_bfloat16* sz = reinterpret_cast<__nv_bfloat16*>(dyn + DVT);
 #pragma unroll 1
         for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
@@ -286,7 +285,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             tmem_ld16(tmem + DKB + i0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) sdkb[(i0 + j) * D + ch] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) sdkb[(i0 + j) * D + ch] = __float2bfloat16_rn(__uint_as_float(r[j]));
             tmem_ld16(tmem + DWN + i0, r);
             tmem_wait_ld();
             *reinterpret_cast<uint4*>(sz + cm_idx(ch, i0, C)) =
@@ -301,7 +300,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
-        tma_store_1d((float*)(sc + L.dKb) + rec * C * D, dyn + DST, C * D * 4);
+        tma_store_1d((__nv_bfloat16*)(sc + L.dKb) + rec * C * D, dyn + DST + 16384, C * D * 2);
         tma_store_commit();
     }
     KDA_PHASE(6);

@@ -72,12 +72,12 @@ def stage_model(name, d, C=64, es=2):
         "bwd_state": (6 * C * d * d + 2 * C * C * d, (4 * t + a + 4 * d) + (t + s)),
         # fused FP32-math backward (validation mode only)
         "bwd_chunk": (6 * C * d * d + 16 * C * C * d + 4 * C ** 3, (5 * t + C * es) + 2 * t + 2 * s + a + (4 * t + C * es)),
-        # dAqk, dWn, dQt, dKh (K=d), dVb, dKb, Z, dMn; reads dO, v, V', dV', S0, dS, T, W; writes dv and the FP32
-        # hand-over (dAqk, dM, dQt, dKh, dKb)
-        "bwd_wy": (10 * C * d * d + 8 * C * C * d, (2 * t) + 3 * t + 2 * s + a + (t + 2 * a4 + 3 * f4)),
+        # dAqk, dWn, dQt, dKh (K=d), dVb, dKb, Z, dMn; reads dO, v, V', dV', S0, dS, T, W; writes dv and the
+        # hand-over (dAqk, dM in FP32; dQt, dKh, dKb in the element type)
+        "bwd_wy": (10 * C * d * d + 8 * C * C * d, (2 * t) + 3 * t + 2 * s + a + (t + 2 * a4 + 3 * t)),
         # three pairwise products over the lower triangle (dense-tile count 6 C^2 d); reads the kept prologue and
         # the hand-over; writes dq, dk, dg, dbeta
-        "bwd_intra": (6 * C * C * d, (f4 + 2 * t + 3 * C * 4) + 2 * a4 + 3 * f4 + (3 * t + C * es)),
+        "bwd_intra": (6 * C * C * d, (f4 + 2 * t + 3 * C * 4) + 2 * a4 + 3 * t + (3 * t + C * es)),
         "param_reduce": (0, 4 * d + 4),
     }
     return m[name]
@@ -435,8 +435,8 @@ def main():
     # DRAM bytes per (chunk, head) unit from the committed ncu capture of the batch-4 case
     # (dram__bytes_read.sum + dram__bytes_write.sum over 768 units, profiles/kda_bf16_kernels_c1_batch4.md);
     # traffic grows in proportion to the units, so a full launch is that figure times its units
-    ncu_bytes_per_unit = {"fwd_intra": 140.2e3, "fwd_state": 84.5e3, "bwd_state": 87.2e3, "bwd_wy": 241.4e3,
-                          "bwd_intra": 227.2e3}
+    ncu_bytes_per_unit = {"fwd_intra": 141.0e3, "fwd_state": 88.2e3, "bwd_state": 85.3e3, "bwd_wy": 213.2e3,
+                          "bwd_intra": 170.5e3}
     traffic = ncu_bytes_per_unit[dom] * units if (dom in ncu_bytes_per_unit and w["d"] == 128 and not sub) else None
     roof.update({"kernel": dom, "kernel_ms": avg[dom], "peak_source": peaks["source"], "traffic": traffic,
                  "traffic_source": "ncu capture of 768 units, scaled by units" if traffic else None,

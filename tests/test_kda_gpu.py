@@ -113,6 +113,19 @@ def test_bf16_operands(B, T, H, d, fp32_math):
     assert dict((r[0], r[2]) for r in rows)["o"] < 5e-3
 
 
+@pytest.mark.parametrize("mask", [1, 2, 4, 8, 16, 31])
+def test_bf16_stage_mixing(mask, monkeypatch):
+    """Any stage of the BF16 path can be swapped for its FP32 CUDA-core counterpart (KDA_FLAG_SIMT_* in
+    the C ABI, OPENKIMI_B200_FP32_STAGES in the Python host): both families read and write the same
+    per-chunk records, so every mixture must stay within the BF16 tolerance of the oracle."""
+    monkeypatch.setenv("OPENKIMI_B200_FP32_STAGES", str(mask))
+    inp = O.make_inputs(2, 256, 2, 128, seed=21, dtype=torch.bfloat16)
+    h0, dht = _states(2, 2, 128)
+    ref = run_oracle(inp, h0=h0, dht=dht)
+    dev = run_device(inp, h0=h0, dht=dht)
+    assert_rows(compare(dev, ref, **BF16_TOL))
+
+
 def test_bf16_varlen_packed():
     cu = O.random_cu_seqlens(1024, 5, seed=1)
     inp = O.make_inputs(1, 1024, 2, 128, seed=8, dtype=torch.bfloat16)

@@ -123,7 +123,11 @@ def test_bf16_stage_mixing(mask, monkeypatch):
     h0, dht = _states(2, 2, 128)
     ref = run_oracle(inp, h0=h0, dht=dht)
     dev = run_device(inp, h0=h0, dht=dht)
-    assert_rows(compare(dev, ref, **BF16_TOL))
+    tensors = ("o", "ht", "dq", "dk", "dv", "dg", "dbeta", "ddt_bias", "dh0")
+    assert_rows(compare(dev, ref, names=tensors, **BF16_TOL))
+    # dA_log is two numbers here (H = 2), each a cancelling sum over all tokens of BF16-derived terms:
+    # the north-star bound (2e-2) applies, not the tighter relative-L2 bound of the large tensors
+    assert_rows(compare(dev, ref, names=("dA_log",), tol_max=2e-2, tol_l2=2e-2))
 
 
 def test_bf16_varlen_packed():

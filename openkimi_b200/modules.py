@@ -179,13 +179,22 @@ class KimiDeltaAttention(nn.Module):
             q = self._heads(self.q_conv(self.q_proj(x), cu_seqlens=cu_seqlens)[0])
             k = self._heads(self.k_conv(self.k_proj(x), cu_seqlens=cu_seqlens)[0])
             v = self._heads(self.v_conv(self.v_proj(x), cu_seqlens=cu_seqlens)[0])
-        raw_decay = self._heads(self.f_b_proj(self.f_a_proj(x)))
-        beta_logits = self.beta_proj(x)
+        # The three narrow projections of x (decay rank, output-gate rank, beta) share one GEMM: x is
+        # read once instead of three times, and the backward has one input-gradient GEMM instead of
+        # three plus two additions.  Same parameters, same arithmetic per output column.
+        hd, nh = self.head_dim, self.n_heads
+        pad = (-(2 * hd + nh)) % 8
+        w_narrow = torch.cat([self.f_a_proj.weight, self.out_gate_a.weight, self.beta_proj.weight]
+                             + ([self.beta_proj.weight.new_zeros(pad, self.d_model)] if pad else []), dim=0)
+        narrow = torch.nn.functional.linear(x, w_narrow)
+        decay_rank, gate_rank = narrow[..., :hd], narrow[..., hd:2 * hd]
+        beta_logits = narrow[..., 2 * hd:2 * hd + nh].contiguous()
+        raw_decay = self._heads(self.f_b_proj(decay_rank))
         out, _ = chunk_kda(q=q, k=k, v=v, g=raw_decay, beta=beta_logits, A_log=self.A_log,
                            dt_bias=self.dt_bias.reshape(-1), scale=self.scale, use_qk_l2norm_in_kernel=True,
                            use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True, safe_gate=False,
                            output_final_state=False, state_v_first=True, cu_seqlens=cu_seqlens,
                            disable_recompute=self.disable_recompute, short_conv_weights=conv_w)
-        gate = self._heads(self.out_gate_b(self.out_gate_a(x)))
+        gate = self._heads(self.out_gate_b(gate_rank))
         out = self.out_norm_gate(out, gate).flatten(2)
         return self.out_proj(out)

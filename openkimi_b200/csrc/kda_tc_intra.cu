@@ -365,14 +365,6 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     fence_async_smem();
     __syncthreads();
     KDA_PHASE(2);
-    if (tid == 0) {  // prologue results for the backward: three bulk stores straight from shared memory
-        tma_store_1d((float*)(ws + L.Gc) + rec * C * D, sG, C * D * 4);
-        tma_store_1d((__nv_bfloat16*)(ws + L.Qn) + rec * C * D, sQ, C * D * 2);
-        tma_store_1d((__nv_bfloat16*)(ws + L.Kn) + rec * C * D, sK, C * D * 2);
-        tma_store_1d((float*)(ws + L.aux) + rec * 3 * C, saux, 3 * C * 4);
-        tma_store_commit();
-    }
-
     // ---- 1: decay-scaled operands.  A warp takes 8 rows x 4 channel groups at a time, so that its
     //      16-byte stores into the core-matrix tiles cover four whole 128-byte core matrices
     //      (no bank conflicts; the row-major loads of q^, k^, G take the conflicts instead, and
@@ -535,6 +527,15 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     __syncthreads();
 
     KDA_PHASE(5);
+    // (issued here rather than before the operand stage, whose shared-memory traffic they would share)
+    if (tid == 0) {  // prologue results for the backward: three bulk stores straight from shared memory
+        tma_store_1d((float*)(ws + L.Gc) + rec * C * D, sG, C * D * 4);
+        tma_store_1d((__nv_bfloat16*)(ws + L.Qn) + rec * C * D, sQ, C * D * 2);
+        tma_store_1d((__nv_bfloat16*)(ws + L.Kn) + rec * C * D, sK, C * D * 2);
+        tma_store_1d((float*)(ws + L.aux) + rec * 3 * C, saux, 3 * C * 4);
+        tma_store_commit();
+    }
+
     // ---- 3: T = (I + diag(beta) L)^-1, column by column.  Column c of T depends only on
     //      column c of the blocks above it, so one lane carries a whole column in registers:
     //      warp w owns block column J = w % 4, columns 8 (w / 4) + lane % 8, and its four lane

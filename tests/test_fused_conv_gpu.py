@@ -69,6 +69,13 @@ def test_fused_varlen_with_initial_state(recompute):
     _same(a, b)
 
 
+@pytest.mark.parametrize("T", [1, 3, 4, 66])
+def test_fused_tiny_sequences(T):
+    """Fewer tokens than filter taps, and a chunk border with a one-row halo."""
+    t = _inputs(2, T, 2, 128, 4, seed=90 + T)
+    _same(_run(t, True), _run(t, False))
+
+
 def test_fused_against_oracle():
     """Oracle: the reference's conv1d + SiLU (k3mini/model.py:76-88) in FP32 rounded to BF16 like the
     module's output, then the recurrent KDA oracle."""

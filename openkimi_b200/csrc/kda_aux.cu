@@ -217,13 +217,23 @@ __global__ void __launch_bounds__(512 / sizeof(T)) short_conv_bwd_kernel(const T
     }
 }
 
-// out[i] = sum_p part[p][i]
-__global__ void partial_reduce_kernel(const float* __restrict__ part, float* __restrict__ out, int n_partial, int n) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    float s = 0.f;
-    for (int p = 0; p < n_partial; ++p) s += part[(size_t)p * n + i];
-    out[i] = s;
+// out[i] = sum_p part[p][i] in a fixed order: a block takes 32 outputs; its eight warps sum the
+// partials p = w, w + 8, ... (independent loads in flight), then warp 0 adds the eight sums in order.
+__global__ void __launch_bounds__(256) partial_reduce_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                                             int n_partial, int n) {
+    __shared__ float sacc[8][33];
+    const int x = threadIdx.x & 31, w = threadIdx.x >> 5, i = blockIdx.x * 32 + x;
+    float acc = 0.f;
+    if (i < n)
+        for (int p = w; p < n_partial; p += 8) acc += part[(size_t)p * n + i];
+    sacc[w][x] = acc;
+    __syncthreads();
+    if (w == 0 && i < n) {
+        float t = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) t += sacc[g][x];
+        out[i] = t;
+    }
 }
 
 // ---- RMSNorm(x) * w * sigmoid(gate): DIM / 8 (BF16) or DIM / 4 (FP32) lanes per row, 16-byte accesses
@@ -376,7 +386,7 @@ int kda_short_conv_bwd(const void* x, const float* weight, const void* dy, void*
         short_conv_bwd_kernel<float><<<grid, block, 0, s>>>((const float*)x, weight, (const float*)dy, (float*)dx, partial,
                                                             total, T, Cch, ksize, cu_seqlens, N);
     int n = Cch * ksize;
-    partial_reduce_kernel<<<(n + 255) / 256, 256, 0, s>>>(partial, dweight, n_partial, n);
+    partial_reduce_kernel<<<(n + 31) / 32, 256, 0, s>>>(partial, dweight, n_partial, n);
     return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
@@ -408,7 +418,7 @@ int kda_norm_gate_bwd(const void* x, const void* gate, const float* weight, cons
     if (dtype == KDA_DTYPE_BF16) { if (dim == 64) NG_BWD(__nv_bfloat16, 64); else NG_BWD(__nv_bfloat16, 128); }
     else { if (dim == 64) NG_BWD(float, 64); else NG_BWD(float, 128); }
 #undef NG_BWD
-    partial_reduce_kernel<<<(dim + 255) / 256, 256, 0, s>>>(partial, dweight, n_partial, dim);
+    partial_reduce_kernel<<<(dim + 31) / 32, 256, 0, s>>>(partial, dweight, n_partial, dim);
     return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 

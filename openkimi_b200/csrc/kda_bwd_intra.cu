@@ -116,15 +116,6 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     KDA_PHASE(1);
     KDA_PHASE(2);
 
-    // ---- guard of the four diagonal tiles (one tile = 16 rows x this warp's 32 channels)
-    unsigned guard_mask = 0;
-#pragma unroll 1
-    for (int I = 0; I < 4; ++I) {
-        float Gt[B], mid_unused;
-#pragma unroll
-        for (int r = 0; r < B; ++r) Gt[r] = sG[(B * I + r) * D + d];
-        if (guard_tile(Gt, p.guard_span, mid_unused)) guard_mask |= 1u << I;
-    }
     if (tid < C) {
         sdiag[tid] = sdA[tid * C + tid];
         sdA[tid * C + tid] = 0.f;
@@ -149,6 +140,9 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             c1[i] = 0.f;
             Gm[i] = gp ? Gb[HB + i] : Gb[i];
         }
+        // guard of this block's diagonal tile (one tile = 16 rows x this warp's 32 channels)
+        float mid;
+        const bool guarded = guard_tile(Gb, p.guard_span, mid);
         // ---- row sums of my 8 tokens over the earlier blocks: k_j 2^(r - G_j), r = G at this block's first row
         for (int J = 0; J < I; ++J) {
             float kd[B];
@@ -202,14 +196,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 qs[r] = scale * __bfloat162float(sQ[rr * D + d]);
                 kb[r] = sbeta[rr] * kk;
             }
-            if ((guard_mask >> I) & 1) {  // midpoint factorisation 2^(G_i - m) 2^(m - G_j)
-                float gmax = Gb[0], gmin = Gb[0];
-#pragma unroll
-                for (int r = 1; r < B; ++r) {
-                    gmax = fmaxf(gmax, Gb[r]);
-                    gmin = fminf(gmin, Gb[r]);
-                }
-                const float mid = 0.5f * (gmax + gmin);
+            if (guarded) {  // midpoint factorisation 2^(G_i - m) 2^(m - G_j), m = (max + min) / 2 per channel
 #pragma unroll
                 for (int r = 0; r < B; ++r) {
                     const float P = ex2_approx(Gb[r] - mid), N = ex2_approx(mid - Gb[r]);

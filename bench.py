@@ -435,8 +435,8 @@ def main():
     # DRAM bytes per (chunk, head) unit from the committed ncu capture of the batch-4 case
     # (dram__bytes_read.sum + dram__bytes_write.sum over 768 units, profiles/kda_bf16_kernels_c1_batch4.md);
     # traffic grows in proportion to the units, so a full launch is that figure times its units
-    ncu_bytes_per_unit = {"fwd_intra": 141.0e3, "fwd_state": 88.2e3, "bwd_state": 85.3e3, "bwd_wy": 213.2e3,
-                          "bwd_intra": 170.5e3}
+    ncu_bytes_per_unit = {"fwd_intra": 140.9e3, "fwd_state": 86.0e3, "bwd_state": 85.1e3, "bwd_wy": 206.5e3,
+                          "bwd_intra": 171.3e3}
     traffic = ncu_bytes_per_unit[dom] * units if (dom in ncu_bytes_per_unit and w["d"] == 128 and not sub) else None
     roof.update({"kernel": dom, "kernel_ms": avg[dom], "peak_source": peaks["source"], "traffic": traffic,
                  "traffic_source": "ncu capture of 768 units, scaled by units" if traffic else None,

@@ -188,6 +188,9 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     __nv_bfloat16* sRaw = reinterpret_cast<__nv_bfloat16*>(dyn + RAW);
     const int half = tid >> 7, dch = tid & 127;
     const int hw = tid >> 4, c8 = (tid & 15) * 8;
+    // gate parameters: requested before anything else so that their latency hides behind the tile copies
+    const float a_log_h = gate ? p.A_log[h] : 0.f;
+    const float bias = (gate && p.dt_bias) ? p.dt_bias[h * D + dch] : 0.f;
     float rb[4];
     float4 tap[2];
     if constexpr (CONV) {  // filter taps of this head, padded to four: entry e = tensor * 128 + channel
@@ -247,8 +250,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     __syncthreads();
     // ---- 0a: gate, channel-wise: thread (half, d) owns rows 32*half .. 32*half+31 of channel d
     {
-        const float negA = gate ? -expf(p.A_log[h]) : 0.f;
-        const float bias = (gate && p.dt_bias) ? p.dt_bias[h * D + dch] : 0.f;
+        const float negA = gate ? -expf(a_log_h) : 0.f;
         float run = 0.f;
 #pragma unroll
         for (int r = 0; r < 32; ++r) {

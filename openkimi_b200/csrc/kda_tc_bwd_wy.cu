@@ -62,6 +62,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
 
     KDA_PHASE_BEGIN();
+    // Gamma_C of my channel: requested now, used after the second MMA group
+    const float gam_c = tid < D ? ((const float*)(ws + L.gamC))[rec * D + tid] : 0.f;
     if (warp == 0) {
         tmem_alloc(&tmem_s, TMEM_COLS);
         tmem_relinquish();
@@ -273,7 +275,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     __syncthreads();
     KDA_PHASE(5);
     if (tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
-    if (tid < D) ((float*)(sc + L.gC))[rec * D + tid] = (spart[tid] + spart[128 + tid]) * ((const float*)(ws + L.gamC))[rec * D + tid];
+    if (tid < D) ((float*)(sc + L.gC))[rec * D + tid] = (spart[tid] + spart[128 + tid]) * gam_c;
 
     // ---- conversions after S2
     {

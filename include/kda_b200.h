@@ -99,6 +99,10 @@ typedef struct KdaParams {
      * none; BF16 with dk = 128 only (else KDA_ERR_UNSUPPORTED). */
     const float *conv_q, *conv_k, *conv_v;
     int32_t conv_ksize;         /* 1..4 */
+    /* Optional with cu_seqlens: device [NT][4] int32 = {sequence, chunk inside the sequence, first
+     * flattened token, valid rows} of every chunk, so that a CTA finds its chunk with one 16-byte load
+     * instead of three dependent ones through chunk_seq / seq_chunk_off / cu_seqlens (16-byte aligned). */
+    const int32_t *chunk_tab;
 } KdaParams;
 
 /* Bytes of forward workspace (saved for the backward) and of backward scratch for these

@@ -35,6 +35,7 @@ class KdaParams(C.Structure):
         ("bwd_scratch", C.c_void_p), ("bwd_scratch_bytes", C.c_size_t),
         ("status", C.c_void_p),
         ("conv_q", C.c_void_p), ("conv_k", C.c_void_p), ("conv_v", C.c_void_p), ("conv_ksize", C.c_int32),
+        ("chunk_tab", C.c_void_p),
     ]
 
 

@@ -59,7 +59,7 @@ static int validate(const KdaParams* p, bool bwd) {
     if ((p->flags & KDA_FLAG_GATE) && !p->A_log) return KDA_ERR_NULL;
     if (!(p->guard_span < 0.f) && !(isfinite(p->guard_span) && p->guard_span <= kda_guard_max_span()))
         return KDA_ERR_GUARD;
-    const void* ptrs[] = {p->q, p->k, p->v, p->g, p->o, p->workspace, p->h0, p->ht};
+    const void* ptrs[] = {p->q, p->k, p->v, p->g, p->o, p->workspace, p->h0, p->ht, p->chunk_tab};
     for (const void* x : ptrs)
         if (!aligned16(x)) return KDA_ERR_ALIGN;
     WsLayout L = ws_layout(p->NT, p->H, p->dk, p->dv, p->dtype);
@@ -87,7 +87,7 @@ using namespace kda;
 
 extern "C" {
 
-int kda_abi_version(void) { return 2; }
+int kda_abi_version(void) { return 3; }
 
 int kda_guard_version(void) { return 1; }
 float kda_guard_max_span(void) { return 232.0f; }

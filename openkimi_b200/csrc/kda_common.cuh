@@ -34,7 +34,13 @@ struct ChunkInfo {
 
 __device__ __forceinline__ ChunkInfo chunk_info(const KdaParams& p, int c) {
     ChunkInfo ci;
-    if (p.cu_seqlens != nullptr) {
+    if (p.cu_seqlens != nullptr && p.chunk_tab != nullptr) {
+        const int4 t = reinterpret_cast<const int4*>(p.chunk_tab)[c];
+        ci.seq = t.x;
+        ci.lc = t.y;
+        ci.tok0 = t.z;
+        ci.len = t.w;
+    } else if (p.cu_seqlens != nullptr) {
         ci.seq = p.chunk_seq[c];
         ci.lc = c - p.seq_chunk_off[ci.seq];
         long long s = p.cu_seqlens[ci.seq], e = p.cu_seqlens[ci.seq + 1];

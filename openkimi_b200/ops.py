@@ -34,9 +34,13 @@ def _chunk_tables_cached(cu: tuple, device_index: int):
     for c in counts:
         off.append(off[-1] + c)
     seq = [n for n, c in enumerate(counts) for _ in range(c)]
+    # per chunk: sequence, chunk inside the sequence, first flattened token, valid rows
+    tab = [(n, j, cu[n] + j * _lib.CHUNK, min(_lib.CHUNK, lens[n] - j * _lib.CHUNK))
+           for n, c in enumerate(counts) for j in range(c)]
     dev = torch.device("cuda", device_index)
     return (torch.tensor(seq if seq else [0], dtype=torch.int32, device=dev),
-            torch.tensor(off, dtype=torch.int32, device=dev), off[-1])
+            torch.tensor(off, dtype=torch.int32, device=dev), off[-1],
+            torch.tensor(tab if tab else [(0, 0, 0, 0)], dtype=torch.int32, device=dev))
 
 
 def _chunk_tables(cu_seqlens, cu_seqlens_cpu, device):
@@ -57,7 +61,7 @@ class _Call:
         self.cu = None
         if cu_seqlens is not None:
             self.cu = cu_seqlens.to(device=q.device, dtype=torch.int64).contiguous()
-            self.chunk_seq, self.seq_off, self.NT = _chunk_tables(cu_seqlens, cu_seqlens_cpu, q.device)
+            self.chunk_seq, self.seq_off, self.NT, self.chunk_tab = _chunk_tables(cu_seqlens, cu_seqlens_cpu, q.device)
             self.N = self.cu.numel() - 1
         else:
             self.chunk_seq = self.seq_off = None
@@ -78,6 +82,7 @@ class _Call:
             p.cu_seqlens = self.cu.data_ptr()
             p.chunk_seq = self.chunk_seq.data_ptr()
             p.seq_chunk_off = self.seq_off.data_ptr()
+            p.chunk_tab = self.chunk_tab.data_ptr()
         if conv is not None:
             p.conv_q, p.conv_k, p.conv_v = (w.data_ptr() for w in conv)
             p.conv_ksize = conv[0].shape[-1]

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.EXPORTS), declared ^ set(_lib.EXPORTS)
     for name in declared:
         assert getattr(lib, name) is not None
-    assert lib.kda_abi_version() == 2
+    assert lib.kda_abi_version() == 3
     assert lib.kda_guard_version() == 1 and lib.kda_guard_max_span() == 232.0
     assert lib.kda_guard_dot_precision() == b"tf32x3"
     assert b"NULL" in lib.kda_status_string(1)

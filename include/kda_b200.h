@@ -190,6 +190,13 @@ int kda_selftest_mma(const float *A, const float *B, float *D, int N, int K, int
                      int lbo_a, int sbo_a, int step_a, int lbo_b, int sbo_b, int step_b, int neg_a,
                      int m_rows, int *status, void *cuda_stream);
 
+/* Device self-test of the bounded wait (no reference counterpart): one CTA arms an mbarrier for
+ * twice the 256 bytes its single bulk copy delivers and polls at most poll_limit (1..4096) times.
+ * The wait runs out by construction; the kernel ORs `code` (1..255) into *status, waits for the
+ * copy that is in flight, copies the 64 floats src -> dst, frees its tensor memory and returns.
+ * The device stays usable; the tests use it to check that a given-up wait is reported. */
+int kda_selftest_wait(const float *src, float *dst, int poll_limit, int code, int *status, void *cuda_stream);
+
 const char *kda_status_string(int status);
 const char *kda_last_cuda_error(void);
 int kda_abi_version(void);

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_PKG, "libkda_b200.so")
 DTYPE_F32, DTYPE_BF16 = 0, 1
 FLAG_QK_L2NORM, FLAG_GATE, FLAG_BETA_SIGMOID, FLAG_STATE_V_FIRST, FLAG_FORCE_SIMT = 1, 2, 4, 8, 16
 CHUNK = 64
+ERR_DEVICE_WAIT = 7
 
 
 class KdaParams(C.Structure):
@@ -50,6 +51,7 @@ EXPORTS = {
     "kda_profile_read": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float), C.c_int]),
     "kda_guarded_diagonal_tiles": (C.c_int, [C.c_void_p] * 10 + [C.c_int, C.c_float, C.c_void_p]),
     "kda_selftest_mma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 12 + [C.c_void_p, C.c_void_p]),
+    "kda_selftest_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "kda_workspace_bytes": (C.c_int, [C.POINTER(KdaParams), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "kda_fwd": (C.c_int, [C.POINTER(KdaParams), C.c_void_p]),
     "kda_bwd": (C.c_int, [C.POINTER(KdaParams), C.c_void_p]),

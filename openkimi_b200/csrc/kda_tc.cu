@@ -96,6 +96,47 @@ mma_selftest_kernel(const float* __restrict__ A, const float* __restrict__ B, fl
 }
 
 // ---------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one CTA allocates tensor memory, arms an mbarrier for
+// 2 * bytes, issues ONE bulk copy of `bytes`, and polls at most `poll_limit` times.  The
+// wait must run out: the kernel records `code` in the status word, accounts for the bytes that
+// were never sent so that the barrier completes as soon as the copy that IS in flight has
+// landed, waits for that (bounded), frees its tensor memory and returns.  Nothing hangs.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128, 1) wait_selftest_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                               uint32_t poll_limit, int code, int* status) {
+    __shared__ __align__(128) float buf[64];
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_base_s;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    constexpr uint32_t BYTES = 64 * sizeof(float);
+    if (warp == 0) {
+        tmem_alloc(&tmem_base_s, 32);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (tid == 0) {
+        mbar_expect_tx(&bar, 2 * BYTES);  // twice what the copy below delivers
+        tma_load_1d(buf, src, BYTES, &bar);
+    }
+    bool ok = mbar_wait(&bar, 0, status, code, poll_limit);
+    ok = __syncthreads_and(ok);
+    if (!ok) {
+        if (tid == 0) mbar_complete_tx(&bar, BYTES);
+        const bool landed = mbar_wait(&bar, 0, status, code << 8);  // the copy in flight, default limit
+        if (__syncthreads_and(landed) && tid < 64) dst[tid] = buf[tid];
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base_s, 32);
+}
+
+// ---------------------------------------------------------------------------------------
 // fwd_state on tensor cores.  One CTA per (sequence, head); thread t owns value column
 // e = t, which is TMEM lane t.  The state is kept TRANSPOSED in tensor memory for the whole
 // sequence: Sacc[e][d] (FP32, 128 columns).  Per chunk:
@@ -570,6 +611,14 @@ extern "C" int kda_selftest_mma(const float* A, const float* B, float* D, int N,
     if (e != cudaSuccess) return KDA_ERR_LAUNCH;
     kda::mma_selftest_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(A, B, D, N, K, a_mode, b_mode, lbo_a, sbo_a, step_a,
                                                                      lbo_b, sbo_b, step_b, neg_a, m_rows, status);
+    return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
+
+extern "C" int kda_selftest_wait(const float* src, float* dst, int poll_limit, int code, int* status, void* stream) {
+    if (!src || !dst || !status) return KDA_ERR_NULL;
+    if (poll_limit < 1 || poll_limit > 4096 || code < 1 || code > 255) return KDA_ERR_SHAPE;
+    if (((uintptr_t)src & 15) != 0) return KDA_ERR_ALIGN;
+    kda::wait_selftest_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(src, dst, (uint32_t)poll_limit, code, status);
     return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 

@@ -69,11 +69,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after ~2^22 polls (each try_wait already blocks for a
 // hardware-defined interval), records the failure and returns false.
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          uint32_t limit = WAIT_LIMIT) {
+    for (uint32_t it = 0; it < limit; ++it)
         if (mbar_try_wait(bar, parity)) return true;
     if (status) atomicOr(status, code);
     return false;
+}
+// account for `bytes` of a transaction that will never arrive (used when a wait is abandoned, so that
+// the barrier still completes once the copies that ARE in flight have landed)
+__device__ __forceinline__ void mbar_complete_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.complete_tx.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------

@@ -105,14 +105,17 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         fence_async_smem();
     }
     KDA_PHASE(0);
+    // A wait that gives up has already recorded its code in the status word; from then on the CTA
+    // issues no MMA and stores nothing (ok is made uniform at every barrier) and leaves through the
+    // common exit, which frees its tensor memory.
     bool ok = mbar_wait(&full, 0, p.status, 16);
     tc_fence_before();
-    __syncthreads();
+    ok = __syncthreads_and(ok);
     KDA_PHASE(1);
 
     const uint32_t sb = smem_u32(dyn);
     // ---- S1
-    if (tid == 0) {
+    if (tid == 0 && ok) {
         tc_fence_after();
         constexpr uint32_t id_aqk = make_idesc(64, 64, false, true);
         constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
@@ -164,13 +167,13 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             for (int j = 0; j < 8; ++j) spart[128 * eh + d8 + j] = acc[j];
         }
         }
-    ok = mbar_wait(&mmabar, 0, p.status, 32) && ok;
+    ok = ok && mbar_wait(&mmabar, 0, p.status, 32);
     tc_fence_after();
-    __syncthreads();  // every warp is done reading dS: its tile becomes the staging area of dQt
+    ok = __syncthreads_and(ok);  // every warp is done reading dS: its tile becomes the staging area of dQt
     KDA_PHASE(2);
 
     // ---- conversions after S1
-    {
+    if (ok) {
         // dQt, dKh (BF16 [64][128] records) and dv (BF16 rows) are transposed through shared memory
         // (lane = channel, so every store is conflict-free) and leave as bulk copies after the barrier
         __nv_bfloat16* sdq = reinterpret_cast<__nv_bfloat16*>(dyn + DST);
@@ -232,7 +235,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     }
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) {
+    if (!ok) {
+    } else if (tid == 0) {
         tma_store_1d((__nv_bfloat16*)(sc + L.dQt) + rec * C * D, dyn + DST, C * D * 2);
         tma_store_1d((__nv_bfloat16*)(sc + L.dKh) + rec * C * D, dyn + SKH, C * D * 2);
         tma_store_commit();
@@ -244,7 +248,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     KDA_PHASE(3);
 
     // ---- S2
-    if (tid == 0) {
+    if (tid == 0 && ok) {
         tc_fence_after();
         constexpr uint32_t id_neg = make_idesc(128, 64, false, true, true);  // -WBF (TMEM) * T (MN-major)
         constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
@@ -270,15 +274,15 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         }
     }
     KDA_PHASE(4);
-    ok = mbar_wait(&mmabar, 1, p.status, 32) && ok;
+    ok = ok && mbar_wait(&mmabar, 1, p.status, 32);
     tc_fence_after();
-    __syncthreads();
+    ok = __syncthreads_and(ok);
     KDA_PHASE(5);
-    if (tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
-    if (tid < D) ((float*)(sc + L.gC))[rec * D + tid] = (spart[tid] + spart[128 + tid]) * gam_c;
+    if (ok && tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
+    if (ok && tid < D) ((float*)(sc + L.gC))[rec * D + tid] = (spart[tid] + spart[128 + tid]) * gam_c;
 
     // ---- conversions after S2
-    {
+    if (ok) {
         __nv_bfloat16* sdkb = reinterpret_cast<__nv_bfloat16*>(dyn + DST + 16384);  // second half: dQt may still be leaving the first
         __nv_bfloat16* sz = reinterpret_cast<__nv_bfloat16*>(dyn + DVT);
 #pragma unroll 1
@@ -301,14 +305,14 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     }
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) {
+    if (tid == 0 && ok) {
         tma_store_1d((__nv_bfloat16*)(sc + L.dKb) + rec * C * D, dyn + DST + 16384, C * D * 2);
         tma_store_commit();
     }
     KDA_PHASE(6);
 
     // ---- S3
-    if (tid == 0) {
+    if (tid == 0 && ok) {
         tc_fence_after();
         constexpr uint32_t id = make_idesc(64, 64, true, true);
 #pragma unroll
@@ -319,10 +323,10 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             mma_ss(tmem0 + DMN, make_desc(sb + DOT + s * 2048, 1024, 128), make_desc(sb + VT + s * 2048, 1024, 128), id, true);
         mma_commit(&mmabar);
     }
-    ok = mbar_wait(&mmabar, 0, p.status, 32) && ok;
+    ok = ok && mbar_wait(&mmabar, 0, p.status, 32);
     tc_fence_after();
     KDA_PHASE(7);
-    {
+    if (ok) {
         float* gdM = (float*)(sc + L.dM) + rec * C * C;
         const int i = 16 * (warp & 3) + (lane & 15);
 #pragma unroll 1
@@ -340,7 +344,6 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             }
         }
     }
-    (void)ok;
     tma_store_wait_all();
     tc_fence_before();
     __syncthreads();

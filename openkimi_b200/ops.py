@@ -51,6 +51,58 @@ def _chunk_tables(cu_seqlens, cu_seqlens_cpu, device):
     return _chunk_tables_cached(tuple(int(x) for x in host.tolist()), device.index or 0)
 
 
+class _DeviceStatus:
+    """One int32 status word per device.  A kernel whose bounded wait gives up ORs a code into it
+    (``KdaParams.status``); after every launch the word is copied to pinned host memory on the
+    same stream, and the next call on that device (or ``check_device_status``) raises if a copy
+    that has completed shows a non-zero word.  No synchronisation on the hot path."""
+
+    _per_device: dict = {}
+
+    def __init__(self, device):
+        self.dev = torch.zeros(1, dtype=torch.int32, device=device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+
+    @classmethod
+    def get(cls, device):
+        key = device.index if device.index is not None else torch.cuda.current_device()
+        st = cls._per_device.get(key)
+        if st is None:
+            st = cls._per_device[key] = cls(torch.device("cuda", key))
+        return st
+
+    def after_launch(self):
+        if torch.cuda.is_current_stream_capturing():
+            return  # a captured graph replays the kernels only; poll with check_device_status(sync=True)
+        self.host.copy_(self.dev, non_blocking=True)
+        self.event.record()
+        self.pending = True
+
+    def poll(self, sync=False):
+        if sync:
+            self.host.copy_(self.dev)
+            self.pending = False
+        elif not (self.pending and self.event.query()):
+            return
+        else:
+            self.pending = False
+        code = int(self.host[0])
+        if code:
+            self.dev.zero_()
+            self.host.zero_()
+            msg = _lib.load().kda_status_string(_lib.ERR_DEVICE_WAIT).decode()
+            raise RuntimeError(f"chunk_kda: {msg} (stage bits 0x{code:x}); the results of the affected call are invalid")
+
+
+def check_device_status(device=None, sync=True):
+    """Raise if a KDA kernel on ``device`` reported a bounded wait that gave up.  ``sync=True``
+    reads the status word now (blocking); ``sync=False`` only looks at copies already finished."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _DeviceStatus.get(dev).poll(sync=sync)
+
+
 class _Call:
     """Builds the KdaParams block for one forward (+ backward) call."""
 
@@ -86,6 +138,9 @@ class _Call:
         if conv is not None:
             p.conv_q, p.conv_k, p.conv_v = (w.data_ptr() for w in conv)
             p.conv_ksize = conv[0].shape[-1]
+        self.status = _DeviceStatus.get(q.device)
+        self.status.poll()  # a wait that gave up in an earlier call surfaces here
+        p.status = self.status.dev.data_ptr()
         self.p = p
         fb, bb = C.c_size_t(0), C.c_size_t(0)
         _lib.check(_lib.load().kda_workspace_bytes(C.byref(p), C.byref(fb), C.byref(bb)), "kda_workspace_bytes")
@@ -93,6 +148,16 @@ class _Call:
 
     def stream(self):
         return C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+
+
+_warned = set()
+
+
+def _warn_once(msg):
+    if msg not in _warned:
+        _warned.add(msg)
+        import warnings
+        warnings.warn(msg, RuntimeWarning, stacklevel=3)
 
 
 def _require_cuda(t):
@@ -145,6 +210,7 @@ class ChunkKDAFunction(torch.autograd.Function):
             p.workspace, p.workspace_bytes = ws.data_ptr(), call.fwd_bytes
             if call.NT > 0:
                 _lib.check(lib.kda_fwd(C.byref(p), call.stream()), "kda_fwd")
+                call.status.after_launch()
             elif ht is not None:
                 ht.copy_(h0 if h0 is not None else torch.zeros_like(ht))
         ctx.save_for_backward(q, k, v, g, beta, A_log, dt_bias, h0, cu_seqlens, cu_seqlens_cpu,
@@ -175,8 +241,9 @@ class ChunkKDAFunction(torch.autograd.Function):
             dq, dk_, dg = torch.empty_like(q), torch.empty_like(k), torch.empty_like(g)
             dv_, dbeta = torch.empty_like(v), torch.empty_like(beta)
             gate = bool(flags & _lib.FLAG_GATE)
-            dA = torch.zeros(H, dtype=torch.float32, device=q.device) if gate else None
-            dbias = torch.zeros(H * dk, dtype=torch.float32, device=q.device) if gate and dt_bias is not None else None
+            # written in full by the fixed-order reduction kernel (no zero fill needed)
+            dA = torch.empty(H, dtype=torch.float32, device=q.device) if gate else None
+            dbias = torch.empty(H * dk, dtype=torch.float32, device=q.device) if gate and dt_bias is not None else None
             dh0 = torch.empty(state_shape, dtype=torch.float32, device=q.device) if h0 is not None else None
             scratch = torch.empty(call.bwd_bytes, dtype=torch.uint8, device=q.device)
             p.o = dq.data_ptr()  # unused by the backward; must be non-NULL
@@ -191,9 +258,11 @@ class ChunkKDAFunction(torch.autograd.Function):
             p.bwd_scratch, p.bwd_scratch_bytes = scratch.data_ptr(), call.bwd_bytes
             if call.NT > 0:
                 _lib.check(lib.kda_bwd(C.byref(p), call.stream()), "kda_bwd")
+                call.status.after_launch()
             else:
-                for t in (dq, dk_, dv_, dg, dbeta):
-                    t.zero_()
+                for t in (dq, dk_, dv_, dg, dbeta, dA, dbias):
+                    if t is not None:
+                        t.zero_()
                 if dh0 is not None:
                     dh0.copy_(dht if dht is not None else torch.zeros_like(dh0))
             dconv = (None, None, None)
@@ -292,7 +361,11 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     # debugging / A-B measurement: bit s of this mask runs stage s (0 fwd_intra, 1 fwd_state,
     # 2 bwd_state, 3 bwd_chunk as one fused kernel, 4 bwd_wy) with FP32 CUDA-core arithmetic
     # instead of tensor cores
-    flags |= (int(os.environ.get("OPENKIMI_B200_FP32_STAGES", "0")) & 31) << 5
+    stage_mask = int(os.environ.get("OPENKIMI_B200_FP32_STAGES", "0")) & 31
+    if stage_mask:
+        _warn_once(f"OPENKIMI_B200_FP32_STAGES={stage_mask}: the selected KDA stages run the FP32 CUDA-core "
+                   "validation kernels instead of the tensor-core kernels (debugging switch, much slower)")
+    flags |= stage_mask << 5
     conv = (None, None, None)
     if short_conv_weights is not None:
         wq, wk, wv = short_conv_weights

@@ -155,6 +155,25 @@ def rms_norm_gate_oracle(x, gate_logits, weight, eps: float = 1e-6) -> torch.Ten
     return (xf * weight.float()).to(x.dtype) * gate_logits.sigmoid()
 
 
+def kda_sublayer_oracle(x, params, *, n_heads, head_dim, cu_seqlens=None, eps=1e-6, dtype=torch.float32):
+    """The reference branch of KimiDeltaAttention.forward (k3mini/model.py:190-227):
+    projections -> causal conv + SiLU -> head split -> prologue -> recurrent oracle -> gated
+    headwise RMSNorm -> output projection.  ``params`` uses the reference module's parameter
+    names (q_proj.weight, q_conv.weight, A_log, dt_bias, out_norm_gate.weight, ...)."""
+    w = lambda n: params[n].to(dtype)
+    xx = x.to(dtype)
+    heads = lambda t: t.view(*t.shape[:2], n_heads, head_dim)
+    q, k, v = (heads(short_conv_oracle(F.linear(xx, w(f"{n}_proj.weight")), w(f"{n}_conv.weight"), cu_seqlens))
+               for n in ("q", "k", "v"))
+    raw = heads(F.linear(F.linear(xx, w("f_a_proj.weight")), w("f_b_proj.weight")))
+    beta_logits = F.linear(xx, w("beta_proj.weight"))
+    o, _ = kda_oracle(q, k, v, raw, beta_logits, a_log=params["A_log"], dt_bias=params["dt_bias"].reshape(-1),
+                      scale=head_dim ** -0.5, cu_seqlens=cu_seqlens, dtype=dtype)
+    gate = heads(F.linear(F.linear(xx, w("out_gate_a.weight")), w("out_gate_b.weight")))
+    y = rms_norm_gate_oracle(o, gate, w("out_norm_gate.weight"), eps).flatten(2)
+    return F.linear(y.to(dtype), w("out_proj.weight"))
+
+
 def gate_tile_spans_oracle(raw, a_log, dt_bias, chunk=64, block=16, ch_tile=32) -> torch.Tensor:
     """log2 span of every [16 rows x 32 channels] tile of the within-chunk cumulative gate
     (scripts/profile_kda_gate_spans.py:21-56): first row of the tile minus the minimum."""

@@ -114,9 +114,44 @@ def main(ref_root: str) -> None:
         ng.weight.uniform_(0.5, 1.5)
     xo, go = torch.randn(2, 9, 3, 32), torch.randn(2, 9, 3, 32)
     misc["norm_gate"] = dict(x=xo, gate=go, weight=ng.weight.detach().clone(), out=ng(xo, go).detach())
+    # the head width the kernels serve (128), with gradients from the reference module's autograd
+    ng128 = ref.HeadwiseRMSNormGate(128, 1e-6)
+    with torch.no_grad():
+        ng128.weight.uniform_(0.5, 1.5)
+    x128 = torch.randn(2, 9, 3, 128).requires_grad_()
+    g128 = torch.randn(2, 9, 3, 128).requires_grad_()
+    dy128 = torch.randn(2, 9, 3, 128)
+    y128 = ng128(x128, g128)
+    y128.backward(dy128)
+    misc["norm_gate_128"] = dict(x=x128.detach().clone(), gate=g128.detach().clone(), weight=ng128.weight.detach().clone(),
+                                 dy=dy128, out=y128.detach().clone(), dx=x128.grad.clone(), dgate=g128.grad.clone(),
+                                 dweight=ng128.weight.grad.clone())
     torch.save(misc, os.path.join(HERE, "misc.pt"))
+
+    # the whole KimiDeltaAttention sublayer (model.py:132-227) through the reference's own module on
+    # its reference branch (recurrent FP32 oracle), FP32, two heads of 128: output, input gradient and
+    # the gradient of every parameter
+    from k3mini.backends import resolve_backend
+    from k3mini.config import KernelBackend, ModelConfig
+
+    torch.manual_seed(8)
+    cfg = ModelConfig(d_model=256, n_heads=2, kda_head_dim=128, kda_conv_kernel=4, kernel_backend=KernelBackend.REFERENCE)
+    mod = ref.KimiDeltaAttention(cfg, resolve_backend(KernelBackend.REFERENCE))
+    with torch.no_grad():
+        mod.dt_bias.normal_(0.0, 0.2)
+        mod.out_norm_gate.weight.uniform_(0.5, 1.5)
+    xs = torch.randn(2, 150, 256).requires_grad_()
+    dys = torch.randn(2, 150, 256)
+    ys = mod(xs)
+    ys.backward(dys)
+    torch.save(dict(state={k: v.detach().clone() for k, v in mod.state_dict().items()}, x=xs.detach().clone(), dy=dys,
+                    out=ys.detach().clone(), dx=xs.grad.clone(),
+                    grads={k: v.grad.clone() for k, v in mod.named_parameters()}),
+               os.path.join(HERE, "sublayer.pt"))
     print("wrote", sorted(os.listdir(HERE)))
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    main(sys.argv[1])

@@ -110,3 +110,19 @@ def test_full_length_sequence_against_oracle():
     rows = compare(dev, ref, tol_max=2e-2, tol_l2=7e-3)
     assert_rows(rows)
     assert dict((r[0], r[2]) for r in rows)["o"] < 5e-3
+
+
+def test_c1_shape_two_sequences_six_heads_against_oracle():
+    """Configuration 1's head count and length, two of its sixteen sequences ([2,2048,6,128], BF16) against
+    the recurrent oracle; the oracle runs one sequence at a time (its autograd graph holds ~3 GB each)."""
+    inp = make_inputs(2, 2048, 6, 128, seed=8, dtype=torch.bfloat16)
+    dev = run_device(inp)
+    refs = []
+    for b in range(2):
+        one = {k: (v[b:b + 1] if v.dim() >= 3 else v) for k, v in inp.items()}
+        refs.append(run_oracle(one))
+    ref = {k: (refs[0][k] + refs[1][k] if k in ("dA_log", "ddt_bias") else torch.cat([refs[0][k], refs[1][k]], 0))
+           for k in refs[0]}
+    rows = compare(dev, ref, tol_max=2e-2, tol_l2=7e-3)
+    assert_rows(rows)
+    assert dict((r[0], r[2]) for r in rows)["o"] < 5e-3

@@ -72,6 +72,46 @@ def test_gate_spans_conv_normgate(golden_dir):
     torch.testing.assert_close(O.rms_norm_gate_oracle(n["x"], n["gate"], n["weight"]), n["out"], atol=1e-6, rtol=1e-6)
 
 
+def test_norm_gate_128_and_sublayer_match_reference(golden_dir):
+    """The head width the kernels serve, and the whole sublayer composition, against results of
+    the reference's own modules (HeadwiseRMSNormGate, KimiDeltaAttention on its reference branch)."""
+    n = _load(golden_dir, "misc.pt")["norm_gate_128"]
+    x, g, w = (n[k].clone().requires_grad_(True) for k in ("x", "gate", "weight"))
+    y = O.rms_norm_gate_oracle(x, g, w)
+    y.backward(n["dy"])
+    for a, b in ((y.detach(), n["out"]), (x.grad, n["dx"]), (g.grad, n["dgate"]), (w.grad, n["dweight"])):
+        torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-5)
+    s = _load(golden_dir, "sublayer.pt")
+    params = {k: v.clone().requires_grad_(True) for k, v in s["state"].items()}
+    xs = s["x"].clone().requires_grad_(True)
+    ys = O.kda_sublayer_oracle(xs, params, n_heads=2, head_dim=128)
+    ys.backward(s["dy"])
+    torch.testing.assert_close(ys.detach(), s["out"], atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(xs.grad, s["dx"], atol=1e-5, rtol=1e-4)
+    for k, v in s["grads"].items():
+        torch.testing.assert_close(params[k].grad, v, atol=1e-4, rtol=1e-4, msg=lambda m, k=k: f"{k}: {m}")
+
+
+def test_state_extensions_against_fla_naive():
+    """Secondary check of what the reference's oracle does not cover (initial state, final state):
+    the third-party ``fla.ops.kda.naive.naive_recurrent_kda`` (upstream FLA, not the pinned fork),
+    where it is installed.  Test-only; skipped if the package or its signature is unavailable."""
+    naive = pytest.importorskip("fla.ops.kda.naive", reason="flash-linear-attention is not installed")
+    fn = getattr(naive, "naive_recurrent_kda", None)
+    if fn is None:
+        pytest.skip("naive_recurrent_kda is not in this FLA version")
+    d = O.make_inputs(2, 70, 2, 16, seed=9, fused=False)
+    h0 = torch.randn(2, 2, 16, 16, generator=torch.Generator().manual_seed(10)) * 0.3
+    o, s = O.kda_recurrent_oracle(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=h0, output_final_state=True,
+                                  scale=16 ** -0.5)
+    try:
+        o2, s2 = fn(d["q"], d["k"], d["v"], d["g"], d["beta"], scale=16 ** -0.5, initial_state=h0, output_final_state=True)
+    except TypeError as e:  # a different signature in another FLA version
+        pytest.skip(f"naive_recurrent_kda signature differs: {e}")
+    torch.testing.assert_close(o, o2.to(o.dtype), atol=2e-5, rtol=2e-5)
+    torch.testing.assert_close(s, s2.to(s.dtype), atol=2e-5, rtol=2e-5)
+
+
 def test_state_extensions_are_consistent():
     """h0 / final state / cu_seqlens have no reference counterpart: check them against the
     recurrence itself (running two halves with the carried state equals one run; packed

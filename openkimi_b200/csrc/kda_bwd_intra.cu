@@ -1,20 +1,39 @@
-// bwd_intra (BF16 path, d = 128): the guarded-diagonal intra-chunk backward, the reverse
+// bwd_intra (BF16 path, d = 128): the guarded intra-chunk backward on tensor cores, the reverse
 // cumulative sum of the gate gradient and the chain rule through gate / L2 norm / sigmoid.
-// One CTA per (chunk, head), one thread per channel d, so that everything that runs along
-// the token axis of one channel -- the pairwise decays, the cumulative sums -- is
-// thread-local, and one warp covers exactly the [16 rows x 32 channels] tile on which the
-// reference evaluates its span guard (experiments/kda_sm90/patch_fla_guarded_intra.py:35-63).
+// One CTA per (chunk, head).
 //
-// With D_ij = 2^(G_i - G_j) per channel (i >= j inside the chunk), dA = dAqk (lower
-// triangle), dM the gradient of I + diag(beta) L (strictly lower):
+// With D_ij = 2^(G_i - G_j) per channel (i >= j inside the chunk), dA = dAqk (strictly lower; its
+// diagonal is handled apart), dM the gradient of I + diag(beta) L (strictly lower):
 //   row side   a1_i = sum_{j<i} dA_ij k_j D_ij          a2_i = sum_{j<i} dM_ij k_j D_ij
 //   col side   c1_j = sum_{i>j} (scale dA_ij q_i + beta_i dM_ij k_i) D_ij
-// The chunk is cut into four 16-row blocks.  Off-diagonal block pairs always factorise
-// D_ij = 2^(G_i - r) 2^(r - G_j) with r = G at the first row of the later block (both factors
-// <= 1).  A diagonal block uses the midpoint factorisation 2^(G_i - m) 2^(m - G_j),
-// m = (max + min) / 2 per channel, only if its tile passes the guard (per-channel monotone
-// non-increasing, finite, max-over-channels span <= the runtime limit); otherwise every pair
-// gets its own exp2.  A negative limit therefore gives the exact evaluation everywhere.
+// The chunk is cut into four 16-row blocks; every [16 rows x 32 channels] tile is one guard tile
+// of the reference (experiments/kda_sm90/patch_fla_guarded_intra.py:35-63): per-channel monotone
+// non-increasing, finite, max-over-channels span <= the runtime limit.  A block X whose tile
+// passes gets the per-channel midpoint m_X = (max + min) / 2 as the reference of all its rows:
+//   keys      KN_j = k_j 2^(m_X - G_j)          queries   QP_i = scale q_i 2^(G_i - m_X),
+//                                                          KP_i = beta_i k_i 2^(G_i - m_X)
+// (every factor within 2^(+-116) at the 232 limit).  Per channel these are contractions over the
+// token index, so they run as tcgen05 MMAs with M = 128 channels:
+//   accR_J[d, i] = sum_{j in J} dA_ij KN_j[d]   (i >= 16 J;  same with dM)       K = 16
+//   accC_I[d, j] = sum_{i in I} dA_ij QP_i[d] + dM_ij KP_i[d]   (j < 16 (I+1))    K = 32
+// and the read-back applies the remaining factor, one exp2 per (row, block):
+//   a1_i = sum_{J <= I(i)} 2^(G_i - m_J) accR_J[d, i]        c1_j = sum_{I >= J(j)} 2^(m_I - G_j) accC_I[d, j]
+// (exponents <= 0 for J < I; inside the diagonal block the pair of factors is the midpoint
+// factorisation).  Precision: the gate gradient is a difference of large terms, plain TF32 products
+// fail it by percents; every operand is therefore split three ways into BF16 (x = p0 + p1 + p2, 24
+// bits) and each product runs as six BF16 passes (p0q0 + p0q1 + p1q0 + p1q1 + p0q2 + p2q0), which
+// is at least the "tf32x3" class of the reference's contract.  dA / dM arrive already split from
+// bwd_wy (three cm(i, j; 64) tiles each) and are used as they are.
+// A tile that fails the guard (or a negative limit = exact mode) has no usable midpoint.  Its rows
+// then take first-row references instead, which need no guard because every factor is <= 1:
+// keys use r = G at the first row of the NEXT block (KN_j = k_j 2^(r - G_j), read-back 2^(G_i - r) for
+// the rows of later blocks), queries use r' = G at the first row of their OWN block (QP_i = scale q_i
+// 2^(G_i - r'), read-back 2^(r' - G_j) for the columns of earlier blocks).  So every off-diagonal block
+// pair runs on the tensor cores whatever the guard says, and only the pairs INSIDE a rejected tile
+// are evaluated on the CUDA cores in FP32 with one exp2 per pair.  Rejected tiles therefore see the
+// same instructions with the guard on or off, hence the same bits.
+#include <type_traits>
+
 #include "kda_common.cuh"
 #include "kda_tc.cuh"
 
@@ -23,356 +42,494 @@ namespace kda {
 using namespace tc;
 
 namespace bi {
-constexpr int D = 128, NTHR = 256, B = 16, HB = 8;
-constexpr uint32_t SQ = 0;                   // q^ bf16 [64][128]
+constexpr int D = 128, NTHR = 256, B = 16;
+constexpr uint32_t SG = 0;                   // G f32 [64][128]
+constexpr uint32_t SQ = SG + 32768;          // q^ bf16 [64][128]
 constexpr uint32_t SK = SQ + 16384;          // k^ bf16 [64][128]
-constexpr uint32_t SG = SK + 16384;          // G f32 [64][128]
-constexpr uint32_t SDA = SG + 32768;         // dAqk f32 [64][64]
-constexpr uint32_t SDM = SDA + 16384;        // dM   f32 [64][64]
-constexpr uint32_t STG = SDM + 16384;        // staging f32 [3][16][128]: dq, dk, dbeta terms of one block
-constexpr uint32_t PF = STG + 24576;         // bf16 [3][64][128]: dQt, dKh, dKb of the whole chunk
-constexpr uint32_t SBETA = PF + 49152;       // f32 [64] 1/|q|, [64] 1/|k|, [64] beta, [64] dbeta
-constexpr uint32_t SX = SBETA + 1024;        // f32 [2][2][128] block totals of dG, f32 [2][128] scratch
-constexpr uint32_t SRED = SX + 3072;         // f32 [8]
-constexpr uint32_t TOTAL = SRED + 64 + 256;
+constexpr uint32_t SB = SK + 16384;          // dAqk p0 p1 p2, dM p0 p1 p2: six cm(i, j; 64) bf16 tiles
+constexpr uint32_t XB = SB + 49152;          // operand buffer X: three parts of cm(d, t; 64) bf16 [128][64]
+constexpr uint32_t YB = XB + 49152;          // operand buffer Y
+constexpr uint32_t SAUX = YB + 49152;        // f32 [64] 1/|q|, [64] 1/|k|, [64] beta
+constexpr uint32_t SDB = SAUX + 768;         // f32 [64] beta gradient so far
+constexpr uint32_t SDIAG = SDB + 256;        // f32 [64] diagonal of dAqk
+constexpr uint32_t SMID = SDIAG + 256;       // f32 [2][4][128] key / query reference of every block and channel
+constexpr uint32_t STOT = SMID + 4096;       // f32 [4][128] block totals of dG
+constexpr uint32_t SSCR = STOT + 2048;       // f32 [2][128]
+constexpr uint32_t SRED = SSCR + 1024;       // f32 [8]
+constexpr uint32_t SREJ = SRED + 64;         // int [4][4]: tile (block, channel group) rejected
+constexpr uint32_t TOTAL = SREJ + 64;
+// later uses of the operand buffers
+constexpr uint32_t PF = YB;                  // bf16 [3][64][128]: dQt, dKh, dKb (after the MMAs that read Y)
+constexpr uint32_t STG = SB;                 // f32 [3][32][128] staging of dq, dk, dbeta terms (once the split tiles are dead)
+constexpr uint32_t FA = XB;                  // f32 [2][4][16][16] diagonal blocks of dAqk, dM rebuilt for rejected tiles
+constexpr uint32_t CST = XB + 8192;          // f32 [2][16][128] column sums of a rejected tile, by thread
+constexpr uint32_t TMEM_COLS = 512;
+// The midpoint factors reach 2^(+-span/2) and the third BF16 part of an operand sits 2^-16 below its
+// value, so the whole FP32 exponent range is used up at span ~205: tiles pass on to the tensor cores
+// only up to TC_SPAN (the rest of the guard's range, up to 232, is evaluated exactly, which is the
+// stricter choice), and every operand is scaled by 2^SHIFT (undone in the read-back factor) to centre
+// the range: largest operand 2^(100+6), smallest third part ~2^(-100+6-7-16) > 2^-126.
+constexpr float TC_SPAN = 200.f, SHIFT = 6.f;
+__host__ __device__ constexpr uint32_t rcol(int J) { return 16u * J * (9 - J); }         // accR_J: 2 (64 - 16 J) columns
+__host__ __device__ constexpr uint32_t ccol(int I) { return 320u + 8u * I * (I + 1); }  // accC_I: 16 (I + 1) columns
 }  // namespace bi
 
-// 256 threads: thread (gp, d) = (tid / 128, tid % 128) owns channel d and, inside every 16-row
-// block, the 8 tokens 8 gp .. 8 gp + 7: their row sums a1, a2, their column sums c1 and their
-// final assembly all stay in its registers.
-// u[0..7] += dA[0..7] * qf + dM[0..7] * kf as packed two-wide FP32 FMAs (one issue slot per two
-// products); dA and dM point at eight consecutive floats in shared memory, 16-byte aligned
-__device__ __forceinline__ void col_accumulate(float2 (&u)[4], const float* dA, const float* dM, float qf, float kf) {
-    const float4 a0 = *reinterpret_cast<const float4*>(dA), a4 = *reinterpret_cast<const float4*>(dA + 4);
-    const float4 m0 = *reinterpret_cast<const float4*>(dM), m4 = *reinterpret_cast<const float4*>(dM + 4);
-    const float2 q2 = make_float2(qf, qf), k2 = make_float2(kf, kf);
-    u[0] = __ffma2_rn(make_float2(a0.x, a0.y), q2, __ffma2_rn(make_float2(m0.x, m0.y), k2, u[0]));
-    u[1] = __ffma2_rn(make_float2(a0.z, a0.w), q2, __ffma2_rn(make_float2(m0.z, m0.w), k2, u[1]));
-    u[2] = __ffma2_rn(make_float2(a4.x, a4.y), q2, __ffma2_rn(make_float2(m4.x, m4.y), k2, u[2]));
-    u[3] = __ffma2_rn(make_float2(a4.z, a4.w), q2, __ffma2_rn(make_float2(m4.z, m4.w), k2, u[3]));
+// 256 threads: thread (h, d) = (tid / 128, tid % 128) owns channel d (= TMEM lane d) and two whole
+// 16-row blocks, {3, 0} for h = 0 and {2, 1} for h = 1 (slot 0, slot 1), so that a warp covers
+// exactly one guard tile per slot and both halves read back the same number of accumulators.
+__device__ __forceinline__ int bi_block(int h, int slot) { return slot == 0 ? 3 - h : h; }
+
+// eight operand values of one channel -> three BF16 parts, one 16-byte row of a core matrix each
+__device__ __forceinline__ void store_parts(unsigned char* buf, int d, int t0, const float (&v)[8]) {
+    uint32_t p0[4], p1[4], p2[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) split3_bf16(v[2 * j], v[2 * j + 1], p0[j], p1[j], p2[j]);
+    const uint32_t off = (uint32_t)cm_idx(d, t0, 64) * 2;
+    *reinterpret_cast<uint4*>(buf + off) = make_uint4(p0[0], p0[1], p0[2], p0[3]);
+    *reinterpret_cast<uint4*>(buf + 16384 + off) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
+    *reinterpret_cast<uint4*>(buf + 32768 + off) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
 }
 
 __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) {
     using namespace bi;
     extern __shared__ __align__(128) unsigned char dyn[];
-    __shared__ uint64_t barA, barB;
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dyn + SQ);
-    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(dyn + SK);
-    float* sG = reinterpret_cast<float*>(dyn + SG);
-    float* sdA = reinterpret_cast<float*>(dyn + SDA);
-    float* sdM = reinterpret_cast<float*>(dyn + SDM);
+    __shared__ uint64_t barA, barB, barH, mma1, mma2, mma3;
+    __shared__ uint32_t tmem_s;
+    const __nv_bfloat16* sQ = reinterpret_cast<const __nv_bfloat16*>(dyn + SQ);
+    const __nv_bfloat16* sK = reinterpret_cast<const __nv_bfloat16*>(dyn + SK);
+    const float* sG = reinterpret_cast<const float*>(dyn + SG);
+    const __nv_bfloat16* sB = reinterpret_cast<const __nv_bfloat16*>(dyn + SB);
     float* stg = reinterpret_cast<float*>(dyn + STG);
     const __nv_bfloat16* spf = reinterpret_cast<const __nv_bfloat16*>(dyn + PF);
-    float* srq = reinterpret_cast<float*>(dyn + SBETA);  // aux record order: 1/|q|, 1/|k|, beta
+    float* srq = reinterpret_cast<float*>(dyn + SAUX);  // aux record order: 1/|q|, 1/|k|, beta
     float* srk = srq + 64;
     float* sbeta = srq + 128;
-    float* sdb = srq + 192;
-    float* stotal = reinterpret_cast<float*>(dyn + SX);  // [parity][gp][d]
-    float* sscr = stotal + 512;                          // [gp][d]
+    float* sdb = reinterpret_cast<float*>(dyn + SDB);
+    float* sdiag = reinterpret_cast<float*>(dyn + SDIAG);
+    float* smid = reinterpret_cast<float*>(dyn + SMID);
+    float* stot = reinterpret_cast<float*>(dyn + STOT);
+    float* sscr = reinterpret_cast<float*>(dyn + SSCR);
     float* sred = reinterpret_cast<float*>(dyn + SRED);
-    float* sdiag = sred + 8;  // f32 [64]: diagonal of dAqk (cleared in sdA so that the pair loops need no mask)
+    int* srej = reinterpret_cast<int*>(dyn + SREJ);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid & 127, gp = tid >> 7;
-    const int c = blockIdx.x / p.H, h = blockIdx.x % p.H;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid & 127, h = tid >> 7, cg = warp & 3;
+    const int c = blockIdx.x / p.H, hd = blockIdx.x % p.H;
     const ChunkInfo ci = chunk_info(p, c);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     char* sc = (char*)p.bwd_scratch;
-    const size_t rec = (size_t)c * p.H + h;
-    const __nv_bfloat16* gdQt = (const __nv_bfloat16*)(sc + L.dQt) + rec * C * D;
-    const __nv_bfloat16* gdKh = (const __nv_bfloat16*)(sc + L.dKh) + rec * C * D;
-    const __nv_bfloat16* gdKb = (const __nv_bfloat16*)(sc + L.dKb) + rec * C * D;
+    const size_t rec = (size_t)c * p.H + hd;
     const bool l2 = p.flags & KDA_FLAG_QK_L2NORM, gate = p.flags & KDA_FLAG_GATE, sig = p.flags & KDA_FLAG_BETA_SIGMOID;
     const float scale = p.scale;
-    const float expA = gate ? expf(p.A_log[h]) : 1.f;
+    const float expA = gate ? expf(p.A_log[hd]) : 1.f;
     const float negA = -expA, rcpA = 1.f / expA;
-    auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
+    auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + hd); };
     KDA_PHASE_BEGIN();
-    // ---- everything the kernel reads arrives by bulk TMA: on barA what the pair sums need (G, the
-    //      normalised q and k, the row norms and beta kept by the forward; dAqk and dM from bwd_wy),
-    //      on barB the three [64][128] hand-over arrays that only the assembly needs
+    if (warp == 0) {
+        tmem_alloc(&tmem_s, TMEM_COLS);
+        tmem_relinquish();
+    }
+    // ---- everything the kernel reads arrives by bulk TMA: on barA what the operands are built from
+    //      (G, the normalised q and k, the row norms and beta kept by the forward), on barB the split
+    //      dAqk / dM tiles and the diagonal of dAqk from bwd_wy; the three [64][128] hand-over arrays
+    //      that only the assembly needs follow on barH once an operand buffer is free
     if (tid == 0) {
         mbar_init(&barA, 1);
         mbar_init(&barB, 1);
+        mbar_init(&barH, 1);
+        mbar_init(&mma1, 4);  // four issuing threads commit each MMA group (one accumulator block each)
+        mbar_init(&mma2, 4);
+        mbar_init(&mma3, 4);
         mbar_fence_init();
         const char* ws = (const char*)p.workspace;
-        mbar_expect_tx(&barA, C * D * 4 + 2 * C * D * 2 + 2 * C * C * 4 + 3 * C * 4);
-        tma_load_1d(sG, (const float*)(ws + L.Gc) + rec * C * D, C * D * 4, &barA);
-        tma_load_1d(sQ, (const __nv_bfloat16*)(ws + L.Qn) + rec * C * D, C * D * 2, &barA);
-        tma_load_1d(sK, (const __nv_bfloat16*)(ws + L.Kn) + rec * C * D, C * D * 2, &barA);
-        tma_load_1d(sdA, (const float*)(sc + L.dAqk) + rec * C * C, C * C * 4, &barA);
-        tma_load_1d(sdM, (const float*)(sc + L.dM) + rec * C * C, C * C * 4, &barA);
+        mbar_expect_tx(&barA, C * D * 4 + 2 * C * D * 2 + 3 * C * 4);
+        tma_load_1d(dyn + SG, (const float*)(ws + L.Gc) + rec * C * D, C * D * 4, &barA);
+        tma_load_1d(dyn + SQ, (const __nv_bfloat16*)(ws + L.Qn) + rec * C * D, C * D * 2, &barA);
+        tma_load_1d(dyn + SK, (const __nv_bfloat16*)(ws + L.Kn) + rec * C * D, C * D * 2, &barA);
         tma_load_1d(srq, (const float*)(ws + L.aux) + rec * 3 * C, 3 * C * 4, &barA);  // 1/|q|, 1/|k|, beta
-        mbar_expect_tx(&barB, 3 * C * D * 2);
-        tma_load_1d(dyn + PF, gdQt, C * D * 2, &barB);
-        tma_load_1d(dyn + PF + C * D * 2, gdKh, C * D * 2, &barB);
-        tma_load_1d(dyn + PF + 2 * C * D * 2, gdKb, C * D * 2, &barB);
+        mbar_expect_tx(&barB, 6 * C * C * 2 + C * 4);
+        tma_load_1d(dyn + SB, (const __nv_bfloat16*)(sc + L.dAM) + rec * 6 * C * C, 6 * C * C * 2, &barB);
+        tma_load_1d(sdiag, (const float*)(sc + L.dAd) + rec * C, C * 4, &barB);
     }
-    const int c8 = (tid & 15) * 8;
     if (tid < C) sdb[tid] = ((const float*)(sc + L.dbp))[rec * C + tid];
-    __syncthreads();  // barrier initialisation is visible
-    if (!mbar_wait(&barA, 0, p.status, 64)) return;  // uniform: every thread polls the same barrier
+    const float carry_in = ((const float*)(sc + L.gC))[rec * D + d];
+    tc_fence_before();
+    __syncthreads();  // barrier initialisation and the TMEM base address are visible
+    tc_fence_after();
+    const uint32_t tmem0 = tmem_s;
+    const uint32_t tlane = tmem0 + ((uint32_t)(32 * cg) << 16);  // this warp's lane quadrant
+    const uint32_t sb = smem_u32(dyn);
+    bool ok = mbar_wait(&barA, 0, p.status, 64);
     KDA_PHASE(0);
-    const float gl = sG[(C - 1) * D + d];
-    KDA_PHASE(1);
-    KDA_PHASE(2);
 
-    if (tid < C) {
-        sdiag[tid] = sdA[tid * C + tid];
-        sdA[tid * C + tid] = 0.f;
+    // ---- my two blocks: guard and midpoint of each tile; round 1: KN_j = k_j 2^(m - G_j) of my rows -> X
+    //      (the slot loops are kept rolled: straight-line code for both slots would not fit the
+    //       instruction cache, and every CTA runs it only once)
+    const float tc_span = fminf(p.guard_span, TC_SPAN);
+#pragma unroll 1
+    for (int s = 0; s < 2; ++s) {
+        const int blk = bi_block(h, s), b0 = B * blk;
+        float G[B], mid;
+#pragma unroll
+        for (int r = 0; r < B; ++r) G[r] = sG[(b0 + r) * D + d];
+        const bool pass = guard_tile(G, tc_span, mid);
+        // references of my rows as keys / as queries: the midpoint, or first rows when there is none
+        const float kref = pass ? mid : (blk < 3 ? sG[(b0 + B) * D + d] : -INFINITY), qref = pass ? mid : G[0];  // (block 3 has no later rows: zero keys)
+        smid[blk * D + d] = kref;
+        smid[(4 + blk) * D + d] = qref;
+        if (lane == 0) srej[blk * 4 + cg] = pass ? 0 : 1;
+#pragma unroll
+        for (int g8 = 0; g8 < 2; ++g8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                v[j] = __bfloat162float(sK[(b0 + 8 * g8 + j) * D + d]) * ex2_approx(kref - G[8 * g8 + j] + SHIFT);
+            store_parts(dyn + XB, d, b0 + 8 * g8, v);
+        }
     }
-    __syncthreads();
-    float carry = ((const float*)(sc + L.gC))[rec * D + d];
-    float dA_acc = 0.f, dbias_acc = 0.f;
-    __nv_bfloat16* dq_out = (__nv_bfloat16*)p.grad_q;
-    __nv_bfloat16* dk_out = (__nv_bfloat16*)p.grad_k;
-    __nv_bfloat16* dg_out = (__nv_bfloat16*)p.grad_g;
-    const int h0 = HB * gp;  // first of my 8 tokens inside a block
-    KDA_PHASE(3);
-
-    for (int I = 3; I >= 0; --I) {
-        float Gb[B], a1[HB], a2[HB], c1[HB], Gm[HB];
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    ok = ok && mbar_wait(&barB, 0, p.status, 64);
+    KDA_PHASE(1);
+    constexpr int PA[6] = {0, 0, 1, 1, 0, 2}, PB[6] = {0, 1, 0, 1, 2, 0};
+    // (descriptors: one base per buffer, the tile / part / block offset is added to its 14-bit address field)
+    const uint64_t dX = make_desc(sb + XB, 128, 1024), dY = make_desc(sb + YB, 128, 1024);
+    const uint64_t dBk = make_desc(sb + SB, 128, 1024), dBm = make_desc(sb + SB, 1024, 128);
+    // Lane 0 of warp J issues the MMAs of accumulator block J: the blocks are independent, and no warp
+    // falls a whole issue sequence behind the others.
+    const bool issuer = lane == 0 && warp < 4;
+    if (issuer && ok) {  // row side: accR_J = KN_J^T dA[i >= 16 J, J]^T (and dM), six passes each
+        tc_fence_after();
 #pragma unroll
-        for (int r = 0; r < B; ++r) Gb[r] = sG[(B * I + r) * D + d];
+        for (int J = 0; J < 4; ++J)
+            if (J == warp) {
+                const int N = 64 - B * J;
+                const uint32_t id = make_idesc(128, N, false, false);
 #pragma unroll
-        for (int i = 0; i < HB; ++i) {
-            a1[i] = 0.f;
-            a2[i] = 0.f;
-            c1[i] = 0.f;
-            Gm[i] = gp ? Gb[HB + i] : Gb[i];
-        }
-        // guard of this block's diagonal tile (one tile = 16 rows x this warp's 32 channels)
-        float mid;
-        const bool guarded = guard_tile(Gb, p.guard_span, mid);
-        // ---- row sums of my 8 tokens over the earlier blocks: k_j 2^(r - G_j), r = G at this block's first row
-        for (int J = 0; J < I; ++J) {
-            float kd[B];
+                for (int mat = 0; mat < 2; ++mat)
 #pragma unroll
-            for (int j = 0; j < B; ++j) {
-                const int jj = B * J + j;
-                kd[j] = __bfloat162float(sK[jj * D + d]) * ex2_approx(Gb[0] - sG[jj * D + d]);
+                    for (int ps = 0; ps < 6; ++ps)
+                        mma_ss(tmem0 + rcol(J) + mat * N, dX + ((PA[ps] * 16384 + 256 * J) >> 4),
+                               dBk + (((mat * 3 + PB[ps]) * 8192 + 2304 * J) >> 4), id, ps > 0);
             }
+        mma_commit(&mma1);
+    }
+    // references and guard decisions of all four blocks for my channel (group)
+    float kr4[4], qr4[4];
+    bool rej[4];
+    bool any_rej = false;
 #pragma unroll
-            for (int i = 0; i < HB; ++i) {
-                const int ii = B * I + h0 + i;
-                float2 u1 = make_float2(0.f, 0.f), u2 = u1;  // even / odd j in the two halves
+    for (int b = 0; b < 4; ++b) {
+        kr4[b] = smid[b * D + d];
+        qr4[b] = smid[(4 + b) * D + d];
+        rej[b] = srej[b * 4 + cg] != 0;
+    }
 #pragma unroll
-                for (int j4 = 0; j4 < B; j4 += 4) {
-                    const float4 a = *reinterpret_cast<const float4*>(sdA + ii * C + B * J + j4);
-                    const float4 m = *reinterpret_cast<const float4*>(sdM + ii * C + B * J + j4);
-                    const float2 k01 = make_float2(kd[j4], kd[j4 + 1]), k23 = make_float2(kd[j4 + 2], kd[j4 + 3]);
-                    u1 = __ffma2_rn(make_float2(a.x, a.y), k01, __ffma2_rn(make_float2(a.z, a.w), k23, u1));
-                    u2 = __ffma2_rn(make_float2(m.x, m.y), k01, __ffma2_rn(make_float2(m.z, m.w), k23, u2));
-                }
-                const float Pi = ex2_approx(Gm[i] - Gb[0]);
-                a1[i] = fmaf(Pi, u1.x + u1.y, a1[i]);
-                a2[i] = fmaf(Pi, u2.x + u2.y, a2[i]);
-            }
-        }
-        // ---- column sums of my 8 tokens over the later blocks: reference r' = G at their first row
-        for (int Ip = I + 1; Ip < 4; ++Ip) {
-            const float r2 = sG[(B * Ip) * D + d];
-            float2 u[HB / 2];
+    for (int b = 0; b < 16; ++b) any_rej = any_rej || srej[b] != 0;
+    // ---- round 2: QP_i = scale q_i 2^(G_i - ref) -> Y;  round 3: KP_i = beta_i k_i 2^(G_i - ref) -> X
+    auto query_operands = [&](const __nv_bfloat16* src, unsigned char* dst, bool with_beta) {
+#pragma unroll 1
+        for (int s = 0; s < 2; ++s) {
+            const int blk = bi_block(h, s), b0 = B * blk;
+            const float qref = blk == 0 ? qr4[0] : blk == 1 ? qr4[1] : blk == 2 ? qr4[2] : qr4[3];
 #pragma unroll
-            for (int j = 0; j < HB / 2; ++j) u[j] = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int i = 0; i < B; ++i) {
-                const int ii = B * Ip + i;
-                const float Pi = ex2_approx(sG[ii * D + d] - r2);
-                const float qp = scale * __bfloat162float(sQ[ii * D + d]) * Pi;
-                const float kp = sbeta[ii] * __bfloat162float(sK[ii * D + d]) * Pi;
-                col_accumulate(u, sdA + ii * C + B * I + h0, sdM + ii * C + B * I + h0, qp, kp);
-            }
-#pragma unroll
-            for (int j = 0; j < HB; ++j) c1[j] = fmaf(ex2_approx(r2 - Gm[j]), j & 1 ? u[j >> 1].y : u[j >> 1].x, c1[j]);
-        }
-        // ---- diagonal block: pairs (i, j) with j < i, at least one of them mine
-        {
-            float kj[B], qs[B], kb[B];
-#pragma unroll
-            for (int r = 0; r < B; ++r) {
-                const int rr = B * I + r;
-                const float kk = __bfloat162float(sK[rr * D + d]);
-                kj[r] = kk;
-                qs[r] = scale * __bfloat162float(sQ[rr * D + d]);
-                kb[r] = sbeta[rr] * kk;
-            }
-            if (guarded) {  // midpoint factorisation 2^(G_i - m) 2^(m - G_j), m = (max + min) / 2 per channel
-#pragma unroll
-                for (int r = 0; r < B; ++r) {
-                    const float P = ex2_approx(Gb[r] - mid), N = ex2_approx(mid - Gb[r]);
-                    kj[r] *= N;   // key side of the row sums
-                    qs[r] *= P;   // row side of the column sums
-                    kb[r] *= P;
-                }
-#pragma unroll
-                for (int i = 0; i < HB; ++i) {  // dA, dM vanish for j >= i (the diagonal of dA was moved to sdiag)
-                    const int ii = B * I + h0 + i;
-                    float2 u1 = make_float2(0.f, 0.f), u2 = u1;
-#pragma unroll
-                    for (int j4 = 0; j4 < B; j4 += 4) {
-                        const float4 a = *reinterpret_cast<const float4*>(sdA + ii * C + B * I + j4);
-                        const float4 m = *reinterpret_cast<const float4*>(sdM + ii * C + B * I + j4);
-                        const float2 k01 = make_float2(kj[j4], kj[j4 + 1]), k23 = make_float2(kj[j4 + 2], kj[j4 + 3]);
-                        u1 = __ffma2_rn(make_float2(a.x, a.y), k01, __ffma2_rn(make_float2(a.z, a.w), k23, u1));
-                        u2 = __ffma2_rn(make_float2(m.x, m.y), k01, __ffma2_rn(make_float2(m.z, m.w), k23, u2));
-                    }
-                    const float Pi = ex2_approx(Gm[i] - mid);
-                    a1[i] = fmaf(Pi, u1.x + u1.y, a1[i]);
-                    a2[i] = fmaf(Pi, u2.x + u2.y, a2[i]);
-                }
-                {  // column side: dA, dM vanish for i <= j
-                    float2 u[HB / 2];
-#pragma unroll
-                    for (int j = 0; j < HB / 2; ++j) u[j] = make_float2(0.f, 0.f);
-#pragma unroll
-                    for (int i = 1; i < B; ++i) {
-                        const int ii = B * I + i;
-                        col_accumulate(u, sdA + ii * C + B * I + h0, sdM + ii * C + B * I + h0, qs[i], kb[i]);
-                    }
-#pragma unroll
-                    for (int j = 0; j < HB; ++j) c1[j] = fmaf(ex2_approx(mid - Gm[j]), j & 1 ? u[j >> 1].y : u[j >> 1].x, c1[j]);
-                }
-            } else {  // one exp2 per pair
-#pragma unroll
-                for (int i = 0; i < HB; ++i) {
-                    const int li = h0 + i, ii = B * I + li;
-#pragma unroll
-                    for (int j = 0; j < B - 1; ++j) {
-                        const bool on = j < li;
-                        const float kp = on ? kj[j] * ex2_approx(Gm[i] - Gb[j]) : 0.f;
-                        a1[i] = fmaf(sdA[ii * C + B * I + j], kp, a1[i]);
-                        a2[i] = fmaf(sdM[ii * C + B * I + j], kp, a2[i]);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < HB; ++j) {
-                    const int lj = h0 + j, jj = B * I + lj;
-#pragma unroll
-                    for (int i = 1; i < B; ++i) {
-                        const bool on = i > lj;
-                        const float e = on ? ex2_approx(Gb[i] - Gm[j]) : 0.f;
-                        const float t = sdA[(B * I + i) * C + jj] * qs[i] + sdM[(B * I + i) * C + jj] * kb[i];
-                        c1[j] = fmaf(t, e, c1[j]);
-                    }
-                }
-            }
-        }
-        KDA_PHASE(4 + 4 * (3 - I));
-        if (I == 3) {
-            if (!mbar_wait(&barB, 0, p.status, 64)) return;
-            // term of the last row: dGamma_C Gamma_C + sum_i dKh_i Kh_i (each group sums its 32 rows);
-            // it joins the carry after the barrier that follows the assembly
-            float s = 0.f;
-#pragma unroll 8
-            for (int r = 0; r < 32; ++r) {
-                const int i = 32 * gp + r;
-                s = fmaf(__bfloat162float(spf[(C + i) * D + d]), __bfloat162float(sK[i * D + d]) * ex2_approx(gl - sG[i * D + d]), s);
-            }
-            sscr[128 * gp + d] = s;
-        }
-        KDA_PHASE(5 + 4 * (3 - I));
-
-        // ---- assembly of my 8 tokens, last first; run[i] = dG summed over the tokens >= i of my half
-        float runl[HB];
-        {
-            float acc = 0.f;
-#pragma unroll
-            for (int i = HB - 1; i >= 0; --i) {
-                const int li = h0 + i, ii = B * I + li;
-                const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
-                const float bi_ = sbeta[ii];
-                const float gam = ex2_approx(Gm[i]), eta = ex2_approx(gl - Gm[i]);
-                const float dQt = __bfloat162float(spf[ii * D + d]), dKh = __bfloat162float(spf[(C + ii) * D + d]),
-                            dKb = __bfloat162float(spf[(2 * C + ii) * D + d]);
-                const float diag = scale * sdiag[ii];
-                const float dq_in = scale * a1[i], dk_row = bi_ * a2[i], dKt = bi_ * dKb;
-                stg[(0 * B + li) * D + d] = dq_in + diag * ki + scale * dQt * gam;
-                stg[(1 * B + li) * D + d] = dk_row + c1[i] + diag * qi + dKt * gam + dKh * eta;
-                stg[(2 * B + li) * D + d] = ki * a2[i] + dKb * (ki * gam);
-                acc += qi * dq_in + ki * dk_row - ki * c1[i] + dQt * (scale * qi * gam) + dKt * (ki * gam) - dKh * (ki * eta);
-                runl[i] = acc;
-            }
-            stotal[((I & 1) * 2 + gp) * D + d] = acc;
-        }
-        // gate chain for one half: base = everything after my half's last token
-        auto finish = [&](float base) {
-#pragma unroll
-            for (int i = HB - 1; i >= 0; --i) {
-                const int ii = B * I + h0 + i;
-                if (ii < ci.len) {
-                    const float run = base + runl[i];
-                    const size_t off = tok(ii) * D + d;
-                    if (gate) {
-                        // per-token log decay g = (G_i - G_{i-1}) ln 2; sigmoid(x + b) = 1 - exp(-softplus) = -expm1(g / e^A)
-                        const float gprev = ii > 0 ? (i > 0 ? Gm[i - 1] : sG[(ii - 1) * D + d]) : 0.f;
-                        const float gnat = (Gm[i] - gprev) * 0.6931471805599453f;
-                        dA_acc = fmaf(run, gnat, dA_acc);
-                        const float dx = run * negA * (1.f - ex2_approx(gnat * rcpA * LOG2E));
-                        dbias_acc += dx;
-                        dg_out[off] = __float2bfloat16_rn(dx);
-                    } else {
-                        dg_out[off] = __float2bfloat16_rn(run);
-                    }
-                }
-            }
-        };
-        __syncthreads();
-        KDA_PHASE(6 + 4 * (3 - I));
-        if (I == 3) carry += sscr[d] + sscr[128 + d];
-        const float upper = stotal[((I & 1) * 2 + 1) * D + d];
-        finish(gp == 0 ? carry + upper : carry);
-        carry += upper + stotal[((I & 1) * 2 + 0) * D + d];
-        // ---- row-wise (one half warp per token): L2-norm chain, beta gradient, 16-byte stores
-        {
-            const int i = tid >> 4, ii = B * I + i;
-            float dq8[8], dk8[8], q8[8], k8[8], db = 0.f, dotq = 0.f, dotk = 0.f;
-            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sQ + ii * D + c8), q8);
-            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sK + ii * D + c8), k8);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                dq8[j] = stg[(0 * B + i) * D + c8 + j];
-                dk8[j] = stg[(1 * B + i) * D + c8 + j];
-                db += stg[(2 * B + i) * D + c8 + j];
-                dotq = fmaf(q8[j], dq8[j], dotq);
-                dotk = fmaf(k8[j], dk8[j], dotk);
-            }
-            db = half_warp_sum(db);
-            if (l2) {
-                dotq = half_warp_sum(dotq);
-                dotk = half_warp_sum(dotk);
-                const float rq = srq[ii], rk = srk[ii];
+            for (int g8 = 0; g8 < 2; ++g8) {
+                float v[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    dq8[j] = (dq8[j] - q8[j] * dotq) * rq;
-                    dk8[j] = (dk8[j] - k8[j] * dotk) * rk;
+                    const int t = b0 + 8 * g8 + j;
+                    const float w = with_beta ? sbeta[t] : scale;
+                    v[j] = w * __bfloat162float(src[t * D + d]) * ex2_approx(sG[t * D + d] - qref + SHIFT);
                 }
-            }
-            if (ii < ci.len) {
-                const size_t row = tok(ii);
-                *reinterpret_cast<uint4*>(dq_out + row * D + c8) = f32_to_bf16x8(dq8);
-                *reinterpret_cast<uint4*>(dk_out + row * D + c8) = f32_to_bf16x8(dk8);
-                if ((tid & 15) == 0) {
-                    float b = sbeta[ii], v = sdb[ii] + db;
-                    if (sig) v *= b * (1.f - b);
-                    ((__nv_bfloat16*)p.grad_beta)[row] = __float2bfloat16_rn(v);
-                }
+                store_parts(dst, d, b0 + 8 * g8, v);
             }
         }
-        __syncthreads();  // the staging buffer may be overwritten
-        KDA_PHASE(7 + 4 * (3 - I));
+    };
+    query_operands(sQ, dyn + YB, false);
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    KDA_PHASE(2);
+    if (issuer && ok) {  // column side, first half: accC_I = QP_I^T dA[I, j < 16 (I+1)]
+        tc_fence_after();
+#pragma unroll
+        for (int I = 0; I < 4; ++I)
+            if (I == warp) {
+                const uint32_t id = make_idesc(128, B * (I + 1), false, true);
+#pragma unroll
+                for (int ps = 0; ps < 6; ++ps)
+                    mma_ss(tmem0 + ccol(I), dY + ((PA[ps] * 16384 + 256 * I) >> 4), dBm + ((PB[ps] * 8192 + 2048 * I) >> 4), id, ps > 0);
+            }
+        mma_commit(&mma2);
     }
-    if (gate) {
-        sscr[128 * gp + d] = dbias_acc;
-        dA_acc = warp_sum(dA_acc);
-        if (lane == 0) sred[warp] = dA_acc;
-        __syncthreads();
-        if (gp == 0) ((float*)(sc + L.dbias_part))[rec * D + d] = sscr[d] + sscr[128 + d];
-        if (tid == 0) {
-            float t = 0.f;
-            for (int w = 0; w < 8; ++w) t += sred[w];
-            ((float*)(sc + L.dA_part))[rec] = t;
+    ok = ok && mbar_wait(&mma1, 0, p.status, 64);  // the row-side MMAs have read X
+    tc_fence_after();
+    query_operands(sK, dyn + XB, true);
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    KDA_PHASE(3);
+    if (issuer && ok) {  // column side, second half: accC_I += KP_I^T dM[I, j < 16 (I+1)]
+        tc_fence_after();
+#pragma unroll
+        for (int I = 0; I < 4; ++I)
+            if (I == warp) {
+                const uint32_t id = make_idesc(128, B * (I + 1), false, true);
+#pragma unroll
+                for (int ps = 0; ps < 6; ++ps)
+                    mma_ss(tmem0 + ccol(I), dX + ((PA[ps] * 16384 + 256 * I) >> 4), dBm + (((3 + PB[ps]) * 8192 + 2048 * I) >> 4), id, true);
+            }
+        mma_commit(&mma3);
+    }
+    // ---- the hand-over arrays may land in Y as soon as the MMAs that read Y are done
+    ok = ok && mbar_wait(&mma2, 0, p.status, 64);
+    if (tid == 0 && ok) {
+        mbar_expect_tx(&barH, 3 * C * D * 2);
+        tma_load_1d(dyn + PF, (const __nv_bfloat16*)(sc + L.dQt) + rec * C * D, C * D * 2, &barH);
+        tma_load_1d(dyn + PF + C * D * 2, (const __nv_bfloat16*)(sc + L.dKh) + rec * C * D, C * D * 2, &barH);
+        tma_load_1d(dyn + PF + 2 * C * D * 2, (const __nv_bfloat16*)(sc + L.dKb) + rec * C * D, C * D * 2, &barH);
+    }
+    ok = ok && mbar_wait(&mma3, 0, p.status, 64);
+    tc_fence_after();
+    KDA_PHASE(4);
+    const float* fA = reinterpret_cast<const float*>(dyn + FA);  // [4][16][16] diagonal blocks of dAqk
+    const float* fM = fA + 4 * B * B;                            // ... and of dM
+    if (any_rej) {  // uniform over the CTA: the diagonal blocks back to FP32 (x = p0 + p1 + p2) for the CUDA-core sums
+        float* w = reinterpret_cast<float*>(dyn + FA);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int e = tid + NTHR * u, mat = e >> 10, blk = (e >> 8) & 3, r = (e >> 4) & 15, j = e & 15;
+            const __nv_bfloat16* t = sB + mat * 3 * C * C + cm_idx(B * blk + r, B * blk + j, C);
+            w[e] = (__bfloat162float(t[0]) + __bfloat162float(t[C * C])) + __bfloat162float(t[2 * C * C]);
         }
     }
+    ok = ok && mbar_wait(&barH, 0, p.status, 64);
+    ok = __syncthreads_and(ok);  // (also: the rebuilt matrices are visible, the split tiles are dead -> staging area)
+    KDA_PHASE(5);
+
+    if (ok) {
+        const float gl = sG[(C - 1) * D + d];
+        // term of the last row: dGamma_C Gamma_C + sum_i dKh_i Kh_i (every thread sums the 32 rows of its half)
+        {
+            float sacc = 0.f;
+#pragma unroll 8
+            for (int r = 0; r < 32; ++r) {
+                const int i = 32 * h + r;
+                sacc = fmaf(__bfloat162float(spf[(C + i) * D + d]), __bfloat162float(sK[i * D + d]) * ex2_approx(gl - sG[i * D + d]), sacc);
+            }
+            sscr[128 * h + d] = sacc;
+        }
+        __nv_bfloat16* dq_out = (__nv_bfloat16*)p.grad_q;
+        __nv_bfloat16* dk_out = (__nv_bfloat16*)p.grad_k;
+        __nv_bfloat16* dg_out = (__nv_bfloat16*)p.grad_g;
+        const int c4 = (tid & 15) * 4;
+        float dA_acc = 0.f, dbias_acc = 0.f;
+#pragma unroll 1
+        for (int s = 0; s < 2; ++s) {
+            const int I = bi_block(h, s), b0 = B * I;
+            float G[B], a1[B], a2[B], c1[B];
+#pragma unroll
+            for (int r = 0; r < B; ++r) {
+                G[r] = sG[(b0 + r) * D + d];
+                a1[r] = a2[r] = c1[r] = 0.f;
+            }
+            // ---- row sums and column sums of my block from the accumulators (the pairs inside my own block
+            //      only if its tile passed the guard)
+#pragma unroll
+            for (int J = 0; J < 4; ++J)
+                if (J < I || (J == I && !rej[J])) {
+                    uint32_t ra[16], rm[16];
+                    const uint32_t col = tlane + rcol(J) + B * (I - J);
+                    tmem_ld16(col, ra);
+                    tmem_ld16(col + 64 - B * J, rm);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int r = 0; r < B; ++r) {
+                        const float f = ex2_approx(G[r] - kr4[J] - SHIFT);
+                        a1[r] = fmaf(f, __uint_as_float(ra[r]), a1[r]);
+                        a2[r] = fmaf(f, __uint_as_float(rm[r]), a2[r]);
+                    }
+                }
+#pragma unroll
+            for (int Ip = 0; Ip < 4; ++Ip)
+                if (Ip > I || (Ip == I && !rej[Ip])) {
+                    uint32_t rc[16];
+                    tmem_ld16(tlane + ccol(Ip) + b0, rc);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int r = 0; r < B; ++r) c1[r] = fmaf(ex2_approx(qr4[Ip] - G[r] - SHIFT), __uint_as_float(rc[r]), c1[r]);
+                }
+            KDA_PHASE(8);
+            // ---- my tile was rejected: the pairs inside the block in FP32 on the CUDA cores, one exp2 per pair
+            if (I == 0 ? rej[0] : I == 1 ? rej[1] : I == 2 ? rej[2] : rej[3]) {
+                // Pair (r, j), j < r, feeds the row sums of r and the column sum of j with the same decay
+                // 2^(G_r - G_j): one exp2 serves both.  The key row j is the rolled loop (four segments, so
+                // that the unrolled rows start right below the diagonal instead of being masked off).
+                const float* dA = fA + I * B * B;
+                const float* dM = fM + I * B * B;
+                float qs[B], kb[B];
+#pragma unroll
+                for (int r = 0; r < B; ++r) {
+                    qs[r] = scale * __bfloat162float(sQ[(b0 + r) * D + d]);
+                    kb[r] = sbeta[b0 + r] * __bfloat162float(sK[(b0 + r) * D + d]);
+                }
+                float* cst = reinterpret_cast<float*>(dyn + CST) + h * B * D + d;  // this thread's column: c1 of the rolled index
+                auto segment = [&](auto r0c, int j0, int j1) {
+                    constexpr int R0 = decltype(r0c)::value;
+#pragma unroll 1
+                    for (int j = j0; j < j1; ++j) {
+                        const float kj = __bfloat162float(sK[(b0 + j) * D + d]), gj = sG[(b0 + j) * D + d];
+                        float cj = 0.f;
+#pragma unroll
+                        for (int r = R0; r < B; ++r) {
+                            const float e = r > j ? ex2_approx(G[r] - gj) : 0.f;
+                            const float a = dA[r * B + j], m = dM[r * B + j], kp = kj * e;
+                            a1[r] = fmaf(a, kp, a1[r]);
+                            a2[r] = fmaf(m, kp, a2[r]);
+                            cj = fmaf(fmaf(a, qs[r], m * kb[r]), e, cj);
+                        }
+                        cst[j * D] = cj;
+                    }
+                };
+                segment(std::integral_constant<int, 1>{}, 0, 4);
+                segment(std::integral_constant<int, 5>{}, 4, 8);
+                segment(std::integral_constant<int, 9>{}, 8, 12);
+                segment(std::integral_constant<int, 13>{}, 12, 15);
+#pragma unroll
+                for (int j = 0; j < B - 1; ++j) c1[j] += cst[j * D];
+            }
+            KDA_PHASE(9);
+            // ---- assembly of my block, last row first; a1[r] is reused for the running sum of dG
+            {
+                float acc = 0.f;
+#pragma unroll
+                for (int r = B - 1; r >= 0; --r) {
+                    const int ii = b0 + r, rr = B * h + r;
+                    const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
+                    const float bi_ = sbeta[ii];
+                    const float gam = ex2_approx(G[r]), eta = ex2_approx(gl - G[r]);
+                    const float dQt = __bfloat162float(spf[ii * D + d]), dKh = __bfloat162float(spf[(C + ii) * D + d]),
+                                dKb = __bfloat162float(spf[(2 * C + ii) * D + d]);
+                    const float diag = scale * sdiag[ii];
+                    const float dq_in = scale * a1[r], dk_row = bi_ * a2[r], dKt = bi_ * dKb;
+                    stg[(0 * 32 + rr) * D + d] = dq_in + diag * ki + scale * dQt * gam;
+                    stg[(1 * 32 + rr) * D + d] = dk_row + c1[r] + diag * qi + dKt * gam + dKh * eta;
+                    stg[(2 * 32 + rr) * D + d] = ki * a2[r] + dKb * (ki * gam);
+                    acc += qi * dq_in + ki * dk_row - ki * c1[r] + dQt * (scale * qi * gam) + dKt * (ki * gam) - dKh * (ki * eta);
+                    a1[r] = acc;
+                }
+                stot[I * D + d] = acc;
+            }
+            KDA_PHASE(10);
+            __syncthreads();
+            KDA_PHASE(11);
+            // ---- reverse cumulative sum across the blocks (the totals of all later blocks are known by
+            //      now: slot 0 holds blocks 3 and 2) and the gate chain
+            {
+                float base = carry_in + sscr[d] + sscr[128 + d];
+#pragma unroll
+                for (int b = 1; b < 4; ++b)
+                    if (b > I) base += stot[b * D + d];
+#pragma unroll
+                for (int r = B - 1; r >= 0; --r) {
+                    const int ii = b0 + r;
+                    if (ii < ci.len) {
+                        const float run = base + a1[r];
+                        const size_t off = tok(ii) * D + d;
+                        if (gate) {
+                            // per-token log decay g = (G_i - G_{i-1}) ln 2; sigmoid(x + b) = 1 - exp(-softplus) = -expm1(g / e^A)
+                            const float gprev = r > 0 ? G[r > 0 ? r - 1 : 0] : (ii > 0 ? sG[(ii - 1) * D + d] : 0.f);
+                            const float gnat = (G[r] - gprev) * 0.6931471805599453f;
+                            dA_acc = fmaf(run, gnat, dA_acc);
+                            const float dx = run * negA * (1.f - ex2_approx(gnat * rcpA * LOG2E));
+                            dbias_acc += dx;
+                            dg_out[off] = __float2bfloat16_rn(dx);
+                        } else {
+                            dg_out[off] = __float2bfloat16_rn(run);
+                        }
+                    }
+                }
+            }
+            KDA_PHASE(12);
+            // ---- row-wise (one half warp per row, 32 rows): L2-norm chain, beta gradient.  Lane l of the half
+            //      warp owns channels 4l .. 4l+3 and 64+4l .. 64+4l+3, so that its 16-byte staging loads and
+            //      8-byte q / k loads are contiguous over the half warp (no bank conflicts)
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const int rr = (tid >> 4) + 16 * m, ii = B * bi_block(rr >> 4, s) + (rr & 15);
+                float dq8[8], dk8[8], q8[8], k8[8], db = 0.f, dotq = 0.f, dotk = 0.f;
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int ch = 64 * hf + c4;
+                    const float4 a = *reinterpret_cast<const float4*>(stg + (0 * 32 + rr) * D + ch);
+                    const float4 b = *reinterpret_cast<const float4*>(stg + (1 * 32 + rr) * D + ch);
+                    const float4 e = *reinterpret_cast<const float4*>(stg + (2 * 32 + rr) * D + ch);
+                    const uint2 qu = *reinterpret_cast<const uint2*>(sQ + ii * D + ch);
+                    const uint2 ku = *reinterpret_cast<const uint2*>(sK + ii * D + ch);
+                    const float2 q01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qu.x));
+                    const float2 q23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qu.y));
+                    const float2 k01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ku.x));
+                    const float2 k23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ku.y));
+                    dq8[4 * hf] = a.x; dq8[4 * hf + 1] = a.y; dq8[4 * hf + 2] = a.z; dq8[4 * hf + 3] = a.w;
+                    dk8[4 * hf] = b.x; dk8[4 * hf + 1] = b.y; dk8[4 * hf + 2] = b.z; dk8[4 * hf + 3] = b.w;
+                    q8[4 * hf] = q01.x; q8[4 * hf + 1] = q01.y; q8[4 * hf + 2] = q23.x; q8[4 * hf + 3] = q23.y;
+                    k8[4 * hf] = k01.x; k8[4 * hf + 1] = k01.y; k8[4 * hf + 2] = k23.x; k8[4 * hf + 3] = k23.y;
+                    db += (e.x + e.y) + (e.z + e.w);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    dotq = fmaf(q8[j], dq8[j], dotq);
+                    dotk = fmaf(k8[j], dk8[j], dotk);
+                }
+                db = half_warp_sum(db);
+                if (l2) {
+                    dotq = half_warp_sum(dotq);
+                    dotk = half_warp_sum(dotk);
+                    const float rq = srq[ii], rk = srk[ii];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        dq8[j] = (dq8[j] - q8[j] * dotq) * rq;
+                        dk8[j] = (dk8[j] - k8[j] * dotk) * rk;
+                    }
+                }
+                if (ii < ci.len) {
+                    const size_t row = tok(ii);
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        *reinterpret_cast<uint2*>(dq_out + row * D + 64 * hf + c4) =
+                            make_uint2(pack_bf16(dq8[4 * hf], dq8[4 * hf + 1]), pack_bf16(dq8[4 * hf + 2], dq8[4 * hf + 3]));
+                        *reinterpret_cast<uint2*>(dk_out + row * D + 64 * hf + c4) =
+                            make_uint2(pack_bf16(dk8[4 * hf], dk8[4 * hf + 1]), pack_bf16(dk8[4 * hf + 2], dk8[4 * hf + 3]));
+                    }
+                    if ((tid & 15) == 0) {
+                        float b = sbeta[ii], v = sdb[ii] + db;
+                        if (sig) v *= b * (1.f - b);
+                        ((__nv_bfloat16*)p.grad_beta)[row] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+            KDA_PHASE(13);
+            __syncthreads();  // the staging buffer may be overwritten
+            KDA_PHASE(14);
+        }
+        KDA_PHASE(6);
+        if (gate) {
+            sscr[128 * h + d] = dbias_acc;  // (every read of the tail term lies before the last barrier)
+            dA_acc = warp_sum(dA_acc);
+            if (lane == 0) sred[warp] = dA_acc;
+            __syncthreads();
+            if (h == 0) ((float*)(sc + L.dbias_part))[rec * D + d] = sscr[d] + sscr[128 + d];
+            if (tid == 0) {
+                float t = 0.f;
+                for (int w = 0; w < 8; ++w) t += sred[w];
+                ((float*)(sc + L.dA_part))[rec] = t;
+            }
+        }
+    }
+    KDA_PHASE(7);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
 }
 
 cudaError_t launch_bwd_intra(const KdaParams& p, cudaStream_t s) {

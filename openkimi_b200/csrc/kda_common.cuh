@@ -84,7 +84,7 @@ struct WsLayout {
     size_t Gc, Qn, Kn, aux, total;                      // prologue results kept for the backward
     size_t Vc, total_conv;                              // convolved v rows (fused short convolution only)
     size_t dS, dVn, dA_part, dbias_part;                // backward scratch
-    size_t dAqk, dM, dQt, dKh, dKb, dbp, gC, bwd_total; // hand-over from bwd_wy to bwd_intra
+    size_t dAM, dAd, dQt, dKh, dKb, dbp, gC, bwd_total; // hand-over from bwd_wy to bwd_intra
 };
 
 __host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -120,14 +120,15 @@ __host__ __device__ inline WsLayout ws_layout(int NT, int H, int dk, int dv, int
     w.dVn = off;        off = align256(off + n * C * dv * es);
     w.dA_part = off;    off = align256(off + n * 4);
     w.dbias_part = off; off = align256(off + n * dk * 4);
-    // Two-kernel backward of the BF16 path: bwd_wy leaves dAqk and dM (float [64][64], lower
-    // triangle; FP32 because the gate gradient is a difference of large terms built from them),
-    // the raw products dQt, dKh, d(beta K~) as [64][dk] in the element type (BF16 on the BF16 path:
-    // rounding them moves no gradient by more than 3e-4 relative L2, and they are half of the
-    // backward's hand-over traffic), the beta gradient collected so far (float [64]) and
-    // dGamma_C * Gamma_C (float [dk]).
-    w.dAqk = off; off = align256(off + n * C * C * 4);
-    w.dM = off;   off = align256(off + n * C * C * 4);
+    // Two-kernel backward of the BF16 path: bwd_wy leaves dAqk and dM, each as THREE BF16 tiles
+    // cm(i, j; 64) whose sum is the FP32 value (x = p0 + p1 + p2: a 24-bit split, because the gate
+    // gradient is a difference of large terms built from them), strictly lower triangle, stored
+    // [dAqk p0, p1, p2, dM p0, p1, p2] -- ready-made tensor-core operands of bwd_intra; the diagonal
+    // of dAqk (float [64]); the raw products dQt, dKh, d(beta K~) as [64][dk] in the element type
+    // (BF16 on the BF16 path: rounding them moves no gradient by more than 3e-4 relative L2); the
+    // beta gradient collected so far (float [64]) and dGamma_C * Gamma_C (float [dk]).
+    w.dAM = off;  off = align256(off + n * 6 * C * C * 2);
+    w.dAd = off;  off = align256(off + n * C * 4);
     w.dQt = off;  off = align256(off + n * C * dk * es);
     w.dKh = off;  off = align256(off + n * C * dk * es);
     w.dKb = off;  off = align256(off + n * C * dk * es);
@@ -146,6 +147,21 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+
+// Three-way BF16 split of two floats: x = p0 + p1 + p2 up to 2^-24 relative (each p is a pair of
+// BF16 values, element 0 in the low half).  The split operands let BF16 tensor-core passes
+// (p0 q0 + p0 q1 + p1 q0 + p1 q1 + p0 q2 + p2 q0) reach FP32-class products.
+__device__ __forceinline__ void split3_bf16(float x0, float x1, uint32_t& p0, uint32_t& p1, uint32_t& p2) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+    p0 = *reinterpret_cast<uint32_t*>(&h);
+    float r0 = x0 - __uint_as_float(p0 << 16), r1 = x1 - __uint_as_float(p0 & 0xffff0000u);
+    h = __floats2bfloat162_rn(r0, r1);
+    p1 = *reinterpret_cast<uint32_t*>(&h);
+    r0 -= __uint_as_float(p1 << 16);
+    r1 -= __uint_as_float(p1 & 0xffff0000u);
+    h = __floats2bfloat162_rn(r0, r1);
+    p2 = *reinterpret_cast<uint32_t*>(&h);
 }
 
 // SiLU and the four-tap causal filter shared by the stand-alone convolution kernels and the

@@ -480,6 +480,17 @@ __global__ void __launch_bounds__(NTHREADS) kda_bwd_state_simt(const KdaParams p
 // ---------------------------------------------------------------------------------------
 // SPLIT = true stops after the chunk-level adjoints and leaves them in the scratch buffer for
 // the separate intra kernel of the BF16 path (used to validate the two halves independently).
+// one entry of the hand-over matrices dAqk / dM in the layout bwd_intra reads: three BF16 tiles
+// cm(i, j; 64) whose sum is x
+__device__ __forceinline__ void store_split3(__nv_bfloat16* base, int i, int j, float x) {
+    uint32_t p0, p1, p2;
+    split3_bf16(x, 0.f, p0, p1, p2);
+    unsigned short* b = reinterpret_cast<unsigned short*>(base) + tc::cm_idx(i, j, C);
+    b[0] = (unsigned short)(p0 & 0xffffu);
+    b[C * C] = (unsigned short)(p1 & 0xffffu);
+    b[2 * C * C] = (unsigned short)(p2 & 0xffffu);
+}
+
 template <typename T, int D, bool SPLIT = false>
 __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParams p) {
     extern __shared__ float smem[];
@@ -541,8 +552,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
             for (int cc = 0; cc < 4; ++cc) {
                 int i = ty + 16 * r, j = tx + 16 * cc;
                 sdA[i * 65 + j] = (i >= j) ? acc[r][cc] : 0.f;
-                if constexpr (SPLIT)
-                    ((float*)(sc + L.dAqk))[rec * C * C + i * C + j] = sdA[i * 65 + j];
+                if constexpr (SPLIT) {
+                    store_split3((__nv_bfloat16*)(sc + L.dAM) + rec * 6 * C * C, i, j, i > j ? sdA[i * 65 + j] : 0.f);
+                    if (i == j) ((float*)(sc + L.dAd))[rec * C + i] = sdA[i * 65 + j];
+                }
             }
     }
     // 2. dW = -dV' S0^T
@@ -592,7 +605,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
                 int i = ty + 16 * r, j = tx + 16 * cc;
                 sdM[i * 65 + j] = (i > j) ? -acc[r][cc] : 0.f;
                 if constexpr (SPLIT)
-                    ((float*)(sc + L.dM))[rec * C * C + i * C + j] = sdM[i * 65 + j];
+                    store_split3((__nv_bfloat16*)(sc + L.dAM) + rec * 6 * C * C + 3 * C * C, i, j, sdM[i * 65 + j]);
             }
     }
     // 5. d(beta K~) = T^T dW

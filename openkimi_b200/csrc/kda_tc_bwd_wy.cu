@@ -13,7 +13,7 @@
 // used, for which masking the intermediate T-gradient is irrelevant.)
 //
 // Outputs: dv, the beta gradient collected so far, dGamma_C * Gamma_C, and the hand-over
-// records of bwd_intra (dAqk, dM in FP32; dQt, dKh, dKb in BF16).
+// records of bwd_intra (dAqk, dM as three-way BF16 splits in operand layout; dQt, dKh, dKb in BF16).
 #include "kda_common.cuh"
 #include "kda_tc.cuh"
 
@@ -38,6 +38,22 @@ constexpr uint32_t SKH = SBETA + 512 + 1024;   // bf16 [64][128] staging of dKh 
 constexpr uint32_t TOTAL = SKH + 16384;
 constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bw
+
+// sixteen consecutive entries (row i, columns j0 .. j0 + 15) of a [64 x 64] FP32 matrix -> the three
+// BF16 tiles cm(i, j; 64) whose sum it is (tile p at base + p * 4096 elements)
+__device__ __forceinline__ void store_split_row(__nv_bfloat16* base, int i, int j0, const float (&f)[16]) {
+    uint32_t p0[8], p1[8], p2[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) split3_bf16(f[2 * j], f[2 * j + 1], p0[j], p1[j], p2[j]);
+    __nv_bfloat16* a = base + cm_idx(i, j0, C);
+    __nv_bfloat16* b = base + cm_idx(i, j0 + 8, C);
+    *reinterpret_cast<uint4*>(a) = make_uint4(p0[0], p0[1], p0[2], p0[3]);
+    *reinterpret_cast<uint4*>(b) = make_uint4(p0[4], p0[5], p0[6], p0[7]);
+    *reinterpret_cast<uint4*>(a + C * C) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
+    *reinterpret_cast<uint4*>(b + C * C) = make_uint4(p1[4], p1[5], p1[6], p1[7]);
+    *reinterpret_cast<uint4*>(a + 2 * C * C) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
+    *reinterpret_cast<uint4*>(b + 2 * C * C) = make_uint4(p2[4], p2[5], p2[6], p2[7]);
+}
 
 __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) {
     using namespace bw;
@@ -211,9 +227,11 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
                 stg[i * D + ch] = x * vv;
             }
         }
-        // dAqk: rows of the M = 64 accumulator sit in lanes 0..15 of every warp's quadrant
+        // dAqk: rows of the M = 64 accumulator sit in lanes 0..15 of every warp's quadrant.  It leaves as
+        // three BF16 tiles cm(i, j; 64) (24-bit split, strictly lower triangle) plus its diagonal
         {
-            float* gdA = (float*)(sc + L.dAqk) + rec * C * C;
+            __nv_bfloat16* gAM = (__nv_bfloat16*)(sc + L.dAM) + rec * 6 * C * C;
+            float* gAd = (float*)(sc + L.dAd) + rec * C;
             const int i = 16 * (warp & 3) + (lane & 15);
 #pragma unroll 1
             for (int j0 = 32 * half; j0 < 32 * half + 32; j0 += 16) {
@@ -223,10 +241,11 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
                 if (lane < 16) {
                     float f[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) f[j] = (j0 + j <= i) ? __uint_as_float(r[j]) : 0.f;
-#pragma unroll
-                    for (int j = 0; j < 16; j += 4)
-                        *reinterpret_cast<float4*>(gdA + i * C + j0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                    for (int j = 0; j < 16; ++j) {
+                        f[j] = (j0 + j < i) ? __uint_as_float(r[j]) : 0.f;
+                        if (j0 + j == i) gAd[i] = __uint_as_float(r[j]);
+                    }
+                    store_split_row(gAM, i, j0, f);
                 }
             }
         }
@@ -327,7 +346,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     tc_fence_after();
     KDA_PHASE(7);
     if (ok) {
-        float* gdM = (float*)(sc + L.dM) + rec * C * C;
+        __nv_bfloat16* gMM = (__nv_bfloat16*)(sc + L.dAM) + rec * 6 * C * C + 3 * C * C;
         const int i = 16 * (warp & 3) + (lane & 15);
 #pragma unroll 1
         for (int j0 = 32 * half; j0 < 32 * half + 32; j0 += 16) {
@@ -338,9 +357,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
                 float f[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) f[j] = (j0 + j < i) ? -__uint_as_float(r[j]) : 0.f;
-#pragma unroll
-                for (int j = 0; j < 16; j += 4)
-                    *reinterpret_cast<float4*>(gdM + i * C + j0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                store_split_row(gMM, i, j0, f);
             }
         }
     }

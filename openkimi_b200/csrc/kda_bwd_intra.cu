@@ -42,7 +42,7 @@ namespace kda {
 using namespace tc;
 
 namespace bi {
-constexpr int D = 128, NTHR = 256, B = 16;
+constexpr int D = 128, NTHR = 512, B = 16;
 constexpr uint32_t SG = 0;                   // G f32 [64][128]
 constexpr uint32_t SQ = SG + 32768;          // q^ bf16 [64][128]
 constexpr uint32_t SK = SQ + 16384;          // k^ bf16 [64][128]
@@ -54,15 +54,14 @@ constexpr uint32_t SDB = SAUX + 768;         // f32 [64] beta gradient so far
 constexpr uint32_t SDIAG = SDB + 256;        // f32 [64] diagonal of dAqk
 constexpr uint32_t SMID = SDIAG + 256;       // f32 [2][4][128] key / query reference of every block and channel
 constexpr uint32_t STOT = SMID + 4096;       // f32 [4][128] block totals of dG
-constexpr uint32_t SSCR = STOT + 2048;       // f32 [2][128]
-constexpr uint32_t SRED = SSCR + 1024;       // f32 [8]
+constexpr uint32_t SSCR = STOT + 2048;       // f32 [4][128]
+constexpr uint32_t SRED = SSCR + 2048;       // f32 [16]
 constexpr uint32_t SREJ = SRED + 64;         // int [4][4]: tile (block, channel group) rejected
-constexpr uint32_t TOTAL = SREJ + 64;
-// later uses of the operand buffers
+constexpr uint32_t FD = SREJ + 64;           // f32 [2][4][16][16] diagonal blocks of dAqk, dM rebuilt for rejected tiles
+constexpr uint32_t TOTAL = FD + 8192;
+// later uses of the dead operand space
 constexpr uint32_t PF = YB;                  // bf16 [3][64][128]: dQt, dKh, dKb (after the MMAs that read Y)
-constexpr uint32_t STG = SB;                 // f32 [3][32][128] staging of dq, dk, dbeta terms (once the split tiles are dead)
-constexpr uint32_t FA = XB;                  // f32 [2][4][16][16] diagonal blocks of dAqk, dM rebuilt for rejected tiles
-constexpr uint32_t CST = XB + 8192;          // f32 [2][16][128] column sums of a rejected tile, by thread
+constexpr uint32_t STG = SB;                 // f32 [3][64][128] staging of dq, dk, dbeta terms over SB and X (after all MMAs)
 constexpr uint32_t TMEM_COLS = 512;
 // The midpoint factors reach 2^(+-span/2) and the third BF16 part of an operand sits 2^-16 below its
 // value, so the whole FP32 exponent range is used up at span ~205: tiles pass on to the tensor cores
@@ -73,11 +72,6 @@ constexpr float TC_SPAN = 200.f, SHIFT = 6.f;
 __host__ __device__ constexpr uint32_t rcol(int J) { return 16u * J * (9 - J); }         // accR_J: 2 (64 - 16 J) columns
 __host__ __device__ constexpr uint32_t ccol(int I) { return 320u + 8u * I * (I + 1); }  // accC_I: 16 (I + 1) columns
 }  // namespace bi
-
-// 256 threads: thread (h, d) = (tid / 128, tid % 128) owns channel d (= TMEM lane d) and two whole
-// 16-row blocks, {3, 0} for h = 0 and {2, 1} for h = 1 (slot 0, slot 1), so that a warp covers
-// exactly one guard tile per slot and both halves read back the same number of accumulators.
-__device__ __forceinline__ int bi_block(int h, int slot) { return slot == 0 ? 3 - h : h; }
 
 // eight operand values of one channel -> three BF16 parts, one 16-byte row of a core matrix each
 __device__ __forceinline__ void store_parts(unsigned char* buf, int d, int t0, const float (&v)[8]) {
@@ -90,6 +84,9 @@ __device__ __forceinline__ void store_parts(unsigned char* buf, int d, int t0, c
     *reinterpret_cast<uint4*>(buf + 32768 + off) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
 }
 
+// 512 threads: thread (blk, d) = (tid / 128, tid % 128) owns channel d (= TMEM lane d) of the 16-row
+// block blk, so that a warp covers exactly one guard tile, everything along the token axis of a
+// block is register-local, and four warps per scheduler hide each other's latencies.
 __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) {
     using namespace bi;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -97,7 +94,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     __shared__ uint32_t tmem_s;
     const __nv_bfloat16* sQ = reinterpret_cast<const __nv_bfloat16*>(dyn + SQ);
     const __nv_bfloat16* sK = reinterpret_cast<const __nv_bfloat16*>(dyn + SK);
-    const float* sG = reinterpret_cast<const float*>(dyn + SG);
+    float* sG = reinterpret_cast<float*>(dyn + SG);
     const __nv_bfloat16* sB = reinterpret_cast<const __nv_bfloat16*>(dyn + SB);
     float* stg = reinterpret_cast<float*>(dyn + STG);
     const __nv_bfloat16* spf = reinterpret_cast<const __nv_bfloat16*>(dyn + PF);
@@ -111,8 +108,10 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     float* sscr = reinterpret_cast<float*>(dyn + SSCR);
     float* sred = reinterpret_cast<float*>(dyn + SRED);
     int* srej = reinterpret_cast<int*>(dyn + SREJ);
+    float* fD = reinterpret_cast<float*>(dyn + FD);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid & 127, h = tid >> 7, cg = warp & 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid & 127, blk = tid >> 7, cg = warp & 3;
+    const int b0 = B * blk;
     const int c = blockIdx.x / p.H, hd = blockIdx.x % p.H;
     const ChunkInfo ci = chunk_info(p, c);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
@@ -120,8 +119,6 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     const size_t rec = (size_t)c * p.H + hd;
     const bool l2 = p.flags & KDA_FLAG_QK_L2NORM, gate = p.flags & KDA_FLAG_GATE, sig = p.flags & KDA_FLAG_BETA_SIGMOID;
     const float scale = p.scale;
-    const float expA = gate ? expf(p.A_log[hd]) : 1.f;
-    const float negA = -expA, rcpA = 1.f / expA;
     auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + hd); };
     KDA_PHASE_BEGIN();
     if (warp == 0) {
@@ -161,19 +158,17 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     bool ok = mbar_wait(&barA, 0, p.status, 64);
     KDA_PHASE(0);
 
-    // ---- my two blocks: guard and midpoint of each tile; round 1: KN_j = k_j 2^(m - G_j) of my rows -> X
-    //      (the slot loops are kept rolled: straight-line code for both slots would not fit the
-    //       instruction cache, and every CTA runs it only once)
-    const float tc_span = fminf(p.guard_span, TC_SPAN);
-#pragma unroll 1
-    for (int s = 0; s < 2; ++s) {
-        const int blk = bi_block(h, s), b0 = B * blk;
-        float G[B], mid;
+    // ---- my block: G of my channel, guard and references; round 1: KN_j = k_j 2^(ref - G_j) -> X
+    float G[B], mid;
 #pragma unroll
-        for (int r = 0; r < B; ++r) G[r] = sG[(b0 + r) * D + d];
-        const bool pass = guard_tile(G, tc_span, mid);
+    for (int r = 0; r < B; ++r) G[r] = sG[(b0 + r) * D + d];
+    const float gl = sG[(C - 1) * D + d];                          // G of the chunk's last row
+    const float gprev = blk > 0 ? sG[(b0 - 1) * D + d] : 0.f;      // G of the row before my block
+    const bool pass = guard_tile(G, fminf(p.guard_span, TC_SPAN), mid);
+    {
         // references of my rows as keys / as queries: the midpoint, or first rows when there is none
-        const float kref = pass ? mid : (blk < 3 ? sG[(b0 + B) * D + d] : -INFINITY), qref = pass ? mid : G[0];  // (block 3 has no later rows: zero keys)
+        // (block 3 has no later rows: zero keys)
+        const float kref = pass ? mid : (blk < 3 ? sG[(b0 + B) * D + d] : -INFINITY), qref = pass ? mid : G[0];
         smid[blk * D + d] = kref;
         smid[(4 + blk) * D + d] = qref;
         if (lane == 0) srej[blk * 4 + cg] = pass ? 0 : 1;
@@ -214,38 +209,28 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         mma_commit(&mma1);
     }
-    // references and guard decisions of all four blocks for my channel (group)
+    // references of all four blocks for my channel, guard decisions for my channel group
     float kr4[4], qr4[4];
-    bool rej[4];
     bool any_rej = false;
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
         kr4[b] = smid[b * D + d];
         qr4[b] = smid[(4 + b) * D + d];
-        rej[b] = srej[b * 4 + cg] != 0;
     }
 #pragma unroll
     for (int b = 0; b < 16; ++b) any_rej = any_rej || srej[b] != 0;
-    // ---- round 2: QP_i = scale q_i 2^(G_i - ref) -> Y;  round 3: KP_i = beta_i k_i 2^(G_i - ref) -> X
-    auto query_operands = [&](const __nv_bfloat16* src, unsigned char* dst, bool with_beta) {
-#pragma unroll 1
-        for (int s = 0; s < 2; ++s) {
-            const int blk = bi_block(h, s), b0 = B * blk;
-            const float qref = blk == 0 ? qr4[0] : blk == 1 ? qr4[1] : blk == 2 ? qr4[2] : qr4[3];
+    // ---- round 2: QP_i = scale q_i 2^(G_i - ref) -> Y
+    {
+        const float qref = pass ? mid : G[0];
 #pragma unroll
-            for (int g8 = 0; g8 < 2; ++g8) {
-                float v[8];
+        for (int g8 = 0; g8 < 2; ++g8) {
+            float v[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int t = b0 + 8 * g8 + j;
-                    const float w = with_beta ? sbeta[t] : scale;
-                    v[j] = w * __bfloat162float(src[t * D + d]) * ex2_approx(sG[t * D + d] - qref + SHIFT);
-                }
-                store_parts(dst, d, b0 + 8 * g8, v);
-            }
+            for (int j = 0; j < 8; ++j)
+                v[j] = scale * __bfloat162float(sQ[(b0 + 8 * g8 + j) * D + d]) * ex2_approx(G[8 * g8 + j] - qref + SHIFT);
+            store_parts(dyn + YB, d, b0 + 8 * g8, v);
         }
-    };
-    query_operands(sQ, dyn + YB, false);
+    }
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
@@ -262,9 +247,22 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         mma_commit(&mma2);
     }
-    ok = ok && mbar_wait(&mma1, 0, p.status, 64);  // the row-side MMAs have read X
+    // ---- round 3: KP_i = beta_i k_i 2^(G_i - ref) -> X, once the row-side MMAs have read X
+    ok = ok && mbar_wait(&mma1, 0, p.status, 64);
     tc_fence_after();
-    query_operands(sK, dyn + XB, true);
+    {
+        const float qref = pass ? mid : G[0];
+#pragma unroll
+        for (int g8 = 0; g8 < 2; ++g8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int t = b0 + 8 * g8 + j;
+                v[j] = sbeta[t] * __bfloat162float(sK[t * D + d]) * ex2_approx(G[8 * g8 + j] - qref + SHIFT);
+            }
+            store_parts(dyn + XB, d, b0 + 8 * g8, v);
+        }
+    }
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
@@ -281,6 +279,29 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         mma_commit(&mma3);
     }
+    // ---- row sums of my block from the accumulators while the column-side MMAs run (the pairs inside my
+    //      own block only if its tile passed the guard)
+    float a1[B], a2[B], c1[B];
+#pragma unroll
+    for (int r = 0; r < B; ++r) a1[r] = a2[r] = c1[r] = 0.f;
+    if (ok) {
+#pragma unroll
+        for (int J = 0; J < 4; ++J)
+            if (J < blk || (J == blk && pass)) {
+                uint32_t ra[16], rm[16];
+                const uint32_t col = tlane + rcol(J) + B * (blk - J);
+                tmem_ld16(col, ra);
+                tmem_ld16(col + 64 - B * J, rm);
+                tmem_wait_ld();
+#pragma unroll
+                for (int r = 0; r < B; ++r) {
+                    const float f = ex2_approx(G[r] - kr4[J] - SHIFT);
+                    a1[r] = fmaf(f, __uint_as_float(ra[r]), a1[r]);
+                    a2[r] = fmaf(f, __uint_as_float(rm[r]), a2[r]);
+                }
+            }
+    }
+    KDA_PHASE(4);
     // ---- the hand-over arrays may land in Y as soon as the MMAs that read Y are done
     ok = ok && mbar_wait(&mma2, 0, p.status, 64);
     if (tid == 0 && ok) {
@@ -291,179 +312,146 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     }
     ok = ok && mbar_wait(&mma3, 0, p.status, 64);
     tc_fence_after();
-    KDA_PHASE(4);
-    const float* fA = reinterpret_cast<const float*>(dyn + FA);  // [4][16][16] diagonal blocks of dAqk
-    const float* fM = fA + 4 * B * B;                            // ... and of dM
-    if (any_rej) {  // uniform over the CTA: the diagonal blocks back to FP32 (x = p0 + p1 + p2) for the CUDA-core sums
-        float* w = reinterpret_cast<float*>(dyn + FA);
+    KDA_PHASE(5);
+    // ---- column sums of my block
+    if (ok) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int e = tid + NTHR * u, mat = e >> 10, blk = (e >> 8) & 3, r = (e >> 4) & 15, j = e & 15;
-            const __nv_bfloat16* t = sB + mat * 3 * C * C + cm_idx(B * blk + r, B * blk + j, C);
-            w[e] = (__bfloat162float(t[0]) + __bfloat162float(t[C * C])) + __bfloat162float(t[2 * C * C]);
+        for (int Ip = 0; Ip < 4; ++Ip)
+            if (Ip > blk || (Ip == blk && pass)) {
+                uint32_t rc[16];
+                tmem_ld16(tlane + ccol(Ip) + b0, rc);
+                tmem_wait_ld();
+#pragma unroll
+                for (int r = 0; r < B; ++r) c1[r] = fmaf(ex2_approx(qr4[Ip] - G[r] - SHIFT), __uint_as_float(rc[r]), c1[r]);
+            }
+    }
+    KDA_PHASE(6);
+    if (any_rej) {  // uniform over the CTA: the diagonal blocks back to FP32 (x = p0 + p1 + p2) for the CUDA-core sums
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = tid + NTHR * u, mat = e >> 10, bb = (e >> 8) & 3, r = (e >> 4) & 15, j = e & 15;
+            const __nv_bfloat16* t = sB + mat * 3 * C * C + cm_idx(B * bb + r, B * bb + j, C);
+            fD[e] = (__bfloat162float(t[0]) + __bfloat162float(t[C * C])) + __bfloat162float(t[2 * C * C]);
         }
     }
     ok = ok && mbar_wait(&barH, 0, p.status, 64);
-    ok = __syncthreads_and(ok);  // (also: the rebuilt matrices are visible, the split tiles are dead -> staging area)
-    KDA_PHASE(5);
+    ok = __syncthreads_and(ok);  // (also: the rebuilt blocks are visible; the split tiles and X are dead -> staging area)
+    KDA_PHASE(7);
 
     if (ok) {
-        const float gl = sG[(C - 1) * D + d];
-        // term of the last row: dGamma_C Gamma_C + sum_i dKh_i Kh_i (every thread sums the 32 rows of its half)
-        {
-            float sacc = 0.f;
-#pragma unroll 8
-            for (int r = 0; r < 32; ++r) {
-                const int i = 32 * h + r;
-                sacc = fmaf(__bfloat162float(spf[(C + i) * D + d]), __bfloat162float(sK[i * D + d]) * ex2_approx(gl - sG[i * D + d]), sacc);
-            }
-            sscr[128 * h + d] = sacc;
-        }
-        __nv_bfloat16* dq_out = (__nv_bfloat16*)p.grad_q;
-        __nv_bfloat16* dk_out = (__nv_bfloat16*)p.grad_k;
-        __nv_bfloat16* dg_out = (__nv_bfloat16*)p.grad_g;
-        const int c4 = (tid & 15) * 4;
-        float dA_acc = 0.f, dbias_acc = 0.f;
-#pragma unroll 1
-        for (int s = 0; s < 2; ++s) {
-            const int I = bi_block(h, s), b0 = B * I;
-            float G[B], a1[B], a2[B], c1[B];
+        // ---- my tile was rejected: the pairs inside the block in FP32 on the CUDA cores, one exp2 per pair.
+        //      Pair (r, j), j < r, feeds the row sums of r and the column sum of j with the same decay
+        //      2^(G_r - G_j).  The key row j is the rolled loop (four segments, so that the unrolled rows
+        //      start right below the diagonal instead of being masked off); its column sum goes through my
+        //      own column of the G tile, which nobody else reads (G itself is in registers by now, and rows
+        //      15 / 31 / 47 / 63, which neighbours did read, are never written).
+        if (!pass) {
+            const float* dA = fD + blk * B * B;
+            const float* dM = fD + (4 + blk) * B * B;
+            float qs[B], kb[B];
 #pragma unroll
             for (int r = 0; r < B; ++r) {
-                G[r] = sG[(b0 + r) * D + d];
-                a1[r] = a2[r] = c1[r] = 0.f;
+                qs[r] = scale * __bfloat162float(sQ[(b0 + r) * D + d]);
+                kb[r] = sbeta[b0 + r] * __bfloat162float(sK[(b0 + r) * D + d]);
             }
-            // ---- row sums and column sums of my block from the accumulators (the pairs inside my own block
-            //      only if its tile passed the guard)
-#pragma unroll
-            for (int J = 0; J < 4; ++J)
-                if (J < I || (J == I && !rej[J])) {
-                    uint32_t ra[16], rm[16];
-                    const uint32_t col = tlane + rcol(J) + B * (I - J);
-                    tmem_ld16(col, ra);
-                    tmem_ld16(col + 64 - B * J, rm);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int r = 0; r < B; ++r) {
-                        const float f = ex2_approx(G[r] - kr4[J] - SHIFT);
-                        a1[r] = fmaf(f, __uint_as_float(ra[r]), a1[r]);
-                        a2[r] = fmaf(f, __uint_as_float(rm[r]), a2[r]);
-                    }
-                }
-#pragma unroll
-            for (int Ip = 0; Ip < 4; ++Ip)
-                if (Ip > I || (Ip == I && !rej[Ip])) {
-                    uint32_t rc[16];
-                    tmem_ld16(tlane + ccol(Ip) + b0, rc);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int r = 0; r < B; ++r) c1[r] = fmaf(ex2_approx(qr4[Ip] - G[r] - SHIFT), __uint_as_float(rc[r]), c1[r]);
-                }
-            KDA_PHASE(8);
-            // ---- my tile was rejected: the pairs inside the block in FP32 on the CUDA cores, one exp2 per pair
-            if (I == 0 ? rej[0] : I == 1 ? rej[1] : I == 2 ? rej[2] : rej[3]) {
-                // Pair (r, j), j < r, feeds the row sums of r and the column sum of j with the same decay
-                // 2^(G_r - G_j): one exp2 serves both.  The key row j is the rolled loop (four segments, so
-                // that the unrolled rows start right below the diagonal instead of being masked off).
-                const float* dA = fA + I * B * B;
-                const float* dM = fM + I * B * B;
-                float qs[B], kb[B];
-#pragma unroll
-                for (int r = 0; r < B; ++r) {
-                    qs[r] = scale * __bfloat162float(sQ[(b0 + r) * D + d]);
-                    kb[r] = sbeta[b0 + r] * __bfloat162float(sK[(b0 + r) * D + d]);
-                }
-                float* cst = reinterpret_cast<float*>(dyn + CST) + h * B * D + d;  // this thread's column: c1 of the rolled index
-                auto segment = [&](auto r0c, int j0, int j1) {
-                    constexpr int R0 = decltype(r0c)::value;
+            float* cst = sG + b0 * D + d;
+            auto segment = [&](auto r0c, int j0, int j1) {
+                constexpr int R0 = decltype(r0c)::value;
 #pragma unroll 1
-                    for (int j = j0; j < j1; ++j) {
-                        const float kj = __bfloat162float(sK[(b0 + j) * D + d]), gj = sG[(b0 + j) * D + d];
-                        float cj = 0.f;
+                for (int j = j0; j < j1; ++j) {
+                    const float kj = __bfloat162float(sK[(b0 + j) * D + d]), gj = cst[j * D];
+                    float cj = 0.f;
 #pragma unroll
-                        for (int r = R0; r < B; ++r) {
-                            const float e = r > j ? ex2_approx(G[r] - gj) : 0.f;
-                            const float a = dA[r * B + j], m = dM[r * B + j], kp = kj * e;
-                            a1[r] = fmaf(a, kp, a1[r]);
-                            a2[r] = fmaf(m, kp, a2[r]);
-                            cj = fmaf(fmaf(a, qs[r], m * kb[r]), e, cj);
-                        }
-                        cst[j * D] = cj;
+                    for (int r = R0; r < B; ++r) {
+                        const float e = r > j ? ex2_approx(G[r] - gj) : 0.f;
+                        const float a = dA[r * B + j], m = dM[r * B + j], kp = kj * e;
+                        a1[r] = fmaf(a, kp, a1[r]);
+                        a2[r] = fmaf(m, kp, a2[r]);
+                        cj = fmaf(fmaf(a, qs[r], m * kb[r]), e, cj);
                     }
-                };
-                segment(std::integral_constant<int, 1>{}, 0, 4);
-                segment(std::integral_constant<int, 5>{}, 4, 8);
-                segment(std::integral_constant<int, 9>{}, 8, 12);
-                segment(std::integral_constant<int, 13>{}, 12, 15);
-#pragma unroll
-                for (int j = 0; j < B - 1; ++j) c1[j] += cst[j * D];
-            }
-            KDA_PHASE(9);
-            // ---- assembly of my block, last row first; a1[r] is reused for the running sum of dG
-            {
-                float acc = 0.f;
-#pragma unroll
-                for (int r = B - 1; r >= 0; --r) {
-                    const int ii = b0 + r, rr = B * h + r;
-                    const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
-                    const float bi_ = sbeta[ii];
-                    const float gam = ex2_approx(G[r]), eta = ex2_approx(gl - G[r]);
-                    const float dQt = __bfloat162float(spf[ii * D + d]), dKh = __bfloat162float(spf[(C + ii) * D + d]),
-                                dKb = __bfloat162float(spf[(2 * C + ii) * D + d]);
-                    const float diag = scale * sdiag[ii];
-                    const float dq_in = scale * a1[r], dk_row = bi_ * a2[r], dKt = bi_ * dKb;
-                    stg[(0 * 32 + rr) * D + d] = dq_in + diag * ki + scale * dQt * gam;
-                    stg[(1 * 32 + rr) * D + d] = dk_row + c1[r] + diag * qi + dKt * gam + dKh * eta;
-                    stg[(2 * 32 + rr) * D + d] = ki * a2[r] + dKb * (ki * gam);
-                    acc += qi * dq_in + ki * dk_row - ki * c1[r] + dQt * (scale * qi * gam) + dKt * (ki * gam) - dKh * (ki * eta);
-                    a1[r] = acc;
+                    cst[j * D] = cj;
                 }
-                stot[I * D + d] = acc;
+            };
+            segment(std::integral_constant<int, 1>{}, 0, 4);
+            segment(std::integral_constant<int, 5>{}, 4, 8);
+            segment(std::integral_constant<int, 9>{}, 8, 12);
+            segment(std::integral_constant<int, 13>{}, 12, 15);
+#pragma unroll
+            for (int j = 0; j < B - 1; ++j) c1[j] += cst[j * D];
+        }
+        KDA_PHASE(8);
+        // ---- assembly of my block, last row first; a1[r] is reused for the running sum of dG
+        {
+            float acc = 0.f, tail = 0.f;
+#pragma unroll
+            for (int r = B - 1; r >= 0; --r) {
+                const int ii = b0 + r;
+                const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
+                const float bi_ = sbeta[ii];
+                const float gam = ex2_approx(G[r]), eta = ex2_approx(gl - G[r]);
+                const float dQt = __bfloat162float(spf[ii * D + d]), dKh = __bfloat162float(spf[(C + ii) * D + d]),
+                            dKb = __bfloat162float(spf[(2 * C + ii) * D + d]);
+                const float diag = scale * sdiag[ii];
+                const float dq_in = scale * a1[r], dk_row = bi_ * a2[r], dKt = bi_ * dKb;
+                stg[(0 * C + ii) * D + d] = dq_in + diag * ki + scale * dQt * gam;
+                stg[(1 * C + ii) * D + d] = dk_row + c1[r] + diag * qi + dKt * gam + dKh * eta;
+                stg[(2 * C + ii) * D + d] = ki * a2[r] + dKb * (ki * gam);
+                const float khe = dKh * (ki * eta);
+                tail += khe;  // the last row also collects sum_i dKh_i Kh_i
+                acc += qi * dq_in + ki * dk_row - ki * c1[r] + dQt * (scale * qi * gam) + dKt * (ki * gam) - khe;
+                a1[r] = acc;
             }
-            KDA_PHASE(10);
-            __syncthreads();
-            KDA_PHASE(11);
-            // ---- reverse cumulative sum across the blocks (the totals of all later blocks are known by
-            //      now: slot 0 holds blocks 3 and 2) and the gate chain
-            {
-                float base = carry_in + sscr[d] + sscr[128 + d];
+            stot[blk * D + d] = acc;
+            sscr[blk * D + d] = tail;
+        }
+        KDA_PHASE(9);
+        __syncthreads();
+        KDA_PHASE(10);
+        // ---- reverse cumulative sum across the blocks and the gate chain
+        float dA_acc = 0.f, dbias_acc = 0.f;
+        {
+            float base = carry_in + ((sscr[d] + sscr[D + d]) + (sscr[2 * D + d] + sscr[3 * D + d]));
 #pragma unroll
-                for (int b = 1; b < 4; ++b)
-                    if (b > I) base += stot[b * D + d];
+            for (int b = 1; b < 4; ++b)
+                if (b > blk) base += stot[b * D + d];
+            const float expA = gate ? expf(p.A_log[hd]) : 1.f;
+            const float negA = -expA, rcpA = 1.f / expA;
+            // (rows past the end of a partial chunk have a constant G, hence a zero decay and zero terms:
+            //  only their stores are masked, so that the rows do not end up in sixteen basic blocks)
+            __nv_bfloat16* dgp = (__nv_bfloat16*)p.grad_g + tok(b0) * D + d;
+            const size_t rstride = (size_t)p.H * D;
 #pragma unroll
-                for (int r = B - 1; r >= 0; --r) {
-                    const int ii = b0 + r;
-                    if (ii < ci.len) {
-                        const float run = base + a1[r];
-                        const size_t off = tok(ii) * D + d;
-                        if (gate) {
-                            // per-token log decay g = (G_i - G_{i-1}) ln 2; sigmoid(x + b) = 1 - exp(-softplus) = -expm1(g / e^A)
-                            const float gprev = r > 0 ? G[r > 0 ? r - 1 : 0] : (ii > 0 ? sG[(ii - 1) * D + d] : 0.f);
-                            const float gnat = (G[r] - gprev) * 0.6931471805599453f;
-                            dA_acc = fmaf(run, gnat, dA_acc);
-                            const float dx = run * negA * (1.f - ex2_approx(gnat * rcpA * LOG2E));
-                            dbias_acc += dx;
-                            dg_out[off] = __float2bfloat16_rn(dx);
-                        } else {
-                            dg_out[off] = __float2bfloat16_rn(run);
-                        }
-                    }
+            for (int r = B - 1; r >= 0; --r) {
+                const float run = base + a1[r];
+                float outv = run;
+                if (gate) {
+                    // per-token log decay g = (G_i - G_{i-1}) ln 2; sigmoid(x + b) = 1 - exp(-softplus) = -expm1(g / e^A)
+                    const float gnat = (G[r] - (r > 0 ? G[r > 0 ? r - 1 : 0] : gprev)) * 0.6931471805599453f;
+                    dA_acc = fmaf(run, gnat, dA_acc);
+                    outv = run * negA * (1.f - ex2_approx(gnat * rcpA * LOG2E));
+                    dbias_acc += outv;
                 }
+                if (b0 + r < ci.len) dgp[r * rstride] = __float2bfloat16_rn(outv);
             }
-            KDA_PHASE(12);
-            // ---- row-wise (one half warp per row, 32 rows): L2-norm chain, beta gradient.  Lane l of the half
-            //      warp owns channels 4l .. 4l+3 and 64+4l .. 64+4l+3, so that its 16-byte staging loads and
-            //      8-byte q / k loads are contiguous over the half warp (no bank conflicts)
+        }
+        KDA_PHASE(11);
+        // ---- row-wise (one half warp per row, 64 rows): L2-norm chain, beta gradient.  Lane l of the half
+        //      warp owns channels 4l .. 4l+3 and 64+4l .. 64+4l+3, so that its 16-byte staging loads and
+        //      8-byte q / k loads are contiguous over the half warp (no bank conflicts)
+        {
+            __nv_bfloat16* dq_out = (__nv_bfloat16*)p.grad_q;
+            __nv_bfloat16* dk_out = (__nv_bfloat16*)p.grad_k;
+            const int c4 = (tid & 15) * 4;
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
-                const int rr = (tid >> 4) + 16 * m, ii = B * bi_block(rr >> 4, s) + (rr & 15);
+                const int ii = (tid >> 4) + 32 * m;
                 float dq8[8], dk8[8], q8[8], k8[8], db = 0.f, dotq = 0.f, dotk = 0.f;
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     const int ch = 64 * hf + c4;
-                    const float4 a = *reinterpret_cast<const float4*>(stg + (0 * 32 + rr) * D + ch);
-                    const float4 b = *reinterpret_cast<const float4*>(stg + (1 * 32 + rr) * D + ch);
-                    const float4 e = *reinterpret_cast<const float4*>(stg + (2 * 32 + rr) * D + ch);
+                    const float4 a = *reinterpret_cast<const float4*>(stg + (0 * C + ii) * D + ch);
+                    const float4 b = *reinterpret_cast<const float4*>(stg + (1 * C + ii) * D + ch);
+                    const float4 e = *reinterpret_cast<const float4*>(stg + (2 * C + ii) * D + ch);
                     const uint2 qu = *reinterpret_cast<const uint2*>(sQ + ii * D + ch);
                     const uint2 ku = *reinterpret_cast<const uint2*>(sK + ii * D + ch);
                     const float2 q01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qu.x));
@@ -508,25 +496,23 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                     }
                 }
             }
-            KDA_PHASE(13);
-            __syncthreads();  // the staging buffer may be overwritten
-            KDA_PHASE(14);
         }
-        KDA_PHASE(6);
+        KDA_PHASE(12);
         if (gate) {
-            sscr[128 * h + d] = dbias_acc;  // (every read of the tail term lies before the last barrier)
+            __syncthreads();  // the tail terms in sscr have been read by every thread
+            sscr[blk * D + d] = dbias_acc;
             dA_acc = warp_sum(dA_acc);
             if (lane == 0) sred[warp] = dA_acc;
             __syncthreads();
-            if (h == 0) ((float*)(sc + L.dbias_part))[rec * D + d] = sscr[d] + sscr[128 + d];
+            if (blk == 0) ((float*)(sc + L.dbias_part))[rec * D + d] = (sscr[d] + sscr[D + d]) + (sscr[2 * D + d] + sscr[3 * D + d]);
             if (tid == 0) {
                 float t = 0.f;
-                for (int w = 0; w < 8; ++w) t += sred[w];
+                for (int w = 0; w < 16; ++w) t += sred[w];
                 ((float*)(sc + L.dA_part))[rec] = t;
             }
         }
     }
-    KDA_PHASE(7);
+    KDA_PHASE(13);
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);

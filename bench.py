@@ -7,7 +7,14 @@ One "step" = one forward + backward of ``chunk_kda`` over one batch of seeded sy
 input (default: B=16, T=2048, H=6, d=128, BF16 operands, FP32 state, final state returned,
 upstream gradient do ~ N(0,1)).  With N > 1 (torchrun, one rank per GPU) every rank runs the
 same per-GPU batch on its own data -- sequences are independent, so there is no collective
-on the kernel path -- and the reported value is all ranks' tokens / the slowest rank's time.
+on the kernel path -- and the reported value is all ranks' tokens / the slowest rank's time
+(``scaling: weak``).  The same line also carries, as extra legs timed after the headline one:
+``strong`` (N > 1): the ONE batch of the workload split over the ranks by sequence
+(``openkimi_b200.partition.shard_batch``), and ``sublayer``: the whole KimiDeltaAttention
+sublayer with its global batch of 64 split over the ranks.
+
+The CPU arm (``--impl reference`` and the ``cpu_baseline`` object) times the oracle port on the
+host cores on one head of one full-length sequence of the workload per step.
 
 Prints ONE JSON line on rank 0.
 """
@@ -188,19 +195,28 @@ def to_device(host, device):
     return dev
 
 
-def cpu_oracle_rate(w, sample_T, threads=None):
-    """tokens/s of the CPU oracle (PyTorch port of k3mini/model.py:101-129 + prologue :217-223)
-    forward + autograd backward on one [1, sample_T, H, d] slice of the workload."""
-    from oracle.kda_oracle import kda_oracle_fwd_bwd, make_inputs
-    if threads:
-        torch.set_num_threads(threads)
-    inp = make_inputs(1, sample_T, w["H"], w["d"], seed=0, dtype=torch.bfloat16, x_mean=w["x_mean"], a_lo=w["a_lo"],
+def cpu_slice_inputs(w, seed=0):
+    """One head of one full-length sequence of the workload ([1, T, 1, d], capped at 2048 tokens)."""
+    from oracle.kda_oracle import make_inputs
+    T = min(w["T"], 2048)
+    inp = make_inputs(1, T, 1, w["d"], seed=seed, dtype=torch.bfloat16, x_mean=w["x_mean"], a_lo=w["a_lo"],
                       a_hi=w["a_hi"], beta_mean=w["beta_mean"])
+    return inp, T
+
+
+def cpu_slice_seconds(w, inp):
+    """Seconds of the CPU oracle (PyTorch port of k3mini/model.py:101-129 + prologue :217-223), forward +
+    autograd backward, on the prepared slice."""
+    from oracle.kda_oracle import kda_oracle_fwd_bwd
     t0 = time.perf_counter()
     kda_oracle_fwd_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["do"], a_log=inp["a_log"],
                        dt_bias=inp["dt_bias"], scale=w["d"] ** -0.5)
-    dt = time.perf_counter() - t0
-    return sample_T / dt, dt
+    return time.perf_counter() - t0
+
+
+def cpu_sample_text(w, T):
+    return (f"each step = oracle fwd+bwd of one head of one full-length sequence, a [1,{T},1,{w['d']}] slice "
+            f"(1/{w['H']} of the per-token work, counted as {T}/{w['H']} tokens); sequences and heads are independent")
 
 
 def run_reference(args, w, rank, world):
@@ -210,24 +226,39 @@ def run_reference(args, w, rank, world):
         return
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    sample_T = 256
+    inp, T = cpu_slice_inputs(w)
     for _ in range(args.warmup):
-        cpu_oracle_rate(w, sample_T)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_oracle_rate(w, sample_T)
-    dt = time.perf_counter() - t0
-    val = args.steps * sample_T / dt / 1e6
-    sample = f"each step = oracle fwd+bwd of one [1,{sample_T},{w['H']},{w['d']}] slice of the workload"
+        cpu_slice_seconds(w, inp)
+    secs = sum(cpu_slice_seconds(w, inp) for _ in range(args.steps))
+    val = args.steps * (T / w["H"]) / secs / 1e6
+    sample = cpu_sample_text(w, T)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": w["label"], "sample": sample},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+def bind_to_gpu_numa_node(gpu_index):
+    """Pin this process to the CPUs NVML lists as local to the GPU (read-only query), so that the pinned
+    host buffers allocated afterwards are first touched on that NUMA node.  Returns the CPU list or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = [64 * i + b for i, wd in enumerate(mask) for b in range(64) if (wd >> b) & 1]
+        cpus = [c for c in cpus if c in os.sched_getaffinity(0)]
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+        return cpus or None
+    except Exception:
+        return None
 
 
 def main():
@@ -238,7 +269,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-sample-tokens", type=int, default=1024)
+    ap.add_argument("--no-extra-legs", action="store_true", help="skip the strong-scaling and sublayer legs")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size (profiling cases)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="profiling case: device-resident steps only (no end-to-end leg, no CPU baseline)")
@@ -260,6 +291,7 @@ def main():
     import torch.distributed as dist
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback")
+    numa_cpus = bind_to_gpu_numa_node(local)  # before any pinned allocation: first touch on the GPU's node
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
@@ -407,6 +439,73 @@ def main():
     if world > 1:
         dist.all_reduce(t2, op=dist.ReduceOp.MAX)
     e2e_ms = float(t2.item()) / e2e_steps
+    # what the copy engines deliver on their own (one direction at a time, this rank's buffers, all ranks
+    # at once): shows whether the end-to-end leg is limited by the host side of the copies
+    def copy_rate(pairs, nbytes):
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        g0.record()
+        for _ in range(3):
+            for dst, src in pairs:
+                dst.copy_(src, non_blocking=True)
+        g1.record()
+        barrier()
+        r = torch.tensor([3 * nbytes / (g0.elapsed_time(g1) / 1e3) / 1e9], device=device)
+        lo = r.clone()
+        if world > 1:
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(r, op=dist.ReduceOp.SUM)
+        return {"per_rank_min": float(lo.item()), "all_ranks": float(r.item())}
+    h2d_rate = copy_rate([(dev_buf[0][k], host[k]) for k in names], h2d)
+    d2h_rate = copy_rate(list(zip(pinned_out[0], [torch.empty_like(x, device=device) for x in pinned_out[0]])), d2h)
+
+    # ---- extra legs (same JSON line): strong scaling of the workload's one batch, and the sublayer -----
+    def timed(fn, steps, warm):
+        for _ in range(warm):
+            fn()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a0.record()
+        for _ in range(steps):
+            fn()
+        a1.record()
+        barrier()
+        tt = torch.tensor([a0.elapsed_time(a1)], device=device)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item()) / steps
+
+    strong = sublayer = None
+    if not args.no_extra_legs and not sub:
+        from openkimi_b200.partition import shard_batch
+        if world > 1 and not w["docs"]:
+            # the ONE batch of the workload (rank 0's data of the weak leg), sequences dealt to the ranks
+            mine = shard_batch(w["B"], world, rank)
+            full = make_workload(w, seed=0)
+            part = {k: (v[mine.start:mine.stop].contiguous() if isinstance(v, torch.Tensor) and v.dim() >= 3 else v)
+                    for k, v in full.items()}
+            dev_part = to_device(part, device) if len(mine) else None
+            ws = dict(w, B=len(mine))
+            ms_s = timed((lambda: step_device(dev_part, ws)) if dev_part is not None else (lambda: None), args.steps, 3)
+            strong = {"value": w["B"] * w["T"] / (ms_s / 1e3) / 1e6, "unit": UNIT, "ms_per_step": ms_s,
+                      "global_batch": w["B"], "sequences_per_rank": len(mine),
+                      "speedup_vs_one_gpu": (ms / args.steps) / ms_s, "efficiency": (ms / args.steps) / ms_s / world,
+                      "how": "config batch split by sequence with partition.shard_batch; one-GPU time = this run's "
+                             "weak-scaling step (every rank runs the whole batch there); no collective"}
+            del dev_part
+        w4 = dict(WORKLOADS["c4"])
+        w4["B"] = max(1, w4["B"] // world)
+        gen4 = torch.Generator().manual_seed(100 + rank)
+        width = w4["H"] * w4["d"]
+        x4 = torch.randn(w4["B"], w4["T"], width, generator=gen4).bfloat16().to(device).requires_grad_(True)
+        dy4 = torch.randn(w4["B"], w4["T"], width, generator=gen4).bfloat16().to(device)
+        model4 = make_sublayer(w4, device)
+        ms4 = timed(lambda: step_sublayer(model4, x4, dy4), max(3, min(args.steps, 5)), 3)
+        sublayer = {"value": world * w4["B"] * w4["T"] / (ms4 / 1e3) / 1e6, "unit": UNIT, "ms_per_step": ms4,
+                    "workload": w4["label"], "batch_per_rank": w4["B"], "scaling": "strong",
+                    "how": "KimiDeltaAttention fwd+bwd under BF16 autocast, conv fused into the KDA load stage, "
+                           "projections by cuBLAS; global batch 64 split over the ranks"}
+        del model4, x4, dy4
 
     if rank != 0:
         if world > 1:
@@ -432,14 +531,19 @@ def main():
     else:
         ach = flops * units / (avg[dom] / 1e3) / 1e12
         roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"]}
-    # DRAM bytes per (chunk, head) unit from the committed ncu capture of the batch-4 case
-    # (dram__bytes_read.sum + dram__bytes_write.sum over 768 units, profiles/kda_bf16_kernels_c1_batch4.md);
-    # traffic grows in proportion to the units, so a full launch is that figure times its units
-    ncu_bytes_per_unit = {"fwd_intra": 140.9e3, "fwd_state": 86.0e3, "bwd_state": 85.1e3, "bwd_wy": 206.5e3,
-                          "bwd_intra": 171.3e3}
-    traffic = ncu_bytes_per_unit[dom] * units if (dom in ncu_bytes_per_unit and w["d"] == 128 and not sub) else None
+    # DRAM bytes per (chunk, head) unit: measured figures of one ncu capture of a small case, kept in a data
+    # file next to the capture's summary together with the commit they were taken at; traffic grows in
+    # proportion to the units, so a full launch is the per-unit figure times its units
+    traffic = traffic_src = None
+    tpath = os.path.join(ROOT, "profiles", "kda_bf16_kernels_c1_batch4.traffic.json")
+    if os.path.exists(tpath) and w["d"] == 128 and not sub:
+        tf = json.load(open(tpath))
+        kt = tf.get("kernels", {}).get(dom)
+        if kt:
+            traffic = (kt["dram_bytes_read"] + kt["dram_bytes_write"]) / tf["units"] * units
+            traffic_src = f"ncu capture of {tf['units']} units at commit {tf['commit']}, scaled by units"
     roof.update({"kernel": dom, "kernel_ms": avg[dom], "peak_source": peaks["source"], "traffic": traffic,
-                 "traffic_source": "ncu capture of 768 units, scaled by units" if traffic else None,
+                 "traffic_source": traffic_src,
                  "units_per_launch": units, "algorithmic_bytes_per_unit": byts, "algorithmic_flops_per_unit": flops})
     # whole-op fractions: dense-tile FLOPs 3*(10*C*d + 6*d^2) per (token, head); minimal HBM bytes
     d = w["d"]
@@ -460,17 +564,29 @@ def main():
         "clocks": clocks,
         "e2e": {"value": world * tokens / (e2e_ms / 1e3) / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                "how": "3 streams (H2D / compute / D2H), 2 buffer sets; every step moves all its bytes"},
+                "how": "3 streams (H2D / compute / D2H), 2 buffer sets; every step moves all its bytes",
+                "copy_only_gbs": {"h2d": h2d_rate, "d2h": d2h_rate}, "cpu_affinity": numa_cpus and len(numa_cpus)},
         "gpu_launches": launches,
         "kernels_ms": avg,
         "roofline": roof,
         "whole_op": whole,
     }
+    if strong:
+        line["strong"] = strong
+    if sublayer:
+        line["sublayer"] = sublayer
     if not args.no_cpu_baseline:
-        rate, secs = cpu_oracle_rate(w, args.cpu_sample_tokens, threads=os.cpu_count())
-        line["cpu_baseline"] = {"value": rate / 1e6, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                                "sample": f"oracle fwd+bwd of one [1,{args.cpu_sample_tokens},{w['H']},{w['d']}] slice, "
-                                          f"{secs:.1f} s"}
+        try:
+            os.sched_setaffinity(0, range(os.cpu_count()))  # the CPU arm may use every host core again
+        except Exception:
+            pass
+        torch.set_num_threads(os.cpu_count() or 1)
+        inp_c, T_c = cpu_slice_inputs(w)
+        cpu_slice_seconds(w, inp_c)  # warm-up (thread pool, allocator)
+        reps = 3
+        secs = sum(cpu_slice_seconds(w, inp_c) for _ in range(reps)) / reps
+        line["cpu_baseline"] = {"value": (T_c / w["H"]) / secs / 1e6, "unit": UNIT, "cores": torch.get_num_threads(),
+                                "kind": "port", "sample": cpu_sample_text(w, T_c) + f"; {secs:.1f} s per slice, mean of {reps}"}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

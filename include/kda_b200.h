@@ -38,7 +38,13 @@ enum {
     KDA_FLAG_FORCE_SIMT = 16,   /* FP32 CUDA-core arithmetic in every stage (validation mode) */
     /* per-stage variants of the same switch (debugging / A-B measurements) */
     KDA_FLAG_SIMT_FWD_INTRA = 32, KDA_FLAG_SIMT_FWD_STATE = 64,
-    KDA_FLAG_SIMT_BWD_STATE = 128, KDA_FLAG_SIMT_BWD_CHUNK = 256, KDA_FLAG_SIMT_BWD_WY = 512
+    KDA_FLAG_SIMT_BWD_STATE = 128, KDA_FLAG_SIMT_BWD_CHUNK = 256, KDA_FLAG_SIMT_BWD_WY = 512,
+    /* Forward-only call: nothing is kept for a backward (no T, chunk-entry states, V' or prologue
+     * records are written) and kda_workspace_bytes reports the smaller workspace.  This is the
+     * forward the reference replays under activation checkpointing (k3mini/model.py:825-831) and
+     * the first forward of the recompute policy (disable_recompute = False, k3mini/model.py:215);
+     * o and the final state are bit-identical to the saving forward.  kda_bwd rejects the flag. */
+    KDA_FLAG_NO_SAVE = 1024
 };
 
 enum {
@@ -103,6 +109,10 @@ typedef struct KdaParams {
      * flattened token, valid rows} of every chunk, so that a CTA finds its chunk with one 16-byte load
      * instead of three dependent ones through chunk_seq / seq_chunk_off / cu_seqlens (16-byte aligned). */
     const int32_t *chunk_tab;
+    /* Optional: a word of PINNED (device-mapped) host memory.  When set, kda_fwd / kda_bwd finish with a
+     * one-thread kernel that copies a non-zero *status into it, so that the host can notice a wait
+     * that gave up by reading its own memory, without a copy engine or a synchronisation. */
+    int32_t *status_host;
 } KdaParams;
 
 /* Bytes of forward workspace (saved for the backward) and of backward scratch for these
@@ -116,6 +126,19 @@ int kda_fwd(const KdaParams *p, void *cuda_stream);
 /* Backward of chunk_kda (what autograd runs for k3mini/model.py:200-216):
  * dq, dk, dv, dg, dbeta, dA_log, ddt_bias, dh0 from do, dht and the forward workspace. */
 int kda_bwd(const KdaParams *p, void *cuda_stream);
+
+/* One decoding step: the recurrence of k3mini/model.py:121-128 for ONE token per (sequence, head),
+ * with the same optional prologue as chunk_kda (KDA_FLAG_QK_L2NORM / GATE / BETA_SIGMOID,
+ * k3mini/model.py:217-223) and the same state layouts (KDA_FLAG_STATE_V_FIRST, model.py:214).  The
+ * reference has no generation path; this is the step its final-state interface implies (the
+ * third-party package it builds on ships it as fused_recurrent_kda).
+ *   q, k, g : [N, H, dk]     v, o : [N, H, dv]     beta : [N, H]     states : [N, H, dk, dv] float
+ * state_out may equal state_in (updated in place).  status may be NULL, else a device word that
+ * receives a non-zero code if the bounded wait for the state copy gives up. */
+int kda_recurrent_step(const void *q, const void *k, const void *v, const void *g, const void *beta,
+                       const float *A_log, const float *dt_bias, const float *state_in, float *state_out,
+                       void *o, int32_t N, int32_t H, int32_t dk, int32_t dv, int32_t dtype, int32_t flags,
+                       float scale, int32_t *status, void *cuda_stream);
 
 /* Causal depthwise short convolution + SiLU over [B, T, C] (k3mini/model.py:76-88; the
  * fast path's fla.modules.ShortConvolution at k3mini/model.py:147-155).  weight is
@@ -143,7 +166,10 @@ int kda_short_conv_bwd(const void *x, const float *weight, const void *dy, void 
  *   - All calls on a device share the one array.  Every element that is read is rewritten by
  *     the same call first, so nothing needs clearing, but two calls that overlap on the GPU
  *     (different streams) race on it: serialise them.
- *   - Results equal kda_short_conv_bwd with n_partial = 64 bit for bit. */
+ *   - Results equal kda_short_conv_bwd with n_partial = 64 bit for bit.
+ *   - The per-device address table holds device ordinals 0..63 (a higher ordinal returns
+ *     KDA_ERR_STATIC_LIMIT), and an address looked up before cudaDeviceReset() is stale afterwards:
+ *     do not reset a device between calls. */
 int kda_short_conv_bwd_static(const void *x, const float *weight, const void *dy, void *dx, float *dweight,
                               int32_t B, int32_t T, int32_t C, int32_t ksize, int32_t dtype,
                               const int64_t *cu_seqlens, int32_t N, void *cuda_stream);
@@ -166,6 +192,13 @@ int kda_norm_gate_bwd(const void *x, const void *gate, const float *weight, cons
 int kda_guarded_diagonal_tiles(const float *gate, const float *q, const float *k, const float *beta,
                                const float *dAqk, const float *dAkk, float *dq, float *dk, float *dkt,
                                int *hits, int n_tiles, float max_log2_span, void *cuda_stream);
+
+/* Gate-span statistic of the reference's span profiler (scripts/profile_kda_gate_spans.py:21-56):
+ * raw [B, T, H, d] (T a multiple of 64, d a multiple of 32, d <= 256), a_log [H], dt_bias [H * d] ->
+ * out [B * T/64 * 4 * H * d/32] float: per [16 rows x 32 channels] tile of the within-chunk cumulative
+ * log2 decay -exp(A_log) softplus(raw + dt_bias) / ln 2, the largest drop below the tile's first row. */
+int kda_gate_tile_spans(const void *raw, const float *a_log, const float *dt_bias, float *out, int32_t B,
+                        int32_t T, int32_t H, int32_t d, int32_t dtype, void *cuda_stream);
 
 /* Guarded-diagonal contract of the reference's backend check (k3mini/backends.py:17-19,
  * 68-109): version 1, "tf32x3"-class precision, span <= 232. */
@@ -196,6 +229,10 @@ int kda_selftest_mma(const float *A, const float *B, float *D, int N, int K, int
  * copy that is in flight, copies the 64 floats src -> dst, frees its tensor memory and returns.
  * The device stays usable; the tests use it to check that a given-up wait is reported. */
 int kda_selftest_wait(const float *src, float *dst, int poll_limit, int code, int *status, void *cuda_stream);
+
+/* Launches the one-thread kernel described at KdaParams.status_host on the given stream (for entry
+ * points that take a bare status pointer, such as kda_recurrent_step). */
+int kda_status_publish(const int32_t *status, int32_t *status_host, void *cuda_stream);
 
 const char *kda_status_string(int status);
 const char *kda_last_cuda_error(void);

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_PKG, "libkda_b200.so")
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 FLAG_QK_L2NORM, FLAG_GATE, FLAG_BETA_SIGMOID, FLAG_STATE_V_FIRST, FLAG_FORCE_SIMT = 1, 2, 4, 8, 16
+FLAG_NO_SAVE = 1024
 CHUNK = 64
 ERR_DEVICE_WAIT = 7
 
@@ -37,6 +38,7 @@ class KdaParams(C.Structure):
         ("status", C.c_void_p),
         ("conv_q", C.c_void_p), ("conv_k", C.c_void_p), ("conv_v", C.c_void_p), ("conv_ksize", C.c_int32),
         ("chunk_tab", C.c_void_p),
+        ("status_host", C.c_void_p),
     ]
 
 
@@ -46,15 +48,18 @@ EXPORTS = {
     "kda_guard_max_span": (C.c_float, []),
     "kda_guard_dot_precision": (C.c_char_p, []),
     "kda_status_string": (C.c_char_p, [C.c_int]),
+    "kda_status_publish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "kda_last_cuda_error": (C.c_char_p, []),
     "kda_profile_begin": (C.c_int, [C.c_int]),
     "kda_profile_read": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float), C.c_int]),
     "kda_guarded_diagonal_tiles": (C.c_int, [C.c_void_p] * 10 + [C.c_int, C.c_float, C.c_void_p]),
+    "kda_gate_tile_spans": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int32] * 5 + [C.c_void_p]),
     "kda_selftest_mma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 12 + [C.c_void_p, C.c_void_p]),
     "kda_selftest_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "kda_workspace_bytes": (C.c_int, [C.POINTER(KdaParams), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "kda_fwd": (C.c_int, [C.POINTER(KdaParams), C.c_void_p]),
     "kda_bwd": (C.c_int, [C.POINTER(KdaParams), C.c_void_p]),
+    "kda_recurrent_step": (C.c_int, [C.c_void_p] * 10 + [C.c_int32] * 6 + [C.c_float, C.c_void_p, C.c_void_p]),
     "kda_short_conv_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                      C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "kda_short_conv_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

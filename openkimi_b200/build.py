@@ -11,7 +11,8 @@ from concurrent.futures import ThreadPoolExecutor
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libkda_b200.so")
-SOURCES = ["kda_api.cu", "kda_simt.cu", "kda_aux.cu", "kda_tc.cu", "kda_tc_intra.cu", "kda_bwd_intra.cu", "kda_tc_bwd_wy.cu"]
+SOURCES = ["kda_api.cu", "kda_simt.cu", "kda_aux.cu", "kda_tc.cu", "kda_tc_intra.cu", "kda_bwd_intra.cu", "kda_tc_bwd_wy.cu",
+           "kda_decode.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-extended-lambda", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC"]
 

@@ -15,7 +15,8 @@ bool tc_supported(const KdaParams& p);
 
 static thread_local char g_last_error[256] = "";
 
-static int fail_cuda(cudaError_t e) {
+// records what the runtime said (kda_last_cuda_error) and returns KDA_ERR_LAUNCH
+int fail_cuda(cudaError_t e) {
     snprintf(g_last_error, sizeof(g_last_error), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
     return KDA_ERR_LAUNCH;
 }
@@ -41,6 +42,11 @@ static void prof_open(int kind, cudaStream_t s) {
         g_cur->kind = kind;
         prof_mark(s);
     }
+}
+
+__global__ void status_publish_kernel(const int32_t* status, int32_t* status_host) {
+    const int v = *status;
+    if (v) *status_host = v;
 }
 
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
@@ -70,7 +76,10 @@ static int validate(const KdaParams* p, bool bwd) {
         if ((p->flags & (KDA_FLAG_FORCE_SIMT | KDA_FLAG_SIMT_FWD_INTRA | KDA_FLAG_SIMT_BWD_CHUNK | KDA_FLAG_SIMT_BWD_WY)) || !tc_supported(*p))
             return KDA_ERR_UNSUPPORTED;
     }
-    if (p->workspace_bytes < (conv ? L.total_conv : L.total) || ((uintptr_t)p->workspace & 255)) return KDA_ERR_WORKSPACE;
+    const bool nosave = p->flags & KDA_FLAG_NO_SAVE;
+    if (bwd && nosave) return KDA_ERR_WORKSPACE;  // the records of a forward-only call do not exist
+    if (p->workspace_bytes < (nosave ? L.total_nosave : conv ? L.total_conv : L.total) || ((uintptr_t)p->workspace & 255))
+        return KDA_ERR_WORKSPACE;
     if (bwd) {
         if (!p->grad_o || !p->grad_q || !p->grad_k || !p->grad_v || !p->grad_g || !p->grad_beta || !p->bwd_scratch) return KDA_ERR_NULL;
         if ((p->flags & KDA_FLAG_GATE) && !p->grad_A_log) return KDA_ERR_NULL;
@@ -87,7 +96,7 @@ using namespace kda;
 
 extern "C" {
 
-int kda_abi_version(void) { return 3; }
+int kda_abi_version(void) { return 4; }
 
 int kda_guard_version(void) { return 1; }
 float kda_guard_max_span(void) { return 232.0f; }
@@ -116,7 +125,7 @@ int kda_workspace_bytes(const KdaParams* p, size_t* fwd_bytes, size_t* bwd_bytes
     if (!p) return KDA_ERR_NULL;
     if (p->NT <= 0 || p->H <= 0 || p->dk <= 0 || p->dv <= 0) return KDA_ERR_SHAPE;
     WsLayout L = ws_layout(p->NT, p->H, p->dk, p->dv, p->dtype);
-    if (fwd_bytes) *fwd_bytes = p->conv_q ? L.total_conv : L.total;
+    if (fwd_bytes) *fwd_bytes = (p->flags & KDA_FLAG_NO_SAVE) ? L.total_nosave : p->conv_q ? L.total_conv : L.total;
     if (bwd_bytes) *bwd_bytes = L.bwd_total;
     return KDA_OK;
 }
@@ -129,6 +138,10 @@ int kda_fwd(const KdaParams* p, void* stream) {
     prof_open(0, s);
     cudaError_t e = tc ? tc_fwd(*p, s) : simt_fwd(*p, s);
     g_cur = nullptr;
+    if (e == cudaSuccess && p->status && p->status_host) {
+        status_publish_kernel<<<1, 1, 0, s>>>(p->status, p->status_host);
+        e = cudaGetLastError();
+    }
     return e == cudaSuccess ? KDA_OK : fail_cuda(e);
 }
 
@@ -140,7 +153,17 @@ int kda_bwd(const KdaParams* p, void* stream) {
     prof_open(1, s);
     cudaError_t e = tc ? tc_bwd(*p, s) : simt_bwd(*p, s);
     g_cur = nullptr;
+    if (e == cudaSuccess && p->status && p->status_host) {
+        status_publish_kernel<<<1, 1, 0, s>>>(p->status, p->status_host);
+        e = cudaGetLastError();
+    }
     return e == cudaSuccess ? KDA_OK : fail_cuda(e);
+}
+
+int kda_status_publish(const int32_t* status, int32_t* status_host, void* stream) {
+    if (!status || !status_host) return KDA_ERR_NULL;
+    status_publish_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(status, status_host);
+    return launch_status();
 }
 
 int kda_profile_begin(int max_calls) {

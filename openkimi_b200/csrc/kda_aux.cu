@@ -338,11 +338,57 @@ __global__ void __launch_bounds__(256) norm_gate_bwd_kernel(const T* __restrict_
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Gate-span statistic (scripts/profile_kda_gate_spans.py:21-56 of the reference): for every
+// [16 rows x 32 channels] tile of the within-chunk cumulative log2 decay, the largest drop below
+// the tile's first row.  One CTA per (sequence, chunk, head), one thread per channel, so the
+// cumulative sum runs in registers and a warp is exactly one channel tile.
+// Output order [B][T/64][4][H][d/32], the flattening the reference's function returns.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) gate_tile_spans_kernel(const T* __restrict__ raw, const float* __restrict__ a_log,
+                                                              const float* __restrict__ dt_bias, float* __restrict__ out,
+                                                              int Tlen, int H, int d) {
+    const int ch = threadIdx.x, h = blockIdx.x % H, cidx = blockIdx.x / H;  // cidx = b * (T / 64) + chunk
+    const int nct = d / 32;
+    const float negA = -expf(a_log[h]) * LOG2E, bias = dt_bias[h * d + ch];
+    const T* src = raw + ((size_t)cidx * C * H + h) * d + ch;
+    float cum = 0.f;
+#pragma unroll 1
+    for (int blk = 0; blk < C / 16; ++blk) {
+        float first = 0.f, span = 0.f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            cum += negA * softplus_f(ldf(src + (size_t)(16 * blk + r) * H * d) + bias);
+            if (r == 0) first = cum;
+            span = fmaxf(span, first - cum);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) span = fmaxf(span, __shfl_xor_sync(0xffffffffu, span, o));
+        if ((ch & 31) == 0) out[(((size_t)cidx * (C / 16) + blk) * H + h) * nct + (ch >> 5)] = span;
+    }
+}
+
 }  // namespace kda
 
 using namespace kda;
 
 extern "C" {
+
+int kda_gate_tile_spans(const void* raw, const float* a_log, const float* dt_bias, float* out, int32_t B, int32_t T,
+                        int32_t H, int32_t d, int32_t dtype, void* stream) {
+    if (!raw || !a_log || !dt_bias || !out) return KDA_ERR_NULL;
+    if (B <= 0 || T <= 0 || H <= 0 || T % C || d <= 0 || d % 32 || d > 256) return KDA_ERR_SHAPE;
+    if (dtype != KDA_DTYPE_BF16 && dtype != KDA_DTYPE_F32) return KDA_ERR_DTYPE;
+    const long long grid = (long long)B * (T / C) * H;
+    if (grid > 0x7fffffffLL) return KDA_ERR_SHAPE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == KDA_DTYPE_BF16)
+        gate_tile_spans_kernel<__nv_bfloat16><<<(int)grid, d, 0, s>>>((const __nv_bfloat16*)raw, a_log, dt_bias, out, T, H, d);
+    else
+        gate_tile_spans_kernel<float><<<(int)grid, d, 0, s>>>((const float*)raw, a_log, dt_bias, out, T, H, d);
+    return launch_status();
+}
 
 int kda_short_conv_fwd(const void* x, const float* weight, void* y, int32_t B, int32_t T, int32_t Cch, int32_t ksize,
                        int32_t dtype, const int64_t* cu_seqlens, int32_t N, void* stream) {
@@ -362,14 +408,15 @@ int kda_short_conv_fwd(const void* x, const float* weight, void* y, int32_t B, i
     else
         short_conv_fwd_kernel<float><<<grid, 128, 0, s>>>((const float*)x, weight, (float*)y, total, T, Cch, ksize,
                                                           cu_seqlens, N);
-    return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+    return launch_status();
 }
 
 int kda_short_conv_bwd(const void* x, const float* weight, const void* dy, void* dx, float* dweight,
                        float* partial, int32_t n_partial, int32_t B, int32_t T, int32_t Cch, int32_t ksize,
                        int32_t dtype, const int64_t* cu_seqlens, int32_t N, void* stream) {
     if (!x || !weight || !dy || !dx || !dweight || !partial) return KDA_ERR_NULL;
-    if (ksize < 1 || ksize > CONV_KMAX || B <= 0 || T <= 0 || n_partial < 1 || (cu_seqlens && B != 1)) return KDA_ERR_SHAPE;
+    if (ksize < 1 || ksize > CONV_KMAX || B <= 0 || T <= 0 || n_partial < 1 || n_partial > 65535 || (cu_seqlens && B != 1))
+        return KDA_ERR_SHAPE;  // (n_partial is a grid dimension)
     if (dtype != KDA_DTYPE_BF16 && dtype != KDA_DTYPE_F32) return KDA_ERR_DTYPE;
     const int V = dtype == KDA_DTYPE_BF16 ? 8 : 4;
     if (Cch % V) return KDA_ERR_SHAPE;
@@ -387,7 +434,7 @@ int kda_short_conv_bwd(const void* x, const float* weight, const void* dy, void*
                                                             total, T, Cch, ksize, cu_seqlens, N);
     int n = Cch * ksize;
     partial_reduce_kernel<<<(n + 31) / 32, 256, 0, s>>>(partial, dweight, n_partial, n);
-    return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+    return launch_status();
 }
 
 int kda_norm_gate_fwd(const void* x, const void* gate, const float* weight, void* y, float* rstd, int64_t rows,
@@ -402,14 +449,14 @@ int kda_norm_gate_fwd(const void* x, const void* gate, const float* weight, void
     if (dtype == KDA_DTYPE_BF16) { if (dim == 64) NG_FWD(__nv_bfloat16, 64); else NG_FWD(__nv_bfloat16, 128); }
     else { if (dim == 64) NG_FWD(float, 64); else NG_FWD(float, 128); }
 #undef NG_FWD
-    return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+    return launch_status();
 }
 
 int kda_norm_gate_bwd(const void* x, const void* gate, const float* weight, const void* dy, void* dx, void* dgate,
                       float* dweight, float* partial, int32_t n_partial, int64_t rows, int32_t dim, float eps,
                       int32_t dtype, void* stream) {
     if (!x || !gate || !weight || !dy || !dx || !dgate || !dweight || !partial) return KDA_ERR_NULL;
-    if (rows <= 0 || (dim != 64 && dim != 128) || n_partial < 1) return KDA_ERR_SHAPE;
+    if (rows <= 0 || (dim != 64 && dim != 128) || n_partial < 1 || n_partial > 65535) return KDA_ERR_SHAPE;
     if (dtype != KDA_DTYPE_BF16 && dtype != KDA_DTYPE_F32) return KDA_ERR_DTYPE;
     cudaStream_t s = (cudaStream_t)stream;
 #define NG_BWD(TT, DD)                                                                                               \
@@ -419,7 +466,7 @@ int kda_norm_gate_bwd(const void* x, const void* gate, const float* weight, cons
     else { if (dim == 64) NG_BWD(float, 64); else NG_BWD(float, 128); }
 #undef NG_BWD
     partial_reduce_kernel<<<(dim + 31) / 32, 256, 0, s>>>(partial, dweight, n_partial, dim);
-    return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+    return launch_status();
 }
 
 // The variant of kda_short_conv_bwd for callers that must not allocate: same kernels, same
@@ -428,19 +475,22 @@ int kda_norm_gate_bwd(const void* x, const void* gate, const float* weight, cons
 int kda_short_conv_bwd_static(const void* x, const float* weight, const void* dy, void* dx, float* dweight, int32_t B,
                               int32_t T, int32_t Cch, int32_t ksize, int32_t dtype, const int64_t* cu_seqlens, int32_t N,
                               void* stream) {
-    if (ksize < 1 || Cch < 1 || (int64_t)Cch * ksize > CONV_STATIC_MAX_WEIGHTS) return KDA_ERR_STATIC_LIMIT;
+    if (ksize < 1 || Cch < 1) return KDA_ERR_SHAPE;
+    if ((int64_t)Cch * ksize > CONV_STATIC_MAX_WEIGHTS) return KDA_ERR_STATIC_LIMIT;
     // One-time set-up per device, with that device current: ask the runtime where this
     // device's copy of the array lives.  The array's name itself is not that address.
     static std::mutex mu;
     static float* dev_ptr[64] = {nullptr};
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KDA_ERR_LAUNCH;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return fail_cuda(cudaGetLastError());
+    if (dev >= 64) return KDA_ERR_STATIC_LIMIT;  // the per-device address table has 64 entries
     float* part = nullptr;
     {
         std::lock_guard<std::mutex> lock(mu);
         if (!dev_ptr[dev]) {
             void* ptr = nullptr;
-            if (cudaGetSymbolAddress(&ptr, g_conv_static_partial) != cudaSuccess || !ptr) return KDA_ERR_LAUNCH;
+            const cudaError_t e = cudaGetSymbolAddress(&ptr, g_conv_static_partial);
+            if (e != cudaSuccess || !ptr) return fail_cuda(e);
             dev_ptr[dev] = static_cast<float*>(ptr);
         }
         part = dev_ptr[dev];

@@ -13,6 +13,14 @@ namespace kda {
 constexpr int C = KDA_CHUNK;       // tokens per chunk
 constexpr float LOG2E = 1.4426950408889634f;
 
+// records what the CUDA runtime said for kda_last_cuda_error() and returns KDA_ERR_LAUNCH
+int fail_cuda(cudaError_t e);
+// status of an entry point after its launches: KDA_OK, or KDA_ERR_LAUNCH with the runtime's message kept
+inline int launch_status() {
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KDA_OK : fail_cuda(e);
+}
+
 // ---------------------------------------------------------------------------------------
 // element access
 // ---------------------------------------------------------------------------------------
@@ -80,7 +88,8 @@ __device__ __forceinline__ void seq_chunks(const KdaParams& p, int n, int& c0, i
 // gamC is a plain float[dk]; Gc, Qn, Kn, aux are plain row-major arrays.
 // ---------------------------------------------------------------------------------------
 struct WsLayout {
-    size_t W, U, Aqk, Qt, Kh, Tm, S0, gamC;             // forward workspace
+    size_t W, U, Aqk, Qt, Kh, gamC, total_nosave;       // what fwd_state consumes (all a forward-only call needs)
+    size_t Tm, S0;                                      // kept for the backward only
     size_t Gc, Qn, Kn, aux, total;                      // prologue results kept for the backward
     size_t Vc, total_conv;                              // convolved v rows (fused short convolution only)
     size_t dS, dVn, dA_part, dbias_part;                // backward scratch
@@ -99,9 +108,12 @@ __host__ __device__ inline WsLayout ws_layout(int NT, int H, int dk, int dv, int
     w.Aqk = off;  off = align256(off + n * C * C * es);
     w.Qt = off;   off = align256(off + n * C * dk * es);
     w.Kh = off;   off = align256(off + n * C * dk * es);
+    w.gamC = off; off = align256(off + n * dk * 4);
+    // a forward that nobody differentiates (KDA_FLAG_NO_SAVE) stops here: T, the chunk-entry states,
+    // the V' overwrite of U and the kept prologue are written only for the backward
+    w.total_nosave = off;
     w.Tm = off;   off = align256(off + n * C * C * es);
     w.S0 = off;   off = align256(off + n * dk * dv * es);
-    w.gamC = off; off = align256(off + n * dk * 4);
     // kept so that the backward does not redo the prologue: cumulative log2 decay G (float
     // [64][dk]), normalised q and k (element type, [64][dk] row-major), and per row
     // 1/|q|, 1/|k|, beta after the sigmoid (float [3][64])

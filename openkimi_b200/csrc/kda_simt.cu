@@ -191,7 +191,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_fwd_intra_simt(const KdaParam
     float* gGam = (float*)(ws + L.gamC) + rec * D;
 
     load_prologue<T, D>(p, ci, h, sq, sk, sG, sv, sbeta, srq, srk);
-    {  // prologue results kept for the backward
+    const bool save = !(p.flags & KDA_FLAG_NO_SAVE);  // forward-only calls keep nothing for a backward
+    if (save) {  // prologue results kept for the backward
         float* gGc = (float*)(ws + L.Gc) + rec * C * D;
         T* gQn = (T*)(ws + L.Qn) + rec * C * D;
         T* gKn = (T*)(ws + L.Kn) + rec * C * D;
@@ -255,7 +256,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_fwd_intra_simt(const KdaParam
     for (int idx = tid; idx < C * C; idx += NTHREADS) {
         int i = idx / C, j = idx % C;
         stf(gA + tc::cm_idx(i, j, C), sA[i * 65 + j]);
-        stf(gT + tc::cm_idx(i, j, C), sT[i * 65 + j]);
+        if (save) stf(gT + tc::cm_idx(i, j, C), sT[i * 65 + j]);
     }
     for (int idx = tid; idx < C * D; idx += NTHREADS) {
         int i = idx / D, d = idx % D;
@@ -331,7 +332,7 @@ __global__ void __launch_bounds__(NTHREADS) kda_fwd_state_simt(const KdaParams p
 
         for (int idx = tid; idx < D * BV; idx += NTHREADS) {
             int d = idx / BV, e = idx % BV;
-            stf(gS0 + tc::cm_idx(e0 + e, d, D), sS[d * (BV + 1) + e]);
+            if (!(p.flags & KDA_FLAG_NO_SAVE)) stf(gS0 + tc::cm_idx(e0 + e, d, D), sS[d * (BV + 1) + e]);
         }
         // V' = U - W S
         {
@@ -346,7 +347,7 @@ __global__ void __launch_bounds__(NTHREADS) kda_fwd_state_simt(const KdaParams p
                     int i = ty + 16 * r, e = tx + 16 * cc;
                     float vn = ldf(gU + tc::cm_idx(e0 + e, i, C)) - acc[r][cc];
                     sVn[i * (BV + 1) + e] = vn;
-                    stf(gU + tc::cm_idx(e0 + e, i, C), vn);
+                    if (!(p.flags & KDA_FLAG_NO_SAVE)) stf(gU + tc::cm_idx(e0 + e, i, C), vn);
                 }
         }
         // O = Qt S + Aqk V'

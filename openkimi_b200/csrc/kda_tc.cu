@@ -192,6 +192,7 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
     const uint32_t tmem = tmem_s + ((uint32_t)(warp * 32) << 16);  // this warp's lane quadrant
     const uint32_t tmem0 = tmem_s;
     const size_t sbase = ((size_t)n * p.H + h) * D * D;
+    const bool save = !(p.flags & KDA_FLAG_NO_SAVE);  // forward-only calls write no checkpoint and no V' record
 
     for (int d0 = 0; d0 < D; d0 += 16) {
         uint32_t r[16];
@@ -239,8 +240,10 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
                 tmem_st8(tmem + SBF + d0 / 2, pk);
-                *reinterpret_cast<uint4*>(gS0 + cm_idx(tid, d0, D)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                *reinterpret_cast<uint4*>(gS0 + cm_idx(tid, d0 + 8, D)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                if (save) {
+                    *reinterpret_cast<uint4*>(gS0 + cm_idx(tid, d0, D)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *reinterpret_cast<uint4*>(gS0 + cm_idx(tid, d0 + 8, D)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                }
 #pragma unroll
                 for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gam[d0 + j]);
                 tmem_st16(tmem + SACC + d0, r);
@@ -294,8 +297,10 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
                 for (int j = 0; j < 8; ++j)
                     pk[j] = pack_bf16(u[2 * j] - __uint_as_float(r[2 * j]), u[2 * j + 1] - __uint_as_float(r[2 * j + 1]));
                 tmem_st8(tmem + VBF + i0 / 2, pk);
-                *reinterpret_cast<uint4*>(gV + cm_idx(tid, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                *reinterpret_cast<uint4*>(gV + cm_idx(tid, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                if (save) {
+                    *reinterpret_cast<uint4*>(gV + cm_idx(tid, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *reinterpret_cast<uint4*>(gV + cm_idx(tid, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                }
             }
             tmem_wait_st();
         }

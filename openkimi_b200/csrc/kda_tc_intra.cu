@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     const __nv_bfloat16* g = (const __nv_bfloat16*)p.g;
     const __nv_bfloat16* beta = (const __nv_bfloat16*)p.beta;
     const bool l2 = p.flags & KDA_FLAG_QK_L2NORM, gate = p.flags & KDA_FLAG_GATE, sig = p.flags & KDA_FLAG_BETA_SIGMOID;
+    const bool save = !(p.flags & KDA_FLAG_NO_SAVE);  // forward-only calls keep nothing for a backward
 
     KDA_PHASE_BEGIN();
     if (warp == 0) {
@@ -293,9 +294,11 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         conv_rows(rq4, 0);
         conv_rows(rk4, 1);
         conv_rows(rv4, 2);
-        __nv_bfloat16* gVc = (__nv_bfloat16*)(ws + L.Vc) + rec * C * D;
+        if (save) {
+            __nv_bfloat16* gVc = (__nv_bfloat16*)(ws + L.Vc) + rec * C * D;
 #pragma unroll
-        for (int m = 0; m < 4; ++m) *reinterpret_cast<uint4*>(gVc + (4 * hw + m) * D + c8) = rv4[m];
+            for (int m = 0; m < 4; ++m) *reinterpret_cast<uint4*>(gVc + (4 * hw + m) * D + c8) = rv4[m];
+        }
     } else {
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
@@ -530,7 +533,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 
     KDA_PHASE(5);
     // (issued here rather than before the operand stage, whose shared-memory traffic they would share)
-    if (tid == 0) {  // prologue results for the backward: three bulk stores straight from shared memory
+    if (tid == 0 && save) {  // prologue results for the backward: three bulk stores straight from shared memory
         tma_store_1d((float*)(ws + L.Gc) + rec * C * D, sG, C * D * 4);
         tma_store_1d((__nv_bfloat16*)(ws + L.Qn) + rec * C * D, sQ, C * D * 2);
         tma_store_1d((__nv_bfloat16*)(ws + L.Kn) + rec * C * D, sK, C * D * 2);
@@ -560,7 +563,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             }
             const uint4 tb = f32_to_bf16x8(t8);
             *reinterpret_cast<uint4*>(gA + cm_idx(i, j8, C)) = f32_to_bf16x8(a8);
-            *reinterpret_cast<uint4*>(gT + cm_idx(i, j8, C)) = tb;
+            if (save) *reinterpret_cast<uint4*>(gT + cm_idx(i, j8, C)) = tb;
             *reinterpret_cast<uint4*>(sTB + cm_idx(i, j8, C)) = tb;
         }
     }

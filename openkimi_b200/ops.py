@@ -52,18 +52,17 @@ def _chunk_tables(cu_seqlens, cu_seqlens_cpu, device):
 
 
 class _DeviceStatus:
-    """One int32 status word per device.  A kernel whose bounded wait gives up ORs a code into it
-    (``KdaParams.status``); after every launch the word is copied to pinned host memory on the
-    same stream, and the next call on that device (or ``check_device_status``) raises if a copy
-    that has completed shows a non-zero word.  No synchronisation on the hot path."""
+    """One int32 status word per device, mirrored in pinned host memory.  A kernel whose bounded wait
+    gives up ORs a code into the device word (``KdaParams.status``); every call ends with a one-thread
+    kernel that copies a non-zero word into the pinned mirror (``KdaParams.status_host``), so the next
+    call on that device (or ``check_device_status``) notices it by reading host memory: no copy engine,
+    no synchronisation on the hot path."""
 
     _per_device: dict = {}
 
     def __init__(self, device):
         self.dev = torch.zeros(1, dtype=torch.int32, device=device)
-        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self.event = torch.cuda.Event()
-        self.pending = False
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()  # device-mapped under unified addressing
 
     @classmethod
     def get(cls, device):
@@ -73,21 +72,9 @@ class _DeviceStatus:
             st = cls._per_device[key] = cls(torch.device("cuda", key))
         return st
 
-    def after_launch(self):
-        if torch.cuda.is_current_stream_capturing():
-            return  # a captured graph replays the kernels only; poll with check_device_status(sync=True)
-        self.host.copy_(self.dev, non_blocking=True)
-        self.event.record()
-        self.pending = True
-
     def poll(self, sync=False):
         if sync:
             self.host.copy_(self.dev)
-            self.pending = False
-        elif not (self.pending and self.event.query()):
-            return
-        else:
-            self.pending = False
         code = int(self.host[0])
         if code:
             self.dev.zero_()
@@ -141,6 +128,7 @@ class _Call:
         self.status = _DeviceStatus.get(q.device)
         self.status.poll()  # a wait that gave up in an earlier call surfaces here
         p.status = self.status.dev.data_ptr()
+        p.status_host = self.status.host.data_ptr()
         self.p = p
         fb, bb = C.c_size_t(0), C.c_size_t(0)
         _lib.check(_lib.load().kda_workspace_bytes(C.byref(p), C.byref(fb), C.byref(bb)), "kda_workspace_bytes")
@@ -198,8 +186,14 @@ class ChunkKDAFunction(torch.autograd.Function):
         if conv_q is not None:
             conv = tuple(w.float().reshape(w.shape[0], w.shape[-1]).contiguous() for w in (conv_q, conv_k, conv_v))
             ctx.conv_dtypes = tuple(w.dtype for w in (conv_q, conv_k, conv_v))
+        # Nothing is kept when nobody will differentiate this call (no_grad, e.g. the forward an
+        # activation-checkpointed block runs first, k3mini/model.py:825-831) or when the backward rebuilds
+        # the records anyway (recompute policy): the forward-only kernels skip every record that only the
+        # backward reads and the workspace is the small one.
+        keep = disable_recompute and any(ctx.needs_input_grad)
+        fwd_flags = flags if keep else flags | _lib.FLAG_NO_SAVE
         with torch.cuda.device(q.device):
-            call = _Call(q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, flags, conv)
+            call = _Call(q, k, v, g, beta, A_log, dt_bias, scale, h0, cu_seqlens, cu_seqlens_cpu, fwd_flags, conv)
             B, T, H, dk, dv = call.shape
             o = torch.empty(B, T, H, dv, dtype=dt, device=q.device)
             state_shape = (call.N, H, dv, dk) if flags & _lib.FLAG_STATE_V_FIRST else (call.N, H, dk, dv)
@@ -210,11 +204,10 @@ class ChunkKDAFunction(torch.autograd.Function):
             p.workspace, p.workspace_bytes = ws.data_ptr(), call.fwd_bytes
             if call.NT > 0:
                 _lib.check(lib.kda_fwd(C.byref(p), call.stream()), "kda_fwd")
-                call.status.after_launch()
             elif ht is not None:
                 ht.copy_(h0 if h0 is not None else torch.zeros_like(ht))
         ctx.save_for_backward(q, k, v, g, beta, A_log, dt_bias, h0, cu_seqlens, cu_seqlens_cpu,
-                              ws if disable_recompute else None, *(conv or ()))
+                              ws if keep else None, *(conv or ()))
         ctx.meta = (scale, flags, in_dtypes, state_shape)
         return o, ht
 
@@ -258,7 +251,6 @@ class ChunkKDAFunction(torch.autograd.Function):
             p.bwd_scratch, p.bwd_scratch_bytes = scratch.data_ptr(), call.bwd_bytes
             if call.NT > 0:
                 _lib.check(lib.kda_bwd(C.byref(p), call.stream()), "kda_bwd")
-                call.status.after_launch()
             else:
                 for t in (dq, dk_, dv_, dg, dbeta, dA, dbias):
                     if t is not None:
@@ -381,3 +373,65 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
                        for x, w in zip((q, k, v), (wq, wk, wv)))
     return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, initial_state, *conv, float(scale), flags,
                                   bool(output_final_state), cu_seqlens, cu_seqlens_cpu, bool(disable_recompute))
+
+
+def recurrent_kda_step(q, k, v, g, beta, state, *, scale=None, A_log=None, dt_bias=None,
+                       use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
+                       state_v_first=False, inplace=False):
+    """One decoding step of KDA: the recurrence of k3mini/model.py:121-128 for a single token.
+
+    q, k, g: [N, H, K]; v: [N, H, V]; beta: [N, H]; ``state``: FP32 ``[N, H, K, V]`` (``[N, H, V, K]``
+    with ``state_v_first``), e.g. the final state ``chunk_kda`` returned for the prompt.  The prologue
+    switches mean what they mean in ``chunk_kda``.  Returns ``(o [N, H, V], new_state)``; with
+    ``inplace=True`` the state tensor itself is updated and returned.  Inference only (no autograd).
+    """
+    for t in (q, k, v, g, beta, state):
+        _require_cuda(t)
+    if q.dim() != 3 or q.shape != k.shape or g.shape != q.shape:
+        raise ValueError(f"q, k, g must share one shape [N,H,K], got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(g.shape)}")
+    N, H, K = q.shape
+    if v.shape != (N, H, K) or K not in (64, 128):
+        raise ValueError(f"the B200 KDA kernels need K == V in (64, 128), got K={K}, v={tuple(v.shape)}")
+    if beta.shape != (N, H):
+        raise ValueError(f"beta must have shape {[N, H]}, got {list(beta.shape)}")
+    if q.dtype not in _DTYPES:
+        raise TypeError(f"q/k/v must be float32 or bfloat16, got {q.dtype}")
+    if state.dtype != torch.float32 or tuple(state.shape) != (N, H, K, K):
+        raise ValueError(f"state must be float32 [N,H,{K},{K}], got {state.dtype} {tuple(state.shape)}")
+    if use_gate_in_kernel and (A_log is None or A_log.numel() != H or (dt_bias is not None and dt_bias.numel() != H * K)):
+        raise ValueError("use_gate_in_kernel=True needs A_log with H entries (and dt_bias with H*K entries)")
+    dt = q.dtype
+    q, k, v, g, beta = (t.detach().to(dt).contiguous() for t in (q, k, v, g, beta))
+    a = A_log.detach().float().contiguous() if use_gate_in_kernel else None
+    b = dt_bias.detach().float().contiguous() if (use_gate_in_kernel and dt_bias is not None) else None
+    s_in = state.detach().contiguous()
+    s_out = s_in if inplace and s_in.data_ptr() == state.data_ptr() else torch.empty_like(s_in)
+    o = torch.empty_like(v)
+    flags = ((_lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0) | (_lib.FLAG_GATE if use_gate_in_kernel else 0)
+             | (_lib.FLAG_BETA_SIGMOID if use_beta_sigmoid_in_kernel else 0)
+             | (_lib.FLAG_STATE_V_FIRST if state_v_first else 0))
+    with torch.cuda.device(q.device):
+        st = _DeviceStatus.get(q.device)
+        st.poll()
+        rc = _lib.load().kda_recurrent_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                                            _ptr(a), _ptr(b), s_in.data_ptr(), s_out.data_ptr(), o.data_ptr(), N, H, K, K,
+                                            _DTYPES[dt], flags, float(K ** -0.5 if scale is None else scale),
+                                            st.dev.data_ptr(), C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream))
+        _lib.check(rc, "kda_recurrent_step")
+    return o, s_out
+
+
+def fused_recurrent_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, **kw):
+    """Token-by-token KDA over ``[B, T, H, K]`` inputs through ``recurrent_kda_step`` (the decoding
+    counterpart of ``chunk_kda``, same prologue keywords; meant for the few tokens of a decode loop).
+    Returns ``(o [B, T, H, V], final_state or None)``."""
+    B, T, H, K = q.shape
+    vfirst = bool(kw.get("state_v_first", False))
+    state = (initial_state.detach().clone() if initial_state is not None
+             else torch.zeros(B, H, K, K, dtype=torch.float32, device=q.device))
+    outs = []
+    for t in range(T):
+        o, state = recurrent_kda_step(q[:, t], k[:, t], v[:, t], g[:, t], beta[:, t], state, scale=scale, inplace=True, **kw)
+        outs.append(o)
+    o = torch.stack(outs, dim=1) if outs else v.new_zeros(B, 0, H, K)
+    return o, (state if output_final_state else None)

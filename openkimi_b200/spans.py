@@ -1,10 +1,10 @@
-"""Gate-span statistic and the guarded diagonal tile as callable utilities.
+"""Gate-span statistic and the guarded diagonal tile as callable utilities on the GPU.
 
-``gate_tile_spans`` mirrors scripts/profile_kda_gate_spans.py:21-56 of the reference (log2
-span of every [16 rows x 32 channels] tile of the within-chunk cumulative gate); it is plain
-tensor arithmetic and runs wherever its inputs live.  ``guarded_diagonal_backward`` runs the
-CUDA tile kernel behind the interface of
-experiments/kda_sm90/guarded_diagonal_oracle.py::guarded_diagonal_backward (midpoint policy)."""
+``gate_tile_spans`` has the interface of scripts/profile_kda_gate_spans.py:21-56 of the reference
+(log2 span of every [16 rows x 32 channels] tile of the within-chunk cumulative gate) and runs the
+CUDA kernel ``kda_gate_tile_spans``.  ``guarded_diagonal_backward`` runs the CUDA tile kernel behind
+the interface of experiments/kda_sm90/guarded_diagonal_oracle.py::guarded_diagonal_backward
+(midpoint policy)."""
 
 from __future__ import annotations
 
@@ -13,26 +13,36 @@ import math
 from dataclasses import dataclass
 
 import torch
-import torch.nn.functional as F
 
 from . import _lib
 
-CHUNK_SIZE, BLOCK_SIZE, CHANNEL_TILE = 64, 16, 32
-RCP_LN2 = 1.0 / math.log(2.0)
+_DT = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16}
 
 
 def gate_tile_spans(raw_decay: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor) -> torch.Tensor:
+    """raw_decay [B, T, H, d] (CUDA, FP32 or BF16), a_log [H], dt_bias [H, d] -> FP32 spans, one per
+    tile, flattened in the order [B][T/64][4][H][d/32]."""
+    if raw_decay.dim() != 4:
+        raise ValueError("raw_decay must have shape [B, T, H, d]")
     batch, seqlen, heads, dim = raw_decay.shape
-    if seqlen % CHUNK_SIZE:
+    if seqlen % 64:
         raise ValueError("sequence length must be divisible by the chunk size")
-    if dim % CHANNEL_TILE:
+    if dim % 32:
         raise ValueError("head dimension must be a multiple of the 32-channel tile")
-    steps = (-a_log.float().exp().view(1, 1, heads, 1)
-             * F.softplus(raw_decay.float() + dt_bias.float().view(1, 1, heads, dim)) * RCP_LN2)
-    cum = steps.view(batch, seqlen // CHUNK_SIZE, CHUNK_SIZE, heads, dim).cumsum(dim=2)
-    tiles = cum.view(batch, seqlen // CHUNK_SIZE, CHUNK_SIZE // BLOCK_SIZE, BLOCK_SIZE, heads, dim // CHANNEL_TILE,
-                     CHANNEL_TILE)
-    return (tiles[:, :, :, :1] - tiles).amax(dim=(3, 6)).flatten()
+    if not raw_decay.is_cuda:
+        raise RuntimeError("gate_tile_spans runs only on a CUDA device; there is no CPU fallback")
+    if a_log.numel() != heads or dt_bias.numel() != heads * dim:
+        raise ValueError("a_log must have H entries and dt_bias H*d entries")
+    raw = raw_decay.contiguous() if raw_decay.dtype in _DT else raw_decay.float().contiguous()
+    a = a_log.to(device=raw.device, dtype=torch.float32).contiguous()
+    b = dt_bias.to(device=raw.device, dtype=torch.float32).contiguous()
+    out = torch.empty(batch * (seqlen // 64) * 4 * heads * (dim // 32), dtype=torch.float32, device=raw.device)
+    with torch.cuda.device(raw.device):
+        rc = _lib.load().kda_gate_tile_spans(raw.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, seqlen,
+                                             heads, dim, _DT[raw.dtype],
+                                             C.c_void_p(torch.cuda.current_stream(raw.device).cuda_stream))
+    _lib.check(rc, "kda_gate_tile_spans")
+    return out
 
 
 @dataclass(frozen=True)

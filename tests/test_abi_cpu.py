@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.EXPORTS), declared ^ set(_lib.EXPORTS)
     for name in declared:
         assert getattr(lib, name) is not None
-    assert lib.kda_abi_version() == 3
+    assert lib.kda_abi_version() == 4
     assert lib.kda_guard_version() == 1 and lib.kda_guard_max_span() == 232.0
     assert lib.kda_guard_dot_precision() == b"tf32x3"
     assert b"NULL" in lib.kda_status_string(1)
@@ -64,6 +64,11 @@ def test_validation_rejects_bad_arguments_without_a_gpu():
     fb, bb = C.c_size_t(), C.c_size_t()
     assert lib.kda_workspace_bytes(C.byref(p), C.byref(fb), C.byref(bb)) == 0
     assert fb.value > 0 and bb.value > 0 and fb.value % 256 == 0
+    # a forward-only call (KDA_FLAG_NO_SAVE) needs less than half of the saving forward's workspace
+    full = fb.value
+    p.flags = _lib.FLAG_NO_SAVE
+    assert lib.kda_workspace_bytes(C.byref(p), C.byref(fb), C.byref(bb)) == 0
+    assert 0 < fb.value < full // 2
 
 
 def test_fused_convolution_arguments_are_validated_without_a_gpu():

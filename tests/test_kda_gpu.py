@@ -203,3 +203,26 @@ def test_argument_errors():
         chunk_kda(q, q, q, q, b, chunk_size=32)
     with pytest.raises(RuntimeError, match="CUDA"):
         chunk_kda(q.cpu(), q.cpu(), q.cpu(), q.cpu(), b.cpu())
+
+
+@pytest.mark.parametrize("dtype,d", [(torch.bfloat16, 128), (torch.float32, 64)])
+def test_forward_only_call_matches_the_saving_forward_bitwise(dtype, d):
+    """Under no_grad (the forward an activation-checkpointed block runs first, k3mini/model.py:825-831)
+    the kernels write none of the records the backward reads; o and the final state must not change."""
+    from openkimi_b200 import chunk_kda
+
+    inp = O.make_inputs(2, 200, 2, d, seed=31, dtype=dtype)
+    cu = torch.tensor([0, 70, 200])
+    for kw in (dict(), dict(cu_seqlens=cu.cuda(), cu_seqlens_cpu=cu)):
+        sl = (lambda t: t[:1]) if kw else (lambda t: t)
+        args = [sl(inp[n]).cuda() for n in ("q", "k", "v", "g", "beta")]
+        common = dict(A_log=inp["a_log"].cuda(), dt_bias=inp["dt_bias"].cuda(), use_qk_l2norm_in_kernel=True,
+                      use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=True, output_final_state=True,
+                      disable_recompute=True, **kw)
+        with torch.no_grad():
+            o0, s0 = chunk_kda(*args, **common)
+        leaves = [a.clone().requires_grad_(True) for a in args]
+        o1, s1 = chunk_kda(*leaves, **common)
+        assert torch.equal(o0, o1) and torch.equal(s0, s1)
+        o1.float().sum().backward()   # the saving forward still feeds a working backward
+        assert all(torch.isfinite(x.grad.float()).all() for x in leaves)

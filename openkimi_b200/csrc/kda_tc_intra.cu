@@ -23,7 +23,7 @@ namespace kda {
 using namespace tc;
 
 namespace fi {
-constexpr int D = 128, NTHR = 256;
+constexpr int D = 128, NTHR = 512;
 constexpr uint32_t SQ = 0;                   // q^  bf16 [64][128] row-major
 constexpr uint32_t SK = SQ + 16384;          // k^  bf16 [64][128]
 constexpr uint32_t SG = SK + 16384;          // G   f32  [64][128]
@@ -35,17 +35,19 @@ constexpr uint32_t SA = BV + 16384;          // f32 [64][65]
 constexpr uint32_t SL = SA + 16640;
 constexpr uint32_t ST = SL + 16640;
 constexpr uint32_t SBETA = ST + 16640;        // f32 [3][64]: 1/|q|, 1/|k|, beta (the aux record)
-constexpr uint32_t STOT = SBETA + 768;       // f32 [128]
-constexpr uint32_t TOTAL = STOT + 512;
+constexpr uint32_t STOT = SBETA + 768;       // f32 [4][128] running gate totals of the four 16-row groups
+constexpr uint32_t TOTAL = STOT + 2048;
 constexpr uint32_t T_D = 0, T_W = 96, T_U = 160, TMEM_COLS = 256;
 }  // namespace fi
 
 // One block column J of T = (I + diag(beta) L)^-1 (see stage 3 of the kernel).  sL holds L
 // (strictly lower, row stride 65), sT receives T; sT must be zero above the diagonal blocks.
+// Four warps share a block column: warp (J, cw) owns columns 4 cw + lane % 4, and its eight lane
+// groups (lane / 4) split the 16 rows of every block below the diagonal, two rows each.
 // J is uniform over the warp; the loops run over all blocks with warp-uniform skips so that the
 // register arrays keep compile-time indices in a single copy of the code.
-__device__ __forceinline__ void solve_block_column(const float* sL, float* sT, const float* sbeta, int J, int warp, int lane) {
-    const int col = 8 * (warp >> 2) + (lane & 7), rq = lane >> 3, gc = 16 * J + col;
+__device__ __forceinline__ void solve_block_column(const float* sL, float* sT, const float* sbeta, int J, int cw, int lane) {
+    const int col = 4 * cw + (lane & 3), rq = lane >> 2, gc = 16 * J + col;
     float t[4][16];
     // diagonal block: forward substitution down the column (every lane group does all 16 rows)
 #pragma unroll
@@ -69,48 +71,49 @@ __device__ __forceinline__ void solve_block_column(const float* sL, float* sT, c
     for (int n = 1; n < 4; ++n) {
         const int I = J + n;
         if (I > 3) break;
-        // y = sum_K (beta L)_IK t_K for my four rows, then all 16 entries from the lane groups
-        float y4[4], y[16];
+        // y = sum_K (beta L)_IK t_K for my two rows, then all 16 entries from the lane groups
+        float y2[2], y[16];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int r = 16 * I + 4 * rq + q;
+        for (int q = 0; q < 2; ++q) {
+            const int r = 16 * I + 2 * rq + q;
             float s = 0.f;
 #pragma unroll
             for (int kn = 0; kn < n; ++kn)
 #pragma unroll
                 for (int m = 0; m < 16; ++m) s = fmaf(sL[r * 65 + 16 * (J + kn) + m], t[kn][m], s);
-            y4[q] = sbeta[r] * s;
+            y2[q] = sbeta[r] * s;
         }
 #pragma unroll
-        for (int g4 = 0; g4 < 4; ++g4)
+        for (int g8 = 0; g8 < 8; ++g8)
 #pragma unroll
-            for (int q = 0; q < 4; ++q) y[4 * g4 + q] = __shfl_sync(0xffffffffu, y4[q], (lane & 7) + 8 * g4);
-        // t_I = -T_II y for my four rows, shared the same way
-        float n4[4];
+            for (int q = 0; q < 2; ++q) y[2 * g8 + q] = __shfl_sync(0xffffffffu, y2[q], (lane & 3) + 4 * g8);
+        // t_I = -T_II y for my two rows, shared the same way
+        float n2[2];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int r = 16 * I + 4 * rq + q;
+        for (int q = 0; q < 2; ++q) {
+            const int r = 16 * I + 2 * rq + q;
             float s = 0.f;
 #pragma unroll
             for (int m = 0; m < 16; ++m) s = fmaf(sT[r * 65 + 16 * I + m], y[m], s);
-            n4[q] = -s;
+            n2[q] = -s;
             sT[r * 65 + gc] = -s;
         }
 #pragma unroll
-        for (int g4 = 0; g4 < 4; ++g4)
+        for (int g8 = 0; g8 < 8; ++g8)
 #pragma unroll
-            for (int q = 0; q < 4; ++q) t[n][4 * g4 + q] = __shfl_sync(0xffffffffu, n4[q], (lane & 7) + 8 * g4);
+            for (int q = 0; q < 2; ++q) t[n][2 * g8 + q] = __shfl_sync(0xffffffffu, n2[q], (lane & 3) + 4 * g8);
     }
 }
 
 // Off-diagonal blocks from tensor memory into sA (Aqk, scaled) and sL: accumulator column
 // 32 (I - 1) + n holds, for key row j (lane), the product with q row n (n < 16) or k row n - 16 of
-// block I.  CBASE is a template argument so that every block / row index is a constant.
+// block I.  One call covers the 32 columns of block I = CBASE / 32 + 1; CBASE is a template argument
+// so that every block / row index is a constant.
 template <int CBASE>
 __device__ __forceinline__ void read_offdiag(uint32_t tmem_d, int qd, int lane, float* sA, float* sL, float scale) {
     const int j = 16 * qd + (lane & 15);
 #pragma unroll
-    for (int cc = 0; cc < 48; cc += 16) {
+    for (int cc = 0; cc < 32; cc += 16) {
         uint32_t r[16];
         tmem_ld16(tmem_d + ((uint32_t)(32 * qd) << 16) + CBASE + cc, r);
         tmem_wait_ld();
@@ -187,38 +190,34 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     static_assert(TAPS + (CONV ? 3 * D * 16 : 0) <= KB, "staging overruns the operand space");
     __nv_bfloat16* sRG = reinterpret_cast<__nv_bfloat16*>(dyn + KB);
     __nv_bfloat16* sRaw = reinterpret_cast<__nv_bfloat16*>(dyn + RAW);
-    const int half = tid >> 7, dch = tid & 127;
-    const int hw = tid >> 4, c8 = (tid & 15) * 8;
+    const int quarter = tid >> 7, dch = tid & 127;  // gate: thread = (16-row group, channel)
+    const int hw = tid >> 4, c8 = (tid & 15) * 8;   // rows: half warp = row, lane = 8 channels
     // gate parameters: requested before anything else so that their latency hides behind the tile copies
     const float a_log_h = gate ? p.A_log[h] : 0.f;
     const float bias = (gate && p.dt_bias) ? p.dt_bias[h * D + dch] : 0.f;
-    float rb[4];
-    float4 tap[2];
+    float rb[2];
+    float4 tap = make_float4(0.f, 0.f, 0.f, 0.f);
     if constexpr (CONV) {  // filter taps of this head, padded to four: entry e = tensor * 128 + channel
         const int K = p.conv_ksize;
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int e = tid + NTHR * u;
+        if (tid < 3 * D) {
             float t4[4] = {0.f, 0.f, 0.f, 0.f};
-            if (e < 3 * D) {
-                const float* w = (e < D ? p.conv_q : e < 2 * D ? p.conv_k : p.conv_v) + (size_t)(h * D + (e & (D - 1))) * K;
+            const float* w = (tid < D ? p.conv_q : tid < 2 * D ? p.conv_k : p.conv_v) + (size_t)(h * D + (tid & (D - 1))) * K;
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (j >= 4 - K) t4[j] = w[j - (4 - K)];
-            }
-            tap[u] = make_float4(t4[0], t4[1], t4[2], t4[3]);
+            for (int j = 0; j < 4; ++j)
+                if (j >= 4 - K) t4[j] = w[j - (4 - K)];
+            tap = make_float4(t4[0], t4[1], t4[2], t4[3]);
         }
     }
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-        const int i = hw + 16 * m;
+    for (int m = 0; m < 2; ++m) {
+        const int i = hw + 32 * m;
         const bool valid = i < ci.len;
         cp_async16_z(sRG + i * D + c8, g + ((size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h) * D + c8, valid);
     }
     cp_async_commit();
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-        const int i = hw + 16 * m;
+    for (int m = 0; m < 2; ++m) {
+        const int i = hw + 32 * m;
         const bool valid = i < ci.len;
         const size_t src = ((size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h) * D + c8;
         const int dst = (HALO + i) * D + c8;
@@ -236,59 +235,57 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     }
     cp_async_commit();
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-        const int i = CONV ? 4 * hw + m : hw + 16 * m;
+    for (int m = 0; m < 2; ++m) {
+        const int i = CONV ? 2 * hw + m : hw + 32 * m;
         rb[m] = ((tid & 15) == 0 && i < ci.len) ? __bfloat162float(beta[(size_t)(ci.tok0 + i) * p.H + h]) : 0.f;
     }
     if constexpr (CONV) {  // taps: entry (tensor, channel) at [tensor][channel % 8][channel / 8], so that the
                            // sixteen lanes of a half warp read consecutive 16-byte words
         float4* sW = reinterpret_cast<float4*>(dyn + TAPS);
-        sW[(tid & ~(D - 1)) + (tid & 7) * 16 + ((tid & (D - 1)) >> 3)] = tap[0];
-        const int e = tid + NTHR;
-        if (e < 3 * D) sW[(e & ~(D - 1)) + (e & 7) * 16 + ((e & (D - 1)) >> 3)] = tap[1];
+        if (tid < 3 * D) sW[(tid & ~(D - 1)) + (tid & 7) * 16 + ((tid & (D - 1)) >> 3)] = tap;
     }
     cp_async_wait<1>();
     __syncthreads();
-    // ---- 0a: gate, channel-wise: thread (half, d) owns rows 32*half .. 32*half+31 of channel d
+    // ---- 0a: gate, channel-wise: thread (quarter, d) owns rows 16*quarter .. 16*quarter+15 of channel d
     {
         const float negA = gate ? -expf(a_log_h) : 0.f;
         float run = 0.f;
 #pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const int i = 32 * half + r;
+        for (int r = 0; r < 16; ++r) {
+            const int i = 16 * quarter + r;
             const float x = __bfloat162float(sRG[i * D + dch]);
             float gl = 0.f;
             if (i < ci.len) gl = gate ? negA * softplus_fast(x + bias) : x;
             run = fmaf(gl, LOG2E, run);  // explicit: both instantiations must round alike
             sG[i * D + dch] = run;
         }
-        if (half == 0) stot[dch] = run;
+        stot[quarter * D + dch] = run;
     }
     cp_async_wait<0>();
     __syncthreads();
     KDA_PHASE(0);
-    // Rows of a half warp: hw + 16 m without the convolution; 4 hw + m with it, so that the seven
-    // input rows 4 hw - 3 .. 4 hw + 3 serve the four outputs of one thread.
-    uint4 rq4[4], rk4[4], rv4[4];
+    // Rows of a half warp: hw and hw + 32 without the convolution; 2 hw and 2 hw + 1 with it, so that
+    // the five input rows 2 hw - 3 .. 2 hw + 1 serve the two outputs of one thread.
+    uint4 rq4[2], rk4[2], rv4[2];
     if constexpr (CONV) {
-        // ---- 0c: y[i] = silu(sum_j tap[j] x[i - 3 + j]) for the thread's four rows, rounded to
+        // ---- 0c: y[i] = silu(sum_j tap[j] x[i - 3 + j]) for the thread's two rows, rounded to
         //      BF16 like the stand-alone convolution; the rest of the stage sees only y
         const float4* sW = reinterpret_cast<const float4*>(dyn + TAPS);
-        auto conv_rows = [&](uint4(&out)[4], int tensor) {
+        auto conv_rows = [&](uint4(&out)[2], int tensor) {
             float4 w[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) w[j] = sW[tensor * D + j * 16 + (c8 >> 3)];
-            float win[7][8];
+            float win[5][8];
 #pragma unroll
-            for (int r = 0; r < 7; ++r)
-                bf16x8_to_f32(*reinterpret_cast<const uint4*>(sRaw + (tensor * ROWS + 4 * hw + r) * D + c8), win[r]);
+            for (int r = 0; r < 5; ++r)
+                bf16x8_to_f32(*reinterpret_cast<const uint4*>(sRaw + (tensor * ROWS + 2 * hw + r) * D + c8), win[r]);
 #pragma unroll
-            for (int m = 0; m < 4; ++m) {
+            for (int m = 0; m < 2; ++m) {
                 float y[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                     y[j] = silu_f(conv_pre(w[j].x, w[j].y, w[j].z, w[j].w, win[m][j], win[m + 1][j], win[m + 2][j], win[m + 3][j]));
-                out[m] = 4 * hw + m < ci.len ? f32_to_bf16x8(y) : make_uint4(0, 0, 0, 0);
+                out[m] = 2 * hw + m < ci.len ? f32_to_bf16x8(y) : make_uint4(0, 0, 0, 0);
             }
         };
         conv_rows(rq4, 0);
@@ -297,22 +294,22 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         if (save) {
             __nv_bfloat16* gVc = (__nv_bfloat16*)(ws + L.Vc) + rec * C * D;
 #pragma unroll
-            for (int m = 0; m < 4; ++m) *reinterpret_cast<uint4*>(gVc + (4 * hw + m) * D + c8) = rv4[m];
+            for (int m = 0; m < 2; ++m) *reinterpret_cast<uint4*>(gVc + (2 * hw + m) * D + c8) = rv4[m];
         }
     } else {
 #pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            const int off = (hw + 16 * m) * D + c8;
+        for (int m = 0; m < 2; ++m) {
+            const int off = (hw + 32 * m) * D + c8;
             rq4[m] = *reinterpret_cast<const uint4*>(sRaw + off);
             rk4[m] = *reinterpret_cast<const uint4*>(sRaw + ROWS * D + off);
             rv4[m] = *reinterpret_cast<const uint4*>(sRaw + 2 * ROWS * D + off);
         }
     }
-    // ---- 0b: q, k, v, beta row-wise: a half warp owns four rows, lane c8 the channels 8 c8 ..
+    // ---- 0b: q, k, v, beta row-wise: a half warp owns two rows, lane c8 the channels 8 c8 ..
     {
 #pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            const int i = CONV ? 4 * hw + m : hw + 16 * m;
+        for (int m = 0; m < 2; ++m) {
+            const int i = CONV ? 2 * hw + m : hw + 32 * m;
             const bool valid = i < ci.len;
             float qf[8], kf[8], vf[8];
             bf16x8_to_f32(rq4[m], qf);
@@ -361,11 +358,12 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem0 = tmem_s;
-    if (tid >= 128) {  // second half of the cumulative sum picks up the first half's total
-        const int d = tid & 127;
-        const float t = stot[d];
-#pragma unroll 8
-        for (int i = 32; i < C; ++i) sG[i * D + d] += t;
+    if (quarter > 0) {  // the later 16-row groups of the cumulative sum pick up the totals of the earlier ones
+        float t = stot[dch];
+        if (quarter > 1) t += stot[D + dch];
+        if (quarter > 2) t += stot[2 * D + dch];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) sG[(16 * quarter + r) * D + dch] += t;
     }
     fence_async_smem();
     __syncthreads();
@@ -376,8 +374,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     //      there are five times fewer of them)
     {
 #pragma unroll 1
-        for (int it = 0; it < 4; ++it) {
-            const int combo = 4 * warp + it;
+        for (int it = 0; it < 2; ++it) {
+            const int combo = 2 * warp + it;
             const int i = 8 * (combo >> 2) + (lane & 7), c8 = 8 * (4 * (combo & 3) + (lane >> 3)), m = i >> 4;
             float G8[8], qf[8], kf[8], o8[8], gl[8];
             {
@@ -452,17 +450,17 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         mma_commit(&bar);
     }
     KDA_PHASE(10);
-    // Thread = (diagonal block b, row pair rp, channel slice cs): it takes rows rp and 15 - rp of the
-    // block (17 (i, j) pairs together, the same for every thread) and the 16 channels 32 u + 4 cs ..+3,
-    // keeps its own row in registers, walks the rows j <= i, and the eight slices of a pair meet
-    // in three shuffles.  Eight lanes read 128 contiguous bytes of a row: no bank conflicts.
+    // Exact diagonal blocks.  Thread = (block b, slot, channel slice cs): the eight lanes of a slot split the
+    // 128 channels (16 each: 32 u + 4 cs .. +3), keep their row i in registers, walk key rows j four at a
+    // time, and the eight slices of a pair meet in three shuffles.  Four warps share a block; the 136
+    // pairs (j <= i) of the block are dealt out so that no warp walks more than twelve key rows:
+    //   warps 0, 1 (slot s = 0..7):  row 8 + s            against keys 0..7   (all valid)
+    //   warps 2, 3 (slot s = 0..7):  row 15 - s           against keys 8..15, then row s against keys 0..7
+    // Eight lanes read 128 contiguous bytes of a row: no bank conflicts.
     {
-        const int cs = lane & 7, rp = (warp & 1) * 4 + (lane >> 3), b = warp >> 1;
-#pragma unroll 1
-        for (int pass = 0; pass < 2; ++pass) {
-            const int i = pass == 0 ? rp : 15 - rp, ri = 16 * b + i;
-            // trip count of the warp: the largest i + 1 among its four row pairs
-            const int nj = pass == 0 ? (warp & 1) * 4 + 4 : 16 - (warp & 1) * 4;
+        const int cs = lane & 7, b = warp >> 2, w4 = warp & 3, slot = 4 * (w4 & 1) + (lane >> 3);
+        auto row_against = [&](int i, int jbeg, int jend) {  // jbeg, jend multiples of four, uniform over the warp
+            const int ri = 16 * b + i;
             float gi[16], qi[16], ki[16];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -478,11 +476,11 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                 qi[4 * u] = qa.x; qi[4 * u + 1] = qa.y; qi[4 * u + 2] = qb.x; qi[4 * u + 3] = qb.y;
                 ki[4 * u] = ka.x; ki[4 * u + 1] = ka.y; ki[4 * u + 2] = kb.x; ki[4 * u + 3] = kb.y;
             }
-            // four rows j at a time (every trip count is a multiple of four): their eight sums (a and l
-            // of each pair) are reduced over the eight slices by a transposing exchange, 7 shuffles
-            // instead of 24, after which lane cs owns sum number cs and stores it
+            // four key rows at a time: their eight sums (a and l of each pair) are reduced over the eight
+            // slices by a transposing exchange, 7 shuffles instead of 24, after which lane cs owns sum
+            // number cs and stores it
 #pragma unroll 1
-            for (int j0 = 0; j0 < nj; j0 += 4) {
+            for (int j0 = jbeg; j0 < jend; j0 += 4) {
                 float v[8];
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {
@@ -505,27 +503,37 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                     v[2 * jj + 1] = lv.x + lv.y;
                 }
                 const bool b2 = cs & 4, b1 = cs & 2, b0 = cs & 1;
-                float w4[4], w2[2];
+                float w4s[4], w2s[2];
 #pragma unroll
-                for (int t = 0; t < 4; ++t) w4[t] = (b2 ? v[t + 4] : v[t]) + __shfl_xor_sync(0xffffffffu, b2 ? v[t] : v[t + 4], 4);
+                for (int t = 0; t < 4; ++t) w4s[t] = (b2 ? v[t + 4] : v[t]) + __shfl_xor_sync(0xffffffffu, b2 ? v[t] : v[t + 4], 4);
 #pragma unroll
-                for (int t = 0; t < 2; ++t) w2[t] = (b1 ? w4[t + 2] : w4[t]) + __shfl_xor_sync(0xffffffffu, b1 ? w4[t] : w4[t + 2], 2);
-                const float sum = (b0 ? w2[1] : w2[0]) + __shfl_xor_sync(0xffffffffu, b0 ? w2[0] : w2[1], 1);
+                for (int t = 0; t < 2; ++t) w2s[t] = (b1 ? w4s[t + 2] : w4s[t]) + __shfl_xor_sync(0xffffffffu, b1 ? w4s[t] : w4s[t + 2], 2);
+                const float sum = (b0 ? w2s[1] : w2s[0]) + __shfl_xor_sync(0xffffffffu, b0 ? w2s[0] : w2s[1], 1);
                 const int j = j0 + (cs >> 1);
                 if (j <= i) {
                     if (!b0) sA[ri * 65 + 16 * b + j] = sum * p.scale;
                     else if (j < i) sL[ri * 65 + 16 * b + j] = sum;
                 }
             }
+        };
+        if (w4 < 2) {
+            row_against(8 + slot, 0, 8);
+        } else {
+            // rows 15 - slot: warp 2 holds rows 15..12 (keys up to 15), warp 3 rows 11..8 (keys up to 11)
+            row_against(15 - slot, 8, w4 == 2 ? 16 : 12);
+            // rows slot: warp 2 holds rows 0..3 (keys 0..3), warp 3 rows 4..7 (keys 0..7)
+            row_against(slot, 0, w4 == 2 ? 4 : 8);
         }
     }
     KDA_PHASE(4);
     bool ok = mbar_wait(&bar, 0, p.status, 8);
     tc_fence_after();
     KDA_PHASE(11);
-    if (ok) {  // warps 0-3 take accumulator columns 0..47, warps 4-7 columns 48..95
-        if (warp < 4) read_offdiag<0>(tmem0 + T_D, warp & 3, lane, sA, sL, p.scale);
-        else read_offdiag<48>(tmem0 + T_D, warp & 3, lane, sA, sL, p.scale);
+    if (ok) {  // warp (quadrant, group): accumulator columns 32 group .. 32 group + 31 = block I = group + 1
+        const int grp = warp >> 2;
+        if (grp == 0) read_offdiag<0>(tmem0 + T_D, warp & 3, lane, sA, sL, p.scale);
+        else if (grp == 1) read_offdiag<32>(tmem0 + T_D, warp & 3, lane, sA, sL, p.scale);
+        else if (grp == 2) read_offdiag<64>(tmem0 + T_D, warp & 3, lane, sA, sL, p.scale);
     }
     KDA_PHASE(12);
     tc_fence_before();
@@ -543,29 +551,26 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 
     // ---- 3: T = (I + diag(beta) L)^-1, column by column.  Column c of T depends only on
     //      column c of the blocks above it, so one lane carries a whole column in registers:
-    //      warp w owns block column J = w % 4, columns 8 (w / 4) + lane % 8, and its four lane
-    //      groups (lane / 8) split the 16 rows of every block below the diagonal.
-    solve_block_column(sL, sT, sbeta, warp & 3, warp, lane);
+    //      warp w owns block column J = w % 4, columns 4 (w / 4) + lane % 4, and its eight lane
+    //      groups (lane / 4) split the 16 rows of every block below the diagonal.
+    solve_block_column(sL, sT, sbeta, warp & 3, warp >> 2, lane);
     __syncthreads();
 
     KDA_PHASE(6);
     // ---- 4: Aqk and T records; T as the B operand of the WY products
     {
         __nv_bfloat16* sTB = reinterpret_cast<__nv_bfloat16*>(dyn + KSC);
+        const int i = tid >> 3, j8 = (tid & 7) * 8;
+        float a8[8], t8[8];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int qq = tid + NTHR * u, i = qq >> 3, j8 = (qq & 7) * 8;
-            float a8[8], t8[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                a8[j] = sA[i * 65 + j8 + j];
-                t8[j] = sT[i * 65 + j8 + j];
-            }
-            const uint4 tb = f32_to_bf16x8(t8);
-            *reinterpret_cast<uint4*>(gA + cm_idx(i, j8, C)) = f32_to_bf16x8(a8);
-            if (save) *reinterpret_cast<uint4*>(gT + cm_idx(i, j8, C)) = tb;
-            *reinterpret_cast<uint4*>(sTB + cm_idx(i, j8, C)) = tb;
+        for (int j = 0; j < 8; ++j) {
+            a8[j] = sA[i * 65 + j8 + j];
+            t8[j] = sT[i * 65 + j8 + j];
         }
+        const uint4 tb = f32_to_bf16x8(t8);
+        *reinterpret_cast<uint4*>(gA + cm_idx(i, j8, C)) = f32_to_bf16x8(a8);
+        if (save) *reinterpret_cast<uint4*>(gT + cm_idx(i, j8, C)) = tb;
+        *reinterpret_cast<uint4*>(sTB + cm_idx(i, j8, C)) = tb;
     }
     fence_async_smem();
     tc_fence_before();
@@ -590,13 +595,14 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     tc_fence_after();
 
     KDA_PHASE(8);
-    // ---- 6: W and U records
+    // ---- 6: W and U records: warp (quadrant, group) takes token columns 32 (group % 2) .. +31 of W (groups
+    //      0, 1) or U (groups 2, 3)
     if (ok) {
-        const int qd = warp & 3, dd = 32 * qd + lane;
-        __nv_bfloat16* dst = warp < 4 ? gW : gU;
-        const uint32_t src = tmem0 + ((uint32_t)(32 * qd) << 16) + (warp < 4 ? T_W : T_U);
+        const int qd = warp & 3, dd = 32 * qd + lane, grp = warp >> 2;
+        __nv_bfloat16* dst = grp < 2 ? gW : gU;
+        const uint32_t src = tmem0 + ((uint32_t)(32 * qd) << 16) + (grp < 2 ? T_W : T_U);
 #pragma unroll
-        for (int i0 = 0; i0 < C; i0 += 16) {
+        for (int i0 = 32 * (grp & 1); i0 < 32 * (grp & 1) + 32; i0 += 16) {
             uint32_t r[16];
             tmem_ld16(src + i0, r);
             tmem_wait_ld();

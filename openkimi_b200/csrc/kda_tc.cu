@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(128, 1) wait_selftest_kernel(const float* __re
 // The per-chunk records arrive by linear bulk TMA copies into a two-stage ring.
 // ---------------------------------------------------------------------------------------
 namespace fs {
-constexpr int D = 128;
+constexpr int D = 128, NTHR = 256;
 constexpr uint32_t WT = 0, QT = 16384, KH = 32768, UT = 49152, AQ = 65536, GAM = 73728, STAGE = 74240;
 constexpr uint32_t OUT = 2 * STAGE, TOTAL = OUT + 16384;  // output tile bf16 [64][128] behind the two stages
 constexpr uint32_t SACC = 0, SBF = 128, WSACC = 192, OACC = 256, VBF = 320, TMEM_COLS = 512;
@@ -164,13 +164,15 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
     }
 }
 
-__global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
+__global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams p) {
     using namespace fs;
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ uint64_t full[2];
     __shared__ uint64_t mmabar;
     __shared__ uint32_t tmem_s;
-    const int tid = threadIdx.x, warp = tid >> 5;
+    // thread (half, e) = (tid / 128, tid % 128): TMEM lane e (value column e), and half of the accumulator
+    // columns in every conversion phase (two warps share a lane quadrant)
+    const int tid = threadIdx.x, warp = tid >> 5, e = tid & 127, half = tid >> 7;
     const int h = blockIdx.x, n = blockIdx.y;
     int c0, nc;
     seq_chunks(p, n, c0, nc);
@@ -189,15 +191,15 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = tmem_s + ((uint32_t)(warp * 32) << 16);  // this warp's lane quadrant
+    const uint32_t tmem = tmem_s + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's lane quadrant
     const uint32_t tmem0 = tmem_s;
     const size_t sbase = ((size_t)n * p.H + h) * D * D;
     const bool save = !(p.flags & KDA_FLAG_NO_SAVE);  // forward-only calls write no checkpoint and no V' record
 
-    for (int d0 = 0; d0 < D; d0 += 16) {
+    for (int d0 = 64 * half; d0 < 64 * half + 64; d0 += 16) {
         uint32_t r[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(p.h0 ? p.h0[sbase + state_idx(p, d0 + j, tid)] : 0.f);
+        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(p.h0 ? p.h0[sbase + state_idx(p, d0 + j, e)] : 0.f);
         tmem_st16(tmem + SACC + d0, r);
     }
     tmem_wait_st();
@@ -233,7 +235,7 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
         {
             const float* gam = reinterpret_cast<const float*>(b + GAM);
             __nv_bfloat16* gS0 = (__nv_bfloat16*)(ws + L.S0) + rec * D * D;
-            for (int d0 = 0; d0 < D; d0 += 16) {
+            for (int d0 = 64 * half; d0 < 64 * half + 64; d0 += 16) {
                 uint32_t r[16], pk[8];
                 tmem_ld16(tmem + SACC + d0, r);
                 tmem_wait_ld();
@@ -241,8 +243,8 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
                 for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
                 tmem_st8(tmem + SBF + d0 / 2, pk);
                 if (save) {
-                    *reinterpret_cast<uint4*>(gS0 + cm_idx(tid, d0, D)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                    *reinterpret_cast<uint4*>(gS0 + cm_idx(tid, d0 + 8, D)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                    *reinterpret_cast<uint4*>(gS0 + cm_idx(e, d0, D)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *reinterpret_cast<uint4*>(gS0 + cm_idx(e, d0 + 8, D)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                 }
 #pragma unroll
                 for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gam[d0 + j]);
@@ -279,17 +281,17 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
         {
             const __nv_bfloat16* sU = reinterpret_cast<const __nv_bfloat16*>(b + UT);
             __nv_bfloat16* gV = (__nv_bfloat16*)(ws + L.U) + rec * C * D;
-            for (int i0 = 0; i0 < C; i0 += 16) {
+            for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
                 uint32_t r[16], pk[8];
                 float u[16];
                 tmem_ld16(tmem + WSACC + i0, r);
                 tmem_wait_ld();
                 {
                     float t8[8];
-                    unpack8(*reinterpret_cast<const uint4*>(sU + cm_idx(tid, i0, C)), t8);
+                    unpack8(*reinterpret_cast<const uint4*>(sU + cm_idx(e, i0, C)), t8);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) u[j] = t8[j];
-                    unpack8(*reinterpret_cast<const uint4*>(sU + cm_idx(tid, i0 + 8, C)), t8);
+                    unpack8(*reinterpret_cast<const uint4*>(sU + cm_idx(e, i0 + 8, C)), t8);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) u[8 + j] = t8[j];
                 }
@@ -298,8 +300,8 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
                     pk[j] = pack_bf16(u[2 * j] - __uint_as_float(r[2 * j]), u[2 * j + 1] - __uint_as_float(r[2 * j + 1]));
                 tmem_st8(tmem + VBF + i0 / 2, pk);
                 if (save) {
-                    *reinterpret_cast<uint4*>(gV + cm_idx(tid, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                    *reinterpret_cast<uint4*>(gV + cm_idx(tid, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                    *reinterpret_cast<uint4*>(gV + cm_idx(e, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *reinterpret_cast<uint4*>(gV + cm_idx(e, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                 }
             }
             tmem_wait_st();
@@ -331,12 +333,12 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
         {
             __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(dyn + OUT);
 #pragma unroll
-            for (int i0 = 0; i0 < C; i0 += 16) {
+            for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(tmem + OACC + i0, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) sO[(i0 + j) * D + tid] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                for (int j = 0; j < 16; ++j) sO[(i0 + j) * D + e] = __float2bfloat16_rn(__uint_as_float(r[j]));
             }
             fence_async_smem();
             __syncthreads();
@@ -348,12 +350,12 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
         KDA_PHASE(5);
     }
     if (ok && p.ht) {
-        for (int d0 = 0; d0 < D; d0 += 16) {
+        for (int d0 = 64 * half; d0 < 64 * half + 64; d0 += 16) {
             uint32_t r[16];
             tmem_ld16(tmem + SACC + d0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) p.ht[sbase + state_idx(p, d0 + j, tid)] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) p.ht[sbase + state_idx(p, d0 + j, e)] = __uint_as_float(r[j]);
         }
     }
     tma_store_wait_all();
@@ -370,19 +372,20 @@ __global__ void __launch_bounds__(128, 1) kda_fwd_state_tc(const KdaParams p) {
 //   2  dSacc -= dVbf * W
 // ---------------------------------------------------------------------------------------
 namespace bs {
-constexpr int D = 128;
+constexpr int D = 128, NTHR = 256;
 constexpr uint32_t WT = 0, QT = 16384, KH = 32768, DO = 49152, AQ = 65536, GAM = 73728, STAGE = 74240;
 constexpr uint32_t TMA_BYTES = 16384 * 3 + 8192 + 512;
 constexpr uint32_t SACC = 0, SBF = 128, VACC = 192, VBF = 256, TMEM_COLS = 512;
 }  // namespace bs
 
-__global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
+__global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams p) {
     using namespace bs;
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ uint64_t full[2];
     __shared__ uint64_t mmabar;
     __shared__ uint32_t tmem_s;
-    const int tid = threadIdx.x, warp = tid >> 5;
+    // thread (half, e) = (tid / 128, tid % 128): TMEM lane e, and half of the columns of every conversion phase
+    const int tid = threadIdx.x, warp = tid >> 5, e = tid & 127, half = tid >> 7;
     const int h = blockIdx.x, n = blockIdx.y;
     int c0, nc;
     seq_chunks(p, n, c0, nc);
@@ -403,14 +406,14 @@ __global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = tmem_s + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tmem = tmem_s + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t tmem0 = tmem_s;
     const size_t sbase = ((size_t)n * p.H + h) * D * D;
 
-    for (int d0 = 0; d0 < D; d0 += 16) {
+    for (int d0 = 64 * half; d0 < 64 * half + 64; d0 += 16) {
         uint32_t r[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(p.grad_ht ? p.grad_ht[sbase + state_idx(p, d0 + j, tid)] : 0.f);
+        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(p.grad_ht ? p.grad_ht[sbase + state_idx(p, d0 + j, e)] : 0.f);
         tmem_st16(tmem + SACC + d0, r);
     }
     tmem_wait_st();
@@ -431,7 +434,7 @@ __global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
         // dO tile -> core-matrix layout cm(i, e; 128), 16-byte chunks, zero rows past the end
         const ChunkInfo ci = chunk_info(p, c0 + lc);
         __nv_bfloat16* sdo = reinterpret_cast<__nv_bfloat16*>(b + DO);
-        for (int q = tid; q < C * (D / 8); q += 128) {
+        for (int q = tid; q < C * (D / 8); q += NTHR) {
             const int i = q >> 4, e8 = (q & 15) * 8;
             const bool valid = i < ci.len;
             const size_t row = (size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h;
@@ -460,15 +463,15 @@ __global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
         {
             const float* gam = reinterpret_cast<const float*>(b + GAM);
             __nv_bfloat16* gdS = (__nv_bfloat16*)(sc + L.dS) + rec * D * D;
-            for (int d0 = 0; d0 < D; d0 += 16) {
+            for (int d0 = 64 * half; d0 < 64 * half + 64; d0 += 16) {
                 uint32_t r[16], pk[8];
                 tmem_ld16(tmem + SACC + d0, r);
                 tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
                 tmem_st8(tmem + SBF + d0 / 2, pk);
-                *reinterpret_cast<uint4*>(gdS + cm_idx(tid, d0, D)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                *reinterpret_cast<uint4*>(gdS + cm_idx(tid, d0 + 8, D)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                *reinterpret_cast<uint4*>(gdS + cm_idx(e, d0, D)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(gdS + cm_idx(e, d0 + 8, D)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gam[d0 + j]);
                 tmem_st16(tmem + SACC + d0, r);
@@ -503,15 +506,15 @@ __global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
 
         {
             __nv_bfloat16* gdV = (__nv_bfloat16*)(sc + L.dVn) + rec * C * D;
-            for (int i0 = 0; i0 < C; i0 += 16) {
+            for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
                 uint32_t r[16], pk[8];
                 tmem_ld16(tmem + VACC + i0, r);
                 tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
                 tmem_st8(tmem + VBF + i0 / 2, pk);
-                *reinterpret_cast<uint4*>(gdV + cm_idx(tid, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                *reinterpret_cast<uint4*>(gdV + cm_idx(tid, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                *reinterpret_cast<uint4*>(gdV + cm_idx(e, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(gdV + cm_idx(e, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
             }
             tmem_wait_st();
         }
@@ -532,12 +535,12 @@ __global__ void __launch_bounds__(128, 1) kda_bwd_state_tc(const KdaParams p) {
         if (!__syncthreads_and(ok)) { ok = false; break; }
     }
     if (ok && p.grad_h0) {
-        for (int d0 = 0; d0 < D; d0 += 16) {
+        for (int d0 = 64 * half; d0 < 64 * half + 64; d0 += 16) {
             uint32_t r[16];
             tmem_ld16(tmem + SACC + d0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) p.grad_h0[sbase + state_idx(p, d0 + j, tid)] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) p.grad_h0[sbase + state_idx(p, d0 + j, e)] = __uint_as_float(r[j]);
         }
     }
     cp_async_wait<0>();
@@ -568,7 +571,7 @@ cudaError_t tc_fwd(const KdaParams& p, cudaStream_t s) {
         constexpr int smem = fs::TOTAL;
         if ((e = cudaFuncSetAttribute(kda_fwd_state_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return e;
-        kda_fwd_state_tc<<<dim3(p.H, p.N), 128, smem, s>>>(p);
+        kda_fwd_state_tc<<<dim3(p.H, p.N), fs::NTHR, smem, s>>>(p);
     }
     prof_mark(s);
     return cudaGetLastError();
@@ -582,7 +585,7 @@ cudaError_t tc_bwd(const KdaParams& p, cudaStream_t s) {
         constexpr int smem = 2 * bs::STAGE;
         if ((e = cudaFuncSetAttribute(kda_bwd_state_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return e;
-        kda_bwd_state_tc<<<dim3(p.H, p.N), 128, smem, s>>>(p);
+        kda_bwd_state_tc<<<dim3(p.H, p.N), bs::NTHR, smem, s>>>(p);
     }
     prof_mark(s);
     if (stage_simt(p, ST_BWD_CHUNK)) {  // fused FP32-math kernel

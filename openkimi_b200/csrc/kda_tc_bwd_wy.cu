@@ -22,7 +22,7 @@ namespace kda {
 using namespace tc;
 
 namespace bw {
-constexpr int D = 128, NTHR = 256;
+constexpr int D = 128, NTHR = 512;
 constexpr uint32_t VT = 0;                  // V'^T  cm(e, i; 64)
 constexpr uint32_t DVT = VT + 16384;        // dV'^T cm(e, i; 64);   later Z^T  cm(d, i; 64)
 constexpr uint32_t S0T = DVT + 16384;       // S0^T  cm(e, d; 128)
@@ -33,8 +33,8 @@ constexpr uint32_t TMA_BYTES = WT + 16384;  // everything above arrives by bulk 
 constexpr uint32_t DOT = TMA_BYTES;         // dO    cm(i, e; 128);  later dVb^T cm(e, i; 64)
 constexpr uint32_t STG = DOT + 16384;       // f32 [64][128] staging for the beta row sums
 constexpr uint32_t SV = STG + 32768;        // v bf16 [64][128] row-major (prefetched with cp.async)
-constexpr uint32_t SBETA = SV + 16384;      // f32 [64] beta, f32 [64] row sums, f32 [2][128] partial dGamma_C
-constexpr uint32_t SKH = SBETA + 512 + 1024;   // bf16 [64][128] staging of dKh (dQt and dKb are staged in the two halves of DST once dS is dead)
+constexpr uint32_t SBETA = SV + 16384;      // f32 [64] beta, f32 [64] row sums, f32 [4][128] partial dGamma_C
+constexpr uint32_t SKH = SBETA + 512 + 2048;   // bf16 [64][128] staging of dKh (dQt and dKb are staged in the two halves of DST once dS is dead)
 constexpr uint32_t TOTAL = SKH + 16384;
 constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bw
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     tc_fence_after();
     const uint32_t tmem0 = tmem_s;
     const uint32_t tmem = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's lane quadrant
-    const int ch = tid & 127, half = tid >> 7;                            // channel (TMEM lane) and column half
+    const int ch = tid & 127, qtr = tid >> 7;                             // channel (TMEM lane) and column quarter (16 columns)
     float* spart = srow + 64;
 
     if (tid == 0) {
@@ -164,8 +164,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll 2
-        for (int eo = 0; eo < 8; ++eo) {
-            const int e = 8 * (8 * eh + eo) + e7;
+        for (int eo = 0; eo < 4; ++eo) {
+            const int e = 8 * (4 * eh + eo) + e7;
             float a[8], b[8];
             bf16x8_to_f32(*reinterpret_cast<const uint4*>(ds + cm_idx(e, d8, D)), a);
             bf16x8_to_f32(*reinterpret_cast<const uint4*>(s0 + cm_idx(e, d8, D)), b);
@@ -196,8 +196,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         __nv_bfloat16* sdkh = reinterpret_cast<__nv_bfloat16*>(dyn + SKH);
         __nv_bfloat16* sdvb = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
         __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(dyn + SV);
-#pragma unroll 1
-        for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
+        {
+            const int i0 = 16 * qtr;
             uint32_t r[16], pk[8];
             tmem_ld16(tmem + DWN + i0, r);
             tmem_wait_ld();
@@ -233,8 +233,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             __nv_bfloat16* gAM = (__nv_bfloat16*)(sc + L.dAM) + rec * 6 * C * C;
             float* gAd = (float*)(sc + L.dAd) + rec * C;
             const int i = 16 * (warp & 3) + (lane & 15);
-#pragma unroll 1
-            for (int j0 = 32 * half; j0 < 32 * half + 32; j0 += 16) {
+            {
+                const int j0 = 16 * qtr;
                 uint32_t r[16];
                 tmem_ld16(tmem + DAQK + j0, r);
                 tmem_wait_ld();
@@ -283,8 +283,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     // meanwhile: beta row sums and dGamma_C * Gamma_C on the CUDA cores
     {
         const int hw = tid >> 4, c8 = (tid & 15) * 8;
-        for (int m = 0; m < 4; ++m) {
-            const int i = hw + 16 * m;
+        for (int m = 0; m < 2; ++m) {
+            const int i = hw + 32 * m;
             float s = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) s += stg[i * D + c8 + j];
@@ -298,14 +298,14 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     ok = __syncthreads_and(ok);
     KDA_PHASE(5);
     if (ok && tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
-    if (ok && tid < D) ((float*)(sc + L.gC))[rec * D + tid] = (spart[tid] + spart[128 + tid]) * gam_c;
+    if (ok && tid < D) ((float*)(sc + L.gC))[rec * D + tid] = ((spart[tid] + spart[128 + tid]) + (spart[256 + tid] + spart[384 + tid])) * gam_c;
 
     // ---- conversions after S2
     if (ok) {
         __nv_bfloat16* sdkb = reinterpret_cast<__nv_bfloat16*>(dyn + DST + 16384);  // second half: dQt may still be leaving the first
         __nv_bfloat16* sz = reinterpret_cast<__nv_bfloat16*>(dyn + DVT);
-#pragma unroll 1
-        for (int i0 = 32 * half; i0 < 32 * half + 32; i0 += 16) {
+        {
+            const int i0 = 16 * qtr;
             uint32_t r[16];
             tmem_ld16(tmem + DKB + i0, r);
             tmem_wait_ld();
@@ -348,8 +348,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
     if (ok) {
         __nv_bfloat16* gMM = (__nv_bfloat16*)(sc + L.dAM) + rec * 6 * C * C + 3 * C * C;
         const int i = 16 * (warp & 3) + (lane & 15);
-#pragma unroll 1
-        for (int j0 = 32 * half; j0 < 32 * half + 32; j0 += 16) {
+        {
+            const int j0 = 16 * qtr;
             uint32_t r[16];
             tmem_ld16(tmem + DMN + j0, r);
             tmem_wait_ld();

@@ -42,12 +42,18 @@ constexpr uint32_t T_D = 0, T_W = 96, T_U = 160, TMEM_COLS = 256;
 
 // One block column J of T = (I + diag(beta) L)^-1 (see stage 3 of the kernel).  sL holds L
 // (strictly lower, row stride 65), sT receives T; sT must be zero above the diagonal blocks.
-// Four warps share a block column: warp (J, cw) owns columns 4 cw + lane % 4, and its eight lane
-// groups (lane / 4) split the 16 rows of every block below the diagonal, two rows each.
+// Eight warps work (the column solve is a dependent chain: more lanes only add redundancy):
+// warp (J, cw) owns columns 8 cw + lane % 8 of block column J, and its four lane groups (lane / 8)
+// split the 16 rows of every block below the diagonal, four rows each.
 // J is uniform over the warp; the loops run over all blocks with warp-uniform skips so that the
 // register arrays keep compile-time indices in a single copy of the code.
-__device__ __forceinline__ void solve_block_column(const float* sL, float* sT, const float* sbeta, int J, int cw, int lane) {
-    const int col = 4 * cw + (lane & 3), rq = lane >> 2, gc = 16 * J + col;
+__device__ __forceinline__ void solve_block_column(const float* sL, float* sT, const float* sbeta, int J, int cw, int lane,
+                                                   bool active) {
+    if (!active) {
+        __syncthreads();  // (matches the barrier below)
+        return;
+    }
+    const int col = 8 * cw + (lane & 7), rq = lane >> 3, gc = 16 * J + col;
     float t[4][16];
     // diagonal block: forward substitution down the column (every lane group does all 16 rows)
 #pragma unroll
@@ -71,37 +77,37 @@ __device__ __forceinline__ void solve_block_column(const float* sL, float* sT, c
     for (int n = 1; n < 4; ++n) {
         const int I = J + n;
         if (I > 3) break;
-        // y = sum_K (beta L)_IK t_K for my two rows, then all 16 entries from the lane groups
-        float y2[2], y[16];
+        // y = sum_K (beta L)_IK t_K for my four rows, then all 16 entries from the lane groups
+        float y4[4], y[16];
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int r = 16 * I + 2 * rq + q;
+        for (int q = 0; q < 4; ++q) {
+            const int r = 16 * I + 4 * rq + q;
             float s = 0.f;
 #pragma unroll
             for (int kn = 0; kn < n; ++kn)
 #pragma unroll
                 for (int m = 0; m < 16; ++m) s = fmaf(sL[r * 65 + 16 * (J + kn) + m], t[kn][m], s);
-            y2[q] = sbeta[r] * s;
+            y4[q] = sbeta[r] * s;
         }
 #pragma unroll
-        for (int g8 = 0; g8 < 8; ++g8)
+        for (int g4 = 0; g4 < 4; ++g4)
 #pragma unroll
-            for (int q = 0; q < 2; ++q) y[2 * g8 + q] = __shfl_sync(0xffffffffu, y2[q], (lane & 3) + 4 * g8);
-        // t_I = -T_II y for my two rows, shared the same way
-        float n2[2];
+            for (int q = 0; q < 4; ++q) y[4 * g4 + q] = __shfl_sync(0xffffffffu, y4[q], (lane & 7) + 8 * g4);
+        // t_I = -T_II y for my four rows, shared the same way
+        float n4[4];
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int r = 16 * I + 2 * rq + q;
+        for (int q = 0; q < 4; ++q) {
+            const int r = 16 * I + 4 * rq + q;
             float s = 0.f;
 #pragma unroll
             for (int m = 0; m < 16; ++m) s = fmaf(sT[r * 65 + 16 * I + m], y[m], s);
-            n2[q] = -s;
+            n4[q] = -s;
             sT[r * 65 + gc] = -s;
         }
 #pragma unroll
-        for (int g8 = 0; g8 < 8; ++g8)
+        for (int g4 = 0; g4 < 4; ++g4)
 #pragma unroll
-            for (int q = 0; q < 2; ++q) t[n][2 * g8 + q] = __shfl_sync(0xffffffffu, n2[q], (lane & 3) + 4 * g8);
+            for (int q = 0; q < 4; ++q) t[n][4 * g4 + q] = __shfl_sync(0xffffffffu, n4[q], (lane & 7) + 8 * g4);
     }
 }
 
@@ -551,9 +557,9 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 
     // ---- 3: T = (I + diag(beta) L)^-1, column by column.  Column c of T depends only on
     //      column c of the blocks above it, so one lane carries a whole column in registers:
-    //      warp w owns block column J = w % 4, columns 4 (w / 4) + lane % 4, and its eight lane
-    //      groups (lane / 4) split the 16 rows of every block below the diagonal.
-    solve_block_column(sL, sT, sbeta, warp & 3, warp >> 2, lane);
+    //      warp w < 8 owns block column J = w % 4, columns 8 (w / 4) + lane % 8, and its four lane
+    //      groups (lane / 8) split the 16 rows of every block below the diagonal.
+    solve_block_column(sL, sT, sbeta, warp & 3, (warp >> 2) & 1, lane, warp < 8);
     __syncthreads();
 
     KDA_PHASE(6);

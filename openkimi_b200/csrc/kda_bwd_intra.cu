@@ -43,9 +43,9 @@ using namespace tc;
 
 namespace bi {
 constexpr int D = 128, NTHR = 512, B = 16;
-constexpr uint32_t SG = 0;                   // G f32 [64][128]
-constexpr uint32_t SQ = SG + 32768;          // q^ bf16 [64][128]
-constexpr uint32_t SK = SQ + 16384;          // k^ bf16 [64][128]
+constexpr uint32_t SG = 0;                   // G f32 [64][128], chunk-swizzled rows (swz_f32) as the forward keeps it
+constexpr uint32_t SQ = SG + 32768;          // q^ bf16 [64][128], chunk-swizzled rows (swz_bf16)
+constexpr uint32_t SK = SQ + 16384;          // k^ bf16 [64][128], chunk-swizzled rows
 constexpr uint32_t SB = SK + 16384;          // dAqk p0 p1 p2, dM p0 p1 p2: six cm(i, j; 64) bf16 tiles
 constexpr uint32_t XB = SB + 49152;          // operand buffer X: three parts of cm(d, t; 64) bf16 [128][64]
 constexpr uint32_t YB = XB + 49152;          // operand buffer Y
@@ -161,14 +161,14 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     // ---- my block: G of my channel, guard and references; round 1: KN_j = k_j 2^(ref - G_j) -> X
     float G[B], mid;
 #pragma unroll
-    for (int r = 0; r < B; ++r) G[r] = sG[(b0 + r) * D + d];
-    const float gl = sG[(C - 1) * D + d];                          // G of the chunk's last row
-    const float gprev = blk > 0 ? sG[(b0 - 1) * D + d] : 0.f;      // G of the row before my block
+    for (int r = 0; r < B; ++r) G[r] = sG[swz_f32(b0 + r, d)];
+    const float gl = sG[swz_f32(C - 1, d)];                          // G of the chunk's last row
+    const float gprev = blk > 0 ? sG[swz_f32(b0 - 1, d)] : 0.f;      // G of the row before my block
     const bool pass = guard_tile(G, fminf(p.guard_span, TC_SPAN), mid);
     {
         // references of my rows as keys / as queries: the midpoint, or first rows when there is none
         // (block 3 has no later rows: zero keys)
-        const float kref = pass ? mid : (blk < 3 ? sG[(b0 + B) * D + d] : -INFINITY), qref = pass ? mid : G[0];
+        const float kref = pass ? mid : (blk < 3 ? sG[swz_f32(b0 + B, d)] : -INFINITY), qref = pass ? mid : G[0];
         smid[blk * D + d] = kref;
         smid[(4 + blk) * D + d] = qref;
         if (lane == 0) srej[blk * 4 + cg] = pass ? 0 : 1;
@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             float v[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                v[j] = __bfloat162float(sK[(b0 + 8 * g8 + j) * D + d]) * ex2_approx(kref - G[8 * g8 + j] + SHIFT);
+                v[j] = __bfloat162float(sK[swz_bf16(b0 + 8 * g8 + j, d)]) * ex2_approx(kref - G[8 * g8 + j] + SHIFT);
             store_parts(dyn + XB, d, b0 + 8 * g8, v);
         }
     }
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             float v[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                v[j] = scale * __bfloat162float(sQ[(b0 + 8 * g8 + j) * D + d]) * ex2_approx(G[8 * g8 + j] - qref + SHIFT);
+                v[j] = scale * __bfloat162float(sQ[swz_bf16(b0 + 8 * g8 + j, d)]) * ex2_approx(G[8 * g8 + j] - qref + SHIFT);
             store_parts(dyn + YB, d, b0 + 8 * g8, v);
         }
     }
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int t = b0 + 8 * g8 + j;
-                v[j] = sbeta[t] * __bfloat162float(sK[t * D + d]) * ex2_approx(G[8 * g8 + j] - qref + SHIFT);
+                v[j] = sbeta[t] * __bfloat162float(sK[swz_bf16(t, d)]) * ex2_approx(G[8 * g8 + j] - qref + SHIFT);
             }
             store_parts(dyn + XB, d, b0 + 8 * g8, v);
         }
@@ -351,15 +351,14 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             float qs[B], kb[B];
 #pragma unroll
             for (int r = 0; r < B; ++r) {
-                qs[r] = scale * __bfloat162float(sQ[(b0 + r) * D + d]);
-                kb[r] = sbeta[b0 + r] * __bfloat162float(sK[(b0 + r) * D + d]);
+                qs[r] = scale * __bfloat162float(sQ[swz_bf16(b0 + r, d)]);
+                kb[r] = sbeta[b0 + r] * __bfloat162float(sK[swz_bf16(b0 + r, d)]);
             }
-            float* cst = sG + b0 * D + d;
             auto segment = [&](auto r0c, int j0, int j1) {
                 constexpr int R0 = decltype(r0c)::value;
 #pragma unroll 1
                 for (int j = j0; j < j1; ++j) {
-                    const float kj = __bfloat162float(sK[(b0 + j) * D + d]), gj = cst[j * D];
+                    const float kj = __bfloat162float(sK[swz_bf16(b0 + j, d)]), gj = sG[swz_f32(b0 + j, d)];
                     float cj = 0.f;
 #pragma unroll
                     for (int r = R0; r < B; ++r) {
@@ -369,7 +368,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                         a2[r] = fmaf(m, kp, a2[r]);
                         cj = fmaf(fmaf(a, qs[r], m * kb[r]), e, cj);
                     }
-                    cst[j * D] = cj;
+                    sG[swz_f32(b0 + j, d)] = cj;
                 }
             };
             segment(std::integral_constant<int, 1>{}, 0, 4);
@@ -377,7 +376,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             segment(std::integral_constant<int, 9>{}, 8, 12);
             segment(std::integral_constant<int, 13>{}, 12, 15);
 #pragma unroll
-            for (int j = 0; j < B - 1; ++j) c1[j] += cst[j * D];
+            for (int j = 0; j < B - 1; ++j) c1[j] += sG[swz_f32(b0 + j, d)];
         }
         KDA_PHASE(8);
         // ---- assembly of my block, last row first; a1[r] is reused for the running sum of dG
@@ -386,7 +385,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 #pragma unroll
             for (int r = B - 1; r >= 0; --r) {
                 const int ii = b0 + r;
-                const float qi = __bfloat162float(sQ[ii * D + d]), ki = __bfloat162float(sK[ii * D + d]);
+                const float qi = __bfloat162float(sQ[swz_bf16(ii, d)]), ki = __bfloat162float(sK[swz_bf16(ii, d)]);
                 const float bi_ = sbeta[ii];
                 const float gam = ex2_approx(G[r]), eta = ex2_approx(gl - G[r]);
                 const float dQt = __bfloat162float(spf[ii * D + d]), dKh = __bfloat162float(spf[(C + ii) * D + d]),
@@ -452,8 +451,8 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                     const float4 a = *reinterpret_cast<const float4*>(stg + (0 * C + ii) * D + ch);
                     const float4 b = *reinterpret_cast<const float4*>(stg + (1 * C + ii) * D + ch);
                     const float4 e = *reinterpret_cast<const float4*>(stg + (2 * C + ii) * D + ch);
-                    const uint2 qu = *reinterpret_cast<const uint2*>(sQ + ii * D + ch);
-                    const uint2 ku = *reinterpret_cast<const uint2*>(sK + ii * D + ch);
+                    const uint2 qu = *reinterpret_cast<const uint2*>(sQ + swz_bf16(ii, ch));
+                    const uint2 ku = *reinterpret_cast<const uint2*>(sK + swz_bf16(ii, ch));
                     const float2 q01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qu.x));
                     const float2 q23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qu.y));
                     const float2 k01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ku.x));

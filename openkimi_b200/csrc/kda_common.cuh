@@ -85,7 +85,8 @@ __device__ __forceinline__ void seq_chunks(const KdaParams& p, int n, int& c0, i
 //   W    as W^T   cm(d, i; 64)      U / V'  as V'^T  cm(e, i; 64)     (i = token in chunk)
 //   Aqk, Tm       cm(i, j; 64)      Qt, Kh           cm(i, d; dk)
 //   S0, dS as S^T cm(e, d; dk)      dVn     as dV'^T cm(e, i; 64)
-// gamC is a plain float[dk]; Gc, Qn, Kn, aux are plain row-major arrays.
+// gamC is a plain float[dk]; aux is a plain row-major array; Gc, Qn, Kn are row-major with their
+// 16-byte chunks XOR-swizzled by the row when dk = 128 (swz_f32 / swz_bf16 in kda_tc.cuh).
 // ---------------------------------------------------------------------------------------
 struct WsLayout {
     size_t W, U, Aqk, Qt, Kh, gamC, total_nosave;       // what fwd_state consumes (all a forward-only call needs)

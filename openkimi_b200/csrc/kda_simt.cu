@@ -198,9 +198,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_fwd_intra_simt(const KdaParam
         T* gKn = (T*)(ws + L.Kn) + rec * C * D;
         float* gaux = (float*)(ws + L.aux) + rec * 3 * C;
         for (int idx = tid; idx < C * D; idx += NTHREADS) {
-            gGc[idx] = sG[idx];
-            stf(gQn + idx, sq[idx]);
-            stf(gKn + idx, sk[idx]);
+            // d = 128: the chunk-swizzled row layout the tensor-core backward reads (swz_f32 / swz_bf16)
+            const int r = idx / D, dd = idx % D;
+            gGc[D == 128 ? tc::swz_f32(r, dd) : idx] = sG[idx];
+            stf(gQn + (D == 128 ? (sizeof(T) == 2 ? tc::swz_bf16(r, dd) : tc::swz_f32(r, dd)) : idx), sq[idx]);
+            stf(gKn + (D == 128 ? (sizeof(T) == 2 ? tc::swz_bf16(r, dd) : tc::swz_f32(r, dd)) : idx), sk[idx]);
         }
         if (tid < C) {
             gaux[tid] = srq[tid];

@@ -22,6 +22,17 @@ __host__ __device__ __forceinline__ int cm_idx(int r, int c, int cols) {
     return (((r >> 3) * (cols >> 3) + (c >> 3)) << 6) + ((r & 7) << 3) + (c & 7);
 }
 
+// ---------------------------------------------------------------------------------------
+// Row-major [rows][128] tiles (the kept prologue: G in FP32, q^ and k^ in BF16) are stored with
+// their 16-byte chunks XOR-swizzled by the row: chunk c of row r sits at chunk position
+// c ^ (r & 7).  A warp that reads eight ROWS at the same channels (the operand stage of the
+// forward) then touches eight different 16-byte bank groups instead of one, while every access
+// that walks the channels of one row (thread = channel, or a half warp per row) stays
+// conflict-free, because the swizzle permutes chunks inside an aligned group of eight.
+// ---------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ int swz_f32(int r, int d) { return r * 128 + ((((d >> 2) ^ (r & 7)) << 2) | (d & 3)); }
+__host__ __device__ __forceinline__ int swz_bf16(int r, int d) { return r * 128 + ((((d >> 3) ^ (r & 7)) << 3) | (d & 7)); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // 64-bit shared-memory matrix descriptor, no swizzle, descriptor version 1 (sm_100)

@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             float gl = 0.f;
             if (i < ci.len) gl = gate ? negA * softplus_fast(x + bias) : x;
             run = fmaf(gl, LOG2E, run);  // explicit: both instantiations must round alike
-            sG[i * D + dch] = run;
+            sG[swz_f32(i, dch)] = run;
         }
         stot[quarter * D + dch] = run;
     }
@@ -344,8 +344,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) vf[j] *= b;
-            *reinterpret_cast<uint4*>(sQ + i * D + c8) = f32_to_bf16x8(qf);
-            *reinterpret_cast<uint4*>(sK + i * D + c8) = f32_to_bf16x8(kf);
+            *reinterpret_cast<uint4*>(sQ + swz_bf16(i, c8)) = f32_to_bf16x8(qf);
+            *reinterpret_cast<uint4*>(sK + swz_bf16(i, c8)) = f32_to_bf16x8(kf);
             *reinterpret_cast<uint4*>(sBV + cm_idx(i, c8, D)) = f32_to_bf16x8(vf);
             if ((tid & 15) == 0) {
                 sbeta[i] = b;
@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         if (quarter > 1) t += stot[D + dch];
         if (quarter > 2) t += stot[2 * D + dch];
 #pragma unroll
-        for (int r = 0; r < 16; ++r) sG[(16 * quarter + r) * D + dch] += t;
+        for (int r = 0; r < 16; ++r) sG[swz_f32(16 * quarter + r, dch)] += t;
     }
     fence_async_smem();
     __syncthreads();
@@ -385,17 +385,17 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             const int i = 8 * (combo >> 2) + (lane & 7), c8 = 8 * (4 * (combo & 3) + (lane >> 3)), m = i >> 4;
             float G8[8], qf[8], kf[8], o8[8], gl[8];
             {
-                const float4 a = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8);
-                const float4 b = *reinterpret_cast<const float4*>(sG + (C - 1) * D + c8 + 4);
+                const float4 a = *reinterpret_cast<const float4*>(sG + swz_f32(C - 1, c8));
+                const float4 b = *reinterpret_cast<const float4*>(sG + swz_f32(C - 1, c8 + 4));
                 gl[0] = a.x; gl[1] = a.y; gl[2] = a.z; gl[3] = a.w; gl[4] = b.x; gl[5] = b.y; gl[6] = b.z; gl[7] = b.w;
             }
             {
-                const float4 a = *reinterpret_cast<const float4*>(sG + i * D + c8);
-                const float4 b = *reinterpret_cast<const float4*>(sG + i * D + c8 + 4);
+                const float4 a = *reinterpret_cast<const float4*>(sG + swz_f32(i, c8));
+                const float4 b = *reinterpret_cast<const float4*>(sG + swz_f32(i, c8 + 4));
                 G8[0] = a.x; G8[1] = a.y; G8[2] = a.z; G8[3] = a.w; G8[4] = b.x; G8[5] = b.y; G8[6] = b.z; G8[7] = b.w;
             }
-            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sQ + i * D + c8), qf);
-            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sK + i * D + c8), kf);
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sQ + swz_bf16(i, c8)), qf);
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(sK + swz_bf16(i, c8)), kf);
             const float bi = sbeta[i];
             float eg[8];
 #pragma unroll
@@ -410,7 +410,12 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             for (int j = 0; j < 8; ++j) o8[j] = kf[j] * ex2_approx(gl[j] - G8[j]);
             *reinterpret_cast<uint4*>(gKh + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
             if (m >= 1) {  // rows of block m as the N operand of block m's products
-                const float* r = sG + (16 * m) * D + c8;
+                float r[8];
+                {
+                    const float4 a = *reinterpret_cast<const float4*>(sG + swz_f32(16 * m, c8));
+                    const float4 b = *reinterpret_cast<const float4*>(sG + swz_f32(16 * m, c8 + 4));
+                    r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w; r[4] = b.x; r[5] = b.y; r[6] = b.z; r[7] = b.w;
+                }
                 __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(dyn + XSC + (m - 1) * 8192);
                 float f[8];
 #pragma unroll
@@ -426,7 +431,9 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             for (int I = 1; I <= 3; ++I) {  // keys scaled for the later blocks
                 __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(dyn + KSC + (I - 1) * 16384);
                 if (m < I) {
-                    const float* r = sG + (16 * I) * D + c8;
+                    const float4 a = *reinterpret_cast<const float4*>(sG + swz_f32(16 * I, c8));
+                    const float4 b = *reinterpret_cast<const float4*>(sG + swz_f32(16 * I, c8 + 4));
+                    const float r[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
                     for (int j = 0; j < 8; ++j) o8[j] = kf[j] * ex2_approx(r[j] - G8[j]);
                     *reinterpret_cast<uint4*>(ks + cm_idx(i, c8, D)) = f32_to_bf16x8(o8);
@@ -465,16 +472,19 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     // Eight lanes read 128 contiguous bytes of a row: no bank conflicts.
     {
         const int cs = lane & 7, b = warp >> 2, w4 = warp & 3, slot = 4 * (w4 & 1) + (lane >> 3);
+        // element offsets of this lane's channels 32 u + 4 cs .. + 3 inside the swizzled row r (swz_f32 / swz_bf16
+        // with the row-dependent part computed once per row): FP32 chunk 8 u + cs, BF16 chunk 4 u + cs / 2
+        auto goff = [&](int r, int u) { return 32 * u + 4 * (cs ^ (r & 7)); };
+        auto boff = [&](int r, int u) { return 8 * (((4 * u + (cs >> 1)) ^ (r & 7))) + 4 * (cs & 1); };
         auto row_against = [&](int i, int jbeg, int jend) {  // jbeg, jend multiples of four, uniform over the warp
             const int ri = 16 * b + i;
             float gi[16], qi[16], ki[16];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int d0 = 32 * u + 4 * cs;
-                const float4 g4 = *reinterpret_cast<const float4*>(sG + ri * D + d0);
+                const float4 g4 = *reinterpret_cast<const float4*>(sG + ri * D + goff(ri, u));
                 gi[4 * u] = g4.x; gi[4 * u + 1] = g4.y; gi[4 * u + 2] = g4.z; gi[4 * u + 3] = g4.w;
-                const uint2 q2 = *reinterpret_cast<const uint2*>(sQ + ri * D + d0);
-                const uint2 k2 = *reinterpret_cast<const uint2*>(sK + ri * D + d0);
+                const uint2 q2 = *reinterpret_cast<const uint2*>(sQ + ri * D + boff(ri, u));
+                const uint2 k2 = *reinterpret_cast<const uint2*>(sK + ri * D + boff(ri, u));
                 const float2 qa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.x));
                 const float2 qb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.y));
                 const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
@@ -493,10 +503,11 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                     const int rj = 16 * b + j0 + jj;
                     float2 av = make_float2(0.f, 0.f), lv = av;  // packed two-wide FMAs: even / odd channels
 #pragma unroll
+                    const int gj0 = goff(rj, 0), kj0 = boff(rj, 0), kj1 = boff(rj, 1);
+#pragma unroll
                     for (int u = 0; u < 4; ++u) {
-                        const int d0 = 32 * u + 4 * cs;
-                        const float4 g4 = *reinterpret_cast<const float4*>(sG + rj * D + d0);
-                        const uint2 k2 = *reinterpret_cast<const uint2*>(sK + rj * D + d0);
+                        const float4 g4 = *reinterpret_cast<const float4*>(sG + rj * D + gj0 + 32 * u);
+                        const uint2 k2 = *reinterpret_cast<const uint2*>(sK + rj * D + ((u & 1) ? kj1 : kj0) + 64 * (u >> 1));
                         const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
                         const float2 kb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.y));
                         // (rows j > i are computed too but never stored; whatever they overflow to is dropped)
@@ -596,7 +607,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             mma_ss(tmem0 + T_U, make_desc(sb + BV + s * 4096, 2048, 128), make_desc(sb + KSC + s * 256, 128, 1024), id, s > 0);
         mma_commit(&bar2);
     }
-    if (tid < D) gGam[tid] = ex2_approx(sG[(C - 1) * D + tid]);
+    if (tid < D) gGam[tid] = ex2_approx(sG[swz_f32(C - 1, tid)]);
     ok = mbar_wait(&bar2, 0, p.status, 8) && ok;
     tc_fence_after();
 

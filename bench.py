@@ -80,11 +80,11 @@ def stage_model(name, d, C=64, es=2):
         # fused FP32-math backward (validation mode only)
         "bwd_chunk": (6 * C * d * d + 16 * C * C * d + 4 * C ** 3, (5 * t + C * es) + 2 * t + 2 * s + a + (4 * t + C * es)),
         # dAqk, dWn, dQt, dKh (K=d), dVb, dKb, Z, dMn; reads dO, v, V', dV', S0, dS, T, W; writes dv and the
-        # hand-over (dAqk, dM in FP32; dQt, dKh, dKb in the element type)
-        "bwd_wy": (10 * C * d * d + 8 * C * C * d, (2 * t) + 3 * t + 2 * s + a + (t + 2 * a4 + 3 * t)),
-        # three pairwise products over the lower triangle (dense-tile count 6 C^2 d); reads the kept prologue and
-        # the hand-over; writes dq, dk, dg, dbeta
-        "bwd_intra": (6 * C * C * d, (f4 + 2 * t + 3 * C * 4) + 2 * a4 + 3 * t + (3 * t + C * es)),
+        # hand-over (dAqk, dM as three BF16 operand tiles each + the diagonal of dAqk; dQt, dKh, dKb in BF16)
+        "bwd_wy": (10 * C * d * d + 8 * C * C * d, (2 * t) + 3 * t + 2 * s + a + (t + 6 * a + C * 4 + 3 * t)),
+        # three pairwise products over the lower triangle (dense-tile count 6 C^2 d; the six BF16 passes of the
+        # split operands are not counted); reads the kept prologue and the hand-over; writes dq, dk, dg, dbeta
+        "bwd_intra": (6 * C * C * d, (f4 + 2 * t + 3 * C * 4) + (6 * a + C * 4) + 3 * t + (3 * t + C * es)),
         "param_reduce": (0, 4 * d + 4),
     }
     return m[name]

@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     const size_t rec = (size_t)c * p.H + hd;
     const bool l2 = p.flags & KDA_FLAG_QK_L2NORM, gate = p.flags & KDA_FLAG_GATE, sig = p.flags & KDA_FLAG_BETA_SIGMOID;
     const float scale = p.scale;
+    const float expA = gate ? expf(p.A_log[hd]) : 1.f;  // requested at kernel start: used only in the gate chain at the end
     auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + hd); };
     KDA_PHASE_BEGIN();
     if (warp == 0) {
@@ -413,7 +414,6 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 #pragma unroll
             for (int b = 1; b < 4; ++b)
                 if (b > blk) base += stot[b * D + d];
-            const float expA = gate ? expf(p.A_log[hd]) : 1.f;
             const float negA = -expA, rcpA = 1.f / expA;
             // (rows past the end of a partial chunk have a constant G, hence a zero decay and zero terms:
             //  only their stores are masked, so that the rows do not end up in sixteen basic blocks)

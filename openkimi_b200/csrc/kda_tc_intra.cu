@@ -36,7 +36,10 @@ constexpr uint32_t SL = SA + 16640;
 constexpr uint32_t ST = SL + 16640;
 constexpr uint32_t SBETA = ST + 16640;        // f32 [3][64]: 1/|q|, 1/|k|, beta (the aux record)
 constexpr uint32_t STOT = SBETA + 768;       // f32 [4][128] running gate totals of the four 16-row groups
-constexpr uint32_t TOTAL = STOT + 2048;
+constexpr uint32_t SMIDF = STOT + 2048;      // f32 [4][128] midpoint of every (block, channel) of the cumulative gate
+constexpr uint32_t SPASS = SMIDF + 2048;     // int [4][4]: guard decision of every [16 rows x 32 channels] tile
+constexpr uint32_t TOTAL = SPASS + 64;
+constexpr uint32_t KN = KSC;                 // f32 [64][128] (chunk-swizzled rows): k_j 2^(m - G_j), live only during the diagonal phase
 constexpr uint32_t T_D = 0, T_W = 96, T_U = 160, TMEM_COLS = 256;
 }  // namespace fi
 
@@ -364,16 +367,180 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem0 = tmem_s;
-    if (quarter > 0) {  // the later 16-row groups of the cumulative sum pick up the totals of the earlier ones
-        float t = stot[dch];
+    // ---- the later 16-row groups of the cumulative sum pick up the totals of the earlier ones; every thread
+    //      keeps the 16 G values of its (block, channel) and evaluates the span guard of its tile (a warp is one
+    //      [16 rows x 32 channels] tile, k3mini/backends.py:17-19): where it passes, the diagonal block may use the
+    //      midpoint factorisation 2^(G_i - m) 2^(m - G_j) in FP32 (every factor within 2^(+-116)), for which the
+    //      thread leaves k_j 2^(m - G_j) of its rows in the (still free) operand space
+    float* smidf = reinterpret_cast<float*>(dyn + SMIDF);
+    int* spass = reinterpret_cast<int*>(dyn + SPASS);
+    float* sKN = reinterpret_cast<float*>(dyn + KN);
+    {
+        float t = 0.f;
+        if (quarter > 0) t = stot[dch];
         if (quarter > 1) t += stot[D + dch];
         if (quarter > 2) t += stot[2 * D + dch];
+        float Gr[16], mid;
 #pragma unroll
-        for (int r = 0; r < 16; ++r) sG[swz_f32(16 * quarter + r, dch)] += t;
+        for (int r = 0; r < 16; ++r) {
+            Gr[r] = sG[swz_f32(16 * quarter + r, dch)] + t;
+            if (quarter > 0) sG[swz_f32(16 * quarter + r, dch)] = Gr[r];
+        }
+        const bool tpass = guard_tile(Gr, p.guard_span, mid);
+        smidf[quarter * D + dch] = mid;
+        if (lane == 0) spass[quarter * 4 + (warp & 3)] = tpass ? 1 : 0;
+        if (tpass) {
+#pragma unroll
+            for (int r = 0; r < 16; ++r)
+                sKN[swz_f32(16 * quarter + r, dch)] =
+                    __bfloat162float(sK[swz_bf16(16 * quarter + r, dch)]) * ex2_approx(mid - Gr[r]);
+        }
     }
     fence_async_smem();
     __syncthreads();
     KDA_PHASE(2);
+    // ---- diagonal blocks on the CUDA cores: midpoint-factorised where all four tiles of the block passed the
+    //      guard, exact (one exp2 per pair and channel) otherwise.  Thread = (block b, slot, channel slice cs): the eight lanes of a slot split the
+    // 128 channels (16 each: 32 u + 4 cs .. +3), keep their row i in registers, walk key rows j four at a
+    // time, and the eight slices of a pair meet in three shuffles.  Four warps share a block; the 136
+    // pairs (j <= i) of the block are dealt out so that no warp walks more than twelve key rows:
+    //   warps 0, 1 (slot s = 0..7):  row 8 + s            against keys 0..7   (all valid)
+    //   warps 2, 3 (slot s = 0..7):  row 15 - s           against keys 8..15, then row s against keys 0..7
+    // Eight lanes read 128 contiguous bytes of a row: no bank conflicts.
+    {
+        const int cs = lane & 7, b = warp >> 2, w4 = warp & 3, slot = 4 * (w4 & 1) + (lane >> 3);
+        // element offsets of this lane's channels 32 u + 4 cs .. + 3 inside the swizzled row r (swz_f32 / swz_bf16
+        // with the row-dependent part computed once per row): FP32 chunk 8 u + cs, BF16 chunk 4 u + cs / 2
+        auto goff = [&](int r, int u) { return 32 * u + 4 * (cs ^ (r & 7)); };
+        auto boff = [&](int r, int u) { return 8 * (((4 * u + (cs >> 1)) ^ (r & 7))) + 4 * (cs & 1); };
+        auto row_against = [&](int i, int jbeg, int jend) {  // jbeg, jend multiples of four, uniform over the warp
+            const int ri = 16 * b + i;
+            float gi[16], qi[16], ki[16];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float4 g4 = *reinterpret_cast<const float4*>(sG + ri * D + goff(ri, u));
+                gi[4 * u] = g4.x; gi[4 * u + 1] = g4.y; gi[4 * u + 2] = g4.z; gi[4 * u + 3] = g4.w;
+                const uint2 q2 = *reinterpret_cast<const uint2*>(sQ + ri * D + boff(ri, u));
+                const uint2 k2 = *reinterpret_cast<const uint2*>(sK + ri * D + boff(ri, u));
+                const float2 qa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.x));
+                const float2 qb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.y));
+                const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
+                const float2 kb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.y));
+                qi[4 * u] = qa.x; qi[4 * u + 1] = qa.y; qi[4 * u + 2] = qb.x; qi[4 * u + 3] = qb.y;
+                ki[4 * u] = ka.x; ki[4 * u + 1] = ka.y; ki[4 * u + 2] = kb.x; ki[4 * u + 3] = kb.y;
+            }
+            // four key rows at a time: their eight sums (a and l of each pair) are reduced over the eight
+            // slices by a transposing exchange, 7 shuffles instead of 24, after which lane cs owns sum
+            // number cs and stores it
+#pragma unroll 1
+            for (int j0 = jbeg; j0 < jend; j0 += 4) {
+                float v[8];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int rj = 16 * b + j0 + jj;
+                    float2 av = make_float2(0.f, 0.f), lv = av;  // packed two-wide FMAs: even / odd channels
+#pragma unroll
+                    const int gj0 = goff(rj, 0), kj0 = boff(rj, 0), kj1 = boff(rj, 1);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float4 g4 = *reinterpret_cast<const float4*>(sG + rj * D + gj0 + 32 * u);
+                        const uint2 k2 = *reinterpret_cast<const uint2*>(sK + rj * D + ((u & 1) ? kj1 : kj0) + 64 * (u >> 1));
+                        const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
+                        const float2 kb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.y));
+                        // (rows j > i are computed too but never stored; whatever they overflow to is dropped)
+                        const float2 k01 = __fmul2_rn(ka, make_float2(ex2_approx(gi[4 * u] - g4.x), ex2_approx(gi[4 * u + 1] - g4.y)));
+                        const float2 k23 = __fmul2_rn(kb, make_float2(ex2_approx(gi[4 * u + 2] - g4.z), ex2_approx(gi[4 * u + 3] - g4.w)));
+                        av = __ffma2_rn(make_float2(qi[4 * u], qi[4 * u + 1]), k01, __ffma2_rn(make_float2(qi[4 * u + 2], qi[4 * u + 3]), k23, av));
+                        lv = __ffma2_rn(make_float2(ki[4 * u], ki[4 * u + 1]), k01, __ffma2_rn(make_float2(ki[4 * u + 2], ki[4 * u + 3]), k23, lv));
+                    }
+                    v[2 * jj] = av.x + av.y;
+                    v[2 * jj + 1] = lv.x + lv.y;
+                }
+                const bool b2 = cs & 4, b1 = cs & 2, b0 = cs & 1;
+                float w4s[4], w2s[2];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) w4s[t] = (b2 ? v[t + 4] : v[t]) + __shfl_xor_sync(0xffffffffu, b2 ? v[t] : v[t + 4], 4);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) w2s[t] = (b1 ? w4s[t + 2] : w4s[t]) + __shfl_xor_sync(0xffffffffu, b1 ? w4s[t] : w4s[t + 2], 2);
+                const float sum = (b0 ? w2s[1] : w2s[0]) + __shfl_xor_sync(0xffffffffu, b0 ? w2s[0] : w2s[1], 1);
+                const int j = j0 + (cs >> 1);
+                if (j <= i) {
+                    if (!b0) sA[ri * 65 + 16 * b + j] = sum * p.scale;
+                    else if (j < i) sL[ri * 65 + 16 * b + j] = sum;
+                }
+            }
+        };
+        // guarded variant of the same walk: no exponential in the pair loop, the key rows come pre-scaled
+        auto row_against_mid = [&](int i, int jbeg, int jend) {
+            const int ri = 16 * b + i;
+            float qP[16], kP[16];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int d0 = 32 * u + 4 * cs;
+                const float4 g4 = *reinterpret_cast<const float4*>(sG + ri * D + goff(ri, u));
+                const float4 m4 = *reinterpret_cast<const float4*>(smidf + b * D + d0);
+                const uint2 q2 = *reinterpret_cast<const uint2*>(sQ + ri * D + boff(ri, u));
+                const uint2 k2 = *reinterpret_cast<const uint2*>(sK + ri * D + boff(ri, u));
+                const float2 qa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.x));
+                const float2 qb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.y));
+                const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
+                const float2 kb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.y));
+                const float p0 = ex2_approx(g4.x - m4.x), p1 = ex2_approx(g4.y - m4.y), p2 = ex2_approx(g4.z - m4.z),
+                            p3 = ex2_approx(g4.w - m4.w);
+                qP[4 * u] = qa.x * p0; qP[4 * u + 1] = qa.y * p1; qP[4 * u + 2] = qb.x * p2; qP[4 * u + 3] = qb.y * p3;
+                kP[4 * u] = ka.x * p0; kP[4 * u + 1] = ka.y * p1; kP[4 * u + 2] = kb.x * p2; kP[4 * u + 3] = kb.y * p3;
+            }
+#pragma unroll 2
+            for (int j0 = jbeg; j0 < jend; j0 += 4) {
+                float v[8];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int rj = 16 * b + j0 + jj;
+                    const int gj0 = goff(rj, 0);
+                    float2 av = make_float2(0.f, 0.f), lv = av;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float4 kn = *reinterpret_cast<const float4*>(sKN + rj * D + gj0 + 32 * u);
+                        const float2 k01 = make_float2(kn.x, kn.y), k23 = make_float2(kn.z, kn.w);
+                        av = __ffma2_rn(make_float2(qP[4 * u], qP[4 * u + 1]), k01, __ffma2_rn(make_float2(qP[4 * u + 2], qP[4 * u + 3]), k23, av));
+                        lv = __ffma2_rn(make_float2(kP[4 * u], kP[4 * u + 1]), k01, __ffma2_rn(make_float2(kP[4 * u + 2], kP[4 * u + 3]), k23, lv));
+                    }
+                    v[2 * jj] = av.x + av.y;
+                    v[2 * jj + 1] = lv.x + lv.y;
+                }
+                const bool b2 = cs & 4, b1 = cs & 2, b0 = cs & 1;
+                float w4s[4], w2s[2];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) w4s[t] = (b2 ? v[t + 4] : v[t]) + __shfl_xor_sync(0xffffffffu, b2 ? v[t] : v[t + 4], 4);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) w2s[t] = (b1 ? w4s[t + 2] : w4s[t]) + __shfl_xor_sync(0xffffffffu, b1 ? w4s[t] : w4s[t + 2], 2);
+                const float sum = (b0 ? w2s[1] : w2s[0]) + __shfl_xor_sync(0xffffffffu, b0 ? w2s[0] : w2s[1], 1);
+                const int j = j0 + (cs >> 1);
+                if (j <= i) {
+                    if (!b0) sA[ri * 65 + 16 * b + j] = sum * p.scale;
+                    else if (j < i) sL[ri * 65 + 16 * b + j] = sum;
+                }
+            }
+        };
+        const bool fast = (spass[4 * b] & spass[4 * b + 1] & spass[4 * b + 2] & spass[4 * b + 3]) != 0;  // uniform over the block
+        if (fast) {
+            if (w4 < 2) {
+                row_against_mid(8 + slot, 0, 8);
+            } else {
+                row_against_mid(15 - slot, 8, w4 == 2 ? 16 : 12);
+                row_against_mid(slot, 0, w4 == 2 ? 4 : 8);
+            }
+        } else if (w4 < 2) {
+            row_against(8 + slot, 0, 8);
+        } else {
+            // rows 15 - slot: warp 2 holds rows 15..12 (keys up to 15), warp 3 rows 11..8 (keys up to 11)
+            row_against(15 - slot, 8, w4 == 2 ? 16 : 12);
+            // rows slot: warp 2 holds rows 0..3 (keys 0..3), warp 3 rows 4..7 (keys 0..7)
+            row_against(slot, 0, w4 == 2 ? 4 : 8);
+        }
+    }
+    __syncthreads();  // the pre-scaled key rows are dead: their space becomes operand space
+    KDA_PHASE(10);
     // ---- 1: decay-scaled operands.  A warp takes 8 rows x 4 channel groups at a time, so that its
     //      16-byte stores into the core-matrix tiles cover four whole 128-byte core matrices
     //      (no bank conflicts; the row-major loads of q^, k^, G take the conflicts instead, and
@@ -461,86 +628,6 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             mma_ss(tmem0 + T_D + 32 * (I - 1), make_desc(sb + KSC + (I - 1) * 16384 + s * 256, 128, 2048),
                    make_desc(sb + XSC + (I - 1) * 8192 + s * 256, 128, 2048), id, s > 0);
         mma_commit(&bar);
-    }
-    KDA_PHASE(10);
-    // Exact diagonal blocks.  Thread = (block b, slot, channel slice cs): the eight lanes of a slot split the
-    // 128 channels (16 each: 32 u + 4 cs .. +3), keep their row i in registers, walk key rows j four at a
-    // time, and the eight slices of a pair meet in three shuffles.  Four warps share a block; the 136
-    // pairs (j <= i) of the block are dealt out so that no warp walks more than twelve key rows:
-    //   warps 0, 1 (slot s = 0..7):  row 8 + s            against keys 0..7   (all valid)
-    //   warps 2, 3 (slot s = 0..7):  row 15 - s           against keys 8..15, then row s against keys 0..7
-    // Eight lanes read 128 contiguous bytes of a row: no bank conflicts.
-    {
-        const int cs = lane & 7, b = warp >> 2, w4 = warp & 3, slot = 4 * (w4 & 1) + (lane >> 3);
-        // element offsets of this lane's channels 32 u + 4 cs .. + 3 inside the swizzled row r (swz_f32 / swz_bf16
-        // with the row-dependent part computed once per row): FP32 chunk 8 u + cs, BF16 chunk 4 u + cs / 2
-        auto goff = [&](int r, int u) { return 32 * u + 4 * (cs ^ (r & 7)); };
-        auto boff = [&](int r, int u) { return 8 * (((4 * u + (cs >> 1)) ^ (r & 7))) + 4 * (cs & 1); };
-        auto row_against = [&](int i, int jbeg, int jend) {  // jbeg, jend multiples of four, uniform over the warp
-            const int ri = 16 * b + i;
-            float gi[16], qi[16], ki[16];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float4 g4 = *reinterpret_cast<const float4*>(sG + ri * D + goff(ri, u));
-                gi[4 * u] = g4.x; gi[4 * u + 1] = g4.y; gi[4 * u + 2] = g4.z; gi[4 * u + 3] = g4.w;
-                const uint2 q2 = *reinterpret_cast<const uint2*>(sQ + ri * D + boff(ri, u));
-                const uint2 k2 = *reinterpret_cast<const uint2*>(sK + ri * D + boff(ri, u));
-                const float2 qa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.x));
-                const float2 qb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q2.y));
-                const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
-                const float2 kb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.y));
-                qi[4 * u] = qa.x; qi[4 * u + 1] = qa.y; qi[4 * u + 2] = qb.x; qi[4 * u + 3] = qb.y;
-                ki[4 * u] = ka.x; ki[4 * u + 1] = ka.y; ki[4 * u + 2] = kb.x; ki[4 * u + 3] = kb.y;
-            }
-            // four key rows at a time: their eight sums (a and l of each pair) are reduced over the eight
-            // slices by a transposing exchange, 7 shuffles instead of 24, after which lane cs owns sum
-            // number cs and stores it
-#pragma unroll 1
-            for (int j0 = jbeg; j0 < jend; j0 += 4) {
-                float v[8];
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    const int rj = 16 * b + j0 + jj;
-                    float2 av = make_float2(0.f, 0.f), lv = av;  // packed two-wide FMAs: even / odd channels
-#pragma unroll
-                    const int gj0 = goff(rj, 0), kj0 = boff(rj, 0), kj1 = boff(rj, 1);
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const float4 g4 = *reinterpret_cast<const float4*>(sG + rj * D + gj0 + 32 * u);
-                        const uint2 k2 = *reinterpret_cast<const uint2*>(sK + rj * D + ((u & 1) ? kj1 : kj0) + 64 * (u >> 1));
-                        const float2 ka = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.x));
-                        const float2 kb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&k2.y));
-                        // (rows j > i are computed too but never stored; whatever they overflow to is dropped)
-                        const float2 k01 = __fmul2_rn(ka, make_float2(ex2_approx(gi[4 * u] - g4.x), ex2_approx(gi[4 * u + 1] - g4.y)));
-                        const float2 k23 = __fmul2_rn(kb, make_float2(ex2_approx(gi[4 * u + 2] - g4.z), ex2_approx(gi[4 * u + 3] - g4.w)));
-                        av = __ffma2_rn(make_float2(qi[4 * u], qi[4 * u + 1]), k01, __ffma2_rn(make_float2(qi[4 * u + 2], qi[4 * u + 3]), k23, av));
-                        lv = __ffma2_rn(make_float2(ki[4 * u], ki[4 * u + 1]), k01, __ffma2_rn(make_float2(ki[4 * u + 2], ki[4 * u + 3]), k23, lv));
-                    }
-                    v[2 * jj] = av.x + av.y;
-                    v[2 * jj + 1] = lv.x + lv.y;
-                }
-                const bool b2 = cs & 4, b1 = cs & 2, b0 = cs & 1;
-                float w4s[4], w2s[2];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) w4s[t] = (b2 ? v[t + 4] : v[t]) + __shfl_xor_sync(0xffffffffu, b2 ? v[t] : v[t + 4], 4);
-#pragma unroll
-                for (int t = 0; t < 2; ++t) w2s[t] = (b1 ? w4s[t + 2] : w4s[t]) + __shfl_xor_sync(0xffffffffu, b1 ? w4s[t] : w4s[t + 2], 2);
-                const float sum = (b0 ? w2s[1] : w2s[0]) + __shfl_xor_sync(0xffffffffu, b0 ? w2s[0] : w2s[1], 1);
-                const int j = j0 + (cs >> 1);
-                if (j <= i) {
-                    if (!b0) sA[ri * 65 + 16 * b + j] = sum * p.scale;
-                    else if (j < i) sL[ri * 65 + 16 * b + j] = sum;
-                }
-            }
-        };
-        if (w4 < 2) {
-            row_against(8 + slot, 0, 8);
-        } else {
-            // rows 15 - slot: warp 2 holds rows 15..12 (keys up to 15), warp 3 rows 11..8 (keys up to 11)
-            row_against(15 - slot, 8, w4 == 2 ? 16 : 12);
-            // rows slot: warp 2 holds rows 0..3 (keys 0..3), warp 3 rows 4..7 (keys 0..7)
-            row_against(slot, 0, w4 == 2 ? 4 : 8);
-        }
     }
     KDA_PHASE(4);
     bool ok = mbar_wait(&bar, 0, p.status, 8);

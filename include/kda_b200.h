@@ -101,8 +101,9 @@ typedef struct KdaParams {
      * FP32 [H*dk][conv_ksize] (channel = head * dk + d; tap j multiplies x[t - (ksize-1) + j]),
      * the window restarts at every sequence start, and the convolved rows are rounded to the
      * element type exactly as the stand-alone kda_short_conv_fwd does.  grad_q, grad_k, grad_v
-     * are then gradients of the CONVOLVED rows; feed them to kda_short_conv_bwd.  All three or
-     * none; BF16 with dk = 128 only (else KDA_ERR_UNSUPPORTED). */
+     * are then gradients of the CONVOLVED rows (feed them to kda_short_conv_bwd) unless
+     * grad_conv_q/k/v below are given.  All three or none; BF16 with dk = 128 only (else
+     * KDA_ERR_UNSUPPORTED). */
     const float *conv_q, *conv_k, *conv_v;
     int32_t conv_ksize;         /* 1..4 */
     /* Optional with cu_seqlens: device [NT][4] int32 = {sequence, chunk inside the sequence, first
@@ -113,6 +114,13 @@ typedef struct KdaParams {
      * one-thread kernel that copies a non-zero *status into it, so that the host can notice a wait
      * that gave up by reading its own memory, without a copy engine or a synchronisation. */
     int32_t *status_host;
+    /* Optional, with conv_q/k/v (kda_bwd only): FP32 [H*dk][conv_ksize] gradients of the three filters.
+     * When all three are given, the backward of the short convolutions runs inside the KDA backward
+     * kernels: grad_q, grad_k, grad_v then receive the gradients of the PRE-convolution projections
+     * (the gradient of the convolved rows never goes to memory) and kda_workspace_bytes reports a
+     * slightly larger backward scratch.  When NULL, grad_q/k/v are gradients of the convolved rows as
+     * before (feed them to kda_short_conv_bwd). */
+    float *grad_conv_q, *grad_conv_k, *grad_conv_v;
 } KdaParams;
 
 /* Bytes of forward workspace (saved for the backward) and of backward scratch for these

@@ -39,6 +39,7 @@ class KdaParams(C.Structure):
         ("conv_q", C.c_void_p), ("conv_k", C.c_void_p), ("conv_v", C.c_void_p), ("conv_ksize", C.c_int32),
         ("chunk_tab", C.c_void_p),
         ("status_host", C.c_void_p),
+        ("grad_conv_q", C.c_void_p), ("grad_conv_k", C.c_void_p), ("grad_conv_v", C.c_void_p),
     ]
 
 

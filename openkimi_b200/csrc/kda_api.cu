@@ -83,7 +83,10 @@ static int validate(const KdaParams* p, bool bwd) {
     if (bwd) {
         if (!p->grad_o || !p->grad_q || !p->grad_k || !p->grad_v || !p->grad_g || !p->grad_beta || !p->bwd_scratch) return KDA_ERR_NULL;
         if ((p->flags & KDA_FLAG_GATE) && !p->grad_A_log) return KDA_ERR_NULL;
-        if (p->bwd_scratch_bytes < L.bwd_total || ((uintptr_t)p->bwd_scratch & 255)) return KDA_ERR_WORKSPACE;
+        const bool cvb = p->grad_conv_q || p->grad_conv_k || p->grad_conv_v;
+        if (cvb && (!conv || !p->grad_conv_q || !p->grad_conv_k || !p->grad_conv_v)) return KDA_ERR_NULL;
+        if (p->bwd_scratch_bytes < (cvb ? L.bwd_total_conv : L.bwd_total) || ((uintptr_t)p->bwd_scratch & 255))
+            return KDA_ERR_WORKSPACE;
         const void* bp[] = {p->grad_o, p->grad_q, p->grad_k, p->grad_v, p->grad_g, p->grad_ht, p->grad_h0};
         for (const void* x : bp)
             if (!aligned16(x)) return KDA_ERR_ALIGN;
@@ -126,7 +129,7 @@ int kda_workspace_bytes(const KdaParams* p, size_t* fwd_bytes, size_t* bwd_bytes
     if (p->NT <= 0 || p->H <= 0 || p->dk <= 0 || p->dv <= 0) return KDA_ERR_SHAPE;
     WsLayout L = ws_layout(p->NT, p->H, p->dk, p->dv, p->dtype);
     if (fwd_bytes) *fwd_bytes = (p->flags & KDA_FLAG_NO_SAVE) ? L.total_nosave : p->conv_q ? L.total_conv : L.total;
-    if (bwd_bytes) *bwd_bytes = L.bwd_total;
+    if (bwd_bytes) *bwd_bytes = p->conv_q ? L.bwd_total_conv : L.bwd_total;
     return KDA_OK;
 }
 

@@ -5,6 +5,7 @@
 #include <mutex>
 
 #include "kda_common.cuh"
+#include "kda_conv_bwd.cuh"
 
 namespace kda {
 
@@ -62,10 +63,6 @@ __device__ __forceinline__ int doc_of(const int64_t* cu, int N, long long t, int
     return lo;
 }
 
-__device__ __forceinline__ float dsilu_f(float x) {
-    const float s = __fdividef(1.f, 1.f + __expf(-x));
-    return s * (1.f + x * (1.f - s));
-}
 
 // the filter padded to four taps: tap j multiplies x[t - 3 + j]
 template <int V>

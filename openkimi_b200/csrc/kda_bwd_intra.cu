@@ -35,6 +35,7 @@
 #include <type_traits>
 
 #include "kda_common.cuh"
+#include "kda_conv_bwd.cuh"
 #include "kda_tc.cuh"
 
 namespace kda {
@@ -62,6 +63,10 @@ constexpr uint32_t TOTAL = FD + 8192;
 // later uses of the dead operand space
 constexpr uint32_t PF = YB;                  // bf16 [3][64][128]: dQt, dKh, dKb (after the MMAs that read Y)
 constexpr uint32_t STG = SB;                 // f32 [3][64][128] staging of dq, dk, dbeta terms over SB and X (after all MMAs)
+// fused short-convolution backward (CONVB): once their first users are done, Y holds the pre-convolution q and
+// k rows -3 .. 63 (bf16 [67][128] each), the G tile holds dq and dk of the convolved rows (bf16 [64][128] each)
+// and the staging area the four blocks' filter-gradient shares
+constexpr uint32_t CXQ = YB, CXK = YB + 67 * 256, CDY = SG, CDW = STG;
 constexpr uint32_t TMEM_COLS = 512;
 // The midpoint factors reach 2^(+-span/2) and the third BF16 part of an operand sits 2^-16 below its
 // value, so the whole FP32 exponent range is used up at span ~205: tiles pass on to the tensor cores
@@ -87,6 +92,9 @@ __device__ __forceinline__ void store_parts(unsigned char* buf, int d, int t0, c
 // 512 threads: thread (blk, d) = (tid / 128, tid % 128) owns channel d (= TMEM lane d) of the 16-row
 // block blk, so that a warp covers exactly one guard tile, everything along the token axis of a
 // block is register-local, and four warps per scheduler hide each other's latencies.
+// CONVB: the backward of the short convolutions of q and k runs here too (KdaParams.grad_conv_*): dq, dk of the
+// convolved rows stay in shared memory and grad_q, grad_k receive the gradients of the projections.
+template <bool CONVB>
 __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) {
     using namespace bi;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -407,6 +415,20 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         KDA_PHASE(9);
         __syncthreads();
         KDA_PHASE(10);
+        if constexpr (CONVB) {  // the hand-over arrays in Y are dead: fetch the projection rows the convolution backward needs
+            const __nv_bfloat16* xq = (const __nv_bfloat16*)p.q;
+            const __nv_bfloat16* xk = (const __nv_bfloat16*)p.k;
+            __nv_bfloat16* sxq = reinterpret_cast<__nv_bfloat16*>(dyn + CXQ);
+            __nv_bfloat16* sxk = reinterpret_cast<__nv_bfloat16*>(dyn + CXK);
+            for (int qq = tid; qq < 67 * (D / 8); qq += NTHR) {
+                const int r = qq >> 4, e8 = (qq & 15) * 8;
+                const bool valid = r >= 3 ? r - 3 < ci.len : ci.lc > 0;
+                const size_t src = ((size_t)(ci.tok0 + (valid ? r - 3 : 0)) * p.H + hd) * D + e8;
+                cp_async16_z(sxq + r * D + e8, xq + src, valid);
+                cp_async16_z(sxk + r * D + e8, xk + src, valid);
+            }
+            cp_async_commit();
+        }
         // ---- reverse cumulative sum across the blocks and the gate chain
         float dA_acc = 0.f, dbias_acc = 0.f;
         {
@@ -479,14 +501,30 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                         dk8[j] = (dk8[j] - k8[j] * dotk) * rk;
                     }
                 }
-                if (ii < ci.len) {
-                    const size_t row = tok(ii);
+                if constexpr (CONVB) {  // rows of the convolved tensors' gradients stay on chip (zero past the end)
+                    __nv_bfloat16* sdyq = reinterpret_cast<__nv_bfloat16*>(dyn + CDY);
+                    __nv_bfloat16* sdyk = sdyq + C * D;
+                    const bool valid = ii < ci.len;
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf) {
-                        *reinterpret_cast<uint2*>(dq_out + row * D + 64 * hf + c4) =
-                            make_uint2(pack_bf16(dq8[4 * hf], dq8[4 * hf + 1]), pack_bf16(dq8[4 * hf + 2], dq8[4 * hf + 3]));
-                        *reinterpret_cast<uint2*>(dk_out + row * D + 64 * hf + c4) =
-                            make_uint2(pack_bf16(dk8[4 * hf], dk8[4 * hf + 1]), pack_bf16(dk8[4 * hf + 2], dk8[4 * hf + 3]));
+                        *reinterpret_cast<uint2*>(sdyq + ii * D + 64 * hf + c4) =
+                            valid ? make_uint2(pack_bf16(dq8[4 * hf], dq8[4 * hf + 1]), pack_bf16(dq8[4 * hf + 2], dq8[4 * hf + 3]))
+                                  : make_uint2(0u, 0u);
+                        *reinterpret_cast<uint2*>(sdyk + ii * D + 64 * hf + c4) =
+                            valid ? make_uint2(pack_bf16(dk8[4 * hf], dk8[4 * hf + 1]), pack_bf16(dk8[4 * hf + 2], dk8[4 * hf + 3]))
+                                  : make_uint2(0u, 0u);
+                    }
+                }
+                if (ii < ci.len) {
+                    const size_t row = tok(ii);
+                    if constexpr (!CONVB) {
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            *reinterpret_cast<uint2*>(dq_out + row * D + 64 * hf + c4) =
+                                make_uint2(pack_bf16(dq8[4 * hf], dq8[4 * hf + 1]), pack_bf16(dq8[4 * hf + 2], dq8[4 * hf + 3]));
+                            *reinterpret_cast<uint2*>(dk_out + row * D + 64 * hf + c4) =
+                                make_uint2(pack_bf16(dk8[4 * hf], dk8[4 * hf + 1]), pack_bf16(dk8[4 * hf + 2], dk8[4 * hf + 3]));
+                        }
                     }
                     if ((tid & 15) == 0) {
                         float b = sbeta[ii], v = sdb[ii] + db;
@@ -497,6 +535,58 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         }
         KDA_PHASE(12);
+        if constexpr (CONVB) {
+            // ---- backward of the short convolutions of q and k: thread (channel, 16-row block) walks its rows of both
+            //      tensors; dx replaces dy in shared memory and leaves in whole rows
+            cp_async_wait<0>();
+            __syncthreads();  // the projection rows have landed, dq / dk of the convolved rows are complete
+            const __nv_bfloat16* sxq = reinterpret_cast<const __nv_bfloat16*>(dyn + CXQ);
+            const __nv_bfloat16* sxk = reinterpret_cast<const __nv_bfloat16*>(dyn + CXK);
+            __nv_bfloat16* sdyq = reinterpret_cast<__nv_bfloat16*>(dyn + CDY);
+            __nv_bfloat16* sdyk = sdyq + C * D;
+            float* sdw = reinterpret_cast<float*>(dyn + CDW);  // [2][4][128][4]
+            int c0s, ncs;
+            seq_chunks(p, ci.seq, c0s, ncs);
+            const bool has_next = ci.lc + 1 < ncs;
+            float wq[4], wk[4], dwq[4] = {0.f, 0.f, 0.f, 0.f}, dwk[4] = {0.f, 0.f, 0.f, 0.f}, oq[16], ok_[16];
+            conv_taps(p.conv_q, hd, d, p.conv_ksize, wq);
+            conv_taps(p.conv_k, hd, d, p.conv_ksize, wk);
+            float* cvh = (float*)(sc + L.cv_head) + (rec * 3 * 3) * D;
+            float* cvt = (float*)(sc + L.cv_tail) + (rec * 3 * 3) * D;
+            conv_bwd_block(sxq, sdyq, wq, d, blk, cvh, cvt, dwq, oq);
+            conv_bwd_block(sxk, sdyk, wk, d, blk, cvh + 3 * D, cvt + 3 * D, dwk, ok_);
+            *reinterpret_cast<float4*>(sdw + (blk * D + d) * 4) = make_float4(dwq[0], dwq[1], dwq[2], dwq[3]);
+            *reinterpret_cast<float4*>(sdw + ((4 + blk) * D + d) * 4) = make_float4(dwk[0], dwk[1], dwk[2], dwk[3]);
+            __syncthreads();  // every read of dy is done, the filter-gradient shares are visible
+#pragma unroll
+            for (int r = 0; r < B; ++r) {
+                sdyq[(b0 + r) * D + d] = __float2bfloat16_rn(oq[r]);
+                sdyk[(b0 + r) * D + d] = __float2bfloat16_rn(ok_[r]);
+            }
+            if (blk < 2) {  // block 0 threads reduce the q filter, block 1 threads the k filter (fixed order)
+                const float* src = sdw + (4 * blk * D + d) * 4;
+                float4 t = *reinterpret_cast<const float4*>(src);
+#pragma unroll
+                for (int b = 1; b < 4; ++b) {
+                    const float4 u = *reinterpret_cast<const float4*>(src + b * D * 4);
+                    t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+                }
+                *reinterpret_cast<float4*>((float*)(sc + L.cv_part) + ((rec * 3 + blk) * D + d) * 4) = t;
+            }
+            __syncthreads();
+            const int lim = has_next ? 61 : ci.len;  // rows 61..63 of a chunk with a successor wait for the fix-up
+            __nv_bfloat16* dq_o = (__nv_bfloat16*)p.grad_q;
+            __nv_bfloat16* dk_o = (__nv_bfloat16*)p.grad_k;
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const int ii = (tid >> 4) + 32 * m, e8 = (tid & 15) * 8;
+                if (ii < lim) {
+                    const size_t row = tok(ii);
+                    *reinterpret_cast<uint4*>(dq_o + row * D + e8) = *reinterpret_cast<const uint4*>(sdyq + ii * D + e8);
+                    *reinterpret_cast<uint4*>(dk_o + row * D + e8) = *reinterpret_cast<const uint4*>(sdyk + ii * D + e8);
+                }
+            }
+        }
         if (gate) {
             __syncthreads();  // the tail terms in sscr have been read by every thread
             sscr[blk * D + d] = dbias_acc;
@@ -517,10 +607,68 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
 }
 
+// The rows a chunk could not finish (61..63 when it has a successor): dx from dpre of its last three rows and
+// of the successor's first three, in the FMA order of conv_bwd_block.  Grid (chunk, head, tensor), thread = channel.
+__global__ void __launch_bounds__(128) conv_bwd_fixup_kernel(const KdaParams p) {
+    const int c = blockIdx.x, h = blockIdx.y, t = blockIdx.z, ch = threadIdx.x;
+    const ChunkInfo ci = chunk_info(p, c);
+    int c0s, ncs;
+    seq_chunks(p, ci.seq, c0s, ncs);
+    if (ci.lc + 1 >= ncs) return;  // the last chunk of a sequence finished all its rows itself
+    const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
+    const char* sc = (const char*)p.bwd_scratch;
+    const size_t rec = (size_t)c * p.H + h, nxt = (size_t)(c + 1) * p.H + h;
+    const float* tl = (const float*)(sc + L.cv_tail) + ((rec * 3 + t) * 3) * 128 + ch;
+    const float* hdp = (const float*)(sc + L.cv_head) + ((nxt * 3 + t) * 3) * 128 + ch;
+    float w[4];
+    conv_taps(t == 0 ? p.conv_q : t == 1 ? p.conv_k : p.conv_v, h, ch, p.conv_ksize, w);
+    const float p61 = tl[0], p62 = tl[128], p63 = tl[256], p64 = hdp[0], p65 = hdp[128], p66 = hdp[256];
+    __nv_bfloat16* dst = (__nv_bfloat16*)(t == 0 ? p.grad_q : t == 1 ? p.grad_k : p.grad_v);
+    const size_t row = ((size_t)(ci.tok0 + 61) * p.H + h) * 128 + ch, rs = (size_t)p.H * 128;
+    dst[row] = __float2bfloat16_rn(fmaf(w[0], p64, fmaf(w[1], p63, fmaf(w[2], p62, w[3] * p61))));
+    dst[row + rs] = __float2bfloat16_rn(fmaf(w[0], p65, fmaf(w[1], p64, fmaf(w[2], p63, w[3] * p62))));
+    dst[row + 2 * rs] = __float2bfloat16_rn(fmaf(w[0], p66, fmaf(w[1], p65, fmaf(w[2], p64, w[3] * p63))));
+}
+
+// Filter gradients: fixed-order sum of the per-chunk shares.  Grid (head, tensor), 8 groups of 128 threads sum
+// every 8th chunk, then the 8 group sums are added in order (the scheme of kda_param_reduce).
+__global__ void __launch_bounds__(1024) conv_bwd_reduce_kernel(const KdaParams p) {
+    __shared__ float4 sb[8][128];
+    const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
+    const float4* part = (const float4*)((const char*)p.bwd_scratch + L.cv_part);
+    const int h = blockIdx.x, t = blockIdx.y, ch = threadIdx.x & 127, grp = threadIdx.x >> 7;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = grp; c < p.NT; c += 8) {
+        const float4 u = part[(((size_t)c * p.H + h) * 3 + t) * 128 + ch];
+        s.x += u.x; s.y += u.y; s.z += u.z; s.w += u.w;
+    }
+    sb[grp][ch] = s;
+    __syncthreads();
+    if (grp == 0) {
+        float4 a = sb[0][ch];
+#pragma unroll
+        for (int gi = 1; gi < 8; ++gi) {
+            a.x += sb[gi][ch].x; a.y += sb[gi][ch].y; a.z += sb[gi][ch].z; a.w += sb[gi][ch].w;
+        }
+        const int K = p.conv_ksize;
+        float* dst = (t == 0 ? p.grad_conv_q : t == 1 ? p.grad_conv_k : p.grad_conv_v) + (size_t)(h * 128 + ch) * K;
+        const float v4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (j >= 4 - K) dst[j - (4 - K)] = v4[j];
+    }
+}
+
 cudaError_t launch_bwd_intra(const KdaParams& p, cudaStream_t s) {
-    cudaError_t e = cudaFuncSetAttribute(kda_bwd_intra, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bi::TOTAL);
+    const bool convb = p.grad_conv_q != nullptr;
+    auto kern = convb ? kda_bwd_intra<true> : kda_bwd_intra<false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bi::TOTAL);
     if (e != cudaSuccess) return e;
-    kda_bwd_intra<<<p.NT * p.H, bi::NTHR, bi::TOTAL, s>>>(p);
+    kern<<<p.NT * p.H, bi::NTHR, bi::TOTAL, s>>>(p);
+    if (convb) {
+        conv_bwd_fixup_kernel<<<dim3(p.NT, p.H, 3), 128, 0, s>>>(p);
+        conv_bwd_reduce_kernel<<<dim3(p.H, 3), 1024, 0, s>>>(p);
+    }
     return cudaGetLastError();
 }
 

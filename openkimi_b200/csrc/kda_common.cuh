@@ -95,6 +95,7 @@ struct WsLayout {
     size_t Vc, total_conv;                              // convolved v rows (fused short convolution only)
     size_t dS, dVn, dA_part, dbias_part;                // backward scratch
     size_t dAM, dAd, dQt, dKh, dKb, dbp, gC, bwd_total; // hand-over from bwd_wy to bwd_intra
+    size_t cv_part, cv_head, cv_tail, bwd_total_conv;   // fused short-convolution backward only
 };
 
 __host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -148,6 +149,13 @@ __host__ __device__ inline WsLayout ws_layout(int NT, int H, int dk, int dv, int
     w.dbp = off;  off = align256(off + n * C * 4);
     w.gC = off;   off = align256(off + n * dk * 4);
     w.bwd_total = off;
+    // fused short-convolution backward (behind everything else, so that the plain call's scratch does not
+    // grow): per unit and tensor (q, k, v) the filter-gradient partial sums float [dk][4], and dpre of the
+    // chunk's first / last three rows float [3][dk] for the rows whose look-ahead crosses the chunk border
+    w.cv_part = off; off = align256(off + n * 3 * dk * 4 * 4);
+    w.cv_head = off; off = align256(off + n * 3 * 3 * dk * 4);
+    w.cv_tail = off; off = align256(off + n * 3 * 3 * dk * 4);
+    w.bwd_total_conv = off;
     return w;
 }
 

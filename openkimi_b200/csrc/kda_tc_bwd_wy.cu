@@ -15,6 +15,7 @@
 // Outputs: dv, the beta gradient collected so far, dGamma_C * Gamma_C, and the hand-over
 // records of bwd_intra (dAqk, dM as three-way BF16 splits in operand layout; dQt, dKh, dKb in BF16).
 #include "kda_common.cuh"
+#include "kda_conv_bwd.cuh"
 #include "kda_tc.cuh"
 
 namespace kda {
@@ -36,6 +37,8 @@ constexpr uint32_t SV = STG + 32768;        // v bf16 [64][128] row-major (prefe
 constexpr uint32_t SBETA = SV + 16384;      // f32 [64] beta, f32 [64] row sums, f32 [4][128] partial dGamma_C
 constexpr uint32_t SKH = SBETA + 512 + 2048;   // bf16 [64][128] staging of dKh (dQt and dKb are staged in the two halves of DST once dS is dead)
 constexpr uint32_t TOTAL = SKH + 16384;
+constexpr uint32_t XV = TOTAL;              // fused conv backward only: pre-convolution v rows -3 .. 63, bf16 [67][128]
+constexpr uint32_t TOTAL_CONVB = XV + 67 * 256;
 constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bw
 
@@ -55,6 +58,9 @@ __device__ __forceinline__ void store_split_row(__nv_bfloat16* base, int i, int 
     *reinterpret_cast<uint4*>(b + 2 * C * C) = make_uint4(p2[4], p2[5], p2[6], p2[7]);
 }
 
+// CONVB: the backward of the short convolution of v runs here too (KdaParams.grad_conv_*): dv of the convolved
+// rows stays in shared memory and grad_v receives the gradient of the v projection.
+template <bool CONVB>
 __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) {
     using namespace bw;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -114,6 +120,14 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
             const bool valid = i < ci.len;
             cp_async16_z(sdo + cm_idx(i, e8, D), dO + tok(valid ? i : 0) * D + e8, valid);
             cp_async16_z(sv + i * D + e8, vrec ? vrec + (valid ? i : 0) * D + e8 : v + tok(valid ? i : 0) * D + e8, valid);
+        }
+        if constexpr (CONVB) {  // rows -3 .. 63 of the v projection (zero where the row does not exist)
+            __nv_bfloat16* sxv = reinterpret_cast<__nv_bfloat16*>(dyn + XV);
+            for (int qq = tid; qq < 67 * (D / 8); qq += NTHR) {
+                const int r = qq >> 4, e8 = (qq & 15) * 8;
+                const bool valid = r >= 3 ? r - 3 < ci.len : ci.lc > 0;
+                cp_async16_z(sxv + r * D + e8, v + ((size_t)(ci.tok0 + (valid ? r - 3 : 0)) * p.H + h) * D + e8, valid);
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         if (tid < C) sbeta[tid] = ((const float*)(ws + L.aux))[rec * 3 * C + 2 * C + tid];  // beta kept by the forward
@@ -259,7 +273,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         tma_store_1d((__nv_bfloat16*)(sc + L.dQt) + rec * C * D, dyn + DST, C * D * 2);
         tma_store_1d((__nv_bfloat16*)(sc + L.dKh) + rec * C * D, dyn + SKH, C * D * 2);
         tma_store_commit();
-    } else if (tid >= 64 && tid - 64 < ci.len) {
+    } else if (!CONVB && tid >= 64 && tid - 64 < ci.len) {
         const int i = tid - 64;
         tma_store_1d((__nv_bfloat16*)p.grad_v + tok(i) * D, dyn + SV + i * D * 2, D * 2);
         tma_store_commit();
@@ -279,6 +293,44 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         for (int s = 0; s < 8; ++s)  // Z^T += S0 * dVb^T (MN-major B from cm(e, i; 64))
             mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 2048, 1024, 128), id_mm, true);
         mma_commit(&mmabar);
+    }
+    if constexpr (CONVB) {
+        // meanwhile: backward of the short convolution of v.  dv (BF16, as the unfused path would store it) is
+        // in shared memory; thread (channel, 16-row block) walks its rows, the four blocks' filter-gradient
+        // shares meet in the (now dead) dV'^T tile, and dx goes out in place of dv.
+        if (ok) {
+            __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(dyn + SV);
+            float* sdw = reinterpret_cast<float*>(dyn + DVT);  // [4][128][4]
+            int c0s, ncs;
+            seq_chunks(p, ci.seq, c0s, ncs);
+            const bool has_next = ci.lc + 1 < ncs;
+            float w4[4], dw[4] = {0.f, 0.f, 0.f, 0.f}, out[16];
+            conv_taps(p.conv_v, h, ch, p.conv_ksize, w4);
+            float* cvh = (float*)(sc + L.cv_head) + ((rec * 3 + 2) * 3) * D;
+            float* cvt = (float*)(sc + L.cv_tail) + ((rec * 3 + 2) * 3) * D;
+            conv_bwd_block(reinterpret_cast<const __nv_bfloat16*>(dyn + XV), sv, w4, ch, qtr, cvh, cvt, dw, out);
+            *reinterpret_cast<float4*>(sdw + (qtr * D + ch) * 4) = make_float4(dw[0], dw[1], dw[2], dw[3]);
+            __syncthreads();  // every read of dv is done, the filter-gradient shares are visible
+#pragma unroll
+            for (int r = 0; r < 16; ++r) sv[(16 * qtr + r) * D + ch] = __float2bfloat16_rn(out[r]);
+            if (qtr == 0) {
+                float4 t = *reinterpret_cast<const float4*>(sdw + ch * 4);
+#pragma unroll
+                for (int b = 1; b < 4; ++b) {
+                    const float4 u = *reinterpret_cast<const float4*>(sdw + (b * D + ch) * 4);
+                    t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+                }
+                *reinterpret_cast<float4*>((float*)(sc + L.cv_part) + ((rec * 3 + 2) * D + ch) * 4) = t;
+            }
+            fence_async_smem();
+            __syncthreads();
+            const int lim = has_next ? 61 : ci.len;  // rows 61..63 of a chunk with a successor wait for the fix-up
+            if (tid >= 64 && tid - 64 < lim) {
+                const int i = tid - 64;
+                tma_store_1d((__nv_bfloat16*)p.grad_v + tok(i) * D, dyn + SV + i * D * 2, D * 2);
+                tma_store_commit();
+            }
+        }
     }
     // meanwhile: beta row sums and dGamma_C * Gamma_C on the CUDA cores
     {
@@ -369,9 +421,12 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
 }
 
 cudaError_t launch_bwd_wy_tc(const KdaParams& p, cudaStream_t s) {
-    cudaError_t e = cudaFuncSetAttribute(kda_bwd_wy_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bw::TOTAL);
+    const bool convb = p.grad_conv_q != nullptr;
+    auto kern = convb ? kda_bwd_wy_tc<true> : kda_bwd_wy_tc<false>;
+    const int smem = convb ? (int)bw::TOTAL_CONVB : (int)bw::TOTAL;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    kda_bwd_wy_tc<<<p.NT * p.H, bw::NTHR, bw::TOTAL, s>>>(p);
+    kern<<<p.NT * p.H, bw::NTHR, smem, s>>>(p);
     return cudaGetLastError();
 }
 

@@ -153,23 +153,6 @@ def _require_cuda(t):
         raise RuntimeError("chunk_kda runs only on a CUDA device (sm_100a); there is no CPU fallback")
 
 
-def _short_conv_bwd(x, w, dy, cu):
-    """Backward of the causal depthwise convolution + SiLU (k3mini/model.py:76-88) for x, dy
-    [B, T, C] and FP32 taps w [C, ksize]; returns (dx, dw [C, 1, ksize] FP32)."""
-    B, T, Cc = x.shape
-    ks = w.shape[-1]
-    n_partial = 128
-    dx = torch.empty_like(x)
-    dw = torch.empty(Cc, 1, ks, dtype=torch.float32, device=x.device)
-    part = torch.empty(n_partial, Cc, ks, dtype=torch.float32, device=x.device)
-    stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
-    _lib.check(_lib.load().kda_short_conv_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), dx.data_ptr(), dw.data_ptr(),
-                                              part.data_ptr(), n_partial, B, T, Cc, ks, _DTYPES[x.dtype],
-                                              None if cu is None else cu.data_ptr(), 0 if cu is None else cu.numel() - 1,
-                                              stream), "kda_short_conv_bwd")
-    return dx, dw
-
-
 class ChunkKDAFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, beta, A_log, dt_bias, h0, conv_q, conv_k, conv_v, scale, flags, output_final_state,
@@ -249,6 +232,14 @@ class ChunkKDAFunction(torch.autograd.Function):
             p.grad_dt_bias = dbias.data_ptr() if dbias is not None else None
             p.grad_h0 = dh0.data_ptr() if dh0 is not None else None
             p.bwd_scratch, p.bwd_scratch_bytes = scratch.data_ptr(), call.bwd_bytes
+            dconv_f32 = None
+            if conv is not None:
+                # the backward of the three short convolutions runs inside the KDA backward kernels: dq, dk_, dv_
+                # come back as gradients of the projections, the filter gradients in FP32 [H*K, ksize]
+                # (written in full by the fixed-order reduction kernel; zero only when there is no chunk at all)
+                mk = torch.empty if call.NT > 0 else torch.zeros
+                dconv_f32 = [mk(H * dk, w.shape[-1], dtype=torch.float32, device=q.device) for w in conv]
+                p.grad_conv_q, p.grad_conv_k, p.grad_conv_v = (t.data_ptr() for t in dconv_f32)
             if call.NT > 0:
                 _lib.check(lib.kda_bwd(C.byref(p), call.stream()), "kda_bwd")
             else:
@@ -259,12 +250,7 @@ class ChunkKDAFunction(torch.autograd.Function):
                     dh0.copy_(dht if dht is not None else torch.zeros_like(dh0))
             dconv = (None, None, None)
             if conv is not None:
-                # dq, dk_, dv_ are gradients of the convolved rows: the stand-alone convolution
-                # backward turns them into gradients of the projections and of the filters
-                outs = [_short_conv_bwd(x.view(B, T, H * dk), w, dy.view(B, T, H * dk), call.cu)
-                        for x, w, dy in zip((q, k, v), conv, (dq, dk_, dv_))]
-                dq, dk_, dv_ = (dx.view(B, T, H, dk) for dx, _ in outs)
-                dconv = tuple(dw.to(wd) for (_, dw), wd in zip(outs, ctx.conv_dtypes))
+                dconv = tuple(dw.view(H * dk, 1, -1).to(wd) for dw, wd in zip(dconv_f32, ctx.conv_dtypes))
         return (dq, dk_, dv_, dg.to(in_dtypes[0]), dbeta.to(in_dtypes[1]), dA, dbias, dh0, *dconv,
                 None, None, None, None, None, None)
 
@@ -293,8 +279,10 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     reference has no such argument) says that q, k, v are the projections BEFORE the three
     causal depthwise convolutions + SiLU of k3mini/model.py:181-185.  For BF16 with K = 128 the
     forward kernel applies the filter while it loads the chunk (three halo rows included, the
-    window restarting at every sequence start); otherwise the stand-alone convolution kernels
-    run first.  Both routes give the same bits as ``ShortConvolution`` followed by ``chunk_kda``.
+    window restarting at every sequence start) and the backward kernels run the convolution
+    backward on the gradient rows while they are still on chip; otherwise the stand-alone
+    convolution kernels run first.  Both routes give the same bits as ``ShortConvolution`` followed
+    by ``chunk_kda`` (the filter gradients agree to FP32 summation accuracy).
     """
     state_v_first = bool(kwargs.pop("transpose_state_layout", state_v_first))
     for name in ("return_intermediate_states", "cp_context"):

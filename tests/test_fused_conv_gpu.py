@@ -1,6 +1,9 @@
-"""Short convolution fused into the KDA load stage (k3mini/model.py:181-185 followed by
-k3mini/model.py:200-216): the fused call must give the same bits as ShortConvolution followed by
-chunk_kda, forward and backward, and both must agree with the CPU oracle."""
+"""Short convolution fused into the KDA kernels (k3mini/model.py:181-185 followed by
+k3mini/model.py:200-216), forward in the load stage and backward inside the backward kernels: the
+fused call must give the same bits as ShortConvolution followed by chunk_kda -- outputs, state and
+every input / parameter gradient -- except the three filter gradients, whose sums run over chunks in
+a different (fixed) order and must agree to FP32 summation accuracy; and both must agree with the
+CPU oracle."""
 import pytest
 import torch
 
@@ -50,7 +53,11 @@ def _run(t, fused, cu=None, h0=None, **kw):
 
 def _same(a, b):
     for n in a:
-        assert torch.equal(a[n], b[n]), (n, (a[n].float() - b[n].float()).abs().max())
+        if n in ("dwq", "dwk", "dwv"):  # same terms, another fixed summation order (then rounded to the filter's type)
+            err = (a[n].float() - b[n].float()).norm() / b[n].float().norm().clamp_min(1e-20)
+            assert torch.isfinite(a[n].float()).all() and err < 2e-3, (n, float(err))
+        else:
+            assert torch.equal(a[n], b[n]), (n, (a[n].float() - b[n].float()).abs().max())
 
 
 @pytest.mark.parametrize("ks", [4, 3, 2, 1])
@@ -110,6 +117,9 @@ def test_sublayer_fused_equals_unfused():
         xi = x.clone().requires_grad_(True)
         y = m(xi)
         y.float().square().mean().backward()
-        outs.append([y.detach(), xi.grad] + [p.grad.clone() for p in m.parameters()])
-    for a, b in zip(*outs):
-        assert torch.equal(a, b)
+        outs.append([("y", y.detach()), ("dx", xi.grad)] + [(n, p.grad.clone()) for n, p in m.named_parameters()])
+    for (n, a), (_, b) in zip(*outs):
+        if n.endswith("conv.weight"):  # filter gradients: another fixed summation order
+            assert (a.float() - b.float()).norm() / b.float().norm() < 2e-3, n
+        else:
+            assert torch.equal(a, b), n

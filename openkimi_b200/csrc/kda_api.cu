@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include "kda_common.cuh"
+#include "kda_tmap.cuh"
 
 namespace kda {
 cudaError_t simt_fwd(const KdaParams& p, cudaStream_t s);
@@ -19,6 +20,32 @@ static thread_local char g_last_error[256] = "";
 int fail_cuda(cudaError_t e) {
     snprintf(g_last_error, sizeof(g_last_error), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
     return KDA_ERR_LAUNCH;
+}
+
+// The tensor-map encoder is a driver function; it is looked up through the runtime so that the library
+// has no link-time dependency on the driver.
+bool make_row_map(CUtensorMap* out, const void* base, long long tokens, int H, int box_rows) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = (EncodeFn)f;
+        tried = true;
+    }
+    if (!fn || !base || tokens <= 0) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)H * 128, (cuuint64_t)tokens};
+    const cuuint64_t strides[1] = {(cuuint64_t)H * 128 * 2};
+    const cuuint32_t box[2] = {128, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // ---- optional per-stage timing (benchmark instrumentation) ---------------------------------

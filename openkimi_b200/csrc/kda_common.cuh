@@ -20,6 +20,17 @@ inline int launch_status() {
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KDA_OK : fail_cuda(e);
 }
+// number of SMs of the current device (grid size of the kernels that walk their units themselves);
+// looked up once per device ordinal, 148 where the runtime does not answer
+inline int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    if (dev >= 0 && dev < 64) cached[dev] = n;
+    return n;
+}
 
 // ---------------------------------------------------------------------------------------
 // element access

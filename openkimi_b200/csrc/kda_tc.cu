@@ -1,6 +1,7 @@
 // Tensor-core (tcgen05 / TMEM) stages of the KDA op for BF16 operands.
 #include "kda_common.cuh"
 #include "kda_tc.cuh"
+#include "kda_tmap.cuh"
 
 namespace kda {
 
@@ -164,7 +165,7 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
     }
 }
 
-__global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams p) {
+__global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams p, const __grid_constant__ RowMaps maps) {
     using namespace fs;
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ uint64_t full[2];
@@ -342,7 +343,12 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
             }
             fence_async_smem();
             __syncthreads();
-            if (tid < ci.len) {
+            if (maps.ok && ci.len == C) {  // the whole tile with one bulk-tensor store
+                if (tid == 0) {
+                    tma_store_tile(&maps.m[0], h * D, (int)ci.tok0, sO);
+                    tma_store_commit();
+                }
+            } else if (tid < ci.len) {
                 tma_store_1d(o + ((size_t)(ci.tok0 + tid) * p.H + h) * D, sO + tid * D, D * 2);
                 tma_store_commit();
             }
@@ -571,7 +577,9 @@ cudaError_t tc_fwd(const KdaParams& p, cudaStream_t s) {
         constexpr int smem = fs::TOTAL;
         if ((e = cudaFuncSetAttribute(kda_fwd_state_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return e;
-        kda_fwd_state_tc<<<dim3(p.H, p.N), fs::NTHR, smem, s>>>(p);
+        RowMaps maps = {};
+        maps.ok = make_row_map(&maps.m[0], p.o, (long long)p.B * p.T, p.H, C);
+        kda_fwd_state_tc<<<dim3(p.H, p.N), fs::NTHR, smem, s>>>(p, maps);
     }
     prof_mark(s);
     return cudaGetLastError();

@@ -17,6 +17,7 @@
 #include "kda_common.cuh"
 #include "kda_conv_bwd.cuh"
 #include "kda_tc.cuh"
+#include "kda_tmap.cuh"
 
 namespace kda {
 
@@ -61,7 +62,7 @@ __device__ __forceinline__ void store_split_row(__nv_bfloat16* base, int i, int 
 // CONVB: the backward of the short convolution of v runs here too (KdaParams.grad_conv_*): dv of the convolved
 // rows stays in shared memory and grad_v receives the gradient of the v projection.
 template <bool CONVB>
-__global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) {
+__global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, const __grid_constant__ RowMaps maps) {
     using namespace bw;
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ uint64_t full, mmabar;
@@ -273,6 +274,11 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p) 
         tma_store_1d((__nv_bfloat16*)(sc + L.dQt) + rec * C * D, dyn + DST, C * D * 2);
         tma_store_1d((__nv_bfloat16*)(sc + L.dKh) + rec * C * D, dyn + SKH, C * D * 2);
         tma_store_commit();
+    } else if (!CONVB && maps.ok && ci.len == C) {  // dv: the whole tile with one bulk-tensor store
+        if (tid == 64) {
+            tma_store_tile(&maps.m[0], h * D, (int)ci.tok0, dyn + SV);
+            tma_store_commit();
+        }
     } else if (!CONVB && tid >= 64 && tid - 64 < ci.len) {
         const int i = tid - 64;
         tma_store_1d((__nv_bfloat16*)p.grad_v + tok(i) * D, dyn + SV + i * D * 2, D * 2);
@@ -426,7 +432,9 @@ cudaError_t launch_bwd_wy_tc(const KdaParams& p, cudaStream_t s) {
     const int smem = convb ? (int)bw::TOTAL_CONVB : (int)bw::TOTAL;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    kern<<<p.NT * p.H, bw::NTHR, smem, s>>>(p);
+    RowMaps maps = {};
+    maps.ok = make_row_map(&maps.m[0], p.grad_v, (long long)p.B * p.T, p.H, C);
+    kern<<<p.NT * p.H, bw::NTHR, smem, s>>>(p, maps);
     return cudaGetLastError();
 }
 

@@ -17,6 +17,7 @@
 //      (M = 128 channels); 6  W, U, gamC records.
 #include "kda_common.cuh"
 #include "kda_tc.cuh"
+#include "kda_tmap.cuh"
 
 namespace kda {
 
@@ -141,10 +142,10 @@ __device__ __forceinline__ void read_offdiag(uint32_t tmem_d, int qd, int lane, 
 }
 
 template <bool CONV>
-__global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams p) {
+__global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams p, const __grid_constant__ RowMaps maps) {
     using namespace fi;
     extern __shared__ __align__(128) unsigned char dyn[];
-    __shared__ uint64_t bar, bar2;
+    __shared__ uint64_t bar, bar2, rowbar, gatebar;
     __shared__ uint32_t tmem_s;
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dyn + SQ);
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(dyn + SK);
@@ -159,18 +160,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     float* stot = reinterpret_cast<float*>(dyn + STOT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int c = blockIdx.x / p.H, h = blockIdx.x % p.H;
-    const ChunkInfo ci = chunk_info(p, c);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     char* ws = (char*)p.workspace;
-    const size_t rec = (size_t)c * p.H + h;
-    __nv_bfloat16* gW = (__nv_bfloat16*)(ws + L.W) + rec * C * D;
-    __nv_bfloat16* gU = (__nv_bfloat16*)(ws + L.U) + rec * C * D;
-    __nv_bfloat16* gA = (__nv_bfloat16*)(ws + L.Aqk) + rec * C * C;
-    __nv_bfloat16* gQt = (__nv_bfloat16*)(ws + L.Qt) + rec * C * D;
-    __nv_bfloat16* gKh = (__nv_bfloat16*)(ws + L.Kh) + rec * C * D;
-    __nv_bfloat16* gT = (__nv_bfloat16*)(ws + L.Tm) + rec * C * C;
-    float* gGam = (float*)(ws + L.gamC) + rec * D;
     const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
     const __nv_bfloat16* k = (const __nv_bfloat16*)p.k;
     const __nv_bfloat16* v = (const __nv_bfloat16*)p.v;
@@ -187,74 +178,120 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     if (tid == 0) {
         mbar_init(&bar, 3);   // three issuing threads commit the off-diagonal products
         mbar_init(&bar2, 1);
+        mbar_init(&rowbar, 1);
+        mbar_init(&gatebar, 1);
         mbar_fence_init();
     }
+    __syncthreads();
 
-    // ---- 0: the chunk's inputs go to shared memory with 16-byte asynchronous copies, two groups:
-    //      the gate tile, then the q, k, v rows.  Staging areas are operand space that stage 1
-    //      fills later: gate rows in KB; q, k, v rows (ROWS each, three halo rows first when the
-    //      convolution is fused) from KSC on; the filter taps behind them.
+    // ---- 0: a unit's inputs arrive as 256-byte bulk copies, one per row, completing on two mbarriers.  The
+    //      CTA walks the units blockIdx.x, blockIdx.x + gridDim.x, ... and requests the inputs of its NEXT
+    //      unit while it still works on the current one, into space that is dead by then: the q, k, v rows
+    //      (ROWS each, three halo rows first when the convolution is fused) go to the operand space behind
+    //      the first key tile once the off-diagonal products have been read; the gate rows go to the L tile
+    //      once T is solved; the few scalars travel in registers.  Rows past the end of the sequence are
+    //      zero-filled by the thread that would have requested them.
     constexpr int HALO = CONV ? 3 : 0, ROWS = C + HALO;
-    constexpr uint32_t RAW = KSC, TAPS = RAW + 3 * ROWS * D * 2;
-    static_assert(TAPS + (CONV ? 3 * D * 16 : 0) <= KB, "staging overruns the operand space");
-    __nv_bfloat16* sRG = reinterpret_cast<__nv_bfloat16*>(dyn + KB);
+    constexpr uint32_t RAW = KSC + 16384, TAPS = ST;
+    static_assert(RAW + 3 * ROWS * D * 2 <= KB, "staging overruns the operand space");
+    __nv_bfloat16* sRG = reinterpret_cast<__nv_bfloat16*>(dyn + SL);
     __nv_bfloat16* sRaw = reinterpret_cast<__nv_bfloat16*>(dyn + RAW);
     const int quarter = tid >> 7, dch = tid & 127;  // gate: thread = (16-row group, channel)
     const int hw = tid >> 4, c8 = (tid & 15) * 8;   // rows: half warp = row, lane = 8 channels
-    // gate parameters: requested before anything else so that their latency hides behind the tile copies
-    const float a_log_h = gate ? p.A_log[h] : 0.f;
-    const float bias = (gate && p.dt_bias) ? p.dt_bias[h * D + dch] : 0.f;
-    float rb[2];
-    float4 tap = make_float4(0.f, 0.f, 0.f, 0.f);
-    if constexpr (CONV) {  // filter taps of this head, padded to four: entry e = tensor * 128 + channel
-        const int K = p.conv_ksize;
-        if (tid < 3 * D) {
-            float t4[4] = {0.f, 0.f, 0.f, 0.f};
-            const float* w = (tid < D ? p.conv_q : tid < 2 * D ? p.conv_k : p.conv_v) + (size_t)(h * D + (tid & (D - 1))) * K;
+    auto zero_row = [&](__nv_bfloat16* dst) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (j >= 4 - K) t4[j] = w[j - (4 - K)];
-            tap = make_float4(t4[0], t4[1], t4[2], t4[3]);
+        for (int j = 0; j < 16; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(0, 0, 0, 0);
+    };
+    const bool tiles = maps.ok != 0;  // whole [64 x 128] tiles with one bulk-tensor copy each (full chunks only)
+    auto request_rows = [&](const ChunkInfo& ci, int h) {
+        if (tid == 0) mbar_expect_tx(&rowbar, (uint32_t)(3 * ci.len + ((CONV && ci.lc > 0) ? 9 : 0)) * 256u);
+        if (tiles && ci.len == C) {
+            if (tid < 3) tma_load_tile(sRaw + (tid * ROWS + HALO) * D, &maps.m[tid], h * D, (int)ci.tok0, &rowbar);
+            if (CONV && (tid & 31) == 0 && tid >= 64 && tid < 64 + 9 * 32) {  // halo rows: one copy each from nine warps
+                const int t3 = (warp - 2) / 3, r = (warp - 2) % 3;
+                __nv_bfloat16* dst = sRaw + (t3 * ROWS + r) * D;
+                if (ci.lc > 0) tma_load_1d(dst, (t3 == 0 ? q : t3 == 1 ? k : v) + ((size_t)(ci.tok0 + r - 3) * p.H + h) * D, 256, &rowbar);
+                else zero_row(dst);
+            }
+        } else if (tid < 3 * C) {
+            const int t3 = tid >> 6, i = tid & 63;
+            __nv_bfloat16* dst = sRaw + (t3 * ROWS + HALO + i) * D;
+            if (i < ci.len) tma_load_1d(dst, (t3 == 0 ? q : t3 == 1 ? k : v) + ((size_t)(ci.tok0 + i) * p.H + h) * D, 256, &rowbar);
+            else zero_row(dst);
+        } else if (CONV && tid < 3 * C + 9) {  // three rows before the chunk: they exist unless the chunk starts its sequence
+            const int t3 = (tid - 3 * C) / 3, r = (tid - 3 * C) % 3;
+            __nv_bfloat16* dst = sRaw + (t3 * ROWS + r) * D;
+            if (ci.lc > 0) tma_load_1d(dst, (t3 == 0 ? q : t3 == 1 ? k : v) + ((size_t)(ci.tok0 + r - 3) * p.H + h) * D, 256, &rowbar);
+            else zero_row(dst);
         }
-    }
-#pragma unroll
-    for (int m = 0; m < 2; ++m) {
-        const int i = hw + 32 * m;
-        const bool valid = i < ci.len;
-        cp_async16_z(sRG + i * D + c8, g + ((size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h) * D + c8, valid);
-    }
-    cp_async_commit();
-#pragma unroll
-    for (int m = 0; m < 2; ++m) {
-        const int i = hw + 32 * m;
-        const bool valid = i < ci.len;
-        const size_t src = ((size_t)(ci.tok0 + (valid ? i : 0)) * p.H + h) * D + c8;
-        const int dst = (HALO + i) * D + c8;
-        cp_async16_z(sRaw + dst, q + src, valid);
-        cp_async16_z(sRaw + ROWS * D + dst, k + src, valid);
-        cp_async16_z(sRaw + 2 * ROWS * D + dst, v + src, valid);
-    }
-    if constexpr (CONV) {  // three rows before the chunk: they exist unless the chunk starts its sequence
-        if (tid < 3 * 3 * 16) {
-            const int t3 = tid / 48, r = (tid % 48) >> 4, x8 = (tid & 15) * 8;
-            const bool valid = ci.lc > 0;
-            const __nv_bfloat16* src = (t3 == 0 ? q : t3 == 1 ? k : v) + ((size_t)(ci.tok0 + (valid ? r - 3 : 0)) * p.H + h) * D + x8;
-            cp_async16_z(sRaw + (t3 * ROWS + r) * D + x8, src, valid);
+    };
+    struct Scalars {
+        float a_log, bias, rb[2];
+        float4 tap;
+    };
+    auto request_gate = [&](const ChunkInfo& ci, int h, Scalars& sc) {
+        if (tid == 256) mbar_expect_tx(&gatebar, (uint32_t)ci.len * 256u);
+        if (tiles && ci.len == C) {
+            if (tid == 256) tma_load_tile(sRG, &maps.m[3], h * D, (int)ci.tok0, &gatebar);
+        } else if (tid >= 256 && tid < 256 + C) {
+            const int i = tid - 256;
+            if (i < ci.len) tma_load_1d(sRG + i * D, g + ((size_t)(ci.tok0 + i) * p.H + h) * D, 256, &gatebar);
+            else zero_row(sRG + i * D);
         }
-    }
-    cp_async_commit();
+        sc.a_log = gate ? p.A_log[h] : 0.f;
+        sc.bias = (gate && p.dt_bias) ? p.dt_bias[h * D + dch] : 0.f;
 #pragma unroll
-    for (int m = 0; m < 2; ++m) {
-        const int i = CONV ? 2 * hw + m : hw + 32 * m;
-        rb[m] = ((tid & 15) == 0 && i < ci.len) ? __bfloat162float(beta[(size_t)(ci.tok0 + i) * p.H + h]) : 0.f;
-    }
-    if constexpr (CONV) {  // taps: entry (tensor, channel) at [tensor][channel % 8][channel / 8], so that the
-                           // sixteen lanes of a half warp read consecutive 16-byte words
-        float4* sW = reinterpret_cast<float4*>(dyn + TAPS);
-        if (tid < 3 * D) sW[(tid & ~(D - 1)) + (tid & 7) * 16 + ((tid & (D - 1)) >> 3)] = tap;
-    }
-    cp_async_wait<1>();
+        for (int m = 0; m < 2; ++m) {
+            const int i = CONV ? 2 * hw + m : hw + 32 * m;
+            sc.rb[m] = ((tid & 15) == 0 && i < ci.len) ? __bfloat162float(beta[(size_t)(ci.tok0 + i) * p.H + h]) : 0.f;
+        }
+        sc.tap = make_float4(0.f, 0.f, 0.f, 0.f);
+        if constexpr (CONV) {  // filter taps of this head, padded to four: entry e = tensor * 128 + channel
+            const int K = p.conv_ksize;
+            if (tid < 3 * D) {
+                float t4[4] = {0.f, 0.f, 0.f, 0.f};
+                const float* w = (tid < D ? p.conv_q : tid < 2 * D ? p.conv_k : p.conv_v) + (size_t)(h * D + (tid & (D - 1))) * K;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (j >= 4 - K) t4[j] = w[j - (4 - K)];
+                sc.tap = make_float4(t4[0], t4[1], t4[2], t4[3]);
+            }
+        }
+    };
+    // taps: entry (tensor, channel) at [tensor][channel % 8][channel / 8], so that the sixteen lanes of a
+    // half warp read consecutive 16-byte words; they wait in the (dead) T tile for the next unit
+    auto park_taps = [&](const Scalars& sc) {
+        if constexpr (CONV) {
+            float4* sW = reinterpret_cast<float4*>(dyn + TAPS);
+            if (tid < 3 * D) sW[(tid & ~(D - 1)) + (tid & 7) * 16 + ((tid & (D - 1)) >> 3)] = sc.tap;
+        }
+    };
+    const int n_units = p.NT * p.H;
+    Scalars nx;
+    ChunkInfo ci = chunk_info(p, blockIdx.x / p.H);
+    request_rows(ci, blockIdx.x % p.H);
+    request_gate(ci, blockIdx.x % p.H, nx);
+    park_taps(nx);
     __syncthreads();
+    uint32_t it = 0;
+    bool ok = true, more = false;
+    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
+    const int c = unit / p.H, h = unit % p.H;
+    const size_t rec = (size_t)c * p.H + h;
+    __nv_bfloat16* gW = (__nv_bfloat16*)(ws + L.W) + rec * C * D;
+    __nv_bfloat16* gU = (__nv_bfloat16*)(ws + L.U) + rec * C * D;
+    __nv_bfloat16* gA = (__nv_bfloat16*)(ws + L.Aqk) + rec * C * C;
+    __nv_bfloat16* gQt = (__nv_bfloat16*)(ws + L.Qt) + rec * C * D;
+    __nv_bfloat16* gKh = (__nv_bfloat16*)(ws + L.Kh) + rec * C * D;
+    __nv_bfloat16* gT = (__nv_bfloat16*)(ws + L.Tm) + rec * C * C;
+    float* gGam = (float*)(ws + L.gamC) + rec * D;
+    const int unit_nx = unit + gridDim.x;
+    more = unit_nx < n_units;
+    const ChunkInfo ci_nx = chunk_info(p, more ? unit_nx / p.H : c);
+    const float a_log_h = nx.a_log, bias = nx.bias;
+    const float rb[2] = {nx.rb[0], nx.rb[1]};
+    ok = mbar_wait(&gatebar, it & 1, p.status, 8);
+    KDA_PHASE(13);
     // ---- 0a: gate, channel-wise: thread (quarter, d) owns rows 16*quarter .. 16*quarter+15 of channel d
     {
         const float negA = gate ? -expf(a_log_h) : 0.f;
@@ -270,9 +307,9 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         }
         stot[quarter * D + dch] = run;
     }
-    cp_async_wait<0>();
-    __syncthreads();
     KDA_PHASE(0);
+    ok = mbar_wait(&rowbar, it & 1, p.status, 8) && ok;
+    KDA_PHASE(14);
     // Rows of a half warp: hw and hw + 32 without the convolution; 2 hw and 2 hw + 1 with it, so that
     // the five input rows 2 hw - 3 .. 2 hw + 1 serve the two outputs of one thread.
     uint4 rq4[2], rk4[2], rv4[2];
@@ -358,14 +395,14 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         }
     }
     KDA_PHASE(1);
+    tc_fence_before();
+    __syncthreads();  // the raw gate rows (in the Aqk staging tile) and the raw q, k, v rows are consumed
+    tc_fence_after();
     for (int idx = tid; idx < C * 65; idx += NTHR) {
         sA[idx] = 0.f;
         sL[idx] = 0.f;
         sT[idx] = 0.f;
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
     const uint32_t tmem0 = tmem_s;
     // ---- the later 16-row groups of the cumulative sum pick up the totals of the earlier ones; every thread
     //      keeps the 16 G values of its (block, channel) and evaluates the span guard of its tile (a warp is one
@@ -439,7 +476,6 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                 for (int jj = 0; jj < 4; ++jj) {
                     const int rj = 16 * b + j0 + jj;
                     float2 av = make_float2(0.f, 0.f), lv = av;  // packed two-wide FMAs: even / odd channels
-#pragma unroll
                     const int gj0 = goff(rj, 0), kj0 = boff(rj, 0), kj1 = boff(rj, 1);
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -630,7 +666,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         mma_commit(&bar);
     }
     KDA_PHASE(4);
-    bool ok = mbar_wait(&bar, 0, p.status, 8);
+    ok = mbar_wait(&bar, it & 1, p.status, 8) && ok;
     tc_fence_after();
     KDA_PHASE(11);
     if (ok) {  // warp (quadrant, group): accumulator columns 32 group .. 32 group + 31 = block I = group + 1
@@ -642,6 +678,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     KDA_PHASE(12);
     tc_fence_before();
     __syncthreads();
+    if (more) request_rows(ci_nx, unit_nx % p.H);  // the operand tiles of the off-diagonal products are dead
+    KDA_PHASE(15);
 
     KDA_PHASE(5);
     // (issued here rather than before the operand stage, whose shared-memory traffic they would share)
@@ -658,7 +696,9 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     //      warp w < 8 owns block column J = w % 4, columns 8 (w / 4) + lane % 8, and its four lane
     //      groups (lane / 8) split the 16 rows of every block below the diagonal.
     solve_block_column(sL, sT, sbeta, warp & 3, (warp >> 2) & 1, lane, warp < 8);
+    fence_async_smem();
     __syncthreads();
+    if (more) request_gate(ci_nx, unit_nx % p.H, nx);  // L is dead: its tile receives the next unit's gate rows
 
     KDA_PHASE(6);
     // ---- 4: Aqk and T records; T as the B operand of the WY products
@@ -679,7 +719,6 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
-
     KDA_PHASE(7);
     // ---- 5: W^T and U^T
     if (tid == 0) {
@@ -695,7 +734,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         mma_commit(&bar2);
     }
     if (tid < D) gGam[tid] = ex2_approx(sG[swz_f32(C - 1, tid)]);
-    ok = mbar_wait(&bar2, 0, p.status, 8) && ok;
+    ok = mbar_wait(&bar2, it & 1, p.status, 8) && ok;
     tc_fence_after();
 
     KDA_PHASE(8);
@@ -718,18 +757,33 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                            pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13])), pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15])));
         }
     }
+    if (more) park_taps(nx);  // (T has left for its record and its operand tile)
     if (tid == 0) tma_store_wait_all();
     tc_fence_before();
-    __syncthreads();
+    ok = __syncthreads_and(ok);
     KDA_PHASE(9);
-    if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
+    if (!ok) break;  // a wait gave up (recorded in the status word): no further unit is started
+    ci = ci_nx;
+    }
+    if (!ok && more) {  // the next unit's copies are in flight: they must have landed before the CTA leaves
+        mbar_wait(&rowbar, (it + 1) & 1, p.status, 8);
+        mbar_wait(&gatebar, (it + 1) & 1, p.status, 8);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_s, TMEM_COLS);
 }
 
 cudaError_t launch_fwd_intra_tc(const KdaParams& p, cudaStream_t s) {
     auto kern = p.conv_q ? kda_fwd_intra_tc<true> : kda_fwd_intra_tc<false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fi::TOTAL);
     if (e != cudaSuccess) return e;
-    kern<<<p.NT * p.H, fi::NTHR, fi::TOTAL, s>>>(p);
+    const int units = p.NT * p.H, sms = sm_count();
+    RowMaps maps = {};
+    const long long tokens = (long long)p.B * p.T;
+    maps.ok = make_row_map(&maps.m[0], p.q, tokens, p.H, C) && make_row_map(&maps.m[1], p.k, tokens, p.H, C) &&
+              make_row_map(&maps.m[2], p.v, tokens, p.H, C) && make_row_map(&maps.m[3], p.g, tokens, p.H, C);
+    kern<<<units < sms ? units : sms, fi::NTHR, fi::TOTAL, s>>>(p, maps);
     return cudaGetLastError();
 }
 

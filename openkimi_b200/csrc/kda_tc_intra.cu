@@ -268,15 +268,19 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     };
     const int n_units = p.NT * p.H;
     Scalars nx;
+    // unit u = (chunk u / H, head (u + chunk) % H): the head is skewed by the chunk index so that the units a
+    // CTA visits (stride gridDim.x) cycle through ALL heads even when the stride shares a factor with H
+    // (heads differ in cost: the ones whose tiles fail the span guard take the exact path)
+    auto head_of = [&](int u) { return (u % p.H + u / p.H) % p.H; };
     ChunkInfo ci = chunk_info(p, blockIdx.x / p.H);
-    request_rows(ci, blockIdx.x % p.H);
-    request_gate(ci, blockIdx.x % p.H, nx);
+    request_rows(ci, head_of(blockIdx.x));
+    request_gate(ci, head_of(blockIdx.x), nx);
     park_taps(nx);
     __syncthreads();
     uint32_t it = 0;
     bool ok = true, more = false;
     for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
-    const int c = unit / p.H, h = unit % p.H;
+    const int c = unit / p.H, h = head_of(unit);
     const size_t rec = (size_t)c * p.H + h;
     __nv_bfloat16* gW = (__nv_bfloat16*)(ws + L.W) + rec * C * D;
     __nv_bfloat16* gU = (__nv_bfloat16*)(ws + L.U) + rec * C * D;
@@ -678,7 +682,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     KDA_PHASE(12);
     tc_fence_before();
     __syncthreads();
-    if (more) request_rows(ci_nx, unit_nx % p.H);  // the operand tiles of the off-diagonal products are dead
+    if (more) request_rows(ci_nx, head_of(unit_nx));  // the operand tiles of the off-diagonal products are dead
     KDA_PHASE(15);
 
     KDA_PHASE(5);
@@ -698,7 +702,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     solve_block_column(sL, sT, sbeta, warp & 3, (warp >> 2) & 1, lane, warp < 8);
     fence_async_smem();
     __syncthreads();
-    if (more) request_gate(ci_nx, unit_nx % p.H, nx);  // L is dead: its tile receives the next unit's gate rows
+    if (more) request_gate(ci_nx, head_of(unit_nx), nx);  // L is dead: its tile receives the next unit's gate rows
 
     KDA_PHASE(6);
     // ---- 4: Aqk and T records; T as the B operand of the WY products

@@ -136,6 +136,48 @@ class FusedRMSNormGated(nn.Module):
         return _NormGateFn.apply(x, g, self.weight, self.eps)
 
 
+class _InputProjections(torch.autograd.Function):
+    """The sublayer's four projections of x (q, k, v and the merged narrow one) as one autograd node.
+    Forward: four library GEMMs, as ``F.linear`` would run them.  Backward: the input gradient is
+    accumulated inside the GEMMs (``addmm_`` with beta = 1, FP32 accumulators) instead of four separate
+    products and three read-modify-write additions over the [tokens, d_model] tensor, and the gradient
+    of the narrow output is assembled from its three slices with one concatenation."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+    def forward(ctx, x, wq, wk, wv, wn, hd, nh):
+        x2 = x.reshape(-1, x.shape[-1])
+        q, k, v, n = (x2 @ w.t() for w in (wq, wk, wv, wn))
+        ctx.save_for_backward(x2, wq, wk, wv, wn)
+        ctx.split = (hd, nh, wn.shape[0])
+        ctx.x_shape = tuple(x.shape)
+        lead = x.shape[:-1]
+        # the three slices of the narrow output leave as separate outputs (views of one buffer)
+        return (q.view(*lead, -1), k.view(*lead, -1), v.view(*lead, -1), n[:, :hd].view(*lead, hd),
+                n[:, hd:2 * hd].view(*lead, hd), n[:, 2 * hd:2 * hd + nh].contiguous().view(*lead, nh))
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, dq, dk, dv, dd, dg, db):
+        x2, wq, wk, wv, wn = ctx.saved_tensors
+        hd, nh, wide = ctx.split
+        flat = lambda t: t.reshape(-1, t.shape[-1])
+        dq, dk, dv = flat(dq), flat(dk), flat(dv)
+        parts = [flat(dd), flat(dg), flat(db)]
+        if wide > 2 * hd + nh:
+            parts.append(dq.new_zeros(dq.shape[0], wide - 2 * hd - nh))
+        dn = torch.cat(parts, dim=1)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = dq @ wq
+            dx.addmm_(dk, wk)
+            dx.addmm_(dv, wv)
+            dx.addmm_(dn, wn)
+            dx = dx.view(*ctx.x_shape)
+        grads = [g.t() @ x2 if need else None for g, need in zip((dq, dk, dv, dn), ctx.needs_input_grad[1:5])]
+        return (dx, *grads, None, None)
+
+
 class KimiDeltaAttention(nn.Module):
     """The KDA sublayer of k3mini/model.py:132-227 on the B200 kernels: q/k/v projections,
     short conv + SiLU, decay and beta projections, ``chunk_kda`` with the fused L2 norm /
@@ -171,24 +213,23 @@ class KimiDeltaAttention(nn.Module):
         return x.view(*x.shape[:2], self.n_heads, self.head_dim)
 
     def forward(self, x, cu_seqlens=None):
-        conv_w = None
-        if self.fuse_short_conv:
-            q, k, v = (self._heads(proj(x)) for proj in (self.q_proj, self.k_proj, self.v_proj))
-            conv_w = (self.q_conv.weight, self.k_conv.weight, self.v_conv.weight)
-        else:
-            q = self._heads(self.q_conv(self.q_proj(x), cu_seqlens=cu_seqlens)[0])
-            k = self._heads(self.k_conv(self.k_proj(x), cu_seqlens=cu_seqlens)[0])
-            v = self._heads(self.v_conv(self.v_proj(x), cu_seqlens=cu_seqlens)[0])
         # The three narrow projections of x (decay rank, output-gate rank, beta) share one GEMM: x is
-        # read once instead of three times, and the backward has one input-gradient GEMM instead of
-        # three plus two additions.  Same parameters, same arithmetic per output column.
+        # read once instead of three times.  Same parameters, same arithmetic per output column.  All four
+        # projections of x form one autograd node (see _InputProjections).
         hd, nh = self.head_dim, self.n_heads
         pad = (-(2 * hd + nh)) % 8
         w_narrow = torch.cat([self.f_a_proj.weight, self.out_gate_a.weight, self.beta_proj.weight]
                              + ([self.beta_proj.weight.new_zeros(pad, self.d_model)] if pad else []), dim=0)
-        narrow = torch.nn.functional.linear(x, w_narrow)
-        decay_rank, gate_rank = narrow[..., :hd], narrow[..., hd:2 * hd]
-        beta_logits = narrow[..., 2 * hd:2 * hd + nh].contiguous()
+        q, k, v, decay_rank, gate_rank, beta_logits = _InputProjections.apply(
+            x, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, w_narrow, hd, nh)
+        conv_w = None
+        if self.fuse_short_conv:
+            q, k, v = self._heads(q), self._heads(k), self._heads(v)
+            conv_w = (self.q_conv.weight, self.k_conv.weight, self.v_conv.weight)
+        else:
+            q = self._heads(self.q_conv(q, cu_seqlens=cu_seqlens)[0])
+            k = self._heads(self.k_conv(k, cu_seqlens=cu_seqlens)[0])
+            v = self._heads(self.v_conv(v, cu_seqlens=cu_seqlens)[0])
         raw_decay = self._heads(self.f_b_proj(decay_rank))
         out, _ = chunk_kda(q=q, k=k, v=v, g=raw_decay, beta=beta_logits, A_log=self.A_log,
                            dt_bias=self.dt_bias.reshape(-1), scale=self.scale, use_qk_l2norm_in_kernel=True,

@@ -120,24 +120,15 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = tid & 127, blk = tid >> 7, cg = warp & 3;
     const int b0 = B * blk;
-    const int c = blockIdx.x / p.H, hd = blockIdx.x % p.H;
-    const ChunkInfo ci = chunk_info(p, c);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     char* sc = (char*)p.bwd_scratch;
-    const size_t rec = (size_t)c * p.H + hd;
     const bool l2 = p.flags & KDA_FLAG_QK_L2NORM, gate = p.flags & KDA_FLAG_GATE, sig = p.flags & KDA_FLAG_BETA_SIGMOID;
     const float scale = p.scale;
-    const float expA = gate ? expf(p.A_log[hd]) : 1.f;  // requested at kernel start: used only in the gate chain at the end
-    auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + hd); };
     KDA_PHASE_BEGIN();
     if (warp == 0) {
         tmem_alloc(&tmem_s, TMEM_COLS);
         tmem_relinquish();
     }
-    // ---- everything the kernel reads arrives by bulk TMA: on barA what the operands are built from
-    //      (G, the normalised q and k, the row norms and beta kept by the forward), on barB the split
-    //      dAqk / dM tiles and the diagonal of dAqk from bwd_wy; the three [64][128] hand-over arrays
-    //      that only the assembly needs follow on barH once an operand buffer is free
     if (tid == 0) {
         mbar_init(&barA, 1);
         mbar_init(&barB, 1);
@@ -146,6 +137,31 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         mbar_init(&mma2, 4);
         mbar_init(&mma3, 4);
         mbar_fence_init();
+    }
+    tc_fence_before();
+    __syncthreads();  // barrier initialisation and the TMEM base address are visible
+    tc_fence_after();
+    const uint32_t tmem0 = tmem_s;
+    const uint32_t tlane = tmem0 + ((uint32_t)(32 * cg) << 16);  // this warp's lane quadrant
+    const uint32_t sb = smem_u32(dyn);
+
+    // The CTA walks the units blockIdx.x, blockIdx.x + gridDim.x, ...: tensor memory, barriers and the CTA itself
+    // are set up once.  Unit u = (chunk u / H, head (u + chunk) % H), so that the units of one CTA cycle through
+    // all heads whatever the stride (heads differ in cost: rejected tiles take the exact path).
+    const int n_units = p.NT * p.H;
+    uint32_t it = 0;
+    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
+    const uint32_t par = it & 1;
+    const int c = unit / p.H, hd = (unit % p.H + c) % p.H;
+    const ChunkInfo ci = chunk_info(p, c);
+    const size_t rec = (size_t)c * p.H + hd;
+    const float expA = gate ? expf(p.A_log[hd]) : 1.f;  // requested at the start of the unit: used only in the gate chain at the end
+    auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + hd); };
+    // ---- everything the kernel reads arrives by bulk TMA: on barA what the operands are built from
+    //      (G, the normalised q and k, the row norms and beta kept by the forward), on barB the split
+    //      dAqk / dM tiles and the diagonal of dAqk from bwd_wy; the three [64][128] hand-over arrays
+    //      that only the assembly needs follow on barH once an operand buffer is free
+    if (tid == 0) {
         const char* ws = (const char*)p.workspace;
         mbar_expect_tx(&barA, C * D * 4 + 2 * C * D * 2 + 3 * C * 4);
         tma_load_1d(dyn + SG, (const float*)(ws + L.Gc) + rec * C * D, C * D * 4, &barA);
@@ -158,13 +174,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     }
     if (tid < C) sdb[tid] = ((const float*)(sc + L.dbp))[rec * C + tid];
     const float carry_in = ((const float*)(sc + L.gC))[rec * D + d];
-    tc_fence_before();
-    __syncthreads();  // barrier initialisation and the TMEM base address are visible
-    tc_fence_after();
-    const uint32_t tmem0 = tmem_s;
-    const uint32_t tlane = tmem0 + ((uint32_t)(32 * cg) << 16);  // this warp's lane quadrant
-    const uint32_t sb = smem_u32(dyn);
-    bool ok = mbar_wait(&barA, 0, p.status, 64);
+    bool ok = mbar_wait(&barA, par, p.status, 64);
     KDA_PHASE(0);
 
     // ---- my block: G of my channel, guard and references; round 1: KN_j = k_j 2^(ref - G_j) -> X
@@ -193,7 +203,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
-    ok = ok && mbar_wait(&barB, 0, p.status, 64);
+    ok = ok && mbar_wait(&barB, par, p.status, 64);
     KDA_PHASE(1);
     constexpr int PA[6] = {0, 0, 1, 1, 0, 2}, PB[6] = {0, 1, 0, 1, 2, 0};
     // (descriptors: one base per buffer, the tile / part / block offset is added to its 14-bit address field)
@@ -257,7 +267,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         mma_commit(&mma2);
     }
     // ---- round 3: KP_i = beta_i k_i 2^(G_i - ref) -> X, once the row-side MMAs have read X
-    ok = ok && mbar_wait(&mma1, 0, p.status, 64);
+    ok = ok && mbar_wait(&mma1, par, p.status, 64);
     tc_fence_after();
     {
         const float qref = pass ? mid : G[0];
@@ -312,14 +322,14 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     }
     KDA_PHASE(4);
     // ---- the hand-over arrays may land in Y as soon as the MMAs that read Y are done
-    ok = ok && mbar_wait(&mma2, 0, p.status, 64);
+    ok = ok && mbar_wait(&mma2, par, p.status, 64);
     if (tid == 0 && ok) {
         mbar_expect_tx(&barH, 3 * C * D * 2);
         tma_load_1d(dyn + PF, (const __nv_bfloat16*)(sc + L.dQt) + rec * C * D, C * D * 2, &barH);
         tma_load_1d(dyn + PF + C * D * 2, (const __nv_bfloat16*)(sc + L.dKh) + rec * C * D, C * D * 2, &barH);
         tma_load_1d(dyn + PF + 2 * C * D * 2, (const __nv_bfloat16*)(sc + L.dKb) + rec * C * D, C * D * 2, &barH);
     }
-    ok = ok && mbar_wait(&mma3, 0, p.status, 64);
+    ok = ok && mbar_wait(&mma3, par, p.status, 64);
     tc_fence_after();
     KDA_PHASE(5);
     // ---- column sums of my block
@@ -343,7 +353,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             fD[e] = (__bfloat162float(t[0]) + __bfloat162float(t[C * C])) + __bfloat162float(t[2 * C * C]);
         }
     }
-    ok = ok && mbar_wait(&barH, 0, p.status, 64);
+    ok = ok && mbar_wait(&barH, par, p.status, 64);
     ok = __syncthreads_and(ok);  // (also: the rebuilt blocks are visible; the split tiles and X are dead -> staging area)
     KDA_PHASE(7);
 
@@ -602,6 +612,11 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         }
     }
     KDA_PHASE(13);
+    fence_async_smem();  // (the tiles this unit wrote are about to receive the next unit's bulk copies)
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (!ok) break;  // a wait gave up (recorded in the status word): no further unit is started
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
@@ -664,7 +679,8 @@ cudaError_t launch_bwd_intra(const KdaParams& p, cudaStream_t s) {
     auto kern = convb ? kda_bwd_intra<true> : kda_bwd_intra<false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bi::TOTAL);
     if (e != cudaSuccess) return e;
-    kern<<<p.NT * p.H, bi::NTHR, bi::TOTAL, s>>>(p);
+    const int units = p.NT * p.H, sms = sm_count();
+    kern<<<units < sms ? units : sms, bi::NTHR, bi::TOTAL, s>>>(p);
     if (convb) {
         conv_bwd_fixup_kernel<<<dim3(p.NT, p.H, 3), 128, 0, s>>>(p);
         conv_bwd_reduce_kernel<<<dim3(p.H, 3), 1024, 0, s>>>(p);

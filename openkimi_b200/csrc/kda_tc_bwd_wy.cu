@@ -68,25 +68,16 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
     __shared__ uint64_t full, mmabar;
     __shared__ uint32_t tmem_s;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int c = blockIdx.x / p.H, h = blockIdx.x % p.H;
-    const ChunkInfo ci = chunk_info(p, c);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     const char* ws = (const char*)p.workspace;
     char* sc = (char*)p.bwd_scratch;
-    const size_t rec = (size_t)c * p.H + h;
     float* stg = reinterpret_cast<float*>(dyn + STG);
     float* sbeta = reinterpret_cast<float*>(dyn + SBETA);
     float* srow = sbeta + 64;
     const __nv_bfloat16* dO = (const __nv_bfloat16*)p.grad_o;
     const __nv_bfloat16* v = (const __nv_bfloat16*)p.v;
-    // with the short convolution fused into the forward, p.v is the pre-convolution projection and
-    // the convolved rows come from the forward's record
-    const __nv_bfloat16* vrec = p.conv_q ? (const __nv_bfloat16*)(ws + L.Vc) + rec * C * D : nullptr;
-    auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
 
     KDA_PHASE_BEGIN();
-    // Gamma_C of my channel: requested now, used after the second MMA group
-    const float gam_c = tid < D ? ((const float*)(ws + L.gamC))[rec * D + tid] : 0.f;
     if (warp == 0) {
         tmem_alloc(&tmem_s, TMEM_COLS);
         tmem_relinquish();
@@ -103,6 +94,23 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
     const uint32_t tmem = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's lane quadrant
     const int ch = tid & 127, qtr = tid >> 7;                             // channel (TMEM lane) and column quarter (16 columns)
     float* spart = srow + 64;
+    const uint32_t sb = smem_u32(dyn);
+
+    // The CTA walks the units blockIdx.x, blockIdx.x + gridDim.x, ...: tensor memory, barriers and the CTA itself
+    // are set up once.  Unit u = (chunk u / H, head (u + chunk) % H), so that the units of one CTA cycle through
+    // all heads whatever the stride.
+    const int n_units = p.NT * p.H;
+    uint32_t it = 0, mph = 0;
+    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
+    const int c = unit / p.H, h = (unit % p.H + c) % p.H;
+    const ChunkInfo ci = chunk_info(p, c);
+    const size_t rec = (size_t)c * p.H + h;
+    // with the short convolution fused into the forward, p.v is the pre-convolution projection and
+    // the convolved rows come from the forward's record
+    const __nv_bfloat16* vrec = p.conv_q ? (const __nv_bfloat16*)(ws + L.Vc) + rec * C * D : nullptr;
+    auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
+    // Gamma_C of my channel: requested now, used after the second MMA group
+    const float gam_c = tid < D ? ((const float*)(ws + L.gamC))[rec * D + tid] : 0.f;
 
     if (tid == 0) {
         mbar_expect_tx(&full, TMA_BYTES);
@@ -139,12 +147,11 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
     // A wait that gives up has already recorded its code in the status word; from then on the CTA
     // issues no MMA and stores nothing (ok is made uniform at every barrier) and leaves through the
     // common exit, which frees its tensor memory.
-    bool ok = mbar_wait(&full, 0, p.status, 16);
+    bool ok = mbar_wait(&full, it & 1, p.status, 16);
     tc_fence_before();
     ok = __syncthreads_and(ok);
     KDA_PHASE(1);
 
-    const uint32_t sb = smem_u32(dyn);
     // ---- S1
     if (tid == 0 && ok) {
         tc_fence_after();
@@ -198,7 +205,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
             for (int j = 0; j < 8; ++j) spart[128 * eh + d8 + j] = acc[j];
         }
         }
-    ok = ok && mbar_wait(&mmabar, 0, p.status, 32);
+    ok = ok && mbar_wait(&mmabar, mph, p.status, 32);
+    mph ^= 1;
     tc_fence_after();
     ok = __syncthreads_and(ok);  // every warp is done reading dS: its tile becomes the staging area of dQt
     KDA_PHASE(2);
@@ -351,7 +359,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
         }
     }
     KDA_PHASE(4);
-    ok = ok && mbar_wait(&mmabar, 1, p.status, 32);
+    ok = ok && mbar_wait(&mmabar, mph, p.status, 32);
+    mph ^= 1;
     tc_fence_after();
     ok = __syncthreads_and(ok);
     KDA_PHASE(5);
@@ -400,7 +409,8 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
             mma_ss(tmem0 + DMN, make_desc(sb + DOT + s * 2048, 1024, 128), make_desc(sb + VT + s * 2048, 1024, 128), id, true);
         mma_commit(&mmabar);
     }
-    ok = ok && mbar_wait(&mmabar, 0, p.status, 32);
+    ok = ok && mbar_wait(&mmabar, mph, p.status, 32);
+    mph ^= 1;
     tc_fence_after();
     KDA_PHASE(7);
     if (ok) {
@@ -420,9 +430,14 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
         }
     }
     tma_store_wait_all();
+    fence_async_smem();  // (the tiles this unit wrote are about to receive the next unit's bulk copies)
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    KDA_PHASE(8);
+    if (!ok) break;  // a wait gave up (recorded in the status word): no further unit is started
+    }
     tc_fence_before();
     __syncthreads();
-    KDA_PHASE(8);
     if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
 }
 
@@ -434,7 +449,8 @@ cudaError_t launch_bwd_wy_tc(const KdaParams& p, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     RowMaps maps = {};
     maps.ok = make_row_map(&maps.m[0], p.grad_v, (long long)p.B * p.T, p.H, C);
-    kern<<<p.NT * p.H, bw::NTHR, smem, s>>>(p, maps);
+    const int units = p.NT * p.H, sms = sm_count();
+    kern<<<units < sms ? units : sms, bw::NTHR, smem, s>>>(p, maps);
     return cudaGetLastError();
 }
 

@@ -225,11 +225,12 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             else zero_row(dst);
         }
     };
-    struct Scalars {
-        float a_log, bias, rb[2];
+    struct Scalars {  // (beta stays in its storage type: a conversion here would wait for the load)
+        float a_log, bias;
+        __nv_bfloat16 rb[2];
         float4 tap;
     };
-    auto request_gate = [&](const ChunkInfo& ci, int h, Scalars& sc) {
+    auto request_gate = [&](const ChunkInfo& ci, int h) {
         if (tid == 256) mbar_expect_tx(&gatebar, (uint32_t)ci.len * 256u);
         if (tiles && ci.len == C) {
             if (tid == 256) tma_load_tile(sRG, &maps.m[3], h * D, (int)ci.tok0, &gatebar);
@@ -238,12 +239,14 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             if (i < ci.len) tma_load_1d(sRG + i * D, g + ((size_t)(ci.tok0 + i) * p.H + h) * D, 256, &gatebar);
             else zero_row(sRG + i * D);
         }
+    };
+    auto request_scalars = [&](const ChunkInfo& ci, int h, Scalars& sc) {
         sc.a_log = gate ? p.A_log[h] : 0.f;
         sc.bias = (gate && p.dt_bias) ? p.dt_bias[h * D + dch] : 0.f;
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
             const int i = CONV ? 2 * hw + m : hw + 32 * m;
-            sc.rb[m] = ((tid & 15) == 0 && i < ci.len) ? __bfloat162float(beta[(size_t)(ci.tok0 + i) * p.H + h]) : 0.f;
+            sc.rb[m] = beta[(size_t)(ci.tok0 + (i < ci.len ? i : 0)) * p.H + h];  // (used by lane 0 of the half warp, rows < len)
         }
         sc.tap = make_float4(0.f, 0.f, 0.f, 0.f);
         if constexpr (CONV) {  // filter taps of this head, padded to four: entry e = tensor * 128 + channel
@@ -274,7 +277,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     auto head_of = [&](int u) { return (u % p.H + u / p.H) % p.H; };
     ChunkInfo ci = chunk_info(p, blockIdx.x / p.H);
     request_rows(ci, head_of(blockIdx.x));
-    request_gate(ci, head_of(blockIdx.x), nx);
+    request_gate(ci, head_of(blockIdx.x));
+    request_scalars(ci, head_of(blockIdx.x), nx);
     park_taps(nx);
     __syncthreads();
     uint32_t it = 0;
@@ -293,7 +297,10 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     more = unit_nx < n_units;
     const ChunkInfo ci_nx = chunk_info(p, more ? unit_nx / p.H : c);
     const float a_log_h = nx.a_log, bias = nx.bias;
-    const float rb[2] = {nx.rb[0], nx.rb[1]};
+    float rb[2];
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+        rb[m] = ((tid & 15) == 0 && (CONV ? 2 * hw + m : hw + 32 * m) < ci.len) ? __bfloat162float(nx.rb[m]) : 0.f;
     ok = mbar_wait(&gatebar, it & 1, p.status, 8);
     KDA_PHASE(13);
     // ---- 0a: gate, channel-wise: thread (quarter, d) owns rows 16*quarter .. 16*quarter+15 of channel d
@@ -682,7 +689,10 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     KDA_PHASE(12);
     tc_fence_before();
     __syncthreads();
-    if (more) request_rows(ci_nx, head_of(unit_nx));  // the operand tiles of the off-diagonal products are dead
+    if (more) {  // the operand tiles of the off-diagonal products are dead; the scalars have the whole solve to arrive
+        request_rows(ci_nx, head_of(unit_nx));
+        request_scalars(ci_nx, head_of(unit_nx), nx);
+    }
     KDA_PHASE(15);
 
     KDA_PHASE(5);
@@ -702,7 +712,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     solve_block_column(sL, sT, sbeta, warp & 3, (warp >> 2) & 1, lane, warp < 8);
     fence_async_smem();
     __syncthreads();
-    if (more) request_gate(ci_nx, head_of(unit_nx), nx);  // L is dead: its tile receives the next unit's gate rows
+    if (more) request_gate(ci_nx, head_of(unit_nx));  // L is dead: its tile receives the next unit's gate rows
 
     KDA_PHASE(6);
     // ---- 4: Aqk and T records; T as the B operand of the WY products

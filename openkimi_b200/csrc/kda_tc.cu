@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
     if (tid == 0) {
         mbar_init(&full[0], 1);
         mbar_init(&full[1], 1);
-        mbar_init(&mmabar, 1);
+        mbar_init(&mmabar, 2);  // two issuing threads per MMA group (one accumulator each): a single thread spends
+                                // ~50 ns on every MMA it issues, which is on the critical path of the chunk loop
         mbar_fence_init();
     }
     tc_fence_before();
@@ -256,22 +257,25 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
         KDA_PHASE(1);
         tc_fence_before();
         __syncthreads();
-        if (tid == 0) {
+        if ((tid & 31) == 0 && warp < 2) {
             tc_fence_after();
             const uint32_t sb = smem_u32(b);
             constexpr uint32_t id_mn = make_idesc(128, 64, false, true);
             constexpr uint32_t id_k = make_idesc(128, 64, false, false);
+            if (warp == 0) {
 #pragma unroll
-            for (int s = 0; s < 8; ++s)  // WSacc = Sbf (K = d) * W^T record, MN-major B
-                mma_ts(tmem0 + WSACC, tmem0 + SBF + s * 8, make_desc(sb + WT + s * 2048, 1024, 128), id_mn, s > 0);
+                for (int s = 0; s < 8; ++s)  // WSacc = Sbf (K = d) * W^T record, MN-major B
+                    mma_ts(tmem0 + WSACC, tmem0 + SBF + s * 8, make_desc(sb + WT + s * 2048, 1024, 128), id_mn, s > 0);
+            } else {
 #pragma unroll
-            for (int s = 0; s < 8; ++s)  // Oacc = Sbf * Qt^T, K-major B (rows = i)
-                mma_ts(tmem0 + OACC, tmem0 + SBF + s * 8, make_desc(sb + QT + s * 256, 128, 2048), id_k, s > 0);
+                for (int s = 0; s < 8; ++s)  // Oacc = Sbf * Qt^T, K-major B (rows = i)
+                    mma_ts(tmem0 + OACC, tmem0 + SBF + s * 8, make_desc(sb + QT + s * 256, 128, 2048), id_k, s > 0);
+            }
             mma_commit(&mmabar);
         }
         // the next chunk's records are requested while the first MMA group runs (the other stage was
         // last read by the previous chunk's MMAs, which have completed)
-        if (tid == 32 && lc + 1 < nc) issue_loads(lc + 1, stage ^ 1);
+        if (tid == 64 && lc + 1 < nc) issue_loads(lc + 1, stage ^ 1);
         ok = mbar_wait(&mmabar, mma_phase, p.status, 4);
         mma_phase ^= 1;
         tc_fence_after();
@@ -310,17 +314,20 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
         KDA_PHASE(3);
         tc_fence_before();
         __syncthreads();
-        if (tid == 0) {
+        if ((tid & 31) == 0 && warp < 2) {
             tc_fence_after();
             const uint32_t sb = smem_u32(b);
             constexpr uint32_t id_k = make_idesc(128, 64, false, false);
             constexpr uint32_t id_s = make_idesc(128, 128, false, true);
+            if (warp == 0) {
 #pragma unroll
-            for (int s = 0; s < 4; ++s)  // Oacc += Vbf (K = j) * Aqk^T, K-major B (rows = i)
-                mma_ts(tmem0 + OACC, tmem0 + VBF + s * 8, make_desc(sb + AQ + s * 256, 128, 1024), id_k, true);
+                for (int s = 0; s < 4; ++s)  // Oacc += Vbf (K = j) * Aqk^T, K-major B (rows = i)
+                    mma_ts(tmem0 + OACC, tmem0 + VBF + s * 8, make_desc(sb + AQ + s * 256, 128, 1024), id_k, true);
+            } else {
 #pragma unroll
-            for (int s = 0; s < 4; ++s)  // Sacc += Vbf (K = i) * Kh, MN-major B
-                mma_ts(tmem0 + SACC, tmem0 + VBF + s * 8, make_desc(sb + KH + s * 4096, 2048, 128), id_s, true);
+                for (int s = 0; s < 4; ++s)  // Sacc += Vbf (K = i) * Kh, MN-major B
+                    mma_ts(tmem0 + SACC, tmem0 + VBF + s * 8, make_desc(sb + KH + s * 4096, 2048, 128), id_s, true);
+            }
             mma_commit(&mmabar);
         }
         ok = mbar_wait(&mmabar, mma_phase, p.status, 4);
@@ -388,7 +395,7 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
     using namespace bs;
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ uint64_t full[2];
-    __shared__ uint64_t mmabar;
+    __shared__ uint64_t mmabar, mmabar2;
     __shared__ uint32_t tmem_s;
     // thread (half, e) = (tid / 128, tid % 128): TMEM lane e, and half of the columns of every conversion phase
     const int tid = threadIdx.x, warp = tid >> 5, e = tid & 127, half = tid >> 7;
@@ -406,7 +413,8 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
     if (tid == 0) {
         mbar_init(&full[0], 1);
         mbar_init(&full[1], 1);
-        mbar_init(&mmabar, 1);
+        mbar_init(&mmabar, 2);   // first group: one issuing thread per accumulator
+        mbar_init(&mmabar2, 1);  // second group: a single product
         mbar_fence_init();
     }
     tc_fence_before();
@@ -450,7 +458,6 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
     };
     if (nc > 0) issue_loads(0, 0);
 
-    uint32_t mma_phase = 0;
     bool ok = true;
     for (int k = 0; k < nc; ++k) {
         const int lc = nc - 1 - k, stage = k & 1;
@@ -486,27 +493,29 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
         }
         tc_fence_before();
         __syncthreads();
-        if (tid == 0) {
+        if ((tid & 31) == 0 && warp < 2) {
             tc_fence_after();
             const uint32_t sb = smem_u32(b);
             constexpr uint32_t id_v1 = make_idesc(128, 64, true, true);    // dO^T (MN-major A) * Aqk (MN-major B)
             constexpr uint32_t id_v2 = make_idesc(128, 64, false, false);  // dSbf (TMEM) * Kh^T (K-major B)
             constexpr uint32_t id_s1 = make_idesc(128, 128, true, true);   // dO^T * Qt (MN-major B)
+            if (warp == 0) {
 #pragma unroll
-            for (int s = 0; s < 4; ++s)
-                mma_ss(tmem0 + VACC, make_desc(sb + DO + s * 4096, 2048, 128), make_desc(sb + AQ + s * 2048, 1024, 128), id_v1,
-                       s > 0);
+                for (int s = 0; s < 4; ++s)
+                    mma_ss(tmem0 + VACC, make_desc(sb + DO + s * 4096, 2048, 128), make_desc(sb + AQ + s * 2048, 1024, 128), id_v1,
+                           s > 0);
 #pragma unroll
-            for (int s = 0; s < 8; ++s)
-                mma_ts(tmem0 + VACC, tmem0 + SBF + s * 8, make_desc(sb + KH + s * 256, 128, 2048), id_v2, true);
+                for (int s = 0; s < 8; ++s)
+                    mma_ts(tmem0 + VACC, tmem0 + SBF + s * 8, make_desc(sb + KH + s * 256, 128, 2048), id_v2, true);
+            } else {
 #pragma unroll
-            for (int s = 0; s < 4; ++s)
-                mma_ss(tmem0 + SACC, make_desc(sb + DO + s * 4096, 2048, 128), make_desc(sb + QT + s * 4096, 2048, 128), id_s1,
-                       true);
+                for (int s = 0; s < 4; ++s)
+                    mma_ss(tmem0 + SACC, make_desc(sb + DO + s * 4096, 2048, 128), make_desc(sb + QT + s * 4096, 2048, 128), id_s1,
+                           true);
+            }
             mma_commit(&mmabar);
         }
-        ok = mbar_wait(&mmabar, mma_phase, p.status, 4);
-        mma_phase ^= 1;
+        ok = mbar_wait(&mmabar, k & 1, p.status, 4);
         tc_fence_after();
         if (!__syncthreads_and(ok)) { ok = false; break; }
 
@@ -533,10 +542,9 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
 #pragma unroll
             for (int s = 0; s < 4; ++s)
                 mma_ts(tmem0 + SACC, tmem0 + VBF + s * 8, make_desc(sb + WT + s * 256, 128, 1024), id_w, true);
-            mma_commit(&mmabar);
+            mma_commit(&mmabar2);
         }
-        ok = mbar_wait(&mmabar, mma_phase, p.status, 4);
-        mma_phase ^= 1;
+        ok = mbar_wait(&mmabar2, k & 1, p.status, 4);
         tc_fence_after();
         if (!__syncthreads_and(ok)) { ok = false; break; }
     }

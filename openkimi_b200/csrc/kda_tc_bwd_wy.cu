@@ -65,7 +65,7 @@ template <bool CONVB>
 __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, const __grid_constant__ RowMaps maps) {
     using namespace bw;
     extern __shared__ __align__(128) unsigned char dyn[];
-    __shared__ uint64_t full, mmabar;
+    __shared__ uint64_t full, mma1, mma2, mma3;
     __shared__ uint32_t tmem_s;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
@@ -84,7 +84,9 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
     }
     if (tid == 0) {
         mbar_init(&full, 1);
-        mbar_init(&mmabar, 1);
+        mbar_init(&mma1, 5);  // one issuing thread per accumulator: a single thread spends ~50 ns on every MMA it issues
+        mbar_init(&mma2, 2);
+        mbar_init(&mma3, 2);
         mbar_fence_init();
     }
     tc_fence_before();
@@ -100,7 +102,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
     // are set up once.  Unit u = (chunk u / H, head (u + chunk) % H), so that the units of one CTA cycle through
     // all heads whatever the stride.
     const int n_units = p.NT * p.H;
-    uint32_t it = 0, mph = 0;
+    uint32_t it = 0;
     for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
     const int c = unit / p.H, h = (unit % p.H + c) % p.H;
     const ChunkInfo ci = chunk_info(p, c);
@@ -152,29 +154,35 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
     ok = __syncthreads_and(ok);
     KDA_PHASE(1);
 
-    // ---- S1
-    if (tid == 0 && ok) {
+    // ---- S1: lane 0 of warps 0..4 issues the product of one accumulator each
+    if (lane == 0 && warp < 5 && ok) {
         tc_fence_after();
         constexpr uint32_t id_aqk = make_idesc(64, 64, false, true);
         constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
         constexpr uint32_t id_mk = make_idesc(128, 64, true, false);
         constexpr uint32_t id_km = make_idesc(128, 64, false, true);
+        if (warp == 0) {
 #pragma unroll
-        for (int s = 0; s < 8; ++s)  // dAqk = dO (K-major) * V' (MN-major view of V'^T)
-            mma_ss(tmem0 + DAQK, make_desc(sb + DOT + s * 256, 128, 2048), make_desc(sb + VT + s * 2048, 1024, 128), id_aqk, s > 0);
+            for (int s = 0; s < 8; ++s)  // dAqk = dO (K-major) * V' (MN-major view of V'^T)
+                mma_ss(tmem0 + DAQK, make_desc(sb + DOT + s * 256, 128, 2048), make_desc(sb + VT + s * 2048, 1024, 128), id_aqk, s > 0);
+        } else if (warp == 1) {
 #pragma unroll
-        for (int s = 0; s < 8; ++s)  // dWn^T = S0 (MN-major view of S0^T) * dV'^T (MN-major)
-            mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DVT + s * 2048, 1024, 128), id_mm, s > 0);
+            for (int s = 0; s < 8; ++s)  // dWn^T = S0 (MN-major view of S0^T) * dV'^T (MN-major)
+                mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DVT + s * 2048, 1024, 128), id_mm, s > 0);
+        } else if (warp == 2) {
 #pragma unroll
-        for (int s = 0; s < 8; ++s)  // dQt^T = S0 * dO^T (K-major, rows = i)
-            mma_ss(tmem0 + DQT, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 256, 128, 2048), id_mk, s > 0);
+            for (int s = 0; s < 8; ++s)  // dQt^T = S0 * dO^T (K-major, rows = i)
+                mma_ss(tmem0 + DQT, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 256, 128, 2048), id_mk, s > 0);
+        } else if (warp == 3) {
 #pragma unroll
-        for (int s = 0; s < 8; ++s)  // dKh^T = dS * V'^T
-            mma_ss(tmem0 + DKH, make_desc(sb + DST + s * 4096, 2048, 128), make_desc(sb + VT + s * 2048, 1024, 128), id_mm, s > 0);
+            for (int s = 0; s < 8; ++s)  // dKh^T = dS * V'^T
+                mma_ss(tmem0 + DKH, make_desc(sb + DST + s * 4096, 2048, 128), make_desc(sb + VT + s * 2048, 1024, 128), id_mm, s > 0);
+        } else {
 #pragma unroll
-        for (int s = 0; s < 4; ++s)  // dVb^T = dV'^T (K-major, rows = e) * T (MN-major, rows = j)
-            mma_ss(tmem0 + DVB, make_desc(sb + DVT + s * 256, 128, 1024), make_desc(sb + TT + s * 2048, 1024, 128), id_km, s > 0);
-        mma_commit(&mmabar);
+            for (int s = 0; s < 4; ++s)  // dVb^T = dV'^T (K-major, rows = e) * T (MN-major, rows = j)
+                mma_ss(tmem0 + DVB, make_desc(sb + DVT + s * 256, 128, 1024), make_desc(sb + TT + s * 2048, 1024, 128), id_km, s > 0);
+        }
+        mma_commit(&mma1);
     }
     {   // while the first MMA group runs:
         // dGamma_C[d] = sum_e dS[d][e] S0[d][e].  Both records are cm(e, d; 128): a warp reads, for one
@@ -205,8 +213,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
             for (int j = 0; j < 8; ++j) spart[128 * eh + d8 + j] = acc[j];
         }
         }
-    ok = ok && mbar_wait(&mmabar, mph, p.status, 32);
-    mph ^= 1;
+    ok = ok && mbar_wait(&mma1, it & 1, p.status, 32);
     tc_fence_after();
     ok = __syncthreads_and(ok);  // every warp is done reading dS: its tile becomes the staging area of dQt
     KDA_PHASE(2);
@@ -294,19 +301,22 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
     }
     KDA_PHASE(3);
 
-    // ---- S2
-    if (tid == 0 && ok) {
+    // ---- S2: two issuing threads (the products into dWn form one chain)
+    if (lane == 0 && warp < 2 && ok) {
         tc_fence_after();
         constexpr uint32_t id_neg = make_idesc(128, 64, false, true, true);  // -WBF (TMEM) * T (MN-major)
         constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
+        if (warp == 0) {
 #pragma unroll
-        for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DKB, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
+            for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DKB, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
+        } else {
 #pragma unroll
-        for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DWN, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
+            for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DWN, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
 #pragma unroll
-        for (int s = 0; s < 8; ++s)  // Z^T += S0 * dVb^T (MN-major B from cm(e, i; 64))
-            mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 2048, 1024, 128), id_mm, true);
-        mma_commit(&mmabar);
+            for (int s = 0; s < 8; ++s)  // Z^T += S0 * dVb^T (MN-major B from cm(e, i; 64))
+                mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 2048, 1024, 128), id_mm, true);
+        }
+        mma_commit(&mma2);
     }
     if constexpr (CONVB) {
         // meanwhile: backward of the short convolution of v.  dv (BF16, as the unfused path would store it) is
@@ -359,8 +369,7 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
         }
     }
     KDA_PHASE(4);
-    ok = ok && mbar_wait(&mmabar, mph, p.status, 32);
-    mph ^= 1;
+    ok = ok && mbar_wait(&mma2, it & 1, p.status, 32);
     tc_fence_after();
     ok = __syncthreads_and(ok);
     KDA_PHASE(5);
@@ -397,20 +406,22 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
     }
     KDA_PHASE(6);
 
-    // ---- S3
-    if (tid == 0 && ok) {
+    // ---- S3: the two products of dMn go to two accumulators (the second one where dAqk was), one issuing thread each
+    if (lane == 0 && warp < 2 && ok) {
         tc_fence_after();
         constexpr uint32_t id = make_idesc(64, 64, true, true);
+        if (warp == 0) {
 #pragma unroll
-        for (int s = 0; s < 8; ++s)  // Z (MN-major view of Z^T) * W^T (MN-major view of the W^T record)
-            mma_ss(tmem0 + DMN, make_desc(sb + DVT + s * 2048, 1024, 128), make_desc(sb + WT + s * 2048, 1024, 128), id, s > 0);
+            for (int s = 0; s < 8; ++s)  // Z (MN-major view of Z^T) * W^T (MN-major view of the W^T record)
+                mma_ss(tmem0 + DMN, make_desc(sb + DVT + s * 2048, 1024, 128), make_desc(sb + WT + s * 2048, 1024, 128), id, s > 0);
+        } else {
 #pragma unroll
-        for (int s = 0; s < 8; ++s)  // dVb * V'^T
-            mma_ss(tmem0 + DMN, make_desc(sb + DOT + s * 2048, 1024, 128), make_desc(sb + VT + s * 2048, 1024, 128), id, true);
-        mma_commit(&mmabar);
+            for (int s = 0; s < 8; ++s)  // dVb * V'^T
+                mma_ss(tmem0 + DAQK, make_desc(sb + DOT + s * 2048, 1024, 128), make_desc(sb + VT + s * 2048, 1024, 128), id, s > 0);
+        }
+        mma_commit(&mma3);
     }
-    ok = ok && mbar_wait(&mmabar, mph, p.status, 32);
-    mph ^= 1;
+    ok = ok && mbar_wait(&mma3, it & 1, p.status, 32);
     tc_fence_after();
     KDA_PHASE(7);
     if (ok) {
@@ -418,13 +429,14 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
         const int i = 16 * (warp & 3) + (lane & 15);
         {
             const int j0 = 16 * qtr;
-            uint32_t r[16];
+            uint32_t r[16], r2[16];
             tmem_ld16(tmem + DMN + j0, r);
+            tmem_ld16(tmem + DAQK + j0, r2);
             tmem_wait_ld();
             if (lane < 16) {
                 float f[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) f[j] = (j0 + j < i) ? -__uint_as_float(r[j]) : 0.f;
+                for (int j = 0; j < 16; ++j) f[j] = (j0 + j < i) ? -(__uint_as_float(r[j]) + __uint_as_float(r2[j])) : 0.f;
                 store_split_row(gMM, i, j0, f);
             }
         }

@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     }
     if (tid == 0) {
         mbar_init(&bar, 3);   // three issuing threads commit the off-diagonal products
-        mbar_init(&bar2, 1);
+        mbar_init(&bar2, 2);  // two issuing threads commit the W and U products
         mbar_init(&rowbar, 1);
         mbar_init(&gatebar, 1);
         mbar_fence_init();
@@ -734,17 +734,15 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     tc_fence_before();
     __syncthreads();
     KDA_PHASE(7);
-    // ---- 5: W^T and U^T
-    if (tid == 0) {
+    // ---- 5: W^T and U^T (one issuing thread each)
+    if (lane == 0 && warp < 2) {
         tc_fence_after();
         const uint32_t sb = smem_u32(dyn);
         constexpr uint32_t id = make_idesc(128, 64, true, false);
+        const uint32_t acc = warp == 0 ? T_W : T_U, a_tile = warp == 0 ? KB : BV;
 #pragma unroll
         for (int s = 0; s < 4; ++s)
-            mma_ss(tmem0 + T_W, make_desc(sb + KB + s * 4096, 2048, 128), make_desc(sb + KSC + s * 256, 128, 1024), id, s > 0);
-#pragma unroll
-        for (int s = 0; s < 4; ++s)
-            mma_ss(tmem0 + T_U, make_desc(sb + BV + s * 4096, 2048, 128), make_desc(sb + KSC + s * 256, 128, 1024), id, s > 0);
+            mma_ss(tmem0 + acc, make_desc(sb + a_tile + s * 4096, 2048, 128), make_desc(sb + KSC + s * 256, 128, 1024), id, s > 0);
         mma_commit(&bar2);
     }
     if (tid < D) gGam[tid] = ex2_approx(sG[swz_f32(C - 1, tid)]);

@@ -44,7 +44,11 @@ enum {
      * forward the reference replays under activation checkpointing (k3mini/model.py:825-831) and
      * the first forward of the recompute policy (disable_recompute = False, k3mini/model.py:215);
      * o and the final state are bit-identical to the saving forward.  kda_bwd rejects the flag. */
-    KDA_FLAG_NO_SAVE = 1024
+    KDA_FLAG_NO_SAVE = 1024,
+    /* Move the [64 x 128] tiles of the token-major tensors (q, k, v, g in, o and dv out) row by row instead of
+     * with one bulk-tensor copy per tile.  Same bytes either way; the library falls back to this by itself
+     * where the driver's tensor-map encoder is not available, and uses it for partial chunks. */
+    KDA_FLAG_ROW_COPIES = 2048
 };
 
 enum {

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_PKG, "libkda_b200.so")
 DTYPE_F32, DTYPE_BF16 = 0, 1
 FLAG_QK_L2NORM, FLAG_GATE, FLAG_BETA_SIGMOID, FLAG_STATE_V_FIRST, FLAG_FORCE_SIMT = 1, 2, 4, 8, 16
 FLAG_NO_SAVE = 1024
+FLAG_ROW_COPIES = 2048
 CHUNK = 64
 ERR_DEVICE_WAIT = 7
 

@@ -586,7 +586,7 @@ cudaError_t tc_fwd(const KdaParams& p, cudaStream_t s) {
         if ((e = cudaFuncSetAttribute(kda_fwd_state_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return e;
         RowMaps maps = {};
-        maps.ok = make_row_map(&maps.m[0], p.o, (long long)p.B * p.T, p.H, C);
+        maps.ok = !(p.flags & KDA_FLAG_ROW_COPIES) && make_row_map(&maps.m[0], p.o, (long long)p.B * p.T, p.H, C);
         kda_fwd_state_tc<<<dim3(p.H, p.N), fs::NTHR, smem, s>>>(p, maps);
     }
     prof_mark(s);

@@ -460,7 +460,7 @@ cudaError_t launch_bwd_wy_tc(const KdaParams& p, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     RowMaps maps = {};
-    maps.ok = make_row_map(&maps.m[0], p.grad_v, (long long)p.B * p.T, p.H, C);
+    maps.ok = !(p.flags & KDA_FLAG_ROW_COPIES) && make_row_map(&maps.m[0], p.grad_v, (long long)p.B * p.T, p.H, C);
     const int units = p.NT * p.H, sms = sm_count();
     kern<<<units < sms ? units : sms, bw::NTHR, smem, s>>>(p, maps);
     return cudaGetLastError();

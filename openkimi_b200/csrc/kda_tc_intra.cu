@@ -793,7 +793,7 @@ cudaError_t launch_fwd_intra_tc(const KdaParams& p, cudaStream_t s) {
     const int units = p.NT * p.H, sms = sm_count();
     RowMaps maps = {};
     const long long tokens = (long long)p.B * p.T;
-    maps.ok = make_row_map(&maps.m[0], p.q, tokens, p.H, C) && make_row_map(&maps.m[1], p.k, tokens, p.H, C) &&
+    maps.ok = !(p.flags & KDA_FLAG_ROW_COPIES) && make_row_map(&maps.m[0], p.q, tokens, p.H, C) && make_row_map(&maps.m[1], p.k, tokens, p.H, C) &&
               make_row_map(&maps.m[2], p.v, tokens, p.H, C) && make_row_map(&maps.m[3], p.g, tokens, p.H, C);
     kern<<<units < sms ? units : sms, fi::NTHR, fi::TOTAL, s>>>(p, maps);
     return cudaGetLastError();

@@ -346,6 +346,8 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         _warn_once(f"OPENKIMI_B200_FP32_STAGES={stage_mask}: the selected KDA stages run the FP32 CUDA-core "
                    "validation kernels instead of the tensor-core kernels (debugging switch, much slower)")
     flags |= stage_mask << 5
+    if os.environ.get("OPENKIMI_B200_ROW_COPIES") == "1":  # A-B switch: row copies instead of bulk-tensor tile copies
+        flags |= _lib.FLAG_ROW_COPIES
     conv = (None, None, None)
     if short_conv_weights is not None:
         wq, wk, wv = short_conv_weights

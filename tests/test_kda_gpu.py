@@ -226,3 +226,19 @@ def test_forward_only_call_matches_the_saving_forward_bitwise(dtype, d):
         assert torch.equal(o0, o1) and torch.equal(s0, s1)
         o1.float().sum().backward()   # the saving forward still feeds a working backward
         assert all(torch.isfinite(x.grad.float()).all() for x in leaves)
+
+
+@pytest.mark.parametrize("varlen", [False, True])
+def test_tile_copies_move_the_same_bytes_as_row_copies(varlen, monkeypatch):
+    """The q / k / v / gate tiles of full chunks arrive (and the o / dv tiles leave) with one bulk-tensor copy
+    through a tensor map; partial chunks, and KDA_FLAG_ROW_COPIES, move the same rows one by one.  Both ways
+    must give the same bits, packed sequences whose chunks start at odd token offsets included."""
+    inp = O.make_inputs(1 if varlen else 2, 1024 if varlen else 320, 2, 128, seed=52, dtype=torch.bfloat16)
+    cu = O.random_cu_seqlens(1024, 5, seed=3) if varlen else None
+    h0, dht = (None, None) if varlen else _states(2, 2, 128)
+    a = run_device(inp, h0=h0, dht=dht, cu=cu)
+    monkeypatch.setenv("OPENKIMI_B200_ROW_COPIES", "1")
+    b = run_device(inp, h0=h0, dht=dht, cu=cu)
+    for name in a:
+        if isinstance(a[name], torch.Tensor):
+            assert torch.equal(a[name], b[name]), name

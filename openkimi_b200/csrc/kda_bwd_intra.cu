@@ -401,23 +401,32 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         // ---- assembly of my block, last row first; a1[r] is reused for the running sum of dG
         {
             float acc = 0.f, tail = 0.f;
+            // my 16 rows of the three hand-over arrays (channel-major, handover_idx): eight rows = one 16-byte word
 #pragma unroll
-            for (int r = B - 1; r >= 0; --r) {
-                const int ii = b0 + r;
-                const float qi = __bfloat162float(sQ[swz_bf16(ii, d)]), ki = __bfloat162float(sK[swz_bf16(ii, d)]);
-                const float bi_ = sbeta[ii];
-                const float gam = ex2_approx(G[r]), eta = ex2_approx(gl - G[r]);
-                const float dQt = __bfloat162float(spf[ii * D + d]), dKh = __bfloat162float(spf[(C + ii) * D + d]),
-                            dKb = __bfloat162float(spf[(2 * C + ii) * D + d]);
-                const float diag = scale * sdiag[ii];
-                const float dq_in = scale * a1[r], dk_row = bi_ * a2[r], dKt = bi_ * dKb;
-                stg[(0 * C + ii) * D + d] = dq_in + diag * ki + scale * dQt * gam;
-                stg[(1 * C + ii) * D + d] = dk_row + c1[r] + diag * qi + dKt * gam + dKh * eta;
-                stg[(2 * C + ii) * D + d] = ki * a2[r] + dKb * (ki * gam);
-                const float khe = dKh * (ki * eta);
-                tail += khe;  // the last row also collects sum_i dKh_i Kh_i
-                acc += qi * dq_in + ki * dk_row - ki * c1[r] + dQt * (scale * qi * gam) + dKt * (ki * gam) - khe;
-                a1[r] = acc;
+            for (int hf = 1; hf >= 0; --hf) {
+                const int o = handover_idx(b0 + 8 * hf, d);
+                const uint4 uq = *reinterpret_cast<const uint4*>(spf + o), ukh = *reinterpret_cast<const uint4*>(spf + C * D + o),
+                            ukb = *reinterpret_cast<const uint4*>(spf + 2 * C * D + o);
+                const __nv_bfloat16* hq = reinterpret_cast<const __nv_bfloat16*>(&uq);
+                const __nv_bfloat16* hkh = reinterpret_cast<const __nv_bfloat16*>(&ukh);
+                const __nv_bfloat16* hkb = reinterpret_cast<const __nv_bfloat16*>(&ukb);
+#pragma unroll
+                for (int r8 = 7; r8 >= 0; --r8) {
+                    const int r = 8 * hf + r8, ii = b0 + r;
+                    const float qi = __bfloat162float(sQ[swz_bf16(ii, d)]), ki = __bfloat162float(sK[swz_bf16(ii, d)]);
+                    const float bi_ = sbeta[ii];
+                    const float gam = ex2_approx(G[r]), eta = ex2_approx(gl - G[r]);
+                    const float dQt = __bfloat162float(hq[r8]), dKh = __bfloat162float(hkh[r8]), dKb = __bfloat162float(hkb[r8]);
+                    const float diag = scale * sdiag[ii];
+                    const float dq_in = scale * a1[r], dk_row = bi_ * a2[r], dKt = bi_ * dKb;
+                    stg[(0 * C + ii) * D + d] = dq_in + diag * ki + scale * dQt * gam;
+                    stg[(1 * C + ii) * D + d] = dk_row + c1[r] + diag * qi + dKt * gam + dKh * eta;
+                    stg[(2 * C + ii) * D + d] = ki * a2[r] + dKb * (ki * gam);
+                    const float khe = dKh * (ki * eta);
+                    tail += khe;  // the last row also collects sum_i dKh_i Kh_i
+                    acc += qi * dq_in + ki * dk_row - ki * c1[r] + dQt * (scale * qi * gam) + dKt * (ki * gam) - khe;
+                    a1[r] = acc;
+                }
             }
             stot[blk * D + d] = acc;
             sscr[blk * D + d] = tail;

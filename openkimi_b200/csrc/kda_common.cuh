@@ -32,6 +32,12 @@ inline int sm_count() {
     return n;
 }
 
+// Hand-over arrays dQt / dKh / dKb of the backward (BF16, 64 rows x 128 channels per unit): channel-major, so
+// that the thread that owns a channel writes and reads 16 consecutive rows as two 16-byte words; the eight
+// 16-byte chunks of a channel are XOR-swizzled by the channel, which makes the shared-memory reads of eight
+// neighbouring channels hit eight different bank groups.
+__host__ __device__ inline int handover_idx(int i, int d) { return d * 64 + ((((i >> 3) ^ (d & 7)) << 3) | (i & 7)); }
+
 // ---------------------------------------------------------------------------------------
 // element access
 // ---------------------------------------------------------------------------------------

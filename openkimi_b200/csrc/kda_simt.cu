@@ -623,7 +623,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
             for (int cc = 0; cc < D / 16; ++cc) {
                 int i = ty + 16 * r, d = tx + 16 * cc;
                 if constexpr (SPLIT) {
-                    stf((T*)(sc + L.dKb) + (rec * C + i) * D + d, acc[r][cc]);
+                    stf((T*)(sc + L.dKb) + rec * C * D + handover_idx(i, d), acc[r][cc]);
                     continue;
                 }
                 float gam = exp2f(sG[i * D + d]);
@@ -664,7 +664,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
             for (int cc = 0; cc < D / 16; ++cc) {
                 int i = ty + 16 * r, d = tx + 16 * cc;
                 if constexpr (SPLIT) {
-                    stf((T*)(sc + L.dQt) + (rec * C + i) * D + d, acc[r][cc]);
+                    stf((T*)(sc + L.dQt) + rec * C * D + handover_idx(i, d), acc[r][cc]);
                     continue;
                 }
                 float gam = exp2f(sG[i * D + d]);
@@ -684,7 +684,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) kda_bwd_chunk_simt(const KdaParam
             for (int cc = 0; cc < D / 16; ++cc) {
                 int i = ty + 16 * r, d = tx + 16 * cc;
                 if constexpr (SPLIT) {
-                    stf((T*)(sc + L.dKh) + (rec * C + i) * D + d, acc[r][cc]);
+                    stf((T*)(sc + L.dKh) + rec * C * D + handover_idx(i, d), acc[r][cc]);
                     sW[i * D + d] = 0.f;
                     continue;
                 }

@@ -501,7 +501,7 @@ __device__ __forceinline__ float warp_sum16(const float (&v)[16], int lane, int&
     return a1;
 }
 
-__global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_pf(const KdaParams p, const __grid_constant__ RowMaps maps) {
+__global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams p, const __grid_constant__ RowMaps maps) {
     using namespace bp;
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ uint64_t fullA[2], fullS, fullD, fullW, mma1, mma2, mma3;
@@ -888,8 +888,8 @@ cudaError_t launch_bwd_wy_tc(const KdaParams& p, cudaStream_t s) {
     maps.ok = !(p.flags & KDA_FLAG_ROW_COPIES) && make_row_map(&maps.m[0], p.grad_v, (long long)p.B * p.T, p.H, C);
     cudaError_t e;
     if (!convb) {
-        if ((e = cudaFuncSetAttribute(kda_bwd_wy_pf, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bp::TOTAL)) != cudaSuccess) return e;
-        kda_bwd_wy_pf<<<units < sms ? units : sms, bp::NTHR, bp::TOTAL, s>>>(p, maps);
+        if ((e = cudaFuncSetAttribute(kda_bwd_wy_tc_pf, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bp::TOTAL)) != cudaSuccess) return e;
+        kda_bwd_wy_tc_pf<<<units < sms ? units : sms, bp::NTHR, bp::TOTAL, s>>>(p, maps);
         return cudaGetLastError();
     }
     auto kern = kda_bwd_wy_tc<true>;

@@ -150,9 +150,11 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     // all heads whatever the stride (heads differ in cost: rejected tiles take the exact path).
     const int n_units = p.NT * p.H;
     uint32_t it = 0;
-    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
+    UnitWalk uw;
+    uw.init(blockIdx.x, gridDim.x, p.H);
+    for (; uw.unit < n_units; uw.next(), ++it) {
     const uint32_t par = it & 1;
-    const int c = unit / p.H, hd = (unit % p.H + c) % p.H;
+    const int c = uw.c, hd = uw.head();
     const ChunkInfo ci = chunk_info(p, c);
     const size_t rec = (size_t)c * p.H + hd;
     const float expA = gate ? expf(p.A_log[hd]) : 1.f;  // requested at the start of the unit: used only in the gate chain at the end

@@ -32,6 +32,26 @@ inline int sm_count() {
     return n;
 }
 
+// The units a CTA of a unit-walking kernel visits: first, first + stride, ...  Unit u is chunk u / H with
+// the head skewed by the chunk, (u % H + chunk) % H, so that the units of one CTA cycle through all heads
+// whatever the stride (heads differ in cost).  Stepping costs additions only: the integer divisions, which
+// are long dependent instruction chains, happen once per kernel.
+struct UnitWalk {
+    int unit, c, r, cm, stride, dq, dr, dqm, H;
+    __device__ __forceinline__ void init(int first, int stride_, int H_) {
+        H = H_; stride = stride_; unit = first;
+        c = first / H; r = first - c * H; cm = c % H;
+        dq = stride / H; dr = stride - dq * H; dqm = dq % H;
+    }
+    __device__ __forceinline__ int head() const { const int h = r + cm; return h >= H ? h - H : h; }
+    __device__ __forceinline__ size_t rec() const { return (size_t)c * H + head(); }  // index of the unit's records
+    __device__ __forceinline__ void next() {
+        unit += stride; c += dq; r += dr; cm += dqm;
+        if (r >= H) { r -= H; ++c; ++cm; }
+        if (cm >= H) cm -= H;
+    }
+};
+
 // Hand-over arrays dQt / dKh / dKb of the backward (BF16, 64 rows x 128 channels per unit): channel-major, so
 // that the thread that owns a channel writes and reads 16 consecutive rows as two 16-byte words; the eight
 // 16-byte chunks of a channel are XOR-swizzled by the channel, which makes the shared-memory reads of eight
@@ -92,6 +112,28 @@ __device__ __forceinline__ void seq_chunks(const KdaParams& p, int n, int& c0, i
         nc = (p.T + C - 1) / C;
         c0 = n * nc;
     }
+}
+
+// first and one-past-last flattened token index of sequence n; chunk lc of the sequence then starts at
+// first + lc * C and holds min(C, end - start) rows (what chunk_info returns, without its division / table load:
+// for the kernels that walk the chunks of ONE sequence)
+__device__ __forceinline__ void seq_tokens(const KdaParams& p, int n, long long& first, long long& end) {
+    if (p.cu_seqlens != nullptr) {
+        first = p.cu_seqlens[n];
+        end = p.cu_seqlens[n + 1];
+    } else {
+        first = (long long)n * p.T;
+        end = first + p.T;
+    }
+}
+__device__ __forceinline__ ChunkInfo chunk_of_seq(int n, int lc, long long first, long long end) {
+    ChunkInfo ci;
+    ci.seq = n;
+    ci.lc = lc;
+    ci.tok0 = first + (long long)lc * C;
+    const long long rem = end - ci.tok0;
+    ci.len = rem < C ? (int)rem : C;
+    return ci;
 }
 
 // ---------------------------------------------------------------------------------------

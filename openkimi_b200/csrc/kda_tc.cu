@@ -177,6 +177,8 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
     const int h = blockIdx.x, n = blockIdx.y;
     int c0, nc;
     seq_chunks(p, n, c0, nc);
+    long long tok_first, tok_end;
+    seq_tokens(p, n, tok_first, tok_end);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     char* ws = (char*)p.workspace;
     if (warp == 0) {
@@ -226,7 +228,7 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
     for (int lc = 0; lc < nc; ++lc) {
         const int stage = lc & 1;
         unsigned char* b = dyn + stage * STAGE;
-        const ChunkInfo ci = chunk_info(p, c0 + lc);
+        const ChunkInfo ci = chunk_of_seq(n, lc, tok_first, tok_end);
         const size_t rec = (size_t)(c0 + lc) * p.H + h;
         tma_store_wait_read();  // the previous chunk's output rows have left the staging tile
         ok = mbar_wait(&full[stage], (lc >> 1) & 1, p.status, 2);
@@ -402,6 +404,8 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
     const int h = blockIdx.x, n = blockIdx.y;
     int c0, nc;
     seq_chunks(p, n, c0, nc);
+    long long tok_first, tok_end;
+    seq_tokens(p, n, tok_first, tok_end);
     const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
     const char* ws = (const char*)p.workspace;
     char* sc = (char*)p.bwd_scratch;
@@ -446,7 +450,7 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
             tma_load_1d(b + GAM, (const float*)(ws + L.gamC) + rec * D, 512, &full[stage]);
         }
         // dO tile -> core-matrix layout cm(i, e; 128), 16-byte chunks, zero rows past the end
-        const ChunkInfo ci = chunk_info(p, c0 + lc);
+        const ChunkInfo ci = chunk_of_seq(n, lc, tok_first, tok_end);
         __nv_bfloat16* sdo = reinterpret_cast<__nv_bfloat16*>(b + DO);
         for (int q = tid; q < C * (D / 8); q += NTHR) {
             const int i = q >> 4, e8 = (q & 15) * 8;

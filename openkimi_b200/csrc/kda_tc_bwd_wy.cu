@@ -113,8 +113,10 @@ __global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, 
     // all heads whatever the stride.
     const int n_units = p.NT * p.H;
     uint32_t it = 0;
-    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
-    const int c = unit / p.H, h = (unit % p.H + c) % p.H;
+    UnitWalk uw;
+    uw.init(blockIdx.x, gridDim.x, p.H);
+    for (; uw.unit < n_units; uw.next(), ++it) {
+    const int c = uw.c, h = uw.head();
     const ChunkInfo ci = chunk_info(p, c);
     const size_t rec = (size_t)c * p.H + h;
     // with the short convolution fused into the forward, p.v is the pre-convolution projection and
@@ -541,7 +543,6 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
     const uint32_t sb = smem_u32(dyn);
 
     const int n_units = p.NT * p.H;
-    auto unit_rec = [&](int u) { return (size_t)(u / p.H) * p.H + (u % p.H + u / p.H) % p.H; };  // (chunk, skewed head)
     auto request_set = [&](size_t r, int set) {  // V'^T and dV'^T of unit record r (one thread)
         mbar_expect_tx(&fullA[set], 2 * 16384);
         tma_load_1d(dyn + VT + set * 16384, (const __nv_bfloat16*)(ws + L.U) + r * C * D, 16384, &fullA[set]);
@@ -556,9 +557,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
         mbar_expect_tx(&fullD, 32768);
         tma_load_1d(dyn + DST, (const __nv_bfloat16*)(sc + L.dS) + r * D * D, 32768, &fullD);
     };
-    auto request_dO = [&](int u, int set) {  // dO rows of unit u into core-matrix layout (all threads; one cp.async group)
-        const int cu = u / p.H, hu = (u % p.H + cu) % p.H;
-        const ChunkInfo cn = chunk_info(p, cu);
+    auto request_dO = [&](const ChunkInfo& cn, int hu, int set) {  // dO rows of a unit into core-matrix layout (all threads; one cp.async group)
         __nv_bfloat16* sdo = reinterpret_cast<__nv_bfloat16*>(dyn + DOT + set * 16384);
         for (int qq = tid; qq < C * (D / 8); qq += NTHR) {
             const int i = qq >> 4, e8 = (qq & 15) * 8;
@@ -570,14 +569,18 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
     uint32_t it = 0;
     float beta_nx = 0.f;
     bool ok = true, ahead = false, early = false;  // copies for the next unit are in flight
-    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
+    UnitWalk uw;
+    uw.init(blockIdx.x, gridDim.x, p.H);
+    ChunkInfo ci = chunk_info(p, uw.c);
+    for (; uw.unit < n_units; uw.next(), ++it) {
     const int set = it & 1;
     const uint32_t par = it & 1;
-    const int c = unit / p.H, h = (unit % p.H + c) % p.H;
-    const ChunkInfo ci = chunk_info(p, c);
+    const int c = uw.c, h = uw.head();
     const size_t rec = (size_t)c * p.H + h;
-    const int unit_nx = unit + gridDim.x;
-    const bool more = unit_nx < n_units;
+    UnitWalk un = uw;  // the next unit of this CTA
+    un.next();
+    const bool more = un.unit < n_units;
+    ChunkInfo ci_nx = ci;
     ahead = early = false;
     // with the short convolution fused into the forward, p.v is the pre-convolution projection and
     // the convolved rows come from the forward's record
@@ -597,7 +600,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
         tma_load_1d(dyn + WT, (const __nv_bfloat16*)(ws + L.W) + rec * C * D, 16384, &fullW);
     }
     if (it == 0) {
-        request_dO(unit, 0);
+        request_dO(ci, h, 0);
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
     {
@@ -652,9 +655,10 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
     }
     // the next unit's V'^T, dV'^T and dO go to the other operand set (its last readers were the previous unit's MMAs)
     if (more && ok) {
-        if (tid == 5 * 32) request_set(unit_rec(unit_nx), set ^ 1);
-        request_dO(unit_nx, set ^ 1);
-        if (tid < C) beta_nx = ((const float*)(ws + L.aux))[unit_rec(unit_nx) * 3 * C + 2 * C + tid];  // (in a register until then)
+        ci_nx = chunk_info(p, un.c);
+        if (tid == 5 * 32) request_set(un.rec(), set ^ 1);
+        request_dO(ci_nx, un.head(), set ^ 1);
+        if (tid < C) beta_nx = ((const float*)(ws + L.aux))[un.rec() * 3 * C + 2 * C + tid];  // (in a register until then)
         ahead = true;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");  // (an empty group when there is no next unit: the waits below count groups)
@@ -797,7 +801,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
     tc_fence_after();
     ok = __syncthreads_and(ok);
     if (tid == 0 && more && ok) {  // S0 and T are dead: their tiles take the next unit's
-        request_state(unit_rec(unit_nx));
+        request_state(un.rec());
         early = true;
     }
     KDA_PHASE(5);
@@ -870,6 +874,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
     ok = __syncthreads_and(ok);
     KDA_PHASE(8);
     if (!ok) break;  // a wait gave up (recorded in the status word): no further unit is started
+    ci = ci_nx;
     }
     if (!ok) {  // the copies in flight for the next unit land before the CTA leaves
         if (ahead) mbar_wait(&fullA[(it + 1) & 1], ((it + 1) >> 1) & 1, p.status, 16);

@@ -145,7 +145,7 @@ template <bool CONV>
 __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams p, const __grid_constant__ RowMaps maps) {
     using namespace fi;
     extern __shared__ __align__(128) unsigned char dyn[];
-    __shared__ uint64_t bar, bar2, rowbar, gatebar;
+    __shared__ uint64_t bar, bar2, rowbar, vbar;
     __shared__ uint32_t tmem_s;
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dyn + SQ);
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(dyn + SK);
@@ -179,23 +179,27 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         mbar_init(&bar, 3);   // three issuing threads commit the off-diagonal products
         mbar_init(&bar2, 2);  // two issuing threads commit the W and U products
         mbar_init(&rowbar, 1);
-        mbar_init(&gatebar, 1);
+        mbar_init(&vbar, 1);
         mbar_fence_init();
     }
     __syncthreads();
 
-    // ---- 0: a unit's inputs arrive as 256-byte bulk copies, one per row, completing on two mbarriers.  The
-    //      CTA walks the units blockIdx.x, blockIdx.x + gridDim.x, ... and requests the inputs of its NEXT
-    //      unit while it still works on the current one, into space that is dead by then: the q, k, v rows
-    //      (ROWS each, three halo rows first when the convolution is fused) go to the operand space behind
-    //      the first key tile once the off-diagonal products have been read; the gate rows go to the L tile
-    //      once T is solved; the few scalars travel in registers.  Rows past the end of the sequence are
-    //      zero-filled by the thread that would have requested them.
+    // ---- 0: a unit's inputs arrive as bulk-tensor tile copies (row by row for partial chunks), completing on two
+    //      mbarriers.  The CTA walks the units blockIdx.x, blockIdx.x + gridDim.x, ... and requests the inputs of
+    //      its NEXT unit while it still works on the current one, into space that is dead by then: the gate, q and
+    //      k rows (q, k: ROWS each, three halo rows first when the convolution is fused; the halo rows of v too)
+    //      go to the operand space behind the first key tile once the off-diagonal products have been read, some
+    //      8 us ahead of their use; the v rows, which are needed last, go to the L tile once T is solved; the few
+    //      scalars travel in registers.  Rows past the end of the sequence are zero-filled by the thread that
+    //      would have requested them.
     constexpr int HALO = CONV ? 3 : 0, ROWS = C + HALO;
-    constexpr uint32_t RAW = KSC + 16384, TAPS = ST;
-    static_assert(RAW + 3 * ROWS * D * 2 <= KB, "staging overruns the operand space");
-    __nv_bfloat16* sRG = reinterpret_cast<__nv_bfloat16*>(dyn + SL);
-    __nv_bfloat16* sRaw = reinterpret_cast<__nv_bfloat16*>(dyn + RAW);
+    constexpr uint32_t RGATE = KSC + 16384, RQ = RGATE + C * D * 2, RK = RQ + ROWS * D * 2, RVH = RK + ROWS * D * 2, TAPS = ST;
+    static_assert(RVH + HALO * D * 2 <= KB, "staging overruns the operand space");
+    __nv_bfloat16* sRG = reinterpret_cast<__nv_bfloat16*>(dyn + RGATE);
+    __nv_bfloat16* sRq = reinterpret_cast<__nv_bfloat16*>(dyn + RQ);    // rows -HALO .. 63 of q
+    __nv_bfloat16* sRk = reinterpret_cast<__nv_bfloat16*>(dyn + RK);
+    __nv_bfloat16* sRvh = reinterpret_cast<__nv_bfloat16*>(dyn + RVH);  // rows -3 .. -1 of v (fused convolution only)
+    __nv_bfloat16* sRv = reinterpret_cast<__nv_bfloat16*>(dyn + SL);    // rows 0 .. 63 of v
     const int quarter = tid >> 7, dch = tid & 127;  // gate: thread = (16-row group, channel)
     const int hw = tid >> 4, c8 = (tid & 15) * 8;   // rows: half warp = row, lane = 8 channels
     auto zero_row = [&](__nv_bfloat16* dst) {
@@ -203,42 +207,40 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         for (int j = 0; j < 16; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(0, 0, 0, 0);
     };
     const bool tiles = maps.ok != 0;  // whole [64 x 128] tiles with one bulk-tensor copy each (full chunks only)
-    auto request_rows = [&](const ChunkInfo& ci, int h) {
+    auto row_src = [&](const __nv_bfloat16* base, const ChunkInfo& ci, int h, int i) { return base + ((size_t)(ci.tok0 + i) * p.H + h) * D; };
+    auto request_rows = [&](const ChunkInfo& ci, int h) {  // gate, q, k (and every halo row)
         if (tid == 0) mbar_expect_tx(&rowbar, (uint32_t)(3 * ci.len + ((CONV && ci.lc > 0) ? 9 : 0)) * 256u);
         if (tiles && ci.len == C) {
-            if (tid < 3) tma_load_tile(sRaw + (tid * ROWS + HALO) * D, &maps.m[tid], h * D, (int)ci.tok0, &rowbar);
-            if (CONV && (tid & 31) == 0 && tid >= 64 && tid < 64 + 9 * 32) {  // halo rows: one copy each from nine warps
-                const int t3 = (warp - 2) / 3, r = (warp - 2) % 3;
-                __nv_bfloat16* dst = sRaw + (t3 * ROWS + r) * D;
-                if (ci.lc > 0) tma_load_1d(dst, (t3 == 0 ? q : t3 == 1 ? k : v) + ((size_t)(ci.tok0 + r - 3) * p.H + h) * D, 256, &rowbar);
-                else zero_row(dst);
-            }
+            if (tid == 0) tma_load_tile(sRG, &maps.m[3], h * D, (int)ci.tok0, &rowbar);
+            if (tid == 1) tma_load_tile(sRq + HALO * D, &maps.m[0], h * D, (int)ci.tok0, &rowbar);
+            if (tid == 2) tma_load_tile(sRk + HALO * D, &maps.m[1], h * D, (int)ci.tok0, &rowbar);
         } else if (tid < 3 * C) {
             const int t3 = tid >> 6, i = tid & 63;
-            __nv_bfloat16* dst = sRaw + (t3 * ROWS + HALO + i) * D;
-            if (i < ci.len) tma_load_1d(dst, (t3 == 0 ? q : t3 == 1 ? k : v) + ((size_t)(ci.tok0 + i) * p.H + h) * D, 256, &rowbar);
+            __nv_bfloat16* dst = (t3 == 0 ? sRG : t3 == 1 ? sRq + HALO * D : sRk + HALO * D) + i * D;
+            if (i < ci.len) tma_load_1d(dst, row_src(t3 == 0 ? g : t3 == 1 ? q : k, ci, h, i), 256, &rowbar);
             else zero_row(dst);
-        } else if (CONV && tid < 3 * C + 9) {  // three rows before the chunk: they exist unless the chunk starts its sequence
-            const int t3 = (tid - 3 * C) / 3, r = (tid - 3 * C) % 3;
-            __nv_bfloat16* dst = sRaw + (t3 * ROWS + r) * D;
-            if (ci.lc > 0) tma_load_1d(dst, (t3 == 0 ? q : t3 == 1 ? k : v) + ((size_t)(ci.tok0 + r - 3) * p.H + h) * D, 256, &rowbar);
+        }
+        if (CONV && lane == 0 && warp >= 6 && warp < 15) {  // three rows before the chunk (one copy each from nine warps):
+            const int t3 = (warp - 6) / 3, r = (warp - 6) % 3;  // they exist unless the chunk starts its sequence
+            __nv_bfloat16* dst = (t3 == 0 ? sRq : t3 == 1 ? sRk : sRvh) + r * D;
+            if (ci.lc > 0) tma_load_1d(dst, row_src(t3 == 0 ? q : t3 == 1 ? k : v, ci, h, r - 3), 256, &rowbar);
             else zero_row(dst);
+        }
+    };
+    auto request_v = [&](const ChunkInfo& ci, int h) {
+        if (tid == 256) mbar_expect_tx(&vbar, (uint32_t)ci.len * 256u);
+        if (tiles && ci.len == C) {
+            if (tid == 256) tma_load_tile(sRv, &maps.m[2], h * D, (int)ci.tok0, &vbar);
+        } else if (tid >= 256 && tid < 256 + C) {
+            const int i = tid - 256;
+            if (i < ci.len) tma_load_1d(sRv + i * D, row_src(v, ci, h, i), 256, &vbar);
+            else zero_row(sRv + i * D);
         }
     };
     struct Scalars {  // (beta stays in its storage type: a conversion here would wait for the load)
         float a_log, bias;
         __nv_bfloat16 rb[2];
         float4 tap;
-    };
-    auto request_gate = [&](const ChunkInfo& ci, int h) {
-        if (tid == 256) mbar_expect_tx(&gatebar, (uint32_t)ci.len * 256u);
-        if (tiles && ci.len == C) {
-            if (tid == 256) tma_load_tile(sRG, &maps.m[3], h * D, (int)ci.tok0, &gatebar);
-        } else if (tid >= 256 && tid < 256 + C) {
-            const int i = tid - 256;
-            if (i < ci.len) tma_load_1d(sRG + i * D, g + ((size_t)(ci.tok0 + i) * p.H + h) * D, 256, &gatebar);
-            else zero_row(sRG + i * D);
-        }
     };
     auto request_scalars = [&](const ChunkInfo& ci, int h, Scalars& sc) {
         sc.a_log = gate ? p.A_log[h] : 0.f;
@@ -274,17 +276,18 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     // unit u = (chunk u / H, head (u + chunk) % H): the head is skewed by the chunk index so that the units a
     // CTA visits (stride gridDim.x) cycle through ALL heads even when the stride shares a factor with H
     // (heads differ in cost: the ones whose tiles fail the span guard take the exact path)
-    auto head_of = [&](int u) { return (u % p.H + u / p.H) % p.H; };
+    UnitWalk uw;
+    uw.init(blockIdx.x, gridDim.x, p.H);
     ChunkInfo ci = chunk_info(p, blockIdx.x / p.H);
-    request_rows(ci, head_of(blockIdx.x));
-    request_gate(ci, head_of(blockIdx.x));
-    request_scalars(ci, head_of(blockIdx.x), nx);
+    request_rows(ci, uw.head());
+    request_v(ci, uw.head());
+    request_scalars(ci, uw.head(), nx);
     park_taps(nx);
     __syncthreads();
     uint32_t it = 0;
     bool ok = true, more = false;
-    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
-    const int c = unit / p.H, h = head_of(unit);
+    for (; uw.unit < n_units; uw.next(), ++it) {
+    const int c = uw.c, h = uw.head();
     const size_t rec = (size_t)c * p.H + h;
     __nv_bfloat16* gW = (__nv_bfloat16*)(ws + L.W) + rec * C * D;
     __nv_bfloat16* gU = (__nv_bfloat16*)(ws + L.U) + rec * C * D;
@@ -293,15 +296,16 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     __nv_bfloat16* gKh = (__nv_bfloat16*)(ws + L.Kh) + rec * C * D;
     __nv_bfloat16* gT = (__nv_bfloat16*)(ws + L.Tm) + rec * C * C;
     float* gGam = (float*)(ws + L.gamC) + rec * D;
-    const int unit_nx = unit + gridDim.x;
-    more = unit_nx < n_units;
-    const ChunkInfo ci_nx = chunk_info(p, more ? unit_nx / p.H : c);
+    UnitWalk un = uw;  // the next unit of this CTA
+    un.next();
+    more = un.unit < n_units;
+    ChunkInfo ci_nx = ci;
     const float a_log_h = nx.a_log, bias = nx.bias;
     float rb[2];
 #pragma unroll
     for (int m = 0; m < 2; ++m)
         rb[m] = ((tid & 15) == 0 && (CONV ? 2 * hw + m : hw + 32 * m) < ci.len) ? __bfloat162float(nx.rb[m]) : 0.f;
-    ok = mbar_wait(&gatebar, it & 1, p.status, 8);
+    ok = mbar_wait(&rowbar, it & 1, p.status, 8);
     KDA_PHASE(13);
     // ---- 0a: gate, channel-wise: thread (quarter, d) owns rows 16*quarter .. 16*quarter+15 of channel d
     {
@@ -319,7 +323,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         stot[quarter * D + dch] = run;
     }
     KDA_PHASE(0);
-    ok = mbar_wait(&rowbar, it & 1, p.status, 8) && ok;
+    ok = mbar_wait(&vbar, it & 1, p.status, 8) && ok;
     KDA_PHASE(14);
     // Rows of a half warp: hw and hw + 32 without the convolution; 2 hw and 2 hw + 1 with it, so that
     // the five input rows 2 hw - 3 .. 2 hw + 1 serve the two outputs of one thread.
@@ -328,14 +332,18 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         // ---- 0c: y[i] = silu(sum_j tap[j] x[i - 3 + j]) for the thread's two rows, rounded to
         //      BF16 like the stand-alone convolution; the rest of the stage sees only y
         const float4* sW = reinterpret_cast<const float4*>(dyn + TAPS);
+        // row x of a tensor's window (x = 0 .. 66 stands for token x - 3 of the chunk); the halo rows of v sit apart
         auto conv_rows = [&](uint4(&out)[2], int tensor) {
             float4 w[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) w[j] = sW[tensor * D + j * 16 + (c8 >> 3)];
             float win[5][8];
 #pragma unroll
-            for (int r = 0; r < 5; ++r)
-                bf16x8_to_f32(*reinterpret_cast<const uint4*>(sRaw + (tensor * ROWS + 2 * hw + r) * D + c8), win[r]);
+            for (int r = 0; r < 5; ++r) {
+                const int x = 2 * hw + r;
+                const __nv_bfloat16* row = tensor == 0 ? sRq + x * D : tensor == 1 ? sRk + x * D : (x < 3 ? sRvh + x * D : sRv + (x - 3) * D);
+                bf16x8_to_f32(*reinterpret_cast<const uint4*>(row + c8), win[r]);
+            }
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
                 float y[8];
@@ -357,9 +365,9 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
             const int off = (hw + 32 * m) * D + c8;
-            rq4[m] = *reinterpret_cast<const uint4*>(sRaw + off);
-            rk4[m] = *reinterpret_cast<const uint4*>(sRaw + ROWS * D + off);
-            rv4[m] = *reinterpret_cast<const uint4*>(sRaw + 2 * ROWS * D + off);
+            rq4[m] = *reinterpret_cast<const uint4*>(sRq + off);
+            rk4[m] = *reinterpret_cast<const uint4*>(sRk + off);
+            rv4[m] = *reinterpret_cast<const uint4*>(sRv + off);
         }
     }
     // ---- 0b: q, k, v, beta row-wise: a half warp owns two rows, lane c8 the channels 8 c8 ..
@@ -407,7 +415,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     }
     KDA_PHASE(1);
     tc_fence_before();
-    __syncthreads();  // the raw gate rows (in the Aqk staging tile) and the raw q, k, v rows are consumed
+    __syncthreads();  // the raw gate, q, k rows (operand space) and the raw v rows (L tile) are consumed
     tc_fence_after();
     for (int idx = tid; idx < C * 65; idx += NTHR) {
         sA[idx] = 0.f;
@@ -690,8 +698,9 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     tc_fence_before();
     __syncthreads();
     if (more) {  // the operand tiles of the off-diagonal products are dead; the scalars have the whole solve to arrive
-        request_rows(ci_nx, head_of(unit_nx));
-        request_scalars(ci_nx, head_of(unit_nx), nx);
+        ci_nx = chunk_info(p, un.c);
+        request_rows(ci_nx, un.head());
+        request_scalars(ci_nx, un.head(), nx);
     }
     KDA_PHASE(15);
 
@@ -712,7 +721,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     solve_block_column(sL, sT, sbeta, warp & 3, (warp >> 2) & 1, lane, warp < 8);
     fence_async_smem();
     __syncthreads();
-    if (more) request_gate(ci_nx, head_of(unit_nx));  // L is dead: its tile receives the next unit's gate rows
+    if (more) request_v(ci_nx, un.head());  // L is dead: its tile receives the next unit's v rows
 
     KDA_PHASE(6);
     // ---- 4: Aqk and T records; T as the B operand of the WY products
@@ -779,7 +788,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     }
     if (!ok && more) {  // the next unit's copies are in flight: they must have landed before the CTA leaves
         mbar_wait(&rowbar, (it + 1) & 1, p.status, 8);
-        mbar_wait(&gatebar, (it + 1) & 1, p.status, 8);
+        mbar_wait(&vbar, (it + 1) & 1, p.status, 8);
     }
     tc_fence_before();
     __syncthreads();

@@ -1,6 +1,6 @@
 // bwd_intra (BF16 path, d = 128): the guarded intra-chunk backward on tensor cores, the reverse
 // cumulative sum of the gate gradient and the chain rule through gate / L2 norm / sigmoid.
-// One CTA per (chunk, head).
+// One CTA per SM walks the (chunk, head) units (UnitWalk).
 //
 // With D_ij = 2^(G_i - G_j) per channel (i >= j inside the chunk), dA = dAqk (strictly lower; its
 // diagonal is handled apart), dM the gradient of I + diag(beta) L (strictly lower):

@@ -1,6 +1,6 @@
 // bwd_wy on tensor cores (BF16 path, d = 128): the chunk-level adjoints of the WY / state
-// products, one CTA per (chunk, head), every [64 x d] result computed TRANSPOSED so that the
-// accumulator rows (TMEM lanes) are the 128 channels:
+// products; one CTA per SM walks the (chunk, head) units (UnitWalk); every [64 x d] result is
+// computed TRANSPOSED so that the accumulator rows (TMEM lanes) are the 128 channels:
 //
 //   S1   dAqk = dO V'^T (M = 64)        dWn^T = S0 dV'^T        dQt^T = S0 dO^T
 //        dKh^T = dS V'^T                dVb^T = dV'^T T
@@ -13,7 +13,9 @@
 // used, for which masking the intermediate T-gradient is irrelevant.)
 //
 // Outputs: dv, the beta gradient collected so far, dGamma_C * Gamma_C, and the hand-over
-// records of bwd_intra (dAqk, dM as three-way BF16 splits in operand layout; dQt, dKh, dKb in BF16).
+// records of bwd_intra (dAqk, dM as three-way BF16 splits in operand layout; dQt, dKh, dKb in BF16,
+// channel-major: handover_idx).  Two kernels: kda_bwd_wy_tc<true> with the fused backward of the short
+// convolution of v, and kda_bwd_wy_tc_pf (further down), which requests its operands a unit ahead.
 #include "kda_common.cuh"
 #include "kda_conv_bwd.cuh"
 #include "kda_tc.cuh"

@@ -1,16 +1,19 @@
-// fwd_intra on tensor cores (BF16 operands, d = 128): one CTA per (chunk, head).
+// fwd_intra on tensor cores (BF16 operands, d = 128).  One CTA per SM walks the (chunk, head) units
+// (UnitWalk) and requests the inputs of its next unit while it works on the current one.
 //
-//   0  load q, k, v, beta row-wise with 16-byte accesses: L2 norm, sigmoid, beta*v operand;
-//      load the gate channel-wise: activation and the within-chunk cumulative sum G (log2).
+//   0  the unit's gate, q, k, v tiles arrive as bulk-tensor tile copies (tensor maps; row by row for
+//      partial chunks).  Gate channel-wise: activation and the within-chunk cumulative sum G (log2);
+//      q, k, v, beta row-wise: L2 norm, sigmoid, beta*v operand.
 //      The CONV instantiation reads the pre-convolution projections instead (three halo rows
 //      before the chunk included) and applies the causal depthwise filter + SiLU of
 //      k3mini/model.py:76-88,181-185 in registers before anything else sees the rows
-//   1  decay-scaled operands: Qt, Kh records; beta*k*2^G; and for every 16-row block I >= 1
+//   1  the four diagonal 16x16 blocks of Aqk and L on the CUDA cores: where all four [16 x 32] tiles
+//      of a block pass the span guard, with the FP32 midpoint factorisation (pre-scaled key rows, no
+//      exponential per pair), otherwise with exact pairwise decays
+//   2  decay-scaled operands: Qt, Kh records; beta*k*2^G; and for every 16-row block I >= 1
 //      the factorised operands  k_j 2^(r_I - G_j) (j < 16 I)  and  x_i 2^(G_i - r_I) (i in I),
-//      r_I = G at the first row of block I, so that every exponent is <= 0
-//   2  off-diagonal blocks of Aqk and L as tcgen05 MMAs (M = 64 keys, N = 32 = q and k rows of
-//      block I, K = 128), while the CUDA cores evaluate the four diagonal 16x16 blocks with
-//      exact pairwise decays
+//      r_I = G at the first row of block I, so that every exponent is <= 0; off-diagonal blocks of
+//      Aqk and L as tcgen05 MMAs (M = 64 keys, N = 32 = q and k rows of block I, K = 128)
 //   3  T = (I + diag(beta) L)^-1: forward substitution inside the diagonal blocks, block
 //      forward substitution for the rest (FP32)
 //   4  Aqk and T records; 5  W^T = (beta k 2^G)^T T^T and U^T = (beta v)^T T^T as tcgen05 MMAs

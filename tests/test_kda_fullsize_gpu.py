@@ -126,3 +126,18 @@ def test_c1_shape_two_sequences_six_heads_against_oracle():
     rows = compare(dev, ref, tol_max=2e-2, tol_l2=7e-3)
     assert_rows(rows)
     assert dict((r[0], r[2]) for r in rows)["o"] < 5e-3
+
+
+@pytest.mark.parametrize("B,T,H", [(3, 512, 7), (7, 320, 5)])
+def test_more_units_than_sms_with_odd_head_counts_against_oracle(B, T, H):
+    """The per-unit kernels run one CTA per SM that walks units first, first + #SMs, ...; with head counts that
+    share no factor with the SM count (and more units than SMs: 168 and 175 chunk-head pairs) every CTA
+    meets several heads and several sequences, and some CTAs get one unit more than others."""
+    inp = make_inputs(B, T, H, 128, seed=60 + H, dtype=torch.bfloat16)
+    dev = run_device(inp)
+    refs = []
+    for b in range(B):
+        one = {k: (v[b:b + 1] if v.dim() >= 3 else v) for k, v in inp.items()}
+        refs.append(run_oracle(one))
+    ref = {k: (sum(r[k] for r in refs) if k in ("dA_log", "ddt_bias") else torch.cat([r[k] for r in refs], 0)) for k in refs[0]}
+    assert_rows(compare(dev, ref, tol_max=2e-2, tol_l2=7e-3))

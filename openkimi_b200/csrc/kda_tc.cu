@@ -230,6 +230,9 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
         unsigned char* b = dyn + stage * STAGE;
         const ChunkInfo ci = chunk_of_seq(n, lc, tok_first, tok_end);
         const size_t rec = (size_t)(c0 + lc) * p.H + h;
+        // the next chunk's records are requested first thing (the other stage was last read by the previous
+        // chunk's MMAs, which completed before that chunk's iteration ended): a whole chunk step ahead of their use
+        if (tid == 64 && lc + 1 < nc) issue_loads(lc + 1, stage ^ 1);
         tma_store_wait_read();  // the previous chunk's output rows have left the staging tile
         ok = mbar_wait(&full[stage], (lc >> 1) & 1, p.status, 2);
         if (!__syncthreads_and(ok)) { ok = false; break; }
@@ -275,9 +278,6 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
             }
             mma_commit(&mmabar);
         }
-        // the next chunk's records are requested while the first MMA group runs (the other stage was
-        // last read by the previous chunk's MMAs, which have completed)
-        if (tid == 64 && lc + 1 < nc) issue_loads(lc + 1, stage ^ 1);
         ok = mbar_wait(&mmabar, mma_phase, p.status, 4);
         mma_phase ^= 1;
         tc_fence_after();
@@ -338,8 +338,8 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
         if (!__syncthreads_and(ok)) { ok = false; break; }
         KDA_PHASE(4);
 
-        // ---- C: output rows.  The accumulator holds O^T (lane = channel), so the tile is transposed
-        //      through shared memory and every valid row leaves as one 256-byte bulk store
+        // ---- C: output rows.  The accumulator holds O^T (lane = channel), so the tile is transposed through
+        //      shared memory and goes out with one bulk-tensor store (row by row for a partial chunk)
         {
             __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(dyn + OUT);
 #pragma unroll
@@ -396,7 +396,7 @@ constexpr uint32_t SACC = 0, SBF = 128, VACC = 192, VBF = 256, TMEM_COLS = 512;
 __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams p) {
     using namespace bs;
     extern __shared__ __align__(128) unsigned char dyn[];
-    __shared__ uint64_t full[2];
+    __shared__ uint64_t full[3];  // three stages: the records of a chunk are requested two chunk steps ahead of their use
     __shared__ uint64_t mmabar, mmabar2;
     __shared__ uint32_t tmem_s;
     // thread (half, e) = (tid / 128, tid % 128): TMEM lane e, and half of the columns of every conversion phase
@@ -417,6 +417,7 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
     if (tid == 0) {
         mbar_init(&full[0], 1);
         mbar_init(&full[1], 1);
+        mbar_init(&full[2], 1);
         mbar_init(&mmabar, 2);   // first group: one issuing thread per accumulator
         mbar_init(&mmabar2, 1);  // second group: a single product
         mbar_fence_init();
@@ -461,20 +462,25 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
         cp_async_commit();
     };
     if (nc > 0) issue_loads(0, 0);
+    if (nc > 1) issue_loads(1, 1);
 
     bool ok = true;
+    int stage = 0;
+    uint32_t ring_phase = 0;  // parity of full[stage]: flips every time the ring wraps
     for (int k = 0; k < nc; ++k) {
-        const int lc = nc - 1 - k, stage = k & 1;
+        const int lc = nc - 1 - k;
         unsigned char* b = dyn + stage * STAGE;
         const size_t rec = (size_t)(c0 + lc) * p.H + h;
-        if (k + 1 < nc) {
-            issue_loads(k + 1, stage ^ 1);
+        if (k + 2 < nc) {  // (the stage behind this one was last read by the previous step's MMAs, which have completed)
+            issue_loads(k + 2, stage == 0 ? 2 : stage - 1);
+            cp_async_wait<2>();
+        } else if (k + 1 < nc) {
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         fence_async_smem();
-        ok = mbar_wait(&full[stage], (k >> 1) & 1, p.status, 2);
+        ok = mbar_wait(&full[stage], ring_phase, p.status, 2);
         if (!__syncthreads_and(ok)) { ok = false; break; }
 
         {
@@ -551,6 +557,10 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
         ok = mbar_wait(&mmabar2, k & 1, p.status, 4);
         tc_fence_after();
         if (!__syncthreads_and(ok)) { ok = false; break; }
+        if (++stage == 3) {
+            stage = 0;
+            ring_phase ^= 1;
+        }
     }
     if (ok && p.grad_h0) {
         for (int d0 = 64 * half; d0 < 64 * half + 64; d0 += 16) {
@@ -602,7 +612,7 @@ cudaError_t tc_bwd(const KdaParams& p, cudaStream_t s) {
     if (stage_simt(p, ST_BWD_STATE)) {
         if ((e = simt_stage(p, ST_BWD_STATE, s)) != cudaSuccess) return e;
     } else {
-        constexpr int smem = 2 * bs::STAGE;
+        constexpr int smem = 3 * bs::STAGE;
         if ((e = cudaFuncSetAttribute(kda_bwd_state_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return e;
         kda_bwd_state_tc<<<dim3(p.H, p.N), bs::NTHR, smem, s>>>(p);

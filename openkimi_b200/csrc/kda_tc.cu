@@ -208,18 +208,28 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
     }
     tmem_wait_st();
 
+    // the six records of a chunk: one copy each from lane 0 of six warps (a thread spends ~30 ns on every bulk
+    // copy it issues, and the chunk step waits for the slowest thread)
     auto issue_loads = [&](int lc, int stage) {
+        if ((tid & 31) != 0 || warp >= 6) return;
         const size_t rec = (size_t)(c0 + lc) * p.H + h;
         unsigned char* b = dyn + stage * STAGE;
-        mbar_expect_tx(&full[stage], STAGE);
-        tma_load_1d(b + WT, (const __nv_bfloat16*)(ws + L.W) + rec * C * D, 16384, &full[stage]);
-        tma_load_1d(b + QT, (const __nv_bfloat16*)(ws + L.Qt) + rec * C * D, 16384, &full[stage]);
-        tma_load_1d(b + KH, (const __nv_bfloat16*)(ws + L.Kh) + rec * C * D, 16384, &full[stage]);
-        tma_load_1d(b + UT, (const __nv_bfloat16*)(ws + L.U) + rec * C * D, 16384, &full[stage]);
-        tma_load_1d(b + AQ, (const __nv_bfloat16*)(ws + L.Aqk) + rec * C * C, 8192, &full[stage]);
-        tma_load_1d(b + GAM, (const float*)(ws + L.gamC) + rec * D, 512, &full[stage]);
+        if (warp == 0) {
+            mbar_expect_tx(&full[stage], STAGE);
+            tma_load_1d(b + WT, (const __nv_bfloat16*)(ws + L.W) + rec * C * D, 16384, &full[stage]);
+        } else if (warp == 1) {
+            tma_load_1d(b + UT, (const __nv_bfloat16*)(ws + L.U) + rec * C * D, 16384, &full[stage]);
+        } else if (warp == 2) {
+            tma_load_1d(b + QT, (const __nv_bfloat16*)(ws + L.Qt) + rec * C * D, 16384, &full[stage]);
+        } else if (warp == 3) {
+            tma_load_1d(b + KH, (const __nv_bfloat16*)(ws + L.Kh) + rec * C * D, 16384, &full[stage]);
+        } else if (warp == 4) {
+            tma_load_1d(b + AQ, (const __nv_bfloat16*)(ws + L.Aqk) + rec * C * C, 8192, &full[stage]);
+        } else {
+            tma_load_1d(b + GAM, (const float*)(ws + L.gamC) + rec * D, 512, &full[stage]);
+        }
     };
-    if (tid == 0 && nc > 0) issue_loads(0, 0);
+    if (nc > 0) issue_loads(0, 0);
 
     uint32_t mma_phase = 0;
     bool ok = true;
@@ -232,7 +242,7 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
         const size_t rec = (size_t)(c0 + lc) * p.H + h;
         // the next chunk's records are requested first thing (the other stage was last read by the previous
         // chunk's MMAs, which completed before that chunk's iteration ended): a whole chunk step ahead of their use
-        if (tid == 64 && lc + 1 < nc) issue_loads(lc + 1, stage ^ 1);
+        if (lc + 1 < nc) issue_loads(lc + 1, stage ^ 1);
         tma_store_wait_read();  // the previous chunk's output rows have left the staging tile
         ok = mbar_wait(&full[stage], (lc >> 1) & 1, p.status, 2);
         if (!__syncthreads_and(ok)) { ok = false; break; }
@@ -442,13 +452,19 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
         const int lc = nc - 1 - k;
         const size_t rec = (size_t)(c0 + lc) * p.H + h;
         unsigned char* b = dyn + stage * STAGE;
-        if (tid == 0) {
-            mbar_expect_tx(&full[stage], TMA_BYTES);
-            tma_load_1d(b + WT, (const __nv_bfloat16*)(ws + L.W) + rec * C * D, 16384, &full[stage]);
-            tma_load_1d(b + QT, (const __nv_bfloat16*)(ws + L.Qt) + rec * C * D, 16384, &full[stage]);
-            tma_load_1d(b + KH, (const __nv_bfloat16*)(ws + L.Kh) + rec * C * D, 16384, &full[stage]);
-            tma_load_1d(b + AQ, (const __nv_bfloat16*)(ws + L.Aqk) + rec * C * C, 8192, &full[stage]);
-            tma_load_1d(b + GAM, (const float*)(ws + L.gamC) + rec * D, 512, &full[stage]);
+        if ((tid & 31) == 0) {  // one bulk copy each from lane 0 of five warps
+            if (warp == 0) {
+                mbar_expect_tx(&full[stage], TMA_BYTES);
+                tma_load_1d(b + WT, (const __nv_bfloat16*)(ws + L.W) + rec * C * D, 16384, &full[stage]);
+            } else if (warp == 1) {
+                tma_load_1d(b + QT, (const __nv_bfloat16*)(ws + L.Qt) + rec * C * D, 16384, &full[stage]);
+            } else if (warp == 2) {
+                tma_load_1d(b + KH, (const __nv_bfloat16*)(ws + L.Kh) + rec * C * D, 16384, &full[stage]);
+            } else if (warp == 3) {
+                tma_load_1d(b + AQ, (const __nv_bfloat16*)(ws + L.Aqk) + rec * C * C, 8192, &full[stage]);
+            } else if (warp == 4) {
+                tma_load_1d(b + GAM, (const float*)(ws + L.gamC) + rec * D, 512, &full[stage]);
+            }
         }
         // dO tile -> core-matrix layout cm(i, e; 128), 16-byte chunks, zero rows past the end
         const ChunkInfo ci = chunk_of_seq(n, lc, tok_first, tok_end);

@@ -581,7 +581,24 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
             }
         };
         const bool fast = (spass[4 * b] & spass[4 * b + 1] & spass[4 * b + 2] & spass[4 * b + 3]) != 0;  // uniform over the block
-        if (fast) {
+        // warps 0, 1 of a block: row 8 + slot against keys 0..7; warp 2: rows 15 - slot (15..12) against keys 8..15, then
+        // rows slot (0..3) against keys 0..3; warp 3: rows 15 - slot (11..8) against keys 8..11, then rows slot (4..7)
+        // against keys 0..7.
+        if constexpr (CONV) {
+            // One rolled loop over the (at most two) segments keeps a single copy of each walk in the code: with the
+            // convolution the kernel is ~190 KB of instructions otherwise, every unit fetches them anew, and above
+            // that size the fetches started to cost (1.89 -> 1.71 ms on the sublayer workload).
+            const int nseg = w4 < 2 ? 1 : 2;
+#pragma unroll 1
+            for (int sgi = 0; sgi < nseg; ++sgi) {
+                int i, jb, je;
+                if (w4 < 2) { i = 8 + slot; jb = 0; je = 8; }
+                else if (sgi == 0) { i = 15 - slot; jb = 8; je = w4 == 2 ? 16 : 12; }
+                else { i = slot; jb = 0; je = w4 == 2 ? 4 : 8; }
+                if (fast) row_against_mid(i, jb, je);
+                else row_against(i, jb, je);
+            }
+        } else if (fast) {  // (without the convolution the straight-line form fits and is 0.3 us per unit faster)
             if (w4 < 2) {
                 row_against_mid(8 + slot, 0, 8);
             } else {
@@ -591,9 +608,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         } else if (w4 < 2) {
             row_against(8 + slot, 0, 8);
         } else {
-            // rows 15 - slot: warp 2 holds rows 15..12 (keys up to 15), warp 3 rows 11..8 (keys up to 11)
             row_against(15 - slot, 8, w4 == 2 ? 16 : 12);
-            // rows slot: warp 2 holds rows 0..3 (keys 0..3), warp 3 rows 4..7 (keys 0..7)
             row_against(slot, 0, w4 == 2 ? 4 : 8);
         }
     }

@@ -212,11 +212,13 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     const bool tiles = maps.ok != 0;  // whole [64 x 128] tiles with one bulk-tensor copy each (full chunks only)
     auto row_src = [&](const __nv_bfloat16* base, const ChunkInfo& ci, int h, int i) { return base + ((size_t)(ci.tok0 + i) * p.H + h) * D; };
     auto request_rows = [&](const ChunkInfo& ci, int h) {  // gate, q, k (and every halo row)
-        if (tid == 0) mbar_expect_tx(&rowbar, (uint32_t)(3 * ci.len + ((CONV && ci.lc > 0) ? 9 : 0)) * 256u);
+        // (issued from the last warp, which has no share in the column solve that follows the in-loop request: the
+        //  issuing warp is held up while the copy unit works through its requests)
+        if (tid == NTHR - 32) mbar_expect_tx(&rowbar, (uint32_t)(3 * ci.len + ((CONV && ci.lc > 0) ? 9 : 0)) * 256u);
         if (tiles && ci.len == C) {
-            if (tid == 0) tma_load_tile(sRG, &maps.m[3], h * D, (int)ci.tok0, &rowbar);
-            if (tid == 1) tma_load_tile(sRq + HALO * D, &maps.m[0], h * D, (int)ci.tok0, &rowbar);
-            if (tid == 2) tma_load_tile(sRk + HALO * D, &maps.m[1], h * D, (int)ci.tok0, &rowbar);
+            if (tid == NTHR - 32) tma_load_tile(sRG, &maps.m[3], h * D, (int)ci.tok0, &rowbar);
+            if (tid == NTHR - 31) tma_load_tile(sRq + HALO * D, &maps.m[0], h * D, (int)ci.tok0, &rowbar);
+            if (tid == NTHR - 30) tma_load_tile(sRk + HALO * D, &maps.m[1], h * D, (int)ci.tok0, &rowbar);
         } else if (tid < 3 * C) {
             const int t3 = tid >> 6, i = tid & 63;
             __nv_bfloat16* dst = (t3 == 0 ? sRG : t3 == 1 ? sRq + HALO * D : sRk + HALO * D) + i * D;
@@ -724,7 +726,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 
     KDA_PHASE(5);
     // (issued here rather than before the operand stage, whose shared-memory traffic they would share)
-    if (tid == 0 && save) {  // prologue results for the backward: three bulk stores straight from shared memory
+    if (tid == NTHR - 64 && save) {  // prologue results for the backward: bulk stores straight from shared memory, issued by a
+                                     // thread of a warp that has no share in the solve
         tma_store_1d((float*)(ws + L.Gc) + rec * C * D, sG, C * D * 4);
         tma_store_1d((__nv_bfloat16*)(ws + L.Qn) + rec * C * D, sQ, C * D * 2);
         tma_store_1d((__nv_bfloat16*)(ws + L.Kn) + rec * C * D, sK, C * D * 2);
@@ -797,7 +800,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         }
     }
     if (more) park_taps(nx);  // (T has left for its record and its operand tile)
-    if (tid == 0) tma_store_wait_all();
+    if (tid == NTHR - 64) tma_store_wait_all();
     tc_fence_before();
     ok = __syncthreads_and(ok);
     KDA_PHASE(9);

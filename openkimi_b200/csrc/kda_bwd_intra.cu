@@ -574,8 +574,8 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             conv_taps(p.conv_k, hd, d, p.conv_ksize, wk);
             float* cvh = (float*)(sc + L.cv_head) + (rec * 3 * 3) * D;
             float* cvt = (float*)(sc + L.cv_tail) + (rec * 3 * 3) * D;
-            conv_bwd_block(sxq, sdyq, wq, d, blk, cvh, cvt, dwq, oq);
-            conv_bwd_block(sxk, sdyk, wk, d, blk, cvh + 3 * D, cvt + 3 * D, dwk, ok_);
+            conv_bwd_block(sxq, sxq + 3 * D, sdyq, wq, d, blk, cvh, cvt, dwq, oq);
+            conv_bwd_block(sxk, sxk + 3 * D, sdyk, wk, d, blk, cvh + 3 * D, cvt + 3 * D, dwk, ok_);
             *reinterpret_cast<float4*>(sdw + (blk * D + d) * 4) = make_float4(dwq[0], dwq[1], dwq[2], dwq[3]);
             *reinterpret_cast<float4*>(sdw + ((4 + blk) * D + d) * 4) = make_float4(dwk[0], dwk[1], dwk[2], dwk[3]);
             __syncthreads();  // every read of dy is done, the filter-gradient shares are visible

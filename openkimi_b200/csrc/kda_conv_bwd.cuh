@@ -21,17 +21,19 @@ __device__ __forceinline__ float dsilu_f(float x) {
 }
 
 // Thread = (channel ch, 16-row block blk) of a 512-thread CTA.
-//   sx   [67][128] BF16: rows -3 .. 63 of the pre-convolution tensor (zero where the row does not exist)
+//   sxh  [3][128] BF16: rows -3 .. -1 of the pre-convolution tensor, sx [64][128]: rows 0 .. 63 (zero where a
+//        row does not exist); the two may be one [67][128] array (sx = sxh + 3 * 128)
 //   sdy  [64][128] BF16: gradient of the convolved rows (zero past the end of a partial chunk)
 //   w    the four padded taps of this channel
 // Returns dx of the block's 16 rows in out[] (rows 61..63 are incomplete when the chunk has a
 // successor), adds the block's share of dw, and hands dpre of rows 0..2 / 61..63 to head / tail
 // ([3][128] FP32 each, written by block 0 / block 3).
-__device__ __forceinline__ void conv_bwd_block(const __nv_bfloat16* __restrict__ sx, const __nv_bfloat16* __restrict__ sdy,
+__device__ __forceinline__ void conv_bwd_block(const __nv_bfloat16* __restrict__ sxh, const __nv_bfloat16* __restrict__ sx,
+                                               const __nv_bfloat16* __restrict__ sdy,
                                                const float (&w)[4], int ch, int blk, float* __restrict__ head,
                                                float* __restrict__ tail, float (&dw)[4], float (&out)[16]) {
     const int b0 = 16 * blk;
-    auto X = [&](int r) { return __bfloat162float(sx[(r + 3) * 128 + ch]); };
+    auto X = [&](int r) { return __bfloat162float(r < 0 ? sxh[(r + 3) * 128 + ch] : sx[r * 128 + ch]); };
     float xa = X(b0 - 3), xb = X(b0 - 2), xc = X(b0 - 1), pa = 0.f, pb = 0.f, pc = 0.f;
 #pragma unroll
     for (int sI = 0; sI < 19; ++sI) {

@@ -14,8 +14,7 @@
 //
 // Outputs: dv, the beta gradient collected so far, dGamma_C * Gamma_C, and the hand-over
 // records of bwd_intra (dAqk, dM as three-way BF16 splits in operand layout; dQt, dKh, dKb in BF16,
-// channel-major: handover_idx).  Two kernels: kda_bwd_wy_tc<true> with the fused backward of the short
-// convolution of v, and kda_bwd_wy_tc_pf (further down), which requests its operands a unit ahead.
+// channel-major: handover_idx).
 #include "kda_common.cuh"
 #include "kda_conv_bwd.cuh"
 #include "kda_tc.cuh"
@@ -24,26 +23,6 @@
 namespace kda {
 
 using namespace tc;
-
-namespace bw {
-constexpr int D = 128, NTHR = 512;
-constexpr uint32_t VT = 0;                  // V'^T  cm(e, i; 64)
-constexpr uint32_t DVT = VT + 16384;        // dV'^T cm(e, i; 64);   later Z^T  cm(d, i; 64)
-constexpr uint32_t S0T = DVT + 16384;       // S0^T  cm(e, d; 128)
-constexpr uint32_t DST = S0T + 32768;       // dS^T  cm(e, d; 128)
-constexpr uint32_t TT = DST + 32768;        // T     cm(i, j; 64)
-constexpr uint32_t WT = TT + 8192;          // W^T   cm(d, j; 64)
-constexpr uint32_t TMA_BYTES = WT + 16384;  // everything above arrives by bulk TMA
-constexpr uint32_t DOT = TMA_BYTES;         // dO    cm(i, e; 128);  later dVb^T cm(e, i; 64)
-constexpr uint32_t STG = DOT + 16384;       // f32 [64][128] staging for the beta row sums
-constexpr uint32_t SV = STG + 32768;        // v bf16 [64][128] row-major (prefetched with cp.async)
-constexpr uint32_t SBETA = SV + 16384;      // f32 [64] beta, f32 [64] row sums, f32 [4][128] partial dGamma_C
-constexpr uint32_t SKH = SBETA + 512 + 2048;   // bf16 staging of dKh (dQt and dKb are staged in the two halves of DST once dS is dead)
-constexpr uint32_t TOTAL = SKH + 16384;
-constexpr uint32_t XV = TOTAL;              // fused conv backward only: pre-convolution v rows -3 .. 63, bf16 [67][128]
-constexpr uint32_t TOTAL_CONVB = XV + 67 * 256;
-constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
-}  // namespace bw
 
 // sixteen consecutive entries (row i, columns j0 .. j0 + 15) of a [64 x 64] FP32 matrix -> the three
 // BF16 tiles cm(i, j; 64) whose sum it is (tile p at base + p * 4096 elements)
@@ -71,406 +50,19 @@ __device__ __forceinline__ void store_handover16(__nv_bfloat16* rec_base, int ch
     *reinterpret_cast<uint4*>(rec_base + handover_idx(i0 + 8, ch)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
 }
 
-// CONVB: the backward of the short convolution of v runs here too (KdaParams.grad_conv_*): dv of the convolved
-// rows stays in shared memory and grad_v receives the gradient of the v projection.
-template <bool CONVB>
-__global__ void __launch_bounds__(bw::NTHR, 1) kda_bwd_wy_tc(const KdaParams p, const __grid_constant__ RowMaps maps) {
-    using namespace bw;
-    extern __shared__ __align__(128) unsigned char dyn[];
-    __shared__ uint64_t full, mma1, mma2, mma3;
-    __shared__ uint32_t tmem_s;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const WsLayout L = ws_layout(p.NT, p.H, p.dk, p.dv, p.dtype);
-    const char* ws = (const char*)p.workspace;
-    char* sc = (char*)p.bwd_scratch;
-    float* stg = reinterpret_cast<float*>(dyn + STG);
-    float* sbeta = reinterpret_cast<float*>(dyn + SBETA);
-    float* srow = sbeta + 64;
-    const __nv_bfloat16* dO = (const __nv_bfloat16*)p.grad_o;
-    const __nv_bfloat16* v = (const __nv_bfloat16*)p.v;
-
-    KDA_PHASE_BEGIN();
-    if (warp == 0) {
-        tmem_alloc(&tmem_s, TMEM_COLS);
-        tmem_relinquish();
-    }
-    if (tid == 0) {
-        mbar_init(&full, 1);
-        mbar_init(&mma1, 5);  // one issuing thread per accumulator: a single thread spends ~50 ns on every MMA it issues
-        mbar_init(&mma2, 2);
-        mbar_init(&mma3, 2);
-        mbar_fence_init();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem0 = tmem_s;
-    const uint32_t tmem = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's lane quadrant
-    const int ch = tid & 127, qtr = tid >> 7;                             // channel (TMEM lane) and column quarter (16 columns)
-    float* spart = srow + 64;
-    const uint32_t sb = smem_u32(dyn);
-
-    // The CTA walks the units blockIdx.x, blockIdx.x + gridDim.x, ...: tensor memory, barriers and the CTA itself
-    // are set up once.  Unit u = (chunk u / H, head (u + chunk) % H), so that the units of one CTA cycle through
-    // all heads whatever the stride.
-    const int n_units = p.NT * p.H;
-    uint32_t it = 0;
-    UnitWalk uw;
-    uw.init(blockIdx.x, gridDim.x, p.H);
-    for (; uw.unit < n_units; uw.next(), ++it) {
-    const int c = uw.c, h = uw.head();
-    const ChunkInfo ci = chunk_info(p, c);
-    const size_t rec = (size_t)c * p.H + h;
-    // with the short convolution fused into the forward, p.v is the pre-convolution projection and
-    // the convolved rows come from the forward's record
-    const __nv_bfloat16* vrec = p.conv_q ? (const __nv_bfloat16*)(ws + L.Vc) + rec * C * D : nullptr;
-    auto tok = [&](int i) { return ((size_t)(ci.tok0 + i) * p.H + h); };
-    // Gamma_C of my channel: requested now, used after the second MMA group
-    const float gam_c = tid < D ? ((const float*)(ws + L.gamC))[rec * D + tid] : 0.f;
-
-    if (tid == 0) {
-        mbar_expect_tx(&full, TMA_BYTES);
-        tma_load_1d(dyn + VT, (const __nv_bfloat16*)(ws + L.U) + rec * C * D, 16384, &full);
-        tma_load_1d(dyn + DVT, (const __nv_bfloat16*)(sc + L.dVn) + rec * C * D, 16384, &full);
-        tma_load_1d(dyn + S0T, (const __nv_bfloat16*)(ws + L.S0) + rec * D * D, 32768, &full);
-        tma_load_1d(dyn + DST, (const __nv_bfloat16*)(sc + L.dS) + rec * D * D, 32768, &full);
-        tma_load_1d(dyn + TT, (const __nv_bfloat16*)(ws + L.Tm) + rec * C * C, 8192, &full);
-        tma_load_1d(dyn + WT, (const __nv_bfloat16*)(ws + L.W) + rec * C * D, 16384, &full);
-    }
-    {
-        __nv_bfloat16* sdo = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
-        __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(dyn + SV);
-        for (int qq = tid; qq < C * (D / 8); qq += NTHR) {
-            const int i = qq >> 4, e8 = (qq & 15) * 8;
-            const bool valid = i < ci.len;
-            cp_async16_z(sdo + cm_idx(i, e8, D), dO + tok(valid ? i : 0) * D + e8, valid);
-            cp_async16_z(sv + i * D + e8, vrec ? vrec + (valid ? i : 0) * D + e8 : v + tok(valid ? i : 0) * D + e8, valid);
-        }
-        if constexpr (CONVB) {  // rows -3 .. 63 of the v projection (zero where the row does not exist)
-            __nv_bfloat16* sxv = reinterpret_cast<__nv_bfloat16*>(dyn + XV);
-            for (int qq = tid; qq < 67 * (D / 8); qq += NTHR) {
-                const int r = qq >> 4, e8 = (qq & 15) * 8;
-                const bool valid = r >= 3 ? r - 3 < ci.len : ci.lc > 0;
-                cp_async16_z(sxv + r * D + e8, v + ((size_t)(ci.tok0 + (valid ? r - 3 : 0)) * p.H + h) * D + e8, valid);
-            }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (tid < C) sbeta[tid] = ((const float*)(ws + L.aux))[rec * 3 * C + 2 * C + tid];  // beta kept by the forward
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        fence_async_smem();
-    }
-    KDA_PHASE(0);
-    // A wait that gives up has already recorded its code in the status word; from then on the CTA
-    // issues no MMA and stores nothing (ok is made uniform at every barrier) and leaves through the
-    // common exit, which frees its tensor memory.
-    bool ok = mbar_wait(&full, it & 1, p.status, 16);
-    tc_fence_before();
-    ok = __syncthreads_and(ok);
-    KDA_PHASE(1);
-
-    // ---- S1: lane 0 of warps 0..4 issues the product of one accumulator each
-    if (lane == 0 && warp < 5 && ok) {
-        tc_fence_after();
-        constexpr uint32_t id_aqk = make_idesc(64, 64, false, true);
-        constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
-        constexpr uint32_t id_mk = make_idesc(128, 64, true, false);
-        constexpr uint32_t id_km = make_idesc(128, 64, false, true);
-        if (warp == 0) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s)  // dAqk = dO (K-major) * V' (MN-major view of V'^T)
-                mma_ss(tmem0 + DAQK, make_desc(sb + DOT + s * 256, 128, 2048), make_desc(sb + VT + s * 2048, 1024, 128), id_aqk, s > 0);
-        } else if (warp == 1) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s)  // dWn^T = S0 (MN-major view of S0^T) * dV'^T (MN-major)
-                mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DVT + s * 2048, 1024, 128), id_mm, s > 0);
-        } else if (warp == 2) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s)  // dQt^T = S0 * dO^T (K-major, rows = i)
-                mma_ss(tmem0 + DQT, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 256, 128, 2048), id_mk, s > 0);
-        } else if (warp == 3) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s)  // dKh^T = dS * V'^T
-                mma_ss(tmem0 + DKH, make_desc(sb + DST + s * 4096, 2048, 128), make_desc(sb + VT + s * 2048, 1024, 128), id_mm, s > 0);
-        } else {
-#pragma unroll
-            for (int s = 0; s < 4; ++s)  // dVb^T = dV'^T (K-major, rows = e) * T (MN-major, rows = j)
-                mma_ss(tmem0 + DVB, make_desc(sb + DVT + s * 256, 128, 1024), make_desc(sb + TT + s * 2048, 1024, 128), id_km, s > 0);
-        }
-        mma_commit(&mma1);
-    }
-    {   // while the first MMA group runs:
-        // dGamma_C[d] = sum_e dS[d][e] S0[d][e].  Both records are cm(e, d; 128): a warp reads, for one
-        // octet of e, 8 rows x 4 channel groups = four contiguous 128-byte core matrices per load.
-        const __nv_bfloat16* s0 = reinterpret_cast<const __nv_bfloat16*>(dyn + S0T);
-        const __nv_bfloat16* ds = reinterpret_cast<const __nv_bfloat16*>(dyn + DST);
-        const int e7 = lane & 7, d8 = 8 * (4 * (warp & 3) + (lane >> 3)), eh = warp >> 2;
-        float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-#pragma unroll 2
-        for (int eo = 0; eo < 4; ++eo) {
-            const int e = 8 * (4 * eh + eo) + e7;
-            float a[8], b[8];
-            bf16x8_to_f32(*reinterpret_cast<const uint4*>(ds + cm_idx(e, d8, D)), a);
-            bf16x8_to_f32(*reinterpret_cast<const uint4*>(s0 + cm_idx(e, d8, D)), b);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = fmaf(a[j], b[j], acc[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 1);
-            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 2);
-            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 4);
-        }
-        if (e7 == 0) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) spart[128 * eh + d8 + j] = acc[j];
-        }
-        }
-    ok = ok && mbar_wait(&mma1, it & 1, p.status, 32);
-    tc_fence_after();
-    ok = __syncthreads_and(ok);  // every warp is done reading dS: its tile becomes the staging area of dQt
-    KDA_PHASE(2);
-
-    // ---- conversions after S1
-    if (ok) {
-        // dQt, dKh (BF16 [64][128] records) and dv (BF16 rows) are transposed through shared memory
-        // (lane = channel, so every store is conflict-free) and leave as bulk copies after the barrier
-        __nv_bfloat16* sdvb = reinterpret_cast<__nv_bfloat16*>(dyn + DOT);
-        __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(dyn + SV);
-        {
-            const int i0 = 16 * qtr;
-            uint32_t r[16], pk[8];
-            tmem_ld16(tmem + DWN + i0, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-            tmem_st8(tmem + WBF + i0 / 2, pk);
-            tmem_ld16(tmem + DQT + i0, r);
-            tmem_wait_ld();
-            store_handover16(reinterpret_cast<__nv_bfloat16*>(dyn + DST), ch, i0, r);
-            tmem_ld16(tmem + DKH + i0, r);
-            tmem_wait_ld();
-            store_handover16(reinterpret_cast<__nv_bfloat16*>(dyn + SKH), ch, i0, r);
-            tmem_ld16(tmem + DVB + i0, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 8; ++j) pk[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-            *reinterpret_cast<uint4*>(sdvb + cm_idx(ch, i0, C)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            *reinterpret_cast<uint4*>(sdvb + cm_idx(ch, i0 + 8, C)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int i = i0 + j;
-                const float x = __uint_as_float(r[j]);
-                const float vv = __bfloat162float(sv[i * D + ch]);  // zero on padding rows
-                sv[i * D + ch] = __float2bfloat16_rn(sbeta[i] * x);  // dv takes the place of v
-                stg[i * D + ch] = x * vv;
-            }
-        }
-        // dAqk: rows of the M = 64 accumulator sit in lanes 0..15 of every warp's quadrant.  It leaves as
-        // three BF16 tiles cm(i, j; 64) (24-bit split, strictly lower triangle) plus its diagonal
-        {
-            __nv_bfloat16* gAM = (__nv_bfloat16*)(sc + L.dAM) + rec * 6 * C * C;
-            float* gAd = (float*)(sc + L.dAd) + rec * C;
-            const int i = 16 * (warp & 3) + (lane & 15);
-            {
-                const int j0 = 16 * qtr;
-                uint32_t r[16];
-                tmem_ld16(tmem + DAQK + j0, r);
-                tmem_wait_ld();
-                if (lane < 16) {
-                    float f[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        f[j] = (j0 + j < i) ? __uint_as_float(r[j]) : 0.f;
-                        if (j0 + j == i) gAd[i] = __uint_as_float(r[j]);
-                    }
-                    store_split_row(gAM, i, j0, f);
-                }
-            }
-        }
-        tmem_wait_st();
-        fence_async_smem();
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (!ok) {
-    } else if (tid == 0) {
-        tma_store_1d((__nv_bfloat16*)(sc + L.dQt) + rec * C * D, dyn + DST, C * D * 2);
-        tma_store_1d((__nv_bfloat16*)(sc + L.dKh) + rec * C * D, dyn + SKH, C * D * 2);
-        tma_store_commit();
-    } else if (!CONVB && maps.ok && ci.len == C) {  // dv: the whole tile with one bulk-tensor store
-        if (tid == 64) {
-            tma_store_tile(&maps.m[0], h * D, (int)ci.tok0, dyn + SV);
-            tma_store_commit();
-        }
-    } else if (!CONVB && tid >= 64 && tid - 64 < ci.len) {
-        const int i = tid - 64;
-        tma_store_1d((__nv_bfloat16*)p.grad_v + tok(i) * D, dyn + SV + i * D * 2, D * 2);
-        tma_store_commit();
-    }
-    KDA_PHASE(3);
-
-    // ---- S2: two issuing threads (the products into dWn form one chain)
-    if (lane == 0 && warp < 2 && ok) {
-        tc_fence_after();
-        constexpr uint32_t id_neg = make_idesc(128, 64, false, true, true);  // -WBF (TMEM) * T (MN-major)
-        constexpr uint32_t id_mm = make_idesc(128, 64, true, true);
-        if (warp == 0) {
-#pragma unroll
-            for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DKB, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
-        } else {
-#pragma unroll
-            for (int s = 0; s < 4; ++s) mma_ts(tmem0 + DWN, tmem0 + WBF + s * 8, make_desc(sb + TT + s * 2048, 1024, 128), id_neg, s > 0);
-#pragma unroll
-            for (int s = 0; s < 8; ++s)  // Z^T += S0 * dVb^T (MN-major B from cm(e, i; 64))
-                mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + DOT + s * 2048, 1024, 128), id_mm, true);
-        }
-        mma_commit(&mma2);
-    }
-    if constexpr (CONVB) {
-        // meanwhile: backward of the short convolution of v.  dv (BF16, as the unfused path would store it) is
-        // in shared memory; thread (channel, 16-row block) walks its rows, the four blocks' filter-gradient
-        // shares meet in the (now dead) dV'^T tile, and dx goes out in place of dv.
-        if (ok) {
-            __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(dyn + SV);
-            float* sdw = reinterpret_cast<float*>(dyn + DVT);  // [4][128][4]
-            int c0s, ncs;
-            seq_chunks(p, ci.seq, c0s, ncs);
-            const bool has_next = ci.lc + 1 < ncs;
-            float w4[4], dw[4] = {0.f, 0.f, 0.f, 0.f}, out[16];
-            conv_taps(p.conv_v, h, ch, p.conv_ksize, w4);
-            float* cvh = (float*)(sc + L.cv_head) + ((rec * 3 + 2) * 3) * D;
-            float* cvt = (float*)(sc + L.cv_tail) + ((rec * 3 + 2) * 3) * D;
-            conv_bwd_block(reinterpret_cast<const __nv_bfloat16*>(dyn + XV), sv, w4, ch, qtr, cvh, cvt, dw, out);
-            *reinterpret_cast<float4*>(sdw + (qtr * D + ch) * 4) = make_float4(dw[0], dw[1], dw[2], dw[3]);
-            __syncthreads();  // every read of dv is done, the filter-gradient shares are visible
-#pragma unroll
-            for (int r = 0; r < 16; ++r) sv[(16 * qtr + r) * D + ch] = __float2bfloat16_rn(out[r]);
-            if (qtr == 0) {
-                float4 t = *reinterpret_cast<const float4*>(sdw + ch * 4);
-#pragma unroll
-                for (int b = 1; b < 4; ++b) {
-                    const float4 u = *reinterpret_cast<const float4*>(sdw + (b * D + ch) * 4);
-                    t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
-                }
-                *reinterpret_cast<float4*>((float*)(sc + L.cv_part) + ((rec * 3 + 2) * D + ch) * 4) = t;
-            }
-            fence_async_smem();
-            __syncthreads();
-            const int lim = has_next ? 61 : ci.len;  // rows 61..63 of a chunk with a successor wait for the fix-up
-            if (tid >= 64 && tid - 64 < lim) {
-                const int i = tid - 64;
-                tma_store_1d((__nv_bfloat16*)p.grad_v + tok(i) * D, dyn + SV + i * D * 2, D * 2);
-                tma_store_commit();
-            }
-        }
-    }
-    // meanwhile: beta row sums and dGamma_C * Gamma_C on the CUDA cores
-    {
-        const int hw = tid >> 4, c8 = (tid & 15) * 8;
-        for (int m = 0; m < 2; ++m) {
-            const int i = hw + 32 * m;
-            float s = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s += stg[i * D + c8 + j];
-            s = half_warp_sum(s);
-            if ((tid & 15) == 0) srow[i] = s;
-        }
-    }
-    KDA_PHASE(4);
-    ok = ok && mbar_wait(&mma2, it & 1, p.status, 32);
-    tc_fence_after();
-    ok = __syncthreads_and(ok);
-    KDA_PHASE(5);
-    if (ok && tid < C) ((float*)(sc + L.dbp))[rec * C + tid] = srow[tid];
-    if (ok && tid < D) ((float*)(sc + L.gC))[rec * D + tid] = ((spart[tid] + spart[128 + tid]) + (spart[256 + tid] + spart[384 + tid])) * gam_c;
-
-    // ---- conversions after S2
-    if (ok) {
-        __nv_bfloat16* sz = reinterpret_cast<__nv_bfloat16*>(dyn + DVT);
-        {
-            const int i0 = 16 * qtr;
-            uint32_t r[16];
-            tmem_ld16(tmem + DKB + i0, r);
-            tmem_wait_ld();
-            store_handover16(reinterpret_cast<__nv_bfloat16*>(dyn + DST + 16384), ch, i0, r);  // second half: dQt may still be leaving the first
-            tmem_ld16(tmem + DWN + i0, r);
-            tmem_wait_ld();
-            *reinterpret_cast<uint4*>(sz + cm_idx(ch, i0, C)) =
-                make_uint4(pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1])), pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3])),
-                           pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5])), pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7])));
-            *reinterpret_cast<uint4*>(sz + cm_idx(ch, i0 + 8, C)) =
-                make_uint4(pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9])), pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11])),
-                           pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13])), pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15])));
-        }
-        fence_async_smem();
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0 && ok) {
-        tma_store_1d((__nv_bfloat16*)(sc + L.dKb) + rec * C * D, dyn + DST + 16384, C * D * 2);
-        tma_store_commit();
-    }
-    KDA_PHASE(6);
-
-    // ---- S3: the two products of dMn go to two accumulators (the second one where dAqk was), one issuing thread each
-    if (lane == 0 && warp < 2 && ok) {
-        tc_fence_after();
-        constexpr uint32_t id = make_idesc(64, 64, true, true);
-        if (warp == 0) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s)  // Z (MN-major view of Z^T) * W^T (MN-major view of the W^T record)
-                mma_ss(tmem0 + DMN, make_desc(sb + DVT + s * 2048, 1024, 128), make_desc(sb + WT + s * 2048, 1024, 128), id, s > 0);
-        } else {
-#pragma unroll
-            for (int s = 0; s < 8; ++s)  // dVb * V'^T
-                mma_ss(tmem0 + DAQK, make_desc(sb + DOT + s * 2048, 1024, 128), make_desc(sb + VT + s * 2048, 1024, 128), id, s > 0);
-        }
-        mma_commit(&mma3);
-    }
-    ok = ok && mbar_wait(&mma3, it & 1, p.status, 32);
-    tc_fence_after();
-    KDA_PHASE(7);
-    if (ok) {
-        __nv_bfloat16* gMM = (__nv_bfloat16*)(sc + L.dAM) + rec * 6 * C * C + 3 * C * C;
-        const int i = 16 * (warp & 3) + (lane & 15);
-        {
-            const int j0 = 16 * qtr;
-            uint32_t r[16], r2[16];
-            tmem_ld16(tmem + DMN + j0, r);
-            tmem_ld16(tmem + DAQK + j0, r2);
-            tmem_wait_ld();
-            if (lane < 16) {
-                float f[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) f[j] = (j0 + j < i) ? -(__uint_as_float(r[j]) + __uint_as_float(r2[j])) : 0.f;
-                store_split_row(gMM, i, j0, f);
-            }
-        }
-    }
-    tma_store_wait_all();
-    fence_async_smem();  // (the tiles this unit wrote are about to receive the next unit's bulk copies)
-    tc_fence_before();
-    ok = __syncthreads_and(ok);
-    KDA_PHASE(8);
-    if (!ok) break;  // a wait gave up (recorded in the status word): no further unit is started
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem0, TMEM_COLS);
-}
-
 // ---------------------------------------------------------------------------------------
-// The same kernel with its loads taken off the critical path (everything but the fused
-// convolution backward, whose extra tile does not fit beside the second operand set).
-// The operands that only the first and last MMA groups touch exist twice (V'^T, dV'^T, dO:
-// set it % 2), so the NEXT unit's copies of them are requested as soon as the current unit's
-// first MMA group is issued; S0 and T follow when the second group has read them; dS, W and
-// the v rows are requested at the start of their unit and are first needed one MMA group
-// (dS), a conversion stage (v) or nearly the whole unit (W) later.  The 32 KB FP32 staging
-// tile of the beta row sums makes room for the second operand set: the row sums are reduced
-// in registers (a transposing butterfly over the 32 channels of a warp) instead.
+// The loads are taken off the critical path.  The operands that only the first and last MMA
+// groups touch exist twice (V'^T, dV'^T, dO: set it % 2), so the NEXT unit's copies of them are
+// requested as soon as the current unit's first MMA group is issued; S0 and T follow when the
+// second group has read them; dS, W and the v rows are requested at the start of their unit
+// and are first needed one MMA group (dS), a conversion stage (v) or nearly the whole unit (W)
+// later.  The beta row sums are reduced in registers (a transposing butterfly over the 32
+// channels of a warp) instead of through a 32 KB FP32 staging tile, which is what makes room for
+// the second operand set.
+// CONVB: the backward of the short convolution of v runs here too (KdaParams.grad_conv_*): dv of
+// the convolved rows stays in shared memory and grad_v receives the gradient of the v
+// projection.  The projection rows it needs (-3 .. 63) are fetched once dS is dead, into the half
+// of its tile that stays free until the second conversion stage.
 // ---------------------------------------------------------------------------------------
 namespace bp {
 constexpr int D = 128, NTHR = 512;
@@ -485,7 +77,10 @@ constexpr uint32_t SV = WT + 16384;          // v bf16 [64][128] row-major; late
 constexpr uint32_t SKH = SV + 16384;         // bf16 staging of dKh (dQt and dKb are staged in the two halves of DST once dS is dead)
 constexpr uint32_t SBETA = SKH + 16384;      // f32: beta [64], row sums [64], partial dGamma_C [4][128], partial row sums [4][64]
 constexpr uint32_t TOTAL = SBETA + 256 + 256 + 2048 + 1024;
-using bw::DAQK; using bw::DWN; using bw::DQT; using bw::DKH; using bw::DVB; using bw::DKB; using bw::DMN; using bw::WBF; using bw::TMEM_COLS;
+constexpr uint32_t XVM = DST + 16384;        // fused conv backward only: pre-convolution v rows 0 .. 63, bf16 [64][128] (dS is dead by then)
+constexpr uint32_t XVH = TOTAL;              //                          rows -3 .. -1, bf16 [3][128]
+constexpr uint32_t TOTAL_CONVB = XVH + 3 * 256;
+constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bp
 
 // Sums of 16 values per lane over the 32 lanes of a warp: afterwards the lane holds the sum of value
@@ -505,6 +100,7 @@ __device__ __forceinline__ float warp_sum16(const float (&v)[16], int lane, int&
     return a1;
 }
 
+template <bool CONVB>
 __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams p, const __grid_constant__ RowMaps maps) {
     using namespace bp;
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -698,6 +294,23 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
     tc_fence_after();
     asm volatile("cp.async.wait_group 1;" ::: "memory");  // my share of the v rows has landed (the next unit's dO may still be on its way)
     ok = __syncthreads_and(ok);  // every warp is done reading dS: its tile becomes the staging area of dQt
+    if constexpr (CONVB) {  // ... and, in its second half, receives rows 0 .. 63 of the v projection (zero where a row does not exist)
+        if (ok) {
+            __nv_bfloat16* sxv = reinterpret_cast<__nv_bfloat16*>(dyn + XVM);
+            __nv_bfloat16* sxh = reinterpret_cast<__nv_bfloat16*>(dyn + XVH);
+            for (int qq = tid; qq < C * (D / 8); qq += NTHR) {
+                const int r = qq >> 4, e8 = (qq & 15) * 8;
+                const bool valid = r < ci.len;
+                cp_async16_z(sxv + r * D + e8, v + tok(valid ? r : 0) * D + e8, valid);
+            }
+            if (tid < 3 * (D / 8)) {  // rows -3 .. -1: they exist unless the chunk starts its sequence
+                const int r = tid >> 4, e8 = (tid & 15) * 8;
+                const bool valid = ci.lc > 0;
+                cp_async16_z(sxh + r * D + e8, v + ((size_t)(ci.tok0 + (valid ? r - 3 : 0)) * p.H + h) * D + e8, valid);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     KDA_PHASE(2);
 
     // ---- conversions after S1
@@ -768,6 +381,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
         tma_store_1d((__nv_bfloat16*)(sc + L.dQt) + rec * C * D, dyn + DST, C * D * 2);
         tma_store_1d((__nv_bfloat16*)(sc + L.dKh) + rec * C * D, dyn + SKH, C * D * 2);
         tma_store_commit();
+    } else if (CONVB) {  // (dv stays on chip for the convolution backward below)
     } else if (maps.ok && ci.len == C) {  // dv: the whole tile with one bulk-tensor store
         if (tid == 64) {
             tma_store_tile(&maps.m[0], h * D, (int)ci.tok0, dyn + SV);
@@ -796,6 +410,47 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
                 mma_ss(tmem0 + DWN, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + oDOT + s * 2048, 1024, 128), id_mm, true);
         }
         mma_commit(&mma2);
+    }
+    if constexpr (CONVB) {
+        // meanwhile: backward of the short convolution of v.  dv (BF16, as the unfused path would store it) is
+        // in shared memory; thread (channel, 16-row block) walks its rows, the four blocks' filter-gradient
+        // shares meet in the (now dead) dV'^T tile, and dx goes out in place of dv.
+        if (ok) {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();  // the projection rows have landed
+            __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(dyn + SV);
+            float* sdw = reinterpret_cast<float*>(dyn + oDVT);  // [4][128][4]
+            int c0s, ncs;
+            seq_chunks(p, ci.seq, c0s, ncs);
+            const bool has_next = ci.lc + 1 < ncs;
+            float w4[4], dw[4] = {0.f, 0.f, 0.f, 0.f}, out[16];
+            conv_taps(p.conv_v, h, ch, p.conv_ksize, w4);
+            float* cvh = (float*)(sc + L.cv_head) + ((rec * 3 + 2) * 3) * D;
+            float* cvt = (float*)(sc + L.cv_tail) + ((rec * 3 + 2) * 3) * D;
+            conv_bwd_block(reinterpret_cast<const __nv_bfloat16*>(dyn + XVH), reinterpret_cast<const __nv_bfloat16*>(dyn + XVM), sv, w4, ch,
+                           qtr, cvh, cvt, dw, out);
+            *reinterpret_cast<float4*>(sdw + (qtr * D + ch) * 4) = make_float4(dw[0], dw[1], dw[2], dw[3]);
+            __syncthreads();  // every read of dv is done, the filter-gradient shares are visible
+#pragma unroll
+            for (int r = 0; r < 16; ++r) sv[(16 * qtr + r) * D + ch] = __float2bfloat16_rn(out[r]);
+            if (qtr == 0) {
+                float4 t = *reinterpret_cast<const float4*>(sdw + ch * 4);
+#pragma unroll
+                for (int b = 1; b < 4; ++b) {
+                    const float4 u = *reinterpret_cast<const float4*>(sdw + (b * D + ch) * 4);
+                    t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+                }
+                *reinterpret_cast<float4*>((float*)(sc + L.cv_part) + ((rec * 3 + 2) * D + ch) * 4) = t;
+            }
+            fence_async_smem();
+            __syncthreads();
+            const int lim = has_next ? 61 : ci.len;  // rows 61..63 of a chunk with a successor wait for the fix-up
+            if (tid >= 64 && tid - 64 < lim) {
+                const int i = tid - 64;
+                tma_store_1d((__nv_bfloat16*)p.grad_v + tok(i) * D, dyn + SV + i * D * 2, D * 2);
+                tma_store_commit();
+            }
+        }
     }
     if (tid < C) srow[tid] = (srp[tid] + srp[C + tid]) + (srp[2 * C + tid] + srp[3 * C + tid]);
     KDA_PHASE(4);
@@ -893,16 +548,11 @@ cudaError_t launch_bwd_wy_tc(const KdaParams& p, cudaStream_t s) {
     const int units = p.NT * p.H, sms = sm_count();
     RowMaps maps = {};
     maps.ok = !(p.flags & KDA_FLAG_ROW_COPIES) && make_row_map(&maps.m[0], p.grad_v, (long long)p.B * p.T, p.H, C);
-    cudaError_t e;
-    if (!convb) {
-        if ((e = cudaFuncSetAttribute(kda_bwd_wy_tc_pf, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bp::TOTAL)) != cudaSuccess) return e;
-        kda_bwd_wy_tc_pf<<<units < sms ? units : sms, bp::NTHR, bp::TOTAL, s>>>(p, maps);
-        return cudaGetLastError();
-    }
-    auto kern = kda_bwd_wy_tc<true>;
-    const int smem = (int)bw::TOTAL_CONVB;
-    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return e;
-    kern<<<units < sms ? units : sms, bw::NTHR, smem, s>>>(p, maps);
+    auto kern = convb ? kda_bwd_wy_tc_pf<true> : kda_bwd_wy_tc_pf<false>;
+    const int smem = convb ? (int)bp::TOTAL_CONVB : (int)bp::TOTAL;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    kern<<<units < sms ? units : sms, bp::NTHR, smem, s>>>(p, maps);
     return cudaGetLastError();
 }
 

@@ -66,7 +66,8 @@ constexpr uint32_t STG = SB;                 // f32 [3][64][128] staging of dq, 
 // fused short-convolution backward (CONVB): once their first users are done, Y holds the pre-convolution q and
 // k rows -3 .. 63 (bf16 [67][128] each), the G tile holds dq and dk of the convolved rows (bf16 [64][128] each)
 // and the staging area the four blocks' filter-gradient shares
-constexpr uint32_t CXQ = YB, CXK = YB + 67 * 256, CDY = SG, CDW = STG;
+constexpr uint32_t CXQ = YB, CXK = YB + 67 * 256, CTAPS = CXK + 67 * 256, CDY = SG, CDW = STG;  // CTAPS: f32 [2][128][4] padded filter taps
+static_assert(CTAPS + 2 * 128 * 16 <= YB + 49152, "the projection rows and the taps share the Y buffer");
 constexpr uint32_t TMEM_COLS = 512;
 // The midpoint factors reach 2^(+-span/2) and the third BF16 part of an operand sits 2^-16 below its
 // value, so the whole FP32 exponent range is used up at span ~205: tiles pass on to the tensor cores
@@ -448,6 +449,8 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
                 cp_async16_z(sxq + r * D + e8, xq + src, valid);
                 cp_async16_z(sxk + r * D + e8, xk + src, valid);
             }
+            // (the filter taps of this head travel with them: thread t < 256 fetches tensor t / 128, channel t % 128)
+            if (tid < 2 * D) stage_taps(reinterpret_cast<float4*>(dyn + CTAPS) + tid, tid < D ? p.conv_q : p.conv_k, hd, tid & (D - 1), p.conv_ksize);
             cp_async_commit();
         }
         // ---- reverse cumulative sum across the blocks and the gate chain
@@ -570,8 +573,11 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             seq_chunks(p, ci.seq, c0s, ncs);
             const bool has_next = ci.lc + 1 < ncs;
             float wq[4], wk[4], dwq[4] = {0.f, 0.f, 0.f, 0.f}, dwk[4] = {0.f, 0.f, 0.f, 0.f}, oq[16], ok_[16];
-            conv_taps(p.conv_q, hd, d, p.conv_ksize, wq);
-            conv_taps(p.conv_k, hd, d, p.conv_ksize, wk);
+            {
+                const float4 tq = reinterpret_cast<const float4*>(dyn + CTAPS)[d], tk = reinterpret_cast<const float4*>(dyn + CTAPS)[D + d];
+                wq[0] = tq.x; wq[1] = tq.y; wq[2] = tq.z; wq[3] = tq.w;
+                wk[0] = tk.x; wk[1] = tk.y; wk[2] = tk.z; wk[3] = tk.w;
+            }
             float* cvh = (float*)(sc + L.cv_head) + (rec * 3 * 3) * D;
             float* cvt = (float*)(sc + L.cv_tail) + (rec * 3 * 3) * D;
             conv_bwd_block(sxq, sxq + 3 * D, sdyq, wq, d, blk, cvh, cvt, dwq, oq);

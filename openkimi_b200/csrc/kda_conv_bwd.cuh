@@ -55,6 +55,21 @@ __device__ __forceinline__ void conv_bwd_block(const __nv_bfloat16* __restrict__
     }
 }
 
+// The padded taps of one channel on their way to shared memory (dst: one float4): a 16-byte cp.async when the
+// filter has four taps and its array is 16-byte aligned (it joins the caller's next commit group, so the
+// latency of the load is not paid where the taps are used), plain loads and a store otherwise.
+__device__ __forceinline__ void stage_taps(float4* dst, const float* __restrict__ wsrc, int h, int ch, int K) {
+    const float* p = wsrc + (size_t)(h * 128 + ch) * K;
+    if (K == 4 && (reinterpret_cast<uintptr_t>(wsrc) & 15) == 0) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(p) : "memory");
+    } else {
+        float w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] = j >= 4 - K ? p[j - (4 - K)] : 0.f;
+        *dst = make_float4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 // the padded taps of channel (head h, ch): tap j multiplies x[s - 3 + j]
 __device__ __forceinline__ void conv_taps(const float* __restrict__ wsrc, int h, int ch, int K, float (&w)[4]) {
     const float* p = wsrc + (size_t)(h * 128 + ch) * K;

@@ -79,7 +79,8 @@ constexpr uint32_t SBETA = SKH + 16384;      // f32: beta [64], row sums [64], p
 constexpr uint32_t TOTAL = SBETA + 256 + 256 + 2048 + 1024;
 constexpr uint32_t XVM = DST + 16384;        // fused conv backward only: pre-convolution v rows 0 .. 63, bf16 [64][128] (dS is dead by then)
 constexpr uint32_t XVH = TOTAL;              //                          rows -3 .. -1, bf16 [3][128]
-constexpr uint32_t TOTAL_CONVB = XVH + 3 * 256;
+constexpr uint32_t XTAPS = XVH + 3 * 256;     //                          f32 [128][4] padded filter taps of v
+constexpr uint32_t TOTAL_CONVB = XTAPS + 128 * 16;
 constexpr uint32_t DAQK = 0, DWN = 64, DQT = 128, DKH = 192, DVB = 256, DKB = 320, DMN = 384, WBF = 448, TMEM_COLS = 512;
 }  // namespace bp
 
@@ -308,6 +309,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
                 const bool valid = ci.lc > 0;
                 cp_async16_z(sxh + r * D + e8, v + ((size_t)(ci.tok0 + (valid ? r - 3 : 0)) * p.H + h) * D + e8, valid);
             }
+            if (tid >= 64 && tid < 64 + D) stage_taps(reinterpret_cast<float4*>(dyn + XTAPS) + tid - 64, p.conv_v, h, tid - 64, p.conv_ksize);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
@@ -424,7 +426,10 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
             seq_chunks(p, ci.seq, c0s, ncs);
             const bool has_next = ci.lc + 1 < ncs;
             float w4[4], dw[4] = {0.f, 0.f, 0.f, 0.f}, out[16];
-            conv_taps(p.conv_v, h, ch, p.conv_ksize, w4);
+            {
+                const float4 t4 = reinterpret_cast<const float4*>(dyn + XTAPS)[ch];
+                w4[0] = t4.x; w4[1] = t4.y; w4[2] = t4.z; w4[3] = t4.w;
+            }
             float* cvh = (float*)(sc + L.cv_head) + ((rec * 3 + 2) * 3) * D;
             float* cvt = (float*)(sc + L.cv_tail) + ((rec * 3 + 2) * 3) * D;
             conv_bwd_block(reinterpret_cast<const __nv_bfloat16*>(dyn + XVH), reinterpret_cast<const __nv_bfloat16*>(dyn + XVM), sv, w4, ch,

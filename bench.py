@@ -382,7 +382,7 @@ def main():
     # and gradient device->host.  Three streams (H2D, compute, D2H) with two buffer sets let
     # step s+1's upload and step s-1's download run under step s's kernels, the way a caller
     # that streams batches through the op would drive it; each step still moves all its bytes.
-    st_h2d, st_cmp, st_d2h = torch.cuda.Stream(device), torch.cuda.Stream(device), torch.cuda.Stream(device)
+    streams = (torch.cuda.Stream(device), torch.cuda.Stream(device), torch.cuda.Stream(device))  # H2D, compute, D2H
     names = [k for k, v in host.items() if isinstance(v, torch.Tensor)]
     dev_buf = [{k: torch.empty_like(host[k], device=device) for k in names} for _ in range(2)]
     pinned_out = [None, None]
@@ -390,8 +390,12 @@ def main():
     ev_cmp = [torch.cuda.Event() for _ in range(2)]
     ev_down = [torch.cuda.Event() for _ in range(2)]
 
-    def e2e_step(sidx):
+    def e2e_step(sidx, overlap=True):
+        # overlap=False puts the three parts of a step on ONE stream: no copy runs under another copy or under the
+        # kernels.  Some hosts deliver far less than the sum when both copy directions run at once; the leg times a
+        # few steps both ways first and keeps the faster schedule (reported in e2e.how).
         b = sidx & 1
+        st_h2d, st_cmp, st_d2h = streams if overlap else (streams[1],) * 3
         with torch.cuda.stream(st_h2d):
             st_h2d.wait_event(ev_cmp[b])          # the compute that last read this buffer set is done
             for k in names:
@@ -425,20 +429,30 @@ def main():
         res = e2e_step(sidx)
     torch.cuda.synchronize()
     d2h = sum(x.numel() * x.element_size() for x in res)
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def e2e_time(nsteps, overlap):
+        """ms per step of nsteps end-to-end steps (device events around the whole pipelined region, max over ranks)."""
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        barrier()
+        f0.record(streams[0] if overlap else streams[1])
+        for sidx in range(nsteps):
+            e2e_step(sidx, overlap)
+        last = streams[2] if overlap else streams[1]
+        last.wait_stream(streams[1])
+        last.wait_stream(streams[0])
+        f1.record(last)
+        torch.cuda.synchronize()
+        barrier()
+        t2 = torch.tensor([f0.elapsed_time(f1)], device=device)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        return float(t2.item()) / nsteps
+
     e2e_steps = max(4, min(args.steps, 10))
-    f0.record(st_h2d)
-    for sidx in range(e2e_steps):
-        e2e_step(sidx)
-    st_d2h.wait_stream(st_cmp)
-    st_d2h.wait_stream(st_h2d)
-    f1.record(st_d2h)
-    barrier()
-    t2 = torch.tensor([f0.elapsed_time(f1)], device=device)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t2.item()) / e2e_steps
+    trial = {True: e2e_time(3, True), False: e2e_time(3, False)}   # (same decision on every rank: the times are maxima over ranks)
+    e2e_overlap = trial[True] <= trial[False]
+    e2e_ms = e2e_time(e2e_steps, e2e_overlap)
     # what the copy engines deliver on their own (one direction at a time, this rank's buffers, all ranks
     # at once): shows whether the end-to-end leg is limited by the host side of the copies
     def copy_rate(pairs, nbytes):
@@ -564,7 +578,9 @@ def main():
         "clocks": clocks,
         "e2e": {"value": world * tokens / (e2e_ms / 1e3) / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                "how": "3 streams (H2D / compute / D2H), 2 buffer sets; every step moves all its bytes",
+                "how": ("3 streams (H2D / compute / D2H), 2 buffer sets" if e2e_overlap else
+                        "one stream (upload, kernels, download in turn), 2 buffer sets") + "; every step moves all its bytes",
+                "schedule_trial_ms": {"overlapped": trial[True], "in_turn": trial[False]},
                 "copy_only_gbs": {"h2d": h2d_rate, "d2h": d2h_rate}, "cpu_affinity": numa_cpus and len(numa_cpus)},
         "gpu_launches": launches,
         "kernels_ms": avg,

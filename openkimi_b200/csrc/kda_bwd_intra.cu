@@ -332,6 +332,19 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         tma_load_1d(dyn + PF + C * D * 2, (const __nv_bfloat16*)(sc + L.dKh) + rec * C * D, C * D * 2, &barH);
         tma_load_1d(dyn + PF + 2 * C * D * 2, (const __nv_bfloat16*)(sc + L.dKb) + rec * C * D, C * D * 2, &barH);
     }
+    // The next unit of this CTA finds what it needs first in L2: the hints go out here, in the middle of the unit,
+    // when the copy unit has nothing else to do (there is no shared memory left to receive the records themselves).
+    if (tid == 5 * 32) {
+        UnitWalk un = uw;
+        un.next();
+        if (un.unit < n_units) {
+            const char* ws = (const char*)p.workspace;
+            const size_t rn = un.rec();
+            l2_prefetch_bulk((const float*)(ws + L.Gc) + rn * C * D, C * D * 4);
+            l2_prefetch_bulk((const __nv_bfloat16*)(ws + L.Kn) + rn * C * D, C * D * 2);
+            l2_prefetch_bulk((const __nv_bfloat16*)(ws + L.Qn) + rn * C * D, C * D * 2);
+        }
+    }
     ok = ok && mbar_wait(&mma3, par, p.status, 64);
     tc_fence_after();
     KDA_PHASE(5);

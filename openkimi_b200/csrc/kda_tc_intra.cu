@@ -35,10 +35,11 @@ constexpr uint32_t KSC = SG + 32768;         // 3 x cm(j, d; 128) bf16; block 0 
 constexpr uint32_t XSC = KSC + 3 * 16384;    // 3 x cm(n, d; 128) bf16, 32 rows each
 constexpr uint32_t KB = XSC + 3 * 8192;      // beta k 2^G  cm(j, d; 128)
 constexpr uint32_t BV = KB + 16384;          // beta v      cm(j, e; 128)
-constexpr uint32_t SA = BV + 16384;          // f32 [64][65]
-constexpr uint32_t SL = SA + 16640;
-constexpr uint32_t ST = SL + 16640;
-constexpr uint32_t SBETA = ST + 16640;        // f32 [3][64]: 1/|q|, 1/|k|, beta (the aux record)
+constexpr int LDR = 68;                      // row stride of A, L, T in floats
+constexpr uint32_t SA = BV + 16384;          // f32 [64][LDR]
+constexpr uint32_t SL = SA + 64 * LDR * 4;
+constexpr uint32_t ST = SL + 64 * LDR * 4;
+constexpr uint32_t SBETA = ST + 64 * LDR * 4;        // f32 [3][64]: 1/|q|, 1/|k|, beta (the aux record)
 constexpr uint32_t STOT = SBETA + 768;       // f32 [4][128] running gate totals of the four 16-row groups
 constexpr uint32_t SMIDF = STOT + 2048;      // f32 [4][128] midpoint of every (block, channel) of the cumulative gate
 constexpr uint32_t SPASS = SMIDF + 2048;     // int [4][4]: guard decision of every [16 rows x 32 channels] tile
@@ -46,9 +47,11 @@ constexpr uint32_t TOTAL = SPASS + 64;
 constexpr uint32_t KN = KSC;                 // f32 [64][128] (chunk-swizzled rows): k_j 2^(m - G_j), live only during the diagonal phase
 constexpr uint32_t T_D = 0, T_W = 96, T_U = 160, TMEM_COLS = 256;
 }  // namespace fi
+using fi::LDR;
 
 // One block column J of T = (I + diag(beta) L)^-1 (see stage 3 of the kernel).  sL holds L
-// (strictly lower, row stride 65), sT receives T; sT must be zero above the diagonal blocks.
+// (strictly lower, row stride LDR: rows start on 16-byte boundaries and are read four floats at a time), sT
+// receives T; sT must be zero above the diagonal blocks.
 // Eight warps work (the column solve is a dependent chain: more lanes only add redundancy):
 // warp (J, cw) owns columns 8 cw + lane % 8 of block column J, and its four lane groups (lane / 8)
 // split the 16 rows of every block below the diagonal, four rows each.
@@ -65,21 +68,26 @@ __device__ __forceinline__ void solve_block_column(const float* sL, float* sT, c
     // diagonal block: forward substitution down the column (every lane group does all 16 rows)
 #pragma unroll
     for (int r = 0; r < 16; ++r) {
+        const float* lrow = sL + (16 * J + r) * LDR + 16 * J;
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-        for (int j = 0; j < r; j += 2) {
-            s0 = fmaf(sL[(16 * J + r) * 65 + 16 * J + j], t[0][j], s0);
-            if (j + 1 < r) s1 = fmaf(sL[(16 * J + r) * 65 + 16 * J + j + 1], t[0][j + 1], s1);
+        for (int j = 0; j < r; j += 4) {
+            const float4 l = *reinterpret_cast<const float4*>(lrow + j);
+            s0 = fmaf(l.x, t[0][j], s0);
+            if (j + 1 < r) s1 = fmaf(l.y, t[0][j + 1], s1);
+            if (j + 2 < r) s0 = fmaf(l.z, t[0][j + 2], s0);
+            if (j + 3 < r) s1 = fmaf(l.w, t[0][j + 3], s1);
         }
         t[0][r] = (r == col ? 1.f : 0.f) - sbeta[16 * J + r] * (s0 + s1);
         if (r < col) t[0][r] = 0.f;
     }
     if (rq == 0) {
 #pragma unroll
-        for (int r = 0; r < 16; ++r) sT[(16 * J + r) * 65 + gc] = t[0][r];
+        for (int r = 0; r < 16; ++r) sT[(16 * J + r) * LDR + gc] = t[0][r];
     }
     __syncthreads();  // every diagonal block of T is in shared memory
-    // t[n] is the column restricted to block J + n
+    // t[n] is the column restricted to block J + n.  Lane group rq owns rows rq, rq + 4, rq + 8, rq + 12 of a
+    // block: the four rows one load instruction touches are adjacent, LDR floats apart, in four different banks.
 #pragma unroll
     for (int n = 1; n < 4; ++n) {
         const int I = J + n;
@@ -88,33 +96,45 @@ __device__ __forceinline__ void solve_block_column(const float* sL, float* sT, c
         float y4[4], y[16];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const int r = 16 * I + 4 * rq + q;
+            const int r = 16 * I + rq + 4 * q;
             float s = 0.f;
 #pragma unroll
             for (int kn = 0; kn < n; ++kn)
 #pragma unroll
-                for (int m = 0; m < 16; ++m) s = fmaf(sL[r * 65 + 16 * (J + kn) + m], t[kn][m], s);
+                for (int m = 0; m < 16; m += 4) {
+                    const float4 l = *reinterpret_cast<const float4*>(sL + r * LDR + 16 * (J + kn) + m);
+                    s = fmaf(l.x, t[kn][m], s);
+                    s = fmaf(l.y, t[kn][m + 1], s);
+                    s = fmaf(l.z, t[kn][m + 2], s);
+                    s = fmaf(l.w, t[kn][m + 3], s);
+                }
             y4[q] = sbeta[r] * s;
         }
 #pragma unroll
         for (int g4 = 0; g4 < 4; ++g4)
 #pragma unroll
-            for (int q = 0; q < 4; ++q) y[4 * g4 + q] = __shfl_sync(0xffffffffu, y4[q], (lane & 7) + 8 * g4);
+            for (int q = 0; q < 4; ++q) y[g4 + 4 * q] = __shfl_sync(0xffffffffu, y4[q], (lane & 7) + 8 * g4);
         // t_I = -T_II y for my four rows, shared the same way
         float n4[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const int r = 16 * I + 4 * rq + q;
+            const int r = 16 * I + rq + 4 * q;
             float s = 0.f;
 #pragma unroll
-            for (int m = 0; m < 16; ++m) s = fmaf(sT[r * 65 + 16 * I + m], y[m], s);
+            for (int m = 0; m < 16; m += 4) {
+                const float4 l = *reinterpret_cast<const float4*>(sT + r * LDR + 16 * I + m);
+                s = fmaf(l.x, y[m], s);
+                s = fmaf(l.y, y[m + 1], s);
+                s = fmaf(l.z, y[m + 2], s);
+                s = fmaf(l.w, y[m + 3], s);
+            }
             n4[q] = -s;
-            sT[r * 65 + gc] = -s;
+            sT[r * LDR + gc] = -s;
         }
 #pragma unroll
         for (int g4 = 0; g4 < 4; ++g4)
 #pragma unroll
-            for (int q = 0; q < 4; ++q) t[n][4 * g4 + q] = __shfl_sync(0xffffffffu, n4[q], (lane & 7) + 8 * g4);
+            for (int q = 0; q < 4; ++q) t[n][g4 + 4 * q] = __shfl_sync(0xffffffffu, n4[q], (lane & 7) + 8 * g4);
     }
 }
 
@@ -136,8 +156,8 @@ __device__ __forceinline__ void read_offdiag(uint32_t tmem_d, int qd, int lane, 
                 const int col = CBASE + cc + u, I = (col >> 5) + 1, nn = col & 31;
                 if (j < 16 * I) {
                     const float val = __uint_as_float(r[u]);
-                    if (nn < 16) sA[(16 * I + nn) * 65 + j] = val * scale;
-                    else sL[(16 * I + nn - 16) * 65 + j] = val;
+                    if (nn < 16) sA[(16 * I + nn) * LDR + j] = val * scale;
+                    else sL[(16 * I + nn - 16) * LDR + j] = val;
                 }
             }
         }
@@ -422,7 +442,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     tc_fence_before();
     __syncthreads();  // the raw gate, q, k rows (operand space) and the raw v rows (L tile) are consumed
     tc_fence_after();
-    for (int idx = tid; idx < C * 65; idx += NTHR) {
+    for (int idx = tid; idx < C * LDR; idx += NTHR) {
         sA[idx] = 0.f;
         sL[idx] = 0.f;
         sT[idx] = 0.f;
@@ -525,8 +545,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                 const float sum = (b0 ? w2s[1] : w2s[0]) + __shfl_xor_sync(0xffffffffu, b0 ? w2s[0] : w2s[1], 1);
                 const int j = j0 + (cs >> 1);
                 if (j <= i) {
-                    if (!b0) sA[ri * 65 + 16 * b + j] = sum * p.scale;
-                    else if (j < i) sL[ri * 65 + 16 * b + j] = sum;
+                    if (!b0) sA[ri * LDR + 16 * b + j] = sum * p.scale;
+                    else if (j < i) sL[ri * LDR + 16 * b + j] = sum;
                 }
             }
         };
@@ -577,8 +597,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
                 const float sum = (b0 ? w2s[1] : w2s[0]) + __shfl_xor_sync(0xffffffffu, b0 ? w2s[0] : w2s[1], 1);
                 const int j = j0 + (cs >> 1);
                 if (j <= i) {
-                    if (!b0) sA[ri * 65 + 16 * b + j] = sum * p.scale;
-                    else if (j < i) sL[ri * 65 + 16 * b + j] = sum;
+                    if (!b0) sA[ri * LDR + 16 * b + j] = sum * p.scale;
+                    else if (j < i) sL[ri * LDR + 16 * b + j] = sum;
                 }
             }
         };
@@ -748,12 +768,15 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     // ---- 4: Aqk and T records; T as the B operand of the WY products
     {
         __nv_bfloat16* sTB = reinterpret_cast<__nv_bfloat16*>(dyn + KSC);
-        const int i = tid >> 3, j8 = (tid & 7) * 8;
+        // eight lanes = eight adjacent rows of one 8-column group: one core matrix of the records, 32 distinct banks
+        const int i = (tid & 7) | ((tid >> 6) << 3), j8 = ((tid >> 3) & 7) * 8;
         float a8[8], t8[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            a8[j] = sA[i * 65 + j8 + j];
-            t8[j] = sT[i * 65 + j8 + j];
+        for (int j = 0; j < 8; j += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(sA + i * LDR + j8 + j);
+            const float4 t = *reinterpret_cast<const float4*>(sT + i * LDR + j8 + j);
+            a8[j] = a.x, a8[j + 1] = a.y, a8[j + 2] = a.z, a8[j + 3] = a.w;
+            t8[j] = t.x, t8[j + 1] = t.y, t8[j + 2] = t.z, t8[j + 3] = t.w;
         }
         const uint4 tb = f32_to_bf16x8(t8);
         *reinterpret_cast<uint4*>(gA + cm_idx(i, j8, C)) = f32_to_bf16x8(a8);

@@ -489,7 +489,9 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     //   warps 2, 3 (slot s = 0..7):  row 15 - s           against keys 8..15, then row s against keys 0..7
     // Eight lanes read 128 contiguous bytes of a row: no bank conflicts.
     {
-        const int cs = lane & 7, b = warp >> 2, w4 = warp & 3, slot = 4 * (w4 & 1) + (lane >> 3);
+        // (role w4 rotates with the block: the four warps of one scheduler, warp % 4 alike, take the four roles,
+        //  two short walks of 8 key rows and two long ones of 12, instead of four of a kind)
+        const int cs = lane & 7, b = warp >> 2, w4 = (warp + b) & 3, slot = 4 * (w4 & 1) + (lane >> 3);
         // element offsets of this lane's channels 32 u + 4 cs .. + 3 inside the swizzled row r (swz_f32 / swz_bf16
         // with the row-dependent part computed once per row): FP32 chunk 8 u + cs, BF16 chunk 4 u + cs / 2
         auto goff = [&](int r, int u) { return 32 * u + 4 * (cs ^ (r & 7)); };
@@ -757,9 +759,10 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 
     // ---- 3: T = (I + diag(beta) L)^-1, column by column.  Column c of T depends only on
     //      column c of the blocks above it, so one lane carries a whole column in registers:
-    //      warp w < 8 owns block column J = w % 4, columns 8 (w / 4) + lane % 8, and its four lane
-    //      groups (lane / 8) split the 16 rows of every block below the diagonal.
-    solve_block_column(sL, sT, sbeta, warp & 3, (warp >> 2) & 1, lane, warp < 8);
+    //      warp w < 8 owns columns 8 (w / 4) + lane % 8 of block column J = w % 4 (w < 4) or 3 - w % 4 (w >= 4),
+    //      and its four lane groups (lane / 8) split the 16 rows of every block below the diagonal.  Warps w and
+    //      w + 4 issue from the same scheduler: with J and 3 - J they bring it 3 block levels whatever J is.
+    solve_block_column(sL, sT, sbeta, (warp & 4) ? 3 - (warp & 3) : (warp & 3), (warp >> 2) & 1, lane, warp < 8);
     fence_async_smem();
     __syncthreads();
     if (more) request_v(ci_nx, un.head());  // L is dead: its tile receives the next unit's v rows

@@ -442,10 +442,17 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     tc_fence_before();
     __syncthreads();  // the raw gate, q, k rows (operand space) and the raw v rows (L tile) are consumed
     tc_fence_after();
-    for (int idx = tid; idx < C * LDR; idx += NTHR) {
-        sA[idx] = 0.f;
-        sL[idx] = 0.f;
-        sT[idx] = 0.f;
+    // A and T must read zero above the diagonal: the stages below write A for j <= i only and T from the diagonal
+    // block down, and the records carry whole 64 x 64 tiles.  Row i is cleared from its diagonal block on, four
+    // floats at a time.  (L needs no clearing: the solve reads its diagonal blocks for j < i only, which the
+    // diagonal walks write, and the blocks below them whole, which the accumulator read-back writes.)
+#pragma unroll
+    for (int idx = tid; idx < C * 16; idx += NTHR) {
+        const int i = idx >> 4, q4 = idx & 15;
+        if (q4 >= 4 * (i >> 4)) {
+            *reinterpret_cast<float4*>(sA + i * LDR + 4 * q4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(sT + i * LDR + 4 * q4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
     const uint32_t tmem0 = tmem_s;
     // ---- the later 16-row groups of the cumulative sum pick up the totals of the earlier ones; every thread

@@ -628,12 +628,11 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         }
         if (gate) {
-            __syncthreads();  // the tail terms in sscr have been read by every thread
-            sscr[blk * D + d] = dbias_acc;
+            fD[blk * D + d] = dbias_acc;  // (the rebuilt diagonal blocks are dead since the assembly: their space is free)
             dA_acc = warp_sum(dA_acc);
             if (lane == 0) sred[warp] = dA_acc;
             __syncthreads();
-            if (blk == 0) ((float*)(sc + L.dbias_part))[rec * D + d] = (sscr[d] + sscr[D + d]) + (sscr[2 * D + d] + sscr[3 * D + d]);
+            if (blk == 0) ((float*)(sc + L.dbias_part))[rec * D + d] = (fD[d] + fD[D + d]) + (fD[2 * D + d] + fD[3 * D + d]);
             if (tid == 0) {
                 float t = 0.f;
                 for (int w = 0; w < 16; ++w) t += sred[w];

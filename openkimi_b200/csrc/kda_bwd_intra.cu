@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     bool ok = mbar_wait(&barA, par, p.status, 64);
     KDA_PHASE(0);
 
-    // ---- my block: G of my channel, guard and references; round 1: KN_j = k_j 2^(ref - G_j) -> X
+    // ---- my block: G of my channel, guard and references; operand step 1: KN_j = k_j 2^(ref - G_j) -> X
     float G[B], mid;
 #pragma unroll
     for (int r = 0; r < B; ++r) G[r] = sG[swz_f32(b0 + r, d)];
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     }
 #pragma unroll
     for (int b = 0; b < 16; ++b) any_rej = any_rej || srej[b] != 0;
-    // ---- round 2: QP_i = scale q_i 2^(G_i - ref) -> Y
+    // ---- operand step 2: QP_i = scale q_i 2^(G_i - ref) -> Y
     {
         const float qref = pass ? mid : G[0];
 #pragma unroll
@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             }
         mma_commit(&mma2);
     }
-    // ---- round 3: KP_i = beta_i k_i 2^(G_i - ref) -> X, once the row-side MMAs have read X
+    // ---- operand step 3: KP_i = beta_i k_i 2^(G_i - ref) -> X, once the row-side MMAs have read X
     ok = ok && mbar_wait(&mma1, par, p.status, 64);
     tc_fence_after();
     {

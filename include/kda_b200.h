@@ -114,9 +114,9 @@ typedef struct KdaParams {
      * flattened token, valid rows} of every chunk, so that a CTA finds its chunk with one 16-byte load
      * instead of three dependent ones through chunk_seq / seq_chunk_off / cu_seqlens (16-byte aligned). */
     const int32_t *chunk_tab;
-    /* Optional: a word of PINNED (device-mapped) host memory.  When set, kda_fwd / kda_bwd finish with a
-     * one-thread kernel that copies a non-zero *status into it, so that the host can notice a wait
-     * that gave up by reading its own memory, without a copy engine or a synchronisation. */
+    /* Optional: a word of PINNED (device-mapped) host memory.  When set, the thread whose wait gave up
+     * stores the status word into it as well, so that the host can notice by reading its own memory,
+     * without a copy engine, a synchronisation or one more launch. */
     int32_t *status_host;
     /* Optional, with conv_q/k/v (kda_bwd only): FP32 [H*dk][conv_ksize] gradients of the three filters.
      * When all three are given, the backward of the short convolutions runs inside the KDA backward
@@ -242,8 +242,8 @@ int kda_selftest_mma(const float *A, const float *B, float *D, int N, int K, int
  * The device stays usable; the tests use it to check that a given-up wait is reported. */
 int kda_selftest_wait(const float *src, float *dst, int poll_limit, int code, int *status, void *cuda_stream);
 
-/* Launches the one-thread kernel described at KdaParams.status_host on the given stream (for entry
- * points that take a bare status pointer, such as kda_recurrent_step). */
+/* Launches a one-thread kernel on the given stream that copies a non-zero *status into *status_host
+ * (pinned, device-mapped): for entry points that take a bare status pointer, such as kda_recurrent_step. */
 int kda_status_publish(const int32_t *status, int32_t *status_host, void *cuda_stream);
 
 const char *kda_status_string(int status);

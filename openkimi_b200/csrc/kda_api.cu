@@ -168,10 +168,6 @@ int kda_fwd(const KdaParams* p, void* stream) {
     prof_open(0, s);
     cudaError_t e = tc ? tc_fwd(*p, s) : simt_fwd(*p, s);
     g_cur = nullptr;
-    if (e == cudaSuccess && p->status && p->status_host) {
-        status_publish_kernel<<<1, 1, 0, s>>>(p->status, p->status_host);
-        e = cudaGetLastError();
-    }
     return e == cudaSuccess ? KDA_OK : fail_cuda(e);
 }
 
@@ -183,10 +179,6 @@ int kda_bwd(const KdaParams* p, void* stream) {
     prof_open(1, s);
     cudaError_t e = tc ? tc_bwd(*p, s) : simt_bwd(*p, s);
     g_cur = nullptr;
-    if (e == cudaSuccess && p->status && p->status_host) {
-        status_publish_kernel<<<1, 1, 0, s>>>(p->status, p->status_host);
-        e = cudaGetLastError();
-    }
     return e == cudaSuccess ? KDA_OK : fail_cuda(e);
 }
 

@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     }
     if (tid < C) sdb[tid] = ((const float*)(sc + L.dbp))[rec * C + tid];
     const float carry_in = ((const float*)(sc + L.gC))[rec * D + d];
-    bool ok = mbar_wait(&barA, par, p.status, 64);
+    bool ok = mbar_wait(&barA, par, p, 64);
     KDA_PHASE(0);
 
     // ---- my block: G of my channel, guard and references; operand step 1: KN_j = k_j 2^(ref - G_j) -> X
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
-    ok = ok && mbar_wait(&barB, par, p.status, 64);
+    ok = ok && mbar_wait(&barB, par, p, 64);
     KDA_PHASE(1);
     constexpr int PA[6] = {0, 0, 1, 1, 0, 2}, PB[6] = {0, 1, 0, 1, 2, 0};
     // (descriptors: one base per buffer, the tile / part / block offset is added to its 14-bit address field)
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
         mma_commit(&mma2);
     }
     // ---- operand step 3: KP_i = beta_i k_i 2^(G_i - ref) -> X, once the row-side MMAs have read X
-    ok = ok && mbar_wait(&mma1, par, p.status, 64);
+    ok = ok && mbar_wait(&mma1, par, p, 64);
     tc_fence_after();
     {
         const float qref = pass ? mid : G[0];
@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
     }
     KDA_PHASE(4);
     // ---- the hand-over arrays may land in Y as soon as the MMAs that read Y are done
-    ok = ok && mbar_wait(&mma2, par, p.status, 64);
+    ok = ok && mbar_wait(&mma2, par, p, 64);
     if (tid == 0 && ok) {
         mbar_expect_tx(&barH, 3 * C * D * 2);
         tma_load_1d(dyn + PF, (const __nv_bfloat16*)(sc + L.dQt) + rec * C * D, C * D * 2, &barH);
@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             l2_prefetch_bulk((const __nv_bfloat16*)(ws + L.Qn) + rn * C * D, C * D * 2);
         }
     }
-    ok = ok && mbar_wait(&mma3, par, p.status, 64);
+    ok = ok && mbar_wait(&mma3, par, p, 64);
     tc_fence_after();
     KDA_PHASE(5);
     // ---- column sums of my block
@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(bi::NTHR, 1) kda_bwd_intra(const KdaParams p) 
             fD[e] = (__bfloat162float(t[0]) + __bfloat162float(t[C * C])) + __bfloat162float(t[2 * C * C]);
         }
     }
-    ok = ok && mbar_wait(&barH, par, p.status, 64);
+    ok = ok && mbar_wait(&barH, par, p, 64);
     ok = __syncthreads_and(ok);  // (also: the rebuilt blocks are visible; the split tiles and X are dead -> staging area)
     KDA_PHASE(7);
 

@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
         // chunk's MMAs, which completed before that chunk's iteration ended): a whole chunk step ahead of their use
         if (lc + 1 < nc) issue_loads(lc + 1, stage ^ 1);
         tma_store_wait_read();  // the previous chunk's output rows have left the staging tile
-        ok = mbar_wait(&full[stage], (lc >> 1) & 1, p.status, 2);
+        ok = mbar_wait(&full[stage], (lc >> 1) & 1, p, 2);
         if (!__syncthreads_and(ok)) { ok = false; break; }
         KDA_PHASE(0);
 
@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
             }
             mma_commit(&mmabar);
         }
-        ok = mbar_wait(&mmabar, mma_phase, p.status, 4);
+        ok = mbar_wait(&mmabar, mma_phase, p, 4);
         mma_phase ^= 1;
         tc_fence_after();
         if (!__syncthreads_and(ok)) { ok = false; break; }
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(fs::NTHR, 1) kda_fwd_state_tc(const KdaParams 
             }
             mma_commit(&mmabar);
         }
-        ok = mbar_wait(&mmabar, mma_phase, p.status, 4);
+        ok = mbar_wait(&mmabar, mma_phase, p, 4);
         mma_phase ^= 1;
         tc_fence_after();
         if (!__syncthreads_and(ok)) { ok = false; break; }
@@ -496,7 +496,7 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
             cp_async_wait<0>();
         }
         fence_async_smem();
-        ok = mbar_wait(&full[stage], ring_phase, p.status, 2);
+        ok = mbar_wait(&full[stage], ring_phase, p, 2);
         if (!__syncthreads_and(ok)) { ok = false; break; }
 
         {
@@ -541,7 +541,7 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
             }
             mma_commit(&mmabar);
         }
-        ok = mbar_wait(&mmabar, k & 1, p.status, 4);
+        ok = mbar_wait(&mmabar, k & 1, p, 4);
         tc_fence_after();
         if (!__syncthreads_and(ok)) { ok = false; break; }
 
@@ -570,7 +570,7 @@ __global__ void __launch_bounds__(bs::NTHR, 1) kda_bwd_state_tc(const KdaParams 
                 mma_ts(tmem0 + SACC, tmem0 + VBF + s * 8, make_desc(sb + WT + s * 256, 128, 1024), id_w, true);
             mma_commit(&mmabar2);
         }
-        ok = mbar_wait(&mmabar2, k & 1, p.status, 4);
+        ok = mbar_wait(&mmabar2, k & 1, p, 4);
         tc_fence_after();
         if (!__syncthreads_and(ok)) { ok = false; break; }
         if (++stage == 3) {

@@ -87,6 +87,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     if (status) atomicOr(status, code);
     return false;
 }
+// The same wait inside kda_fwd / kda_bwd kernels (P = KdaParams): the thread whose wait gave up also leaves the
+// status word in the caller's pinned host word (status_host, device-mapped), so that the host can notice by
+// reading its own memory, without a copy, a synchronisation or one more launch.
+template <class P>
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const P& p, int code) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    int v = code;
+    if (p.status) v |= atomicOr(p.status, code);
+    if (p.status_host) *reinterpret_cast<volatile int32_t*>(p.status_host) = v;
+    return false;
+}
 // account for `bytes` of a transaction that will never arrive (used when a wait is abandoned, so that
 // the barrier still completes once the copies that ARE in flight have landed)
 __device__ __forceinline__ void mbar_complete_tx(uint64_t* bar, uint32_t bytes) {

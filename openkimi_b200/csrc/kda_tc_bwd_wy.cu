@@ -214,8 +214,8 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
         asm volatile("cp.async.wait_group 1;" ::: "memory");  // dO of this unit (requested one unit ago) has landed
         fence_async_smem();
     }
-    ok = mbar_wait(&fullA[set], (it >> 1) & 1, p.status, 16);
-    ok = mbar_wait(&fullS, par, p.status, 16) && ok;
+    ok = mbar_wait(&fullA[set], (it >> 1) & 1, p, 16);
+    ok = mbar_wait(&fullS, par, p, 16) && ok;
     tc_fence_before();
     ok = __syncthreads_and(ok);
     KDA_PHASE(0);
@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
             for (int s = 0; s < 8; ++s)  // dQt^T = S0 * dO^T (K-major, rows = i)
                 mma_ss(tmem0 + DQT, make_desc(sb + S0T + s * 4096, 2048, 128), make_desc(sb + oDOT + s * 256, 128, 2048), id_mk, s > 0);
         } else if (warp == 3) {
-            if (mbar_wait(&fullD, par, p.status, 16)) {
+            if (mbar_wait(&fullD, par, p, 16)) {
 #pragma unroll
                 for (int s = 0; s < 8; ++s)  // dKh^T = dS * V'^T
                     mma_ss(tmem0 + DKH, make_desc(sb + DST + s * 4096, 2048, 128), make_desc(sb + oVT + s * 2048, 1024, 128), id_mm, s > 0);
@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
         ahead = true;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");  // (an empty group when there is no next unit: the waits below count groups)
-    ok = mbar_wait(&fullD, par, p.status, 16) && ok;
+    ok = mbar_wait(&fullD, par, p, 16) && ok;
     {   // while the first MMA group runs:
         // dGamma_C[d] = sum_e dS[d][e] S0[d][e].  Both records are cm(e, d; 128): a warp reads, for one
         // octet of e, 8 rows x 4 channel groups = four contiguous 128-byte core matrices per load.
@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
             for (int j = 0; j < 8; ++j) spart[128 * eh + d8 + j] = acc[j];
         }
     }
-    ok = ok && mbar_wait(&mma1, par, p.status, 32);
+    ok = ok && mbar_wait(&mma1, par, p, 32);
     tc_fence_after();
     asm volatile("cp.async.wait_group 1;" ::: "memory");  // my share of the v rows has landed (the next unit's dO may still be on its way)
     ok = __syncthreads_and(ok);  // every warp is done reading dS: its tile becomes the staging area of dQt
@@ -459,7 +459,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
     }
     if (tid < C) srow[tid] = (srp[tid] + srp[C + tid]) + (srp[2 * C + tid] + srp[3 * C + tid]);
     KDA_PHASE(4);
-    ok = ok && mbar_wait(&mma2, par, p.status, 32);
+    ok = ok && mbar_wait(&mma2, par, p, 32);
     tc_fence_after();
     ok = __syncthreads_and(ok);
     if (tid == 0 && more && ok) {  // S0 and T are dead: their tiles take the next unit's
@@ -488,7 +488,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
                        pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13])), pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15])));
         fence_async_smem();
     }
-    ok = ok && mbar_wait(&fullW, par, p.status, 16);  // W, for the last MMA group
+    ok = ok && mbar_wait(&fullW, par, p, 16);  // W, for the last MMA group
     tc_fence_before();
     ok = __syncthreads_and(ok);
     if (tid == 0 && ok) {
@@ -512,7 +512,7 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
         }
         mma_commit(&mma3);
     }
-    ok = ok && mbar_wait(&mma3, par, p.status, 32);
+    ok = ok && mbar_wait(&mma3, par, p, 32);
     tc_fence_after();
     KDA_PHASE(7);
     if (ok) {
@@ -539,8 +539,8 @@ __global__ void __launch_bounds__(bp::NTHR, 1) kda_bwd_wy_tc_pf(const KdaParams 
     ci = ci_nx;
     }
     if (!ok) {  // the copies in flight for the next unit land before the CTA leaves
-        if (ahead) mbar_wait(&fullA[(it + 1) & 1], ((it + 1) >> 1) & 1, p.status, 16);
-        if (early) mbar_wait(&fullS, (it + 1) & 1, p.status, 16);
+        if (ahead) mbar_wait(&fullA[(it + 1) & 1], ((it + 1) >> 1) & 1, p, 16);
+        if (early) mbar_wait(&fullS, (it + 1) & 1, p, 16);
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     tc_fence_before();

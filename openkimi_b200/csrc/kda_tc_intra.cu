@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
 #pragma unroll
     for (int m = 0; m < 2; ++m)
         rb[m] = ((tid & 15) == 0 && (CONV ? 2 * hw + m : hw + 32 * m) < ci.len) ? __bfloat162float(nx.rb[m]) : 0.f;
-    ok = mbar_wait(&rowbar, it & 1, p.status, 8);
+    ok = mbar_wait(&rowbar, it & 1, p, 8);
     KDA_PHASE(13);
     // ---- 0a: gate, channel-wise: thread (quarter, d) owns rows 16*quarter .. 16*quarter+15 of channel d
     {
@@ -348,7 +348,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         stot[quarter * D + dch] = run;
     }
     KDA_PHASE(0);
-    ok = mbar_wait(&vbar, it & 1, p.status, 8) && ok;
+    ok = mbar_wait(&vbar, it & 1, p, 8) && ok;
     KDA_PHASE(14);
     // Rows of a half warp: hw and hw + 32 without the convolution; 2 hw and 2 hw + 1 with it, so that
     // the five input rows 2 hw - 3 .. 2 hw + 1 serve the two outputs of one thread.
@@ -734,7 +734,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         mma_commit(&bar);
     }
     KDA_PHASE(4);
-    ok = mbar_wait(&bar, it & 1, p.status, 8) && ok;
+    ok = mbar_wait(&bar, it & 1, p, 8) && ok;
     tc_fence_after();
     KDA_PHASE(11);
     if (ok) {  // warp (quadrant, group): accumulator columns 32 group .. 32 group + 31 = block I = group + 1
@@ -809,7 +809,7 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
         mma_commit(&bar2);
     }
     if (tid < D) gGam[tid] = ex2_approx(sG[swz_f32(C - 1, tid)]);
-    ok = mbar_wait(&bar2, it & 1, p.status, 8) && ok;
+    ok = mbar_wait(&bar2, it & 1, p, 8) && ok;
     tc_fence_after();
 
     KDA_PHASE(8);
@@ -841,8 +841,8 @@ __global__ void __launch_bounds__(fi::NTHR, 1) kda_fwd_intra_tc(const KdaParams 
     ci = ci_nx;
     }
     if (!ok && more) {  // the next unit's copies are in flight: they must have landed before the CTA leaves
-        mbar_wait(&rowbar, (it + 1) & 1, p.status, 8);
-        mbar_wait(&vbar, (it + 1) & 1, p.status, 8);
+        mbar_wait(&rowbar, (it + 1) & 1, p, 8);
+        mbar_wait(&vbar, (it + 1) & 1, p, 8);
     }
     tc_fence_before();
     __syncthreads();

@@ -53,8 +53,8 @@ def _chunk_tables(cu_seqlens, cu_seqlens_cpu, device):
 
 class _DeviceStatus:
     """One int32 status word per device, mirrored in pinned host memory.  A kernel whose bounded wait
-    gives up ORs a code into the device word (``KdaParams.status``); every call ends with a one-thread
-    kernel that copies a non-zero word into the pinned mirror (``KdaParams.status_host``), so the next
+    gives up ORs a code into the device word (``KdaParams.status``) and stores the word into the pinned
+    mirror (``KdaParams.status_host``, device-mapped) itself, so the next
     call on that device (or ``check_device_status``) notices it by reading host memory: no copy engine,
     no synchronisation on the hot path."""
 

@@ -851,9 +851,19 @@ __global__ void __launch_bounds__(1024) kda_param_reduce(const KdaParams p) {
     const int h = blockIdx.x, d = threadIdx.x & 127, grp = threadIdx.x >> 7;
     const float* pb = (const float*)(sc + L.dbias_part);
     const float* pa = (const float*)(sc + L.dA_part);
+    // (sixteen loads in flight per thread, added in chunk order: the loop is a chain of round trips otherwise)
     float s = 0.f;
     if (d < p.dk)
-        for (int c = grp; c < p.NT; c += 8) s += pb[((size_t)c * p.H + h) * p.dk + d];
+        for (int c0 = grp; c0 < p.NT; c0 += 8 * 16) {
+            float v[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int c = c0 + 8 * u;
+                v[u] = c < p.NT ? pb[((size_t)c * p.H + h) * p.dk + d] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 16; ++u) s += v[u];
+        }
     sb[grp][d] = s;
     // dA_log: lanes 0..31 of every group take every 32nd of the group's chunks
     float a = 0.f;
